@@ -1,0 +1,14 @@
+"""Torch-free control plane (plans, registry, compiler, work objects)."""
+
+from .backend import AutoStrategySelector, BackendCapabilities, CommunicationBackend, StrategyChoice
+from .chunking import ChunkPlan, GroupShardPlan
+from .compiler import CompileCache, ResolvedPlan, compile, default_registry, resolve_plan
+from .executor import CompileCacheKey, CompiledCommunicationPlan, CompiledExecutor, ObjectIdentity
+from .info import ExecutionCounters, ExecutionCounterSnapshot, ExecutionInfo
+from .plan import CommunicationPlan, CommunicationStage, CompileContext, WorkspacePolicy
+from .registry import BackendKey, BackendRegistry
+from .shard import ReducedShard
+from .work import (BoundCollectiveWork, CollectiveWork, CompletionWork, ImmediateWork,
+                   bind_execution_work)
+
+__all__ = [name for name in dir() if not name.startswith("_")]

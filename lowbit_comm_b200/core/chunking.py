@@ -1,0 +1,97 @@
+"""Equal-shard chunk plans.
+
+`ChunkPlan` mirrors the reference's element-granular plan
+(ccdl_comm/cuda/transports/compressed_reduce_scatter.py:8-94: shard = ceil(n/W),
+rank r owns chunk r).  `GroupShardPlan` is the plan the fused sm_100a kernels
+use: shards are counted in quantization groups and rounded up to a multiple of
+`align_groups` so every shard's value and scale regions start on a 16-byte
+boundary inside a planar payload.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+def _ceil_div(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+@dataclass(frozen=True)
+class ChunkPlan:
+    numel: int
+    world_size: int
+    shard_numel: int
+    padded_numel: int
+
+    @classmethod
+    def build(cls, numel: int, world_size: int) -> "ChunkPlan":
+        if numel < 0:
+            raise ValueError("numel must be >= 0")
+        if world_size <= 0:
+            raise ValueError("world_size must be > 0")
+        shard = _ceil_div(numel, world_size) if numel else 0
+        return cls(numel, world_size, shard, shard * world_size)
+
+    @property
+    def padding_numel(self) -> int:
+        return self.padded_numel - self.numel
+
+    def owner(self, chunk: int) -> int:
+        self._check(chunk)
+        return chunk
+
+    def bounds(self, chunk: int) -> tuple[int, int]:
+        """Half-open element range of `chunk` inside the padded tensor."""
+
+        self._check(chunk)
+        return chunk * self.shard_numel, (chunk + 1) * self.shard_numel
+
+    def valid_bounds(self, chunk: int) -> tuple[int, int]:
+        lo, hi = self.bounds(chunk)
+        return min(lo, self.numel), min(hi, self.numel)
+
+    def _check(self, chunk: int) -> None:
+        if not 0 <= chunk < self.world_size:
+            raise ValueError("chunk index out of range")
+
+
+@dataclass(frozen=True)
+class GroupShardPlan:
+    """Shard plan in units of quantization groups (fused-kernel layout)."""
+
+    numel: int
+    world_size: int
+    group_size: int
+    align_groups: int
+    num_groups: int          # groups that hold real data: ceil(numel / group_size)
+    shard_groups: int        # groups per rank (multiple of align_groups)
+
+    @classmethod
+    def build(cls, numel: int, world_size: int, group_size: int, align_groups: int = 8) -> "GroupShardPlan":
+        if numel < 0 or world_size <= 0 or group_size <= 0 or align_groups <= 0:
+            raise ValueError("invalid shard plan arguments")
+        groups = _ceil_div(numel, group_size)
+        per_rank = _ceil_div(groups, world_size)
+        per_rank = _ceil_div(per_rank, align_groups) * align_groups if per_rank else 0
+        return cls(numel, world_size, group_size, align_groups, groups, per_rank)
+
+    @property
+    def total_groups(self) -> int:
+        return self.shard_groups * self.world_size
+
+    @property
+    def shard_numel(self) -> int:
+        return self.shard_groups * self.group_size
+
+    @property
+    def padded_numel(self) -> int:
+        return self.shard_numel * self.world_size
+
+    def shard_valid_numel(self, rank: int) -> int:
+        lo = rank * self.shard_numel
+        return max(0, min(self.numel, lo + self.shard_numel) - lo)
+
+    def shard_valid_groups(self, rank: int) -> int:
+        lo = rank * self.shard_groups
+        return max(0, min(self.num_groups, lo + self.shard_groups) - lo)

@@ -1,0 +1,507 @@
+// Production-profile kernels (linear quantization, no top-k, nearest-even
+// rounding) for sm_100a.  Two kernels cover the whole fused data path:
+//
+//   quant_push : [error-feedback add] -> group abs-max -> int8/int4 pack ->
+//                stores into one or many destination payloads (local memory or
+//                NVLink peer memory) -> release signal
+//   reduce     : [bounded wait] -> dequantize R payloads -> fp32 sum -> scale ->
+//                {dense output | residual update | requantize + broadcast
+//                 into peer payloads + release signal}
+//
+// Math parity with the reference kernels: quantization/quant_pack_kernel.cu:84-163
+// (prepared value and stored scale are rounded to the source dtype before use),
+// quantization/dequant_reduce_kernel.cu:38-69, 150-221 (scale/127 decode, fp32
+// accumulate, one rounding, residual = prepared - mean).
+//
+// Thread mapping: each thread owns 16 consecutive elements (one 16-byte vector
+// of int8 codes, two 32-byte sectors of bf16), so a warp reads and writes fully
+// coalesced 512 B / 1 KiB spans and a group of G elements is G/16 adjacent lanes.
+
+#include "common.cuh"
+#include "lbc_api.h"
+
+namespace lbc {
+
+template <int G>
+__device__ __forceinline__ float group_max(float v) {
+    constexpr int lanes = G / kElemsPerThread;
+#pragma unroll
+    for (int off = lanes / 2; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off, lanes));
+    return v;
+}
+
+// Alignment-agnostic store of `n` bytes (n = 8 or 16) held in `v`.
+__device__ __forceinline__ void store_codes(uint8_t* p, uint4 v, int n) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    if (n == 16 && (a & 15) == 0) {
+        st16(p, v);
+    } else if ((a & 7) == 0 && n == 8) {
+        *reinterpret_cast<uint2*>(p) = make_uint2(v.x, v.y);
+    } else if ((a & 3) == 0) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        for (int i = 0; i < n / 4; ++i) reinterpret_cast<uint32_t*>(p)[i] = w[i];
+    } else {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        for (int i = 0; i < n / 2; ++i)
+            reinterpret_cast<uint16_t*>(p)[i] = uint16_t(w[i / 2] >> (16 * (i & 1)));
+    }
+}
+
+__device__ __forceinline__ uint4 load_codes(const uint8_t* p, int n) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    if (n == 16 && (a & 15) == 0) return ld16(p);
+    uint32_t w[4] = {0, 0, 0, 0};
+    if ((a & 3) == 0) {
+        for (int i = 0; i < n / 4; ++i) w[i] = reinterpret_cast<const uint32_t*>(p)[i];
+    } else {
+        for (int i = 0; i < n / 2; ++i)
+            w[i / 2] |= uint32_t(reinterpret_cast<const uint16_t*>(p)[i]) << (16 * (i & 1));
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template <typename T>
+__device__ __forceinline__ void store_scale(uint8_t* p, float stored) {
+    if constexpr (sizeof(T) == 2)
+        *reinterpret_cast<uint16_t*>(p) = Src<T>::down(stored);
+    else
+        *reinterpret_cast<float*>(p) = stored;
+}
+
+template <typename T>
+__device__ __forceinline__ float load_scale(const uint8_t* p) {
+    if constexpr (sizeof(T) == 2)
+        return Src<T>::up(*reinterpret_cast<const uint16_t*>(p));
+    else
+        return *reinterpret_cast<const float*>(p);
+}
+
+// Quantizes 16 rounded values with the group's stored scale; returns packed codes.
+template <typename T, int BIT>
+__device__ __forceinline__ uint4 encode16(const float (&vals)[16], float stored_scale, float (*decoded)[16]) {
+    constexpr int lim = BIT == 8 ? 127 : 7;
+    const float safe = fmaxf(stored_scale, 1.0e-6f);
+    const float mul = float(lim) / safe;
+    int q[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) q[i] = quant_rn(vals[i], mul, lim);
+    if (decoded != nullptr) {
+        const float step = stored_scale / float(lim);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) (*decoded)[i] = float(q[i]) * step;
+    }
+    if constexpr (BIT == 8) {
+        return pack16_i8<sizeof(T)>(q);
+    } else {
+        const uint2 h = pack16_i4<sizeof(T)>(q);
+        return make_uint4(h.x, h.y, 0, 0);
+    }
+}
+
+template <typename T, int BIT>
+__device__ __forceinline__ void decode16(uint4 codes, float stored_scale, float (&out)[16]) {
+    constexpr int lim = BIT == 8 ? 127 : 7;
+    const float step = stored_scale / float(lim);
+    if constexpr (BIT == 8) {
+        unpack16_i8<sizeof(T)>(codes, out);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out[i] *= step;
+    } else {
+        int c[16];
+        unpack16_i4<sizeof(T)>(make_uint2(codes.x, codes.y), c);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out[i] = int4_value(c[i]) * step;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// quant_push
+// ---------------------------------------------------------------------------
+template <typename T, int G, int BIT>
+__global__ void __launch_bounds__(kThreads) quant_push_kernel(const LbcQuantPush p) {
+    constexpr int lanes = G / kElemsPerThread;
+    constexpr int VB = G * BIT / 8;                 // value bytes per group
+    constexpr int MB = sizeof(T);                   // scale bytes per group
+    constexpr int CB = kElemsPerThread * BIT / 8;   // code bytes per thread
+    const T* x = static_cast<const T*>(p.x);
+    const T* res = static_cast<const T*>(p.residual);
+    T* prep = static_cast<T*>(p.prepared_out);
+    T* lef = static_cast<T*>(p.local_ef_out);
+    const int64_t n = p.numel;
+    const int64_t num_groups = (n + G - 1) / G;
+    const int64_t num_chunks = num_groups * lanes;  // 16-element chunks, whole groups only
+    const bool x_vec = (reinterpret_cast<uintptr_t>(x) & 31) == 0;
+    const bool r_vec = res == nullptr || (reinterpret_cast<uintptr_t>(res) & 31) == 0;
+    const bool p_vec = prep == nullptr || (reinterpret_cast<uintptr_t>(prep) & 31) == 0;
+    const bool l_vec = lef == nullptr || (reinterpret_cast<uintptr_t>(lef) & 31) == 0;
+
+    // Chunks are rounded up to a whole warp so that the shuffles stay convergent.
+    const int64_t chunk_span = (num_chunks + 31) / 32 * 32;
+    for (int64_t chunk = int64_t(blockIdx.x) * kThreads + threadIdx.x; chunk < chunk_span;
+         chunk += int64_t(gridDim.x) * kThreads) {
+        const bool live = chunk < num_chunks;
+        const int64_t first = chunk * kElemsPerThread;
+        float v[16];
+        if (live) {
+            load16<T>(x, first, n, x_vec, v, true);
+            if (res != nullptr) {
+                float r[16];
+                load16<T>(res, first, n, r_vec, r, prep != res);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] += r[i];
+                round16<T>(v);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0.0f;
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        amax = group_max<G>(amax);
+        if (!live) continue;
+        float stored = amax;
+        if constexpr (sizeof(T) == 2) stored = Src<T>::up(Src<T>::down(amax));
+        if (prep != nullptr) store16<T>(prep, first, n, p_vec, v);
+        float dq[16];
+        const uint4 codes = encode16<T, BIT>(v, stored, lef != nullptr ? &dq : nullptr);
+        if (lef != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) dq[i] = v[i] - dq[i];
+            store16<T>(lef, first, n, l_vec, dq);
+        }
+        const int64_t g = chunk / lanes;
+        const int lane = int(chunk - g * lanes);
+        if (p.mode == LBC_PUSH_COMPACT_LOCAL) {
+            uint8_t* rec = p.dst[0] + g * (VB + MB);
+            store_codes(rec + lane * CB, codes, CB);
+            if (lane == 0) store_scale<T>(rec + VB, stored);
+        } else if (p.mode == LBC_PUSH_SCATTER) {
+            const int64_t d = g / p.shard_groups;
+            const int64_t gl = g - d * p.shard_groups;
+            uint8_t* base = p.dst[d];
+            store_codes(base + gl * VB + lane * CB, codes, CB);
+            if (lane == 0) store_scale<T>(base + p.layout_groups * VB + gl * MB, stored);
+        } else {
+            const int64_t gl = p.group_offset + g;
+            for (int d = 0; d < p.num_dst; ++d) {
+                uint8_t* base = p.dst[d];
+                store_codes(base + gl * VB + lane * CB, codes, CB);
+                if (lane == 0) store_scale<T>(base + p.layout_groups * VB + gl * MB, stored);
+            }
+        }
+    }
+    grid_signal(p.signal);
+}
+
+// ---------------------------------------------------------------------------
+// reduce
+// ---------------------------------------------------------------------------
+template <typename T, int G, int BIT>
+__global__ void __launch_bounds__(kThreads) reduce_kernel(const LbcReduce p) {
+    constexpr int lanes = G / kElemsPerThread;
+    constexpr int VB = G * BIT / 8;
+    constexpr int MB = sizeof(T);
+    constexpr int CB = kElemsPerThread * BIT / 8;
+
+    if (!block_wait(p.wait)) return;
+
+    T* out = static_cast<T*>(p.out);
+    const T* prep = static_cast<const T*>(p.prepared);
+    T* rout = static_cast<T*>(p.residual_out);
+    const int64_t n = p.numel;
+    const int64_t num_groups = (n + G - 1) / G;
+    const int64_t num_chunks = num_groups * lanes;
+    const int64_t chunk_span = (num_chunks + 31) / 32 * 32;
+    const bool o_vec = out == nullptr || (reinterpret_cast<uintptr_t>(out) & 31) == 0;
+    const bool p_vec = prep == nullptr || (reinterpret_cast<uintptr_t>(prep) & 31) == 0;
+    const bool r_vec = rout == nullptr || (reinterpret_cast<uintptr_t>(rout) & 31) == 0;
+    const int R = p.num_src;
+    const int64_t rec = p.compact ? (VB + MB) : VB;
+
+    for (int64_t chunk = int64_t(blockIdx.x) * kThreads + threadIdx.x; chunk < chunk_span;
+         chunk += int64_t(gridDim.x) * kThreads) {
+        const bool live = chunk < num_chunks;
+        const int64_t first = chunk * kElemsPerThread;
+        const int64_t g = chunk / lanes;
+        const int lane = int(chunk - g * lanes);
+        const int64_t gs = p.group_offset + g;
+        float acc[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+        if (live) {
+            const int64_t voff = gs * rec + lane * CB;
+            const int64_t soff = p.compact ? gs * rec + VB : p.layout_groups * VB + gs * MB;
+#pragma unroll 4
+            for (int r = 0; r < R; ++r) {
+                const uint8_t* base = p.src[r];
+                const uint4 codes = load_codes(base + voff, CB);
+                const float s = load_scale<T>(base + soff);
+                float d[16];
+                decode16<T, BIT>(codes, s, d);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[i] += d[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] *= p.scale;
+            if (rout != nullptr) {
+                float pv[16];
+                load16<T>(prep, first, n, p_vec, pv, prep != rout);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) pv[i] -= acc[i];
+                store16<T>(rout, first, n, r_vec, pv);
+            }
+        }
+        // y = T(sum * scale): the value every consumer sees
+        round16<T>(acc);
+        if (live && out != nullptr) {
+            if (p.accumulate) {
+                float prev[16];
+                load16<T>(out, first, n, o_vec, prev, false);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) prev[i] += acc[i];
+                store16<T>(out, first, n, o_vec, prev);
+            } else {
+                store16<T>(out, first, n, o_vec, acc);
+            }
+        }
+        if (p.num_dst > 0) {
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(acc[i]));
+            amax = group_max<G>(amax);
+            if (live) {
+                float stored = amax;
+                if constexpr (sizeof(T) == 2) stored = Src<T>::up(Src<T>::down(amax));
+                const uint4 codes = encode16<T, BIT>(acc, stored, nullptr);
+                const int64_t gl = p.dst_group_offset + g;
+                for (int d = 0; d < p.num_dst; ++d) {
+                    uint8_t* base = p.dst[d];
+                    store_codes(base + gl * VB + lane * CB, codes, CB);
+                    if (lane == 0) store_scale<T>(base + p.dst_layout_groups * VB + gl * MB, stored);
+                }
+            }
+        }
+    }
+    grid_signal(p.signal);
+}
+
+// ---------------------------------------------------------------------------
+// elementwise helpers
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads) ef_update_kernel(const T* prepared, const T* restored, T* residual,
+                                                              int64_t n) {
+    const bool vec = ((reinterpret_cast<uintptr_t>(prepared) | reinterpret_cast<uintptr_t>(restored) |
+                       reinterpret_cast<uintptr_t>(residual)) & 31) == 0;
+    const int64_t chunks = (n + 15) / 16;
+    for (int64_t c = int64_t(blockIdx.x) * kThreads + threadIdx.x; c < chunks; c += int64_t(gridDim.x) * kThreads) {
+        float a[16], b[16];
+        load16<T>(prepared, c * 16, n, vec, a, true);
+        load16<T>(restored, c * 16, n, vec, b, true);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) a[i] -= b[i];
+        store16<T>(residual, c * 16, n, vec, a);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) scale_kernel(T* x, float scale, int64_t n) {
+    const bool vec = (reinterpret_cast<uintptr_t>(x) & 31) == 0;
+    const int64_t chunks = (n + 15) / 16;
+    for (int64_t c = int64_t(blockIdx.x) * kThreads + threadIdx.x; c < chunks; c += int64_t(gridDim.x) * kThreads) {
+        float a[16];
+        load16<T>(x, c * 16, n, vec, a, false);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) a[i] *= scale;
+        store16<T>(x, c * 16, n, vec, a);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// transport helpers
+// ---------------------------------------------------------------------------
+struct PushBytesArgs {
+    const uint8_t* src;
+    int64_t nvec;  // 16-byte vectors
+    uint8_t* dst[kMaxRanks];
+    int num_dst;
+    LbcWait wait;
+    LbcSignal signal;
+};
+
+__global__ void __launch_bounds__(kThreads) push_bytes_kernel(const PushBytesArgs a) {
+    if (!block_wait(a.wait)) return;
+    for (int64_t i = int64_t(blockIdx.x) * kThreads + threadIdx.x; i < a.nvec; i += int64_t(gridDim.x) * kThreads) {
+        const uint4 v = ld16_stream(a.src + i * 16);
+        for (int d = 0; d < a.num_dst; ++d) st16(a.dst[d] + i * 16, v);
+    }
+    grid_signal(a.signal);
+}
+
+struct WaitSignalArgs {
+    LbcWait wait;
+    LbcSignal signal;
+};
+
+__global__ void wait_signal_kernel(const WaitSignalArgs a) {
+    if (!block_wait(a.wait)) return;
+    grid_signal(a.signal);
+}
+
+// ---------------------------------------------------------------------------
+// launch helpers
+// ---------------------------------------------------------------------------
+static int g_max_blocks = 0;
+
+static int default_max_blocks() {
+    if (g_max_blocks == 0) {
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        g_max_blocks = sms * 8;  // 8 resident 256-thread blocks per SM
+    }
+    return g_max_blocks;
+}
+
+static int grid_for(int64_t chunks, int max_blocks) {
+    const int cap = max_blocks > 0 ? max_blocks : default_max_blocks();
+    int64_t want = (chunks + kThreads - 1) / kThreads;
+    if (want < 1) want = 1;
+    return int(want < cap ? want : cap);
+}
+
+template <template <typename, int, int> class Launcher, typename P>
+static cudaError_t dispatch(const P* p, cudaStream_t stream) {
+#define LBC_CASE(TT, GG, BB)                                                        \
+    if (p->group_size == GG && p->bit == BB) return Launcher<TT, GG, BB>::run(p, stream);
+#define LBC_TYPE(TT)                                                                \
+    LBC_CASE(TT, 64, 8) LBC_CASE(TT, 32, 8) LBC_CASE(TT, 16, 8)                     \
+    LBC_CASE(TT, 64, 4) LBC_CASE(TT, 32, 4) LBC_CASE(TT, 16, 4)
+    switch (p->dtype) {
+        case LBC_BF16: LBC_TYPE(__nv_bfloat16) break;
+        case LBC_FP16: LBC_TYPE(__half) break;
+        case LBC_FP32: LBC_TYPE(float) break;
+        default: break;
+    }
+#undef LBC_TYPE
+#undef LBC_CASE
+    return cudaErrorInvalidValue;
+}
+
+template <typename T, int G, int BIT>
+struct QuantPushLauncher {
+    static cudaError_t run(const LbcQuantPush* p, cudaStream_t stream) {
+        const int64_t groups = (p->numel + G - 1) / G;
+        if (groups == 0 && p->signal.num_remote == 0) return cudaSuccess;
+        const int grid = grid_for(groups * (G / kElemsPerThread), p->max_blocks);
+        quant_push_kernel<T, G, BIT><<<grid, kThreads, 0, stream>>>(*p);
+        return cudaGetLastError();
+    }
+};
+
+template <typename T, int G, int BIT>
+struct ReduceLauncher {
+    static cudaError_t run(const LbcReduce* p, cudaStream_t stream) {
+        const int64_t groups = (p->numel + G - 1) / G;
+        if (groups == 0 && p->signal.num_remote == 0 && p->wait.flags == nullptr) return cudaSuccess;
+        const int grid = grid_for(groups * (G / kElemsPerThread), p->max_blocks);
+        reduce_kernel<T, G, BIT><<<grid, kThreads, 0, stream>>>(*p);
+        return cudaGetLastError();
+    }
+};
+
+}  // namespace lbc
+
+extern "C" {
+
+int lbc_default_max_blocks(void) { return lbc::default_max_blocks(); }
+
+cudaError_t lbc_quant_push(const LbcQuantPush* p, cudaStream_t stream) {
+    if (p == nullptr || p->numel < 0 || p->num_dst < 0 || p->num_dst > LBC_MAX_RANKS) return cudaErrorInvalidValue;
+    if (p->signal.num_remote < 0 || p->signal.num_remote > LBC_MAX_RANKS) return cudaErrorInvalidValue;
+    if (p->mode == LBC_PUSH_SCATTER && p->shard_groups <= 0) return cudaErrorInvalidValue;
+    return lbc::dispatch<lbc::QuantPushLauncher>(p, stream);
+}
+
+cudaError_t lbc_reduce(const LbcReduce* p, cudaStream_t stream) {
+    if (p == nullptr || p->numel < 0 || p->num_src < 0 || p->num_src > LBC_MAX_RANKS) return cudaErrorInvalidValue;
+    if (p->num_dst < 0 || p->num_dst > LBC_MAX_RANKS) return cudaErrorInvalidValue;
+    if (p->signal.num_remote < 0 || p->signal.num_remote > LBC_MAX_RANKS) return cudaErrorInvalidValue;
+    if (p->wait.count < 0 || p->wait.count > lbc::kThreads) return cudaErrorInvalidValue;
+    return lbc::dispatch<lbc::ReduceLauncher>(p, stream);
+}
+
+cudaError_t lbc_error_feedback_update(int dtype, const void* prepared, const void* restored, void* residual,
+                                      int64_t numel, cudaStream_t stream) {
+    if (numel <= 0) return numel == 0 ? cudaSuccess : cudaErrorInvalidValue;
+    const int grid = lbc::grid_for((numel + 15) / 16, 0);
+    switch (dtype) {
+        case LBC_BF16:
+            lbc::ef_update_kernel<__nv_bfloat16><<<grid, lbc::kThreads, 0, stream>>>(
+                static_cast<const __nv_bfloat16*>(prepared), static_cast<const __nv_bfloat16*>(restored),
+                static_cast<__nv_bfloat16*>(residual), numel);
+            break;
+        case LBC_FP16:
+            lbc::ef_update_kernel<__half><<<grid, lbc::kThreads, 0, stream>>>(
+                static_cast<const __half*>(prepared), static_cast<const __half*>(restored),
+                static_cast<__half*>(residual), numel);
+            break;
+        case LBC_FP32:
+            lbc::ef_update_kernel<float><<<grid, lbc::kThreads, 0, stream>>>(
+                static_cast<const float*>(prepared), static_cast<const float*>(restored),
+                static_cast<float*>(residual), numel);
+            break;
+        default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t lbc_scale_inplace(int dtype, void* x, float scale, int64_t numel, cudaStream_t stream) {
+    if (numel <= 0) return numel == 0 ? cudaSuccess : cudaErrorInvalidValue;
+    const int grid = lbc::grid_for((numel + 15) / 16, 0);
+    switch (dtype) {
+        case LBC_BF16:
+            lbc::scale_kernel<__nv_bfloat16><<<grid, lbc::kThreads, 0, stream>>>(static_cast<__nv_bfloat16*>(x), scale, numel);
+            break;
+        case LBC_FP16:
+            lbc::scale_kernel<__half><<<grid, lbc::kThreads, 0, stream>>>(static_cast<__half*>(x), scale, numel);
+            break;
+        case LBC_FP32:
+            lbc::scale_kernel<float><<<grid, lbc::kThreads, 0, stream>>>(static_cast<float*>(x), scale, numel);
+            break;
+        default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t lbc_push_bytes(const uint8_t* src, int64_t nbytes, uint8_t* const* dst, int num_dst,
+                           const LbcWait* wait_before, const LbcSignal* signal, int max_blocks,
+                           cudaStream_t stream) {
+    if (nbytes < 0 || (nbytes & 15) != 0 || num_dst < 0 || num_dst > LBC_MAX_RANKS) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(src) & 15) != 0) return cudaErrorInvalidValue;
+    lbc::PushBytesArgs a{};
+    a.src = src;
+    a.nvec = nbytes / 16;
+    a.num_dst = num_dst;
+    for (int d = 0; d < num_dst; ++d) {
+        if ((reinterpret_cast<uintptr_t>(dst[d]) & 15) != 0) return cudaErrorInvalidValue;
+        a.dst[d] = dst[d];
+    }
+    if (wait_before != nullptr) a.wait = *wait_before;
+    if (signal != nullptr) a.signal = *signal;
+    if (a.wait.count < 0 || a.wait.count > lbc::kThreads) return cudaErrorInvalidValue;
+    const int grid = lbc::grid_for(a.nvec, max_blocks);
+    lbc::push_bytes_kernel<<<grid, lbc::kThreads, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t lbc_wait_signal(const LbcWait* wait, const LbcSignal* signal, cudaStream_t stream) {
+    lbc::WaitSignalArgs a{};
+    if (wait != nullptr) a.wait = *wait;
+    if (signal != nullptr) a.signal = *signal;
+    if (a.wait.count < 0 || a.wait.count > lbc::kThreads) return cudaErrorInvalidValue;
+    lbc::wait_signal_kernel<<<1, lbc::kThreads, 0, stream>>>(a);
+    return cudaGetLastError();
+}
+
+}  // extern "C"

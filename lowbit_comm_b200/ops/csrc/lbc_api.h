@@ -1,0 +1,132 @@
+// Host-callable launchers of the sm_100a kernels.  Everything here takes raw
+// device pointers and a stream, so the kernels build without any torch header.
+//
+// Parity map (reference, csrc/): quantize_pack_kernel (quantization/
+// quant_pack_kernel.cu:25-163) -> lbc_quant_push; dequant_kernel* and
+// dequant_reduce*_fused kernels (quantization/dequant_kernel.cuh:62-292,
+// dequant_reduce_kernel.cu:71-221) -> lbc_reduce; quant_kernel* with top-k,
+// 4-bit code-books and stochastic rounding (quant_kernel.cuh:155-400) ->
+// lbc_quant_general / lbc_dequant_general.  The scatter/broadcast modes, the
+// signals and the bounded waits have no counterpart in the reference: there the
+// payload moves through a NCCL call between kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LBC_MAX_RANKS 16
+
+enum LbcDType { LBC_FP16 = 0, LBC_BF16 = 1, LBC_FP32 = 2 };
+enum LbcQuantType { LBC_LINEAR = 0, LBC_NORMAL = 1, LBC_UNIFORM = 2, LBC_E3M0 = 3, LBC_E2M1 = 4 };
+enum LbcPushMode { LBC_PUSH_BROADCAST = 0, LBC_PUSH_SCATTER = 1, LBC_PUSH_COMPACT_LOCAL = 2 };
+
+typedef struct {
+    unsigned int* remote_flags[LBC_MAX_RANKS];  // flag arrays (one per destination)
+    int num_remote;                             // 0 = no signalling
+    int my_slot;                                // index written inside every flag array
+    unsigned int epoch;                         // value written
+    unsigned int* block_counter;                // local scratch counter, zero between launches
+} LbcSignal;
+
+typedef struct {
+    const unsigned int* flags;   // local flag array, NULL = no wait
+    int count;                   // flags[0..count) must reach `epoch`
+    unsigned int epoch;
+    unsigned long long timeout_ns;
+    void* status;                // LbcStatus*, device visible
+    unsigned int phase;
+} LbcWait;
+
+typedef struct {
+    unsigned int code, phase, peer, seen, expected, reserved[3];
+} LbcStatus;
+
+// ---- fast path: linear, top-k 0, deterministic rounding ---------------------
+typedef struct {
+    int dtype, group_size, bit;
+    const void* x;             // T[numel]
+    const void* residual;      // optional T[numel]: prepared = T(x + residual)
+    void* prepared_out;        // optional T[numel]: receives `prepared` (may alias residual)
+    void* local_ef_out;        // optional T[numel]: receives T(prepared - dequant(quant(prepared)))
+    int64_t numel;
+    int mode;                  // LbcPushMode
+    uint8_t* dst[LBC_MAX_RANKS];
+    int num_dst;
+    int64_t shard_groups;      // scatter: groups per destination
+    int64_t layout_groups;     // groups in the destination planar layout (start of the scale region)
+    int64_t group_offset;      // broadcast: index of group 0 inside the destination layout
+    LbcSignal signal;
+    int max_blocks;            // 0 = library default
+} LbcQuantPush;
+
+typedef struct {
+    int dtype, group_size, bit;
+    const uint8_t* src[LBC_MAX_RANKS];
+    int num_src;
+    int64_t layout_groups;     // groups in every source layout
+    int64_t group_offset;      // first group to read inside the source layout
+    int compact;               // sources use the per-group record layout
+    int64_t numel;             // elements to produce
+    float scale;               // applied to the fp32 sum (1/W for a mean)
+    void* out;                 // optional T[numel]
+    int accumulate;            // out = T(float(out) + float(T(y)))   (unfused SUM parity)
+    const void* prepared;      // optional T[numel]
+    void* residual_out;        // optional T[numel] = T(float(prepared) - y_fp32); may alias prepared
+    uint8_t* dst[LBC_MAX_RANKS];  // optional: requantize T(y) and broadcast it (planar)
+    int num_dst;
+    int64_t dst_layout_groups;
+    int64_t dst_group_offset;
+    LbcSignal signal;
+    LbcWait wait;
+    int max_blocks;
+} LbcReduce;
+
+cudaError_t lbc_quant_push(const LbcQuantPush* p, cudaStream_t stream);
+cudaError_t lbc_reduce(const LbcReduce* p, cudaStream_t stream);
+
+// ---- general path: top-k, 4-bit code-books, stochastic rounding --------------
+typedef struct {
+    int dtype, group_size, bit, topk, quant_type, stochastic, compact;
+    const void* x;
+    const void* residual;
+    void* prepared_out;
+    int64_t numel;
+    uint8_t* out;
+    unsigned long long seed;
+} LbcQuantGeneral;
+
+typedef struct {
+    int dtype, group_size, bit, topk, quant_type, compact;
+    const uint8_t* src;
+    int64_t numel;
+    void* out;
+    int accumulate;
+} LbcDequantGeneral;
+
+cudaError_t lbc_quant_general(const LbcQuantGeneral* p, cudaStream_t stream);
+cudaError_t lbc_dequant_general(const LbcDequantGeneral* p, cudaStream_t stream);
+
+// ---- elementwise helpers ----------------------------------------------------
+// residual = T(float(prepared) - float(restored))
+cudaError_t lbc_error_feedback_update(int dtype, const void* prepared, const void* restored, void* residual,
+                                      int64_t numel, cudaStream_t stream);
+// x = T(float(x) * scale)
+cudaError_t lbc_scale_inplace(int dtype, void* x, float scale, int64_t numel, cudaStream_t stream);
+
+// ---- transport helpers ------------------------------------------------------
+// Copies `nbytes` (multiple of 16, 16-byte aligned) to every dst, then signals.
+cudaError_t lbc_push_bytes(const uint8_t* src, int64_t nbytes, uint8_t* const* dst, int num_dst,
+                           const LbcWait* wait_before, const LbcSignal* signal, int max_blocks,
+                           cudaStream_t stream);
+// Waits (bounded) for flags; optionally signals afterwards (acknowledgement).
+cudaError_t lbc_wait_signal(const LbcWait* wait, const LbcSignal* signal, cudaStream_t stream);
+
+int lbc_default_max_blocks(void);
+
+#ifdef __cplusplus
+}
+#endif
