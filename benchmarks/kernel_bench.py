@@ -1,0 +1,114 @@
+"""Single-GPU microbenchmark of the codec and fused kernels (HBM roofline check).
+
+Usage: python benchmarks/kernel_bench.py [--mib 64] [--out gpurun_out/kernel_bench.json]
+Every kernel is timed with CUDA events after warm-up with an L2 flush between
+iterations; bandwidth = algorithmic bytes / median time, reported as a fraction
+of the measured copy bandwidth in MEASURED_PEAKS.json (fallback 6650 GB/s).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from lowbit_comm_b200.config import CompressionConfig  # noqa: E402
+from lowbit_comm_b200.ops import codec  # noqa: E402
+from lowbit_comm_b200.parallel.fused import FusedWorkspace, run_loopback  # noqa: E402
+from lowbit_comm_b200.parallel.peer_memory import PeerGroup  # noqa: E402
+from lowbit_comm_b200.utils.timing import L2Flusher, time_cuda  # noqa: E402
+
+
+def peak_gbs() -> tuple[float, str]:
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--mib", type=int, nargs="+", default=[64, 256])
+    ap.add_argument("--worlds", type=int, nargs="+", default=[1, 2, 8])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--out", default="gpurun_out/kernel_bench.json")
+    args = ap.parse_args()
+    cfg = CompressionConfig()
+    peak, peak_kind = peak_gbs()
+    flush = L2Flusher()
+    rows = []
+
+    def record(name, mib, nbytes, t, **extra):
+        gbs = nbytes / (t["median_ms"] * 1e-3) / 1e9
+        row = {"kernel": name, "mib": mib, "bytes": nbytes, **t, "gbs": gbs, "frac_of_peak": gbs / peak,
+               "peak_gbs": peak, "peak_kind": peak_kind, **extra}
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+
+    for mib in args.mib:
+        n = mib * 1024 * 1024 // 2
+        x = (torch.randn(n, device="cuda") * 1e-3).to(torch.bfloat16)
+        res = torch.zeros_like(x)
+        out = codec.allocate_quantized_buffer(x, cfg)
+        pb = out.numel()
+        t = time_cuda(lambda: codec.quantize_tensor(x, cfg, output=out), iters=args.iters, flush=flush)
+        record("quant_push(local)", mib, 2 * n + pb, t)
+        t = time_cuda(lambda: codec.quantize_tensor(x, cfg, output=out, residual=res, prepared_out=res),
+                      iters=args.iters, flush=flush)
+        record("quant_push(local,+EF in place)", mib, 6 * n + pb, t)
+        y = torch.empty_like(x)
+        t = time_cuda(lambda: codec.dequantize_tensor(out, x.shape, cfg, dtype="bf16", output=y),
+                      iters=args.iters, flush=flush)
+        record("reduce(1 payload)", mib, 2 * n + pb, t)
+        t = time_cuda(lambda: codec.inplace_dequantize_reduce_mean_update_error_feedback(
+            [out], res, y, res, cfg, reduce="mean"), iters=args.iters, flush=flush)
+        record("reduce(1 payload,+EF in place)", mib, 6 * n + pb, t)
+        bufs = [out] + [out.clone() for _ in range(7)]
+        t = time_cuda(lambda: codec.inplace_dequantize_reduce_mean(bufs, y, cfg, reduce="mean"),
+                      iters=args.iters, flush=flush)
+        record("reduce(8 payloads)", mib, 2 * n + 8 * pb, t)
+        z = torch.empty_like(x)
+        t = time_cuda(lambda: z.copy_(x), iters=args.iters, flush=flush)
+        record("torch copy_ (reference point)", mib, 4 * n, t)
+        del bufs
+        for world in args.worlds:
+            need = FusedWorkspace.required_bytes(world, "bf16", cfg, n, world <= 2) + (1 << 20)
+            if need * world > 60 * (1 << 30):
+                continue
+            groups = PeerGroup.loopback(world, need)
+            wss = [FusedWorkspace(g, dtype="bf16", config=cfg, max_numel=n) for g in groups]
+            xs = [x] + [x.clone() for _ in range(world - 1)]
+            rs = [torch.zeros_like(x) for _ in range(world)]
+
+            def step():
+                run_loopback(wss, "all_reduce", [(xs[r],) for r in range(world)],
+                             [{"residual": rs[r]} for r in range(world)])
+
+            t = time_cuda(step, iters=max(3, args.iters // 2), flush=flush)
+            # all emulated ranks share one GPU: per-rank time = total / world
+            per_rank_ms = t["median_ms"] / world
+            stages = 1 if world <= 2 else 2
+            c = pb / n
+            hbm = (6 * n + c * n) + (stages == 2) * (2 * c * n) + (c * n * (world if stages == 1 else 1) + 6 * n)
+            rows.append({"kernel": f"all_reduce loopback W={world} ({stages}-stage, EF)", "mib": mib,
+                         "per_rank_ms": per_rank_ms, "hbm_bytes_model": hbm,
+                         "gbs": hbm / (per_rank_ms * 1e-3) / 1e9, "frac_of_peak": hbm / (per_rank_ms * 1e-3) / 1e9 / peak,
+                         "launches_per_rank": wss[0].launches // max(1, (3 + max(3, args.iters // 2)))})
+            print(json.dumps(rows[-1]), flush=True)
+            torch.cuda.synchronize()
+            groups[0].check_status()
+            PeerGroup.close_loopback(groups)
+            del wss, xs, rs
+        del x, res, out, y, z
+        torch.cuda.empty_cache()
+    os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+    json.dump(rows, open(args.out, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -282,12 +282,16 @@ __device__ __forceinline__ bool block_wait(const WaitSpec& w) {
                 if (int(seen - w.epoch) >= 0) break;
                 if ((++spins & 63u) == 0 && global_ns() - t0 > w.timeout_ns) {
                     ok = 0;
-                    DeviceStatus* st = static_cast<DeviceStatus*>(w.status);
-                    if (st != nullptr && atomicCAS(&st->code, 0u, 1u) == 0u) {
+                    // plain stores: the status word may live in mapped host memory, where
+                    // device atomics are not guaranteed; any timed-out thread's report will do
+                    volatile DeviceStatus* st = static_cast<volatile DeviceStatus*>(w.status);
+                    if (st != nullptr) {
                         st->phase = w.phase;
                         st->peer = threadIdx.x;
                         st->seen = seen;
                         st->expected = w.epoch;
+                        __threadfence_system();
+                        st->code = 1u;
                         __threadfence_system();
                     }
                     break;

@@ -86,9 +86,10 @@ __device__ __forceinline__ uint4 encode16(const float (&vals)[16], float stored_
 #pragma unroll
     for (int i = 0; i < 16; ++i) q[i] = quant_rn(vals[i], mul, lim);
     if (decoded != nullptr) {
+        // this rank's own quantization error, one rounding: fma(-code, step, value)
         const float step = stored_scale / float(lim);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) (*decoded)[i] = float(q[i]) * step;
+        for (int i = 0; i < 16; ++i) (*decoded)[i] = __fmaf_rn(-float(q[i]), step, vals[i]);
     }
     if constexpr (BIT == 8) {
         return pack16_i8<sizeof(T)>(q);
@@ -98,19 +99,16 @@ __device__ __forceinline__ uint4 encode16(const float (&vals)[16], float stored_
     }
 }
 
+// Unpacks 16 codes to their integer values (as floats); the caller multiplies by the step.
 template <typename T, int BIT>
-__device__ __forceinline__ void decode16(uint4 codes, float stored_scale, float (&out)[16]) {
-    constexpr int lim = BIT == 8 ? 127 : 7;
-    const float step = stored_scale / float(lim);
+__device__ __forceinline__ void codes16(uint4 codes, float (&out)[16]) {
     if constexpr (BIT == 8) {
         unpack16_i8<sizeof(T)>(codes, out);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) out[i] *= step;
     } else {
         int c[16];
         unpack16_i4<sizeof(T)>(make_uint2(codes.x, codes.y), c);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) out[i] = int4_value(c[i]) * step;
+        for (int i = 0; i < 16; ++i) out[i] = int4_value(c[i]);
     }
 }
 
@@ -165,11 +163,7 @@ __global__ void __launch_bounds__(kThreads) quant_push_kernel(const LbcQuantPush
         if (prep != nullptr) store16<T>(prep, first, n, p_vec, v);
         float dq[16];
         const uint4 codes = encode16<T, BIT>(v, stored, lef != nullptr ? &dq : nullptr);
-        if (lef != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) dq[i] = v[i] - dq[i];
-            store16<T>(lef, first, n, l_vec, dq);
-        }
+        if (lef != nullptr) store16<T>(lef, first, n, l_vec, dq);
         const int64_t g = chunk / lanes;
         const int lane = int(chunk - g * lanes);
         if (p.mode == LBC_PUSH_COMPACT_LOCAL) {
@@ -237,10 +231,14 @@ __global__ void __launch_bounds__(kThreads) reduce_kernel(const LbcReduce p) {
                 const uint8_t* base = p.src[r];
                 const uint4 codes = load_codes(base + voff, CB);
                 const float s = load_scale<T>(base + soff);
+                // acc = fma(code, scale / L, acc): one rounding per payload, stated explicitly so
+                // that the result does not depend on the compiler's contraction choices
+                constexpr int lim = BIT == 8 ? 127 : 7;
+                const float step = s / float(lim);
                 float d[16];
-                decode16<T, BIT>(codes, s, d);
+                codes16<T, BIT>(codes, d);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) acc[i] += d[i];
+                for (int i = 0; i < 16; ++i) acc[i] = __fmaf_rn(d[i], step, acc[i]);
             }
 #pragma unroll
             for (int i = 0; i < 16; ++i) acc[i] *= p.scale;

@@ -220,6 +220,30 @@ def decode_fp32(payload: torch.Tensor, numel: int, config: CompressionConfig, dt
     return out.reshape(-1)[:numel]
 
 
+def _codes_and_steps(payload: torch.Tensor, numel: int, config: CompressionConfig, dtype: str):
+    """Linear profiles: signed integer codes and the per-element step `scale / L`, both fp32."""
+
+    tdt = TORCH_DTYPES[dtype]
+    word = 2 if dtype != "fp32" else 4
+    vbytes, mbytes = _split(payload, numel, config, dtype)
+    meta = mbytes.contiguous().view(_INT_VIEW[word]).reshape(vbytes.shape[0], -1)
+    scale = meta[:, 0].contiguous().view(tdt).float()
+    codes = _unpack_words(vbytes, config.bit, word)
+    half = 128 if config.bit == 8 else 8
+    signed = torch.where(codes >= half, codes - 2 * half, codes).float()
+    step = (scale / torch.tensor(_levels(config.bit), dtype=torch.float32))[:, None].expand_as(signed)
+    return signed.reshape(-1)[:numel], step.reshape(-1)[:numel]
+
+
+def local_error(prepared: torch.Tensor, payload: torch.Tensor, config: CompressionConfig) -> torch.Tensor:
+    """This rank's own quantization error T(prepared - code * step), one fused rounding."""
+
+    name = dtype_name(prepared)
+    code, step = _codes_and_steps(payload, prepared.numel(), config, name)
+    err = (prepared.reshape(-1).double() - code.double() * step.double()).float()
+    return err.to(prepared.dtype)
+
+
 def decode(payload: torch.Tensor, numel: int, config: CompressionConfig, dtype: str) -> torch.Tensor:
     return decode_fp32(payload, numel, config, dtype).to(TORCH_DTYPES[dtype])
 
@@ -239,8 +263,15 @@ def reduce_mean(payloads, numel: int, config: CompressionConfig, dtype: str, div
     """
 
     acc = torch.zeros(numel, dtype=torch.float32)
+    fused = config.quant_type == "linear" and config.topk == 0
     for p in payloads:
-        acc = acc + decode_fp32(p, numel, config, dtype)
+        if fused:
+            # the kernels accumulate with one fused multiply-add per payload:
+            # acc = round_fp32(code * step + acc), emulated here in float64
+            code, step = _codes_and_steps(p, numel, config, dtype)
+            acc = (code.double() * step.double() + acc.double()).float()
+        else:
+            acc = acc + decode_fp32(p, numel, config, dtype)
     div = float(len(payloads)) if divisor is None else float(divisor)
     inv = torch.tensor(1.0, dtype=torch.float32) / torch.tensor(div, dtype=torch.float32)
     y32 = acc * inv

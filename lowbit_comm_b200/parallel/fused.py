@@ -1,0 +1,324 @@
+"""Host drivers of the fused compression + NVLink collectives.
+
+One `FusedWorkspace` owns symmetric receive regions inside a `PeerGroup` arena
+and one signal channel.  Its methods only enqueue kernels on the current CUDA
+stream; nothing here synchronises with the host.
+
+Two-stage all-reduce (W >= 3 by default), per rank:
+  K1 quant_push/scatter : x (+residual) -> int8 groups; group g goes to the rank
+                          owning shard g // shard_groups, into that rank's RS
+                          region slot [me]; then signals RS[me] on every rank
+  K2 reduce             : waits RS[0..W); dequantizes the W slots of its shard,
+                          sums in fp32, scales, requantizes and writes the shard
+                          into every rank's AG region; then signals AG[me]
+  K3 reduce             : waits AG[0..W); decodes the AG region (a planar payload
+                          of the whole tensor) into `out`; updates the residual
+One-stage all-reduce (W <= 2): K1 broadcasts the whole payload to every rank's
+gather region slot [me]; one reduce kernel sums the W slots.
+
+Why reuse of the regions is safe without extra barriers: all ranks enqueue the
+same kernel sequence on one in-order stream.  K3(t) of a rank finishes only
+after every peer's K2(t) signalled, so by the time the rank's K1(t+1) overwrites
+a peer's RS slot that peer has finished reading it; K2(t+1) writes peers' AG
+regions only after every peer's K1(t+1) signalled, which those peers enqueue
+after their K3(t).  Regions that are read by a kernel not followed by such a
+barrier (gather region, RS region used by reduce-scatter alone) are double
+buffered by epoch parity, which the same argument makes sufficient.
+
+This replaces the reference's quantize -> NCCL all_to_all / all_gather ->
+dequantize chains (ccdl_comm/communication/reduce_scatter_transport.py:186-377,
+ccdl_comm/collectives/all_reduce.py:158-271).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..config import CompressionConfig
+from ..core.chunking import GroupShardPlan
+from ..ops import oracle
+from ..ops.codec import _DTYPE_CODE, is_fast_profile
+from ..ops.sizing import dtype_bytes
+from .peer_memory import PHASE_ALL_GATHER, PHASE_REDUCE_SCATTER, PeerGroup
+
+ALIGN_GROUPS = 8
+
+
+def _round_up(value: int, align: int) -> int:
+    return -(-value // align) * align
+
+
+@dataclass(frozen=True)
+class FusedGeometry:
+    numel: int
+    world_size: int
+    group_size: int
+    value_bytes: int     # per group
+    scale_bytes: int     # per group
+    shard_groups: int
+    num_groups: int
+
+    @property
+    def group_bytes(self) -> int:
+        return self.value_bytes + self.scale_bytes
+
+    @property
+    def total_groups(self) -> int:
+        return self.shard_groups * self.world_size
+
+    @property
+    def full_groups(self) -> int:
+        """Groups of a whole-tensor payload, padded to the alignment unit."""
+
+        return _round_up(self.num_groups, ALIGN_GROUPS)
+
+    @property
+    def shard_numel(self) -> int:
+        return self.shard_groups * self.group_size
+
+    def shard_valid_numel(self, rank: int) -> int:
+        lo = rank * self.shard_numel
+        return max(0, min(self.numel, lo + self.shard_numel) - lo)
+
+
+def geometry(numel: int, world_size: int, dtype: str, config: CompressionConfig) -> FusedGeometry:
+    plan = GroupShardPlan.build(numel, world_size, config.group_size, ALIGN_GROUPS)
+    return FusedGeometry(numel, world_size, config.group_size, config.group_size * config.bit // 8,
+                         dtype_bytes(dtype), plan.shard_groups, plan.num_groups)
+
+
+class FusedWorkspace:
+    """Symmetric regions + channel for tensors of up to `max_numel` elements."""
+
+    def __init__(self, group: PeerGroup, *, dtype: str, config: CompressionConfig, max_numel: int,
+                 max_blocks: int = 0, with_gather_region: bool | None = None) -> None:
+        if not is_fast_profile(config):
+            raise ValueError("fused collectives serve linear / top-k 0 / deterministic profiles")
+        self.group = group
+        self.dtype = dtype
+        self.config = config
+        self.max_numel = int(max_numel)
+        self.max_blocks = int(max_blocks)
+        self.ext = group._ext
+        cap = geometry(self.max_numel, group.world_size, dtype, config)
+        self.cap = cap
+        W = group.world_size
+        self.shard_stride = _round_up(max(cap.shard_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
+        self.rs_bytes = W * self.shard_stride
+        self.rs_off = [group.alloc(self.rs_bytes), group.alloc(self.rs_bytes)]
+        self.ag_bytes = _round_up(max(cap.total_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
+        self.ag_off = group.alloc(self.ag_bytes)
+        self.gather_stride = _round_up(max(cap.full_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
+        self.gather_off: list[int] | None = None
+        if with_gather_region or (with_gather_region is None and W <= 2):
+            self._ensure_gather()
+        self.channel = group.new_channel()
+        self.launches = 0
+
+    @staticmethod
+    def required_bytes(world_size: int, dtype: str, config: CompressionConfig, max_numel: int,
+                       with_gather_region: bool) -> int:
+        cap = geometry(max_numel, world_size, dtype, config)
+        shard = _round_up(max(cap.shard_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
+        total = 2 * world_size * shard + _round_up(max(cap.total_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
+        if with_gather_region:
+            total += 2 * world_size * _round_up(max(cap.full_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
+        return total + 8 * 256
+
+    def _ensure_gather(self) -> list[int]:
+        if self.gather_off is None:
+            size = self.group.world_size * self.gather_stride
+            self.gather_off = [self.group.alloc(size), self.group.alloc(size)]
+        return self.gather_off
+
+    # -- helpers ---------------------------------------------------------------
+    def _geom(self, x: torch.Tensor) -> FusedGeometry:
+        if x.numel() > self.max_numel:
+            raise ValueError(f"tensor has {x.numel()} elements, workspace holds {self.max_numel}")
+        if oracle.dtype_name(x) != self.dtype:
+            raise TypeError(f"workspace was built for {self.dtype}")
+        if not x.is_contiguous():
+            raise ValueError("tensor must be contiguous")
+        return geometry(x.numel(), self.group.world_size, self.dtype, self.config)
+
+    @property
+    def _code(self) -> int:
+        return _DTYPE_CODE[self.dtype]
+
+    def _scale(self, op: str) -> float:
+        if op == "mean":
+            return 1.0 / self.group.world_size
+        if op == "sum":
+            return 1.0
+        raise ValueError(f"unsupported reduce op {op!r}")
+
+    # -- kernels ---------------------------------------------------------------
+    def _k1_scatter(self, x, residual, prepared_out, local_ef_out, geo: FusedGeometry, epoch: int, parity: int):
+        g, me = self.group, self.group.rank
+        dst = [g.addr(d, self.rs_off[parity] + me * self.shard_stride) for d in range(g.world_size)]
+        self.ext.quant_push(x, residual, prepared_out, local_ef_out, dst, self.ext.PUSH_SCATTER,
+                            geo.shard_groups, geo.shard_groups, 0, geo.group_size, self.config.bit,
+                            g.signal_all(self.channel, PHASE_REDUCE_SCATTER, epoch), self.max_blocks)
+        self.launches += 1
+
+    def _k2_reduce(self, geo: FusedGeometry, epoch: int, parity: int, scale: float, out, broadcast: bool):
+        g, me = self.group, self.group.rank
+        src = [g.local_ptr + self.rs_off[parity] + r * self.shard_stride for r in range(g.world_size)]
+        dst = [g.addr(d, self.ag_off) for d in range(g.world_size)] if broadcast else []
+        signal = g.signal_all(self.channel, PHASE_ALL_GATHER, epoch) if broadcast else None
+        self.ext.reduce(src, geo.shard_groups, 0, False, geo.shard_valid_numel(me), self._code, geo.group_size,
+                        self.config.bit, scale, out, False, None, None, dst, geo.total_groups,
+                        me * geo.shard_groups, signal, g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch),
+                        self.max_blocks)
+        self.launches += 1
+
+    def _k3_gather(self, geo: FusedGeometry, epoch: int, out, prepared, residual_out):
+        g = self.group
+        self.ext.reduce([g.local_ptr + self.ag_off], geo.total_groups, 0, False, geo.numel, self._code,
+                        geo.group_size, self.config.bit, 1.0, out, False, prepared, residual_out, [], 0, 0, None,
+                        g.wait_all(self.channel, PHASE_ALL_GATHER, epoch), self.max_blocks)
+        self.launches += 1
+
+    def _k1_broadcast(self, x, residual, prepared_out, local_ef_out, geo: FusedGeometry, epoch: int, parity: int):
+        g, me = self.group, self.group.rank
+        region = self._ensure_gather()[parity]
+        dst = [g.addr(d, region + me * self.gather_stride) for d in range(g.world_size)]
+        self.ext.quant_push(x, residual, prepared_out, local_ef_out, dst, self.ext.PUSH_BROADCAST, 0,
+                            geo.full_groups, 0, geo.group_size, self.config.bit,
+                            g.signal_all(self.channel, PHASE_REDUCE_SCATTER, epoch), self.max_blocks)
+        self.launches += 1
+
+    # -- collectives -------------------------------------------------------------
+    def all_reduce(self, x: torch.Tensor, out: torch.Tensor | None = None, *, residual: torch.Tensor | None = None,
+                   update_residual: bool = True, op: str = "mean", stages: int | None = None,
+                   ef_mode: str = "reference") -> torch.Tensor:
+        """Compressed all-reduce of `x` into `out` (default: in place).
+
+        `residual` is added before quantization.  With `update_residual` it is
+        rewritten: ef_mode="reference" stores T(prepared - result) (the rule of
+        ccdl_comm/communication/ddp_hook.py:268-277), ef_mode="local" stores this
+        rank's own quantization error.
+        """
+
+        geo = self._geom(x)
+        flat = x.reshape(-1)
+        out_flat = flat if out is None else out.reshape(-1)
+        res = None if residual is None else residual.reshape(-1)
+        if stages is None:
+            stages = 1 if self.group.world_size <= 2 else 2
+        scale = self._scale(op)
+        epoch = self.group.next_epoch(self.channel)
+        parity = epoch & 1
+        want_ref = res is not None and update_residual and ef_mode == "reference"
+        want_local = res is not None and update_residual and ef_mode == "local"
+        prepared_out = res if want_ref else None
+        local_out = res if want_local else None
+        if geo.numel == 0:
+            return x if out is None else out
+        if stages == 1:
+            self._k1_broadcast(flat, res, prepared_out, local_out, geo, epoch, parity)
+            region = self.gather_off[parity]
+            src = [self.group.local_ptr + region + r * self.gather_stride for r in range(self.group.world_size)]
+            self.ext.reduce(src, geo.full_groups, 0, False, geo.numel, self._code, geo.group_size, self.config.bit,
+                            scale, out_flat, False, res if want_ref else None, res if want_ref else None, [], 0, 0,
+                            None, self.group.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch), self.max_blocks)
+            self.launches += 1
+        else:
+            self._k1_scatter(flat, res, prepared_out, local_out, geo, epoch, parity)
+            self._k2_reduce(geo, epoch, parity, scale, None, True)
+            self._k3_gather(geo, epoch, out_flat, res if want_ref else None, res if want_ref else None)
+        return x if out is None else out
+
+    def reduce_scatter(self, x: torch.Tensor, out_shard: torch.Tensor, *, residual: torch.Tensor | None = None,
+                       update_residual: bool = True, op: str = "mean") -> FusedGeometry:
+        """Rank r receives the reduced elements [r*shard_numel, (r+1)*shard_numel).
+
+        `out_shard` holds `shard_numel` elements (group aligned); elements past
+        the end of the tensor are zero.  Error feedback, when a residual is
+        given, uses this rank's own quantization error.
+        """
+
+        geo = self._geom(x)
+        if out_shard.numel() != geo.shard_numel:
+            raise ValueError(f"out_shard must hold {geo.shard_numel} elements")
+        res = None if residual is None else residual.reshape(-1)
+        epoch = self.group.next_epoch(self.channel)
+        parity = epoch & 1
+        valid = geo.shard_valid_numel(self.group.rank)
+        flat_out = out_shard.reshape(-1)
+        if valid < geo.shard_numel:
+            flat_out[valid:].zero_()
+        self._k1_scatter(x.reshape(-1), res, None, res if (res is not None and update_residual) else None, geo,
+                         epoch, parity)
+        self._k2_reduce(geo, epoch, parity, self._scale(op), flat_out[:valid] if valid else None, False)
+        return geo
+
+    def all_gather(self, x: torch.Tensor, outs: list[torch.Tensor]) -> list[torch.Tensor]:
+        """Every rank contributes `x` (same shape everywhere); outs[r] = decode(rank r's payload)."""
+
+        geo = self._geom(x)
+        g = self.group
+        if len(outs) != g.world_size:
+            raise ValueError("one output per rank is required")
+        epoch = g.next_epoch(self.channel)
+        parity = epoch & 1
+        if geo.numel == 0:
+            return outs
+        self._k1_broadcast(x.reshape(-1), None, None, None, geo, epoch, parity)
+        region = self.gather_off[parity]
+        for r, out in enumerate(outs):
+            wait = g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch) if r == 0 else None
+            self.ext.reduce([g.local_ptr + region + r * self.gather_stride], geo.full_groups, 0, False, geo.numel,
+                            self._code, geo.group_size, self.config.bit, 1.0, out.reshape(-1), False, None, None,
+                            [], 0, 0, None, wait, self.max_blocks)
+            self.launches += 1
+        return outs
+
+
+def run_loopback(workspaces: list[FusedWorkspace], method: str, per_rank_args: list[tuple],
+                 per_rank_kwargs: list[dict] | None = None, **kwargs) -> list:
+    """Single-GPU emulation: run one collective for all emulated ranks, phase by phase.
+
+    Kernels that wait must start only after the kernels that signal them were
+    enqueued for *all* emulated ranks (one stream, one GPU), so the launches of
+    the ranks are interleaved by phase rather than run rank after rank.
+    """
+
+    extra = per_rank_kwargs or [{}] * len(workspaces)
+    plans = [_PhasedCall(ws, method, args, {**kwargs, **kw}) for ws, args, kw in zip(workspaces, per_rank_args, extra)]
+    depth = max(len(p.steps) for p in plans)
+    for level in range(depth):
+        for p in plans:
+            if level < len(p.steps):
+                p.steps[level]()
+    return [p.result for p in plans]
+
+
+class _PhasedCall:
+    """Records the kernel launches of one collective call so they can be replayed by phase."""
+
+    def __init__(self, ws: FusedWorkspace, method: str, args: tuple, kwargs: dict) -> None:
+        self.steps: list = []
+        recorder = _Recorder(ws.ext, self.steps)
+        real = ws.ext
+        ws.ext = recorder
+        try:
+            self.result = getattr(ws, method)(*args, **kwargs)
+        finally:
+            ws.ext = real
+
+
+class _Recorder:
+    def __init__(self, ext, steps: list) -> None:
+        self._ext = ext
+        self._steps = steps
+
+    def __getattr__(self, name):
+        attr = getattr(self._ext, name)
+        if name in ("quant_push", "reduce", "push_bytes", "wait_signal"):
+            def defer(*a, **k):
+                self._steps.append(lambda: attr(*a, **k))
+            return defer
+        return attr

@@ -1,0 +1,229 @@
+"""Symmetric peer-visible arenas, flag pads and status words.
+
+Every rank of a single-node group allocates one device arena, exports it with
+a CUDA IPC handle and maps the arenas of all other ranks.  Offsets inside the
+arena mean the same thing on every rank (symmetric allocation), so a kernel can
+address "my slot in rank d's receive region" as `peer_base[d] + offset`.
+
+Arena layout:
+  [0, 16 KiB)      flags[channel][phase][source rank]  (uint32 epochs, written by peers)
+  [16, 20 KiB)     block counters[channel][phase]      (local scratch of the signalling kernels)
+  [64 KiB, ...)    data regions handed out by `alloc`
+
+The reference has no counterpart (its payloads travel through torch.distributed
+calls, ccdl_comm/communication/torch_transport.py:61-188).
+"""
+
+from __future__ import annotations
+
+import threading
+from typing import Any
+
+import torch
+
+from ..exceptions import AsyncCommunicationError, CCDLUnavailableError
+from ..ops.loader import require_extension
+
+MAX_CHANNELS = 64
+NUM_PHASES = 4
+MAX_RANKS = 16
+FLAG_BYTES = MAX_CHANNELS * NUM_PHASES * MAX_RANKS * 4
+COUNTER_OFFSET = FLAG_BYTES
+DATA_OFFSET = 64 * 1024
+DEFAULT_TIMEOUT_NS = 20_000_000_000  # 20 s: far above any real skew, far below a watchdog
+
+PHASE_REDUCE_SCATTER, PHASE_ALL_GATHER, PHASE_P2P_DATA, PHASE_P2P_ACK = range(NUM_PHASES)
+
+
+def _round_up(value: int, align: int) -> int:
+    return -(-value // align) * align
+
+
+class PeerGroup:
+    """One rank's handle on the group's arenas."""
+
+    def __init__(self, *, rank: int, world_size: int, device: torch.device, nbytes: int, peer_ptrs: list[int],
+                 ext: Any, owner: bool, process_group: Any = None, opened: list[int] | None = None,
+                 timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+        if world_size > MAX_RANKS:
+            raise CCDLUnavailableError(f"peer groups support at most {MAX_RANKS} ranks")
+        self.rank = rank
+        self.world_size = world_size
+        self.device = device
+        self.nbytes = nbytes
+        self.peer_ptrs = list(peer_ptrs)
+        self.local_ptr = self.peer_ptrs[rank]
+        self.process_group = process_group
+        self.timeout_ns = timeout_ns
+        self._ext = ext
+        self._owner = owner
+        self._opened = list(opened or [])
+        self._cursor = DATA_OFFSET
+        self._epochs = [0] * MAX_CHANNELS
+        self._channels_used = 0
+        self._lock = threading.Lock()
+        self._closed = False
+        host, dev = ext.status_alloc()
+        self.status_host, self.status_device = host, dev
+
+    # -- construction -------------------------------------------------------
+    @classmethod
+    def create(cls, process_group: Any, nbytes: int, device: torch.device | None = None, *,
+               timeout_ns: int = DEFAULT_TIMEOUT_NS) -> "PeerGroup":
+        """Collective: every rank of `process_group` (one node) calls this."""
+
+        import torch.distributed as dist
+
+        ext = require_extension()
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        rank = dist.get_rank(process_group)
+        world = dist.get_world_size(process_group)
+        nbytes = _round_up(max(nbytes, DATA_OFFSET + 4096), 2 << 20)
+        with torch.cuda.device(device):
+            local = ext.arena_alloc(nbytes)
+            handle = ext.ipc_get_handle(local) if world > 1 else b""
+            infos: list[Any] = [None] * world
+            dist.all_gather_object(infos, (device.index, handle), group=process_group)
+            ptrs, opened = [], []
+            for peer, (peer_dev, peer_handle) in enumerate(infos):
+                if peer == rank:
+                    ptrs.append(local)
+                    continue
+                if not ext.can_access_peer(device.index, peer_dev):
+                    ext.arena_free(local)
+                    raise CCDLUnavailableError(f"GPU {device.index} cannot access GPU {peer_dev} as a peer")
+                mapped = ext.ipc_open_handle(peer_handle)
+                ptrs.append(mapped)
+                opened.append(mapped)
+            torch.cuda.synchronize(device)
+        dist.barrier(group=process_group)
+        return cls(rank=rank, world_size=world, device=device, nbytes=nbytes, peer_ptrs=ptrs, ext=ext, owner=True,
+                   process_group=process_group, opened=opened, timeout_ns=timeout_ns)
+
+    @classmethod
+    def loopback(cls, world_size: int, nbytes: int, device: torch.device | None = None, *,
+                 timeout_ns: int = DEFAULT_TIMEOUT_NS) -> list["PeerGroup"]:
+        """`world_size` emulated ranks whose arenas all live on one GPU.
+
+        For single-GPU tests and benchmarks: the phases of a collective are run
+        one after the other for all emulated ranks on one stream, so every flag
+        is already set when a waiting kernel starts.
+        """
+
+        ext = require_extension()
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        nbytes = _round_up(max(nbytes, DATA_OFFSET + 4096), 2 << 20)
+        with torch.cuda.device(device):
+            ptrs = [ext.arena_alloc(nbytes) for _ in range(world_size)]
+        return [cls(rank=r, world_size=world_size, device=device, nbytes=nbytes, peer_ptrs=ptrs, ext=ext,
+                    owner=True, timeout_ns=timeout_ns, opened=[]) for r in range(world_size)]
+
+    # -- symmetric allocation ----------------------------------------------
+    def alloc(self, nbytes: int, align: int = 256) -> int:
+        """Reserve `nbytes`; returns the offset (identical on every rank)."""
+
+        with self._lock:
+            start = _round_up(self._cursor, align)
+            if start + nbytes > self.nbytes:
+                raise CCDLUnavailableError(
+                    f"peer arena exhausted: need {nbytes} bytes at {start}, arena has {self.nbytes}")
+            self._cursor = start + nbytes
+            return start
+
+    def new_channel(self) -> int:
+        with self._lock:
+            if self._channels_used >= MAX_CHANNELS:
+                raise CCDLUnavailableError("no free signal channel")
+            self._channels_used += 1
+            return self._channels_used - 1
+
+    @property
+    def bytes_free(self) -> int:
+        return self.nbytes - self._cursor
+
+    # -- addresses ----------------------------------------------------------
+    def addr(self, rank: int, offset: int) -> int:
+        return self.peer_ptrs[rank] + offset
+
+    def flags_addr(self, rank: int, channel: int, phase: int) -> int:
+        return self.peer_ptrs[rank] + ((channel * NUM_PHASES + phase) * MAX_RANKS) * 4
+
+    def counter_addr(self, channel: int, phase: int) -> int:
+        return self.local_ptr + COUNTER_OFFSET + (channel * NUM_PHASES + phase) * 4
+
+    def local_view(self, offset: int, nbytes: int) -> torch.Tensor:
+        """uint8 tensor aliasing a region of this rank's own arena."""
+
+        return self._ext.tensor_from_address(self.local_ptr + offset, nbytes, self.device.index)
+
+    # -- signalling helpers ---------------------------------------------------
+    def next_epoch(self, channel: int) -> int:
+        self._epochs[channel] = (self._epochs[channel] + 1) & 0x7FFFFFFF
+        return self._epochs[channel]
+
+    def signal_all(self, channel: int, phase: int, epoch: int, ranks=None):
+        """Signal tuple: write `epoch` into slot `rank` of the flag pad of every listed rank."""
+
+        ranks = range(self.world_size) if ranks is None else ranks
+        return ([self.flags_addr(r, channel, phase) for r in ranks], self.rank, epoch,
+                self.counter_addr(channel, phase))
+
+    def wait_all(self, channel: int, phase: int, epoch: int, count: int | None = None, first: int = 0):
+        """Wait tuple: local flags [first, first+count) of (channel, phase) must reach `epoch`."""
+
+        count = self.world_size if count is None else count
+        return (self.flags_addr(self.rank, channel, phase) + 4 * first, count, epoch, self.timeout_ns,
+                self.status_device, phase)
+
+    # -- status ---------------------------------------------------------------
+    def read_status(self) -> dict:
+        code, phase, peer, seen, expected = self._ext.status_read(self.status_host)
+        return {"code": code, "phase": phase, "peer": peer, "seen": seen, "expected": expected}
+
+    def check_status(self) -> None:
+        st = self.read_status()
+        if st["code"] != 0:
+            raise AsyncCommunicationError(
+                f"device wait timed out on rank {self.rank} (phase {st['phase']}, flag {st['peer']}, "
+                f"saw epoch {st['seen']}, expected {st['expected']})", status=st)
+
+    def clear_status(self) -> None:
+        self._ext.status_clear(self.status_host)
+
+    def reset_after_error(self) -> None:
+        """Zero this rank's counters after a failed collective (flags keep their epochs)."""
+
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            self._ext.memset_async(self.local_ptr + COUNTER_OFFSET, 0, DATA_OFFSET - COUNTER_OFFSET)
+            torch.cuda.synchronize(self.device)
+        self.clear_status()
+
+    # -- teardown ---------------------------------------------------------------
+    def close(self, *, free_arena: bool = True) -> None:
+        if self._closed:
+            return
+        self._closed = True
+        try:
+            torch.cuda.synchronize(self.device)
+        except Exception:  # noqa: BLE001
+            pass
+        for ptr in self._opened:
+            try:
+                self._ext.ipc_close_handle(ptr)
+            except Exception:  # noqa: BLE001
+                pass
+        self._ext.status_free(self.status_host)
+        if self._owner and free_arena and self.process_group is not None:
+            self._ext.arena_free(self.local_ptr)
+
+    @staticmethod
+    def close_loopback(groups: list["PeerGroup"]) -> None:
+        if not groups:
+            return
+        torch.cuda.synchronize(groups[0].device)
+        for g in groups:
+            g._closed = True
+            g._ext.status_free(g.status_host)
+        for ptr in groups[0].peer_ptrs:
+            groups[0]._ext.arena_free(ptr)

@@ -1,0 +1,135 @@
+"""Fused push/reduce collectives on ONE GPU with emulated ranks.
+
+Every emulated rank has its own arena on the same device; the phases of a
+collective are enqueued for all ranks in turn on one stream, so a kernel that
+waits for a flag always starts after the kernels that set it.  Results are
+compared with the torch oracle composed the same way.
+"""
+
+import pytest
+import torch
+
+from lowbit_comm_b200.config import CompressionConfig
+from lowbit_comm_b200.exceptions import AsyncCommunicationError
+from lowbit_comm_b200.ops import oracle
+from lowbit_comm_b200.parallel.fused import FusedWorkspace, geometry, run_loopback
+from lowbit_comm_b200.parallel.peer_memory import PHASE_P2P_DATA, PeerGroup
+
+pytestmark = pytest.mark.gpu
+
+DT = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}
+
+
+def _inputs(world, n, dtype, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [(torch.randn(n, generator=g) * 1e-2 * (r + 1)).to(DT[dtype]) for r in range(world)]
+
+
+def _expected_two_stage(xs, residuals, cfg, dtype, op="mean"):
+    n = xs[0].numel()
+    prepared = [oracle.prepare(x, r) for x, r in zip(xs, residuals)]
+    payloads = [oracle.encode(p, cfg) for p in prepared]
+    y, _ = oracle.reduce_mean(payloads, n, cfg, dtype, None if op == "mean" else 1.0)
+    again = oracle.encode(y, cfg)
+    z32 = oracle.decode_fp32(again, n, cfg, dtype)
+    return z32.to(DT[dtype]), [oracle.residual_update(p, z32) for p in prepared], prepared
+
+
+def _expected_one_stage(xs, residuals, cfg, dtype, op="mean"):
+    n = xs[0].numel()
+    prepared = [oracle.prepare(x, r) for x, r in zip(xs, residuals)]
+    payloads = [oracle.encode(p, cfg) for p in prepared]
+    y, y32 = oracle.reduce_mean(payloads, n, cfg, dtype, None if op == "mean" else 1.0)
+    return y, [oracle.residual_update(p, y32) for p in prepared], prepared
+
+
+def _make(world, dtype, cfg, max_numel, **kw):
+    need = FusedWorkspace.required_bytes(world, dtype, cfg, max_numel, True) + (1 << 20)
+    groups = PeerGroup.loopback(world, need, timeout_ns=2_000_000_000)
+    return groups, [FusedWorkspace(g, dtype=dtype, config=cfg, max_numel=max_numel, with_gather_region=True, **kw)
+                    for g in groups]
+
+
+@pytest.mark.parametrize("world", (1, 2, 4, 8))
+@pytest.mark.parametrize("dtype,bit,group", [("bf16", 8, 64), ("fp16", 8, 32), ("fp32", 8, 64), ("bf16", 4, 16)])
+@pytest.mark.parametrize("stages", (1, 2))
+def test_all_reduce_matches_oracle(ext, world, dtype, bit, group, stages):
+    cfg = CompressionConfig(bit=bit, group_size=group, allow_experimental=True)
+    max_numel = 40_000
+    groups, wss = _make(world, dtype, cfg, max_numel)
+    try:
+        for step, n in enumerate((world * group * 8, 3001, 1, max_numel, 64 * 511 + 7)):
+            xs = _inputs(world, n, dtype, seed=step)
+            rs = _inputs(world, n, dtype, seed=100 + step)
+            dev_x = [x.cuda() for x in xs]
+            dev_r = [r.cuda() for r in rs]
+            outs = [torch.empty_like(x) for x in dev_x]
+            run_loopback(wss, "all_reduce", [(dev_x[r], outs[r]) for r in range(world)],
+                         residual=None, stages=stages)
+            expect = (_expected_one_stage if stages == 1 else _expected_two_stage)(xs, [None] * world, cfg, dtype)
+            for r in range(world):
+                assert torch.equal(outs[r].cpu().view(torch.uint8), expect[0].view(torch.uint8)), (n, r)
+            # with error feedback, in place (the DDP hook's form)
+            dev_x = [x.cuda() for x in xs]
+            run_loopback(wss, "all_reduce", [(dev_x[r],) for r in range(world)],
+                         [{"residual": dev_r[r]} for r in range(world)], stages=stages)
+            expect = (_expected_one_stage if stages == 1 else _expected_two_stage)(xs, rs, cfg, dtype)
+            for r in range(world):
+                assert torch.equal(dev_x[r].cpu().view(torch.uint8), expect[0].view(torch.uint8)), (n, r, "ef")
+                assert torch.equal(dev_r[r].cpu().view(torch.uint8), expect[1][r].view(torch.uint8)), (n, r, "res")
+        torch.cuda.synchronize()
+        for g in groups:
+            g.check_status()
+    finally:
+        PeerGroup.close_loopback(groups)
+
+
+@pytest.mark.parametrize("world", (2, 4, 8))
+def test_reduce_scatter_and_all_gather(ext, world):
+    cfg = CompressionConfig()
+    dtype, n = "bf16", 64 * 300 + 17
+    groups, wss = _make(world, dtype, cfg, n)
+    try:
+        xs = _inputs(world, n, dtype, seed=5)
+        dev = [x.cuda() for x in xs]
+        geo = geometry(n, world, dtype, cfg)
+        shards = [torch.full((geo.shard_numel,), 7.0, dtype=DT[dtype], device="cuda") for _ in range(world)]
+        run_loopback(wss, "reduce_scatter", [(dev[r], shards[r]) for r in range(world)])
+        payloads = [oracle.encode(x, cfg) for x in xs]
+        y, _ = oracle.reduce_mean(payloads, n, cfg, dtype)
+        padded = torch.zeros(geo.shard_numel * world, dtype=DT[dtype])
+        padded[:n] = y
+        for r in range(world):
+            want = padded[r * geo.shard_numel:(r + 1) * geo.shard_numel]
+            assert torch.equal(shards[r].cpu().view(torch.uint8), want.view(torch.uint8)), r
+        outs = [[torch.empty(n, dtype=DT[dtype], device="cuda") for _ in range(world)] for _ in range(world)]
+        run_loopback(wss, "all_gather", [(dev[r], outs[r]) for r in range(world)])
+        for r in range(world):
+            for s in range(world):
+                want = oracle.decode(payloads[s], n, cfg, dtype)
+                assert torch.equal(outs[r][s].cpu().view(torch.uint8), want.view(torch.uint8)), (r, s)
+        torch.cuda.synchronize()
+        for g in groups:
+            g.check_status()
+    finally:
+        PeerGroup.close_loopback(groups)
+
+
+def test_bounded_wait_reports_status_instead_of_hanging(ext):
+    """A flag that nothing sets: the kernel gives up after its time limit and says why."""
+
+    groups = PeerGroup.loopback(2, 1 << 20, timeout_ns=50_000_000)  # 50 ms
+    try:
+        g = groups[0]
+        ch = g.new_channel()
+        ext.wait_signal(g.wait_all(ch, PHASE_P2P_DATA, epoch=1), None)
+        torch.cuda.synchronize()  # returns: the wait is bounded
+        with pytest.raises(AsyncCommunicationError) as info:
+            g.check_status()
+        assert info.value.status["expected"] == 1 and info.value.status["seen"] == 0
+        g.reset_after_error()
+        g.check_status()
+        # the context is still usable
+        assert torch.ones(4, device="cuda").sum().item() == 4
+    finally:
+        PeerGroup.close_loopback(groups)
