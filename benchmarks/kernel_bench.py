@@ -34,13 +34,17 @@ def peak_gbs() -> tuple[float, str]:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--mib", type=int, nargs="+", default=[64, 256])
-    ap.add_argument("--worlds", type=int, nargs="+", default=[1, 2, 8])
+    ap.add_argument("--worlds", type=int, nargs="*", default=[1, 2, 8])
+    ap.add_argument("--profile", action="store_true", help="one warm-up + one timed launch per kernel (for ncu)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--out", default="gpurun_out/kernel_bench.json")
     args = ap.parse_args()
     cfg = CompressionConfig()
     peak, peak_kind = peak_gbs()
-    flush = L2Flusher()
+    flush = None if args.profile else L2Flusher()
+    warm = 1 if args.profile else 3
+    if args.profile:
+        args.iters = 1
     rows = []
 
     def record(name, mib, nbytes, t, **extra):
@@ -56,24 +60,24 @@ def main() -> None:
         res = torch.zeros_like(x)
         out = codec.allocate_quantized_buffer(x, cfg)
         pb = out.numel()
-        t = time_cuda(lambda: codec.quantize_tensor(x, cfg, output=out), iters=args.iters, flush=flush)
+        t = time_cuda(lambda: codec.quantize_tensor(x, cfg, output=out), iters=args.iters, flush=flush, warmup=warm)
         record("quant_push(local)", mib, 2 * n + pb, t)
         t = time_cuda(lambda: codec.quantize_tensor(x, cfg, output=out, residual=res, prepared_out=res),
-                      iters=args.iters, flush=flush)
+                      iters=args.iters, flush=flush, warmup=warm)
         record("quant_push(local,+EF in place)", mib, 6 * n + pb, t)
         y = torch.empty_like(x)
         t = time_cuda(lambda: codec.dequantize_tensor(out, x.shape, cfg, dtype="bf16", output=y),
-                      iters=args.iters, flush=flush)
+                      iters=args.iters, flush=flush, warmup=warm)
         record("reduce(1 payload)", mib, 2 * n + pb, t)
         t = time_cuda(lambda: codec.inplace_dequantize_reduce_mean_update_error_feedback(
-            [out], res, y, res, cfg, reduce="mean"), iters=args.iters, flush=flush)
+            [out], res, y, res, cfg, reduce="mean"), iters=args.iters, flush=flush, warmup=warm)
         record("reduce(1 payload,+EF in place)", mib, 6 * n + pb, t)
         bufs = [out] + [out.clone() for _ in range(7)]
         t = time_cuda(lambda: codec.inplace_dequantize_reduce_mean(bufs, y, cfg, reduce="mean"),
-                      iters=args.iters, flush=flush)
+                      iters=args.iters, flush=flush, warmup=warm)
         record("reduce(8 payloads)", mib, 2 * n + 8 * pb, t)
         z = torch.empty_like(x)
-        t = time_cuda(lambda: z.copy_(x), iters=args.iters, flush=flush)
+        t = time_cuda(lambda: z.copy_(x), iters=args.iters, flush=flush, warmup=warm)
         record("torch copy_ (reference point)", mib, 4 * n, t)
         del bufs
         for world in args.worlds:

@@ -43,11 +43,29 @@ template <> struct Src<__nv_bfloat16> {
     static constexpr int kBytes = 2;
     __device__ __forceinline__ static float up(uint16_t bits) { return __uint_as_float(uint32_t(bits) << 16); }
     __device__ __forceinline__ static uint16_t down(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
+    // two elements per 32-bit word: one conversion instruction per pair
+    __device__ __forceinline__ static void up2(uint32_t w, float& lo, float& hi) {
+        lo = __uint_as_float(w << 16);
+        hi = __uint_as_float(w & 0xffff0000u);
+    }
+    __device__ __forceinline__ static uint32_t down2(float lo, float hi) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
 };
 template <> struct Src<__half> {
     static constexpr int kBytes = 2;
     __device__ __forceinline__ static float up(uint16_t bits) { return __half2float(__ushort_as_half(bits)); }
     __device__ __forceinline__ static uint16_t down(float v) { return __half_as_ushort(__float2half_rn(v)); }
+    __device__ __forceinline__ static void up2(uint32_t w, float& lo, float& hi) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+        lo = f.x;
+        hi = f.y;
+    }
+    __device__ __forceinline__ static uint32_t down2(float lo, float hi) {
+        const __half2 v = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
 };
 template <> struct Src<float> {
     static constexpr int kBytes = 4;
@@ -104,10 +122,7 @@ __device__ __forceinline__ void load16(const T* base, int64_t first, int64_t num
         if constexpr (sizeof(T) == 2) {
             U8x32 v = streaming ? ld32_stream(base + first) : ld32(base + first);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                out[2 * i] = Src<T>::up(uint16_t(v.w[i] & 0xffffu));
-                out[2 * i + 1] = Src<T>::up(uint16_t(v.w[i] >> 16));
-            }
+            for (int i = 0; i < 8; ++i) Src<T>::up2(v.w[i], out[2 * i], out[2 * i + 1]);
         } else {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -137,7 +152,7 @@ template <typename T>
 __device__ __forceinline__ void round16(float (&vals)[16]) {
     if constexpr (sizeof(T) == 2) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) vals[i] = Src<T>::up(Src<T>::down(vals[i]));
+        for (int i = 0; i < 8; ++i) Src<T>::up2(Src<T>::down2(vals[2 * i], vals[2 * i + 1]), vals[2 * i], vals[2 * i + 1]);
     }
 }
 
@@ -147,8 +162,7 @@ __device__ __forceinline__ void store16(T* base, int64_t first, int64_t numel, b
         if constexpr (sizeof(T) == 2) {
             U8x32 v;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-                v.w[i] = uint32_t(Src<T>::down(vals[2 * i])) | (uint32_t(Src<T>::down(vals[2 * i + 1])) << 16);
+            for (int i = 0; i < 8; ++i) v.w[i] = Src<T>::down2(vals[2 * i], vals[2 * i + 1]);
             st32(base + first, v);
         } else {
 #pragma unroll
@@ -198,6 +212,51 @@ __device__ __forceinline__ uint4 pack16_i8(const int (&q)[16]) {
         w[j] = wire_perm8<WordBytes>(nat);
     }
     return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Round-to-nearest-even quantization without a float->int conversion: adding
+// 1.5 * 2^23 to t = v * mul leaves rint(t) in the low mantissa bits, so the low
+// byte (nibble) of the result's bit pattern is the two's-complement code.  The
+// product is rounded to fp32 first, exactly as rint(v * mul) would see it.
+constexpr float kRoundMagic = 12582912.0f;  // bits 0x4B400000
+
+template <int LIM>
+__device__ __forceinline__ uint32_t quant_bits(float v, float mul) {
+    float r = __fadd_rn(__fmul_rn(v, mul), kRoundMagic);
+    r = fminf(fmaxf(r, kRoundMagic - float(LIM)), kRoundMagic + float(LIM));
+    return __float_as_uint(r);
+}
+__device__ __forceinline__ int code_of_bits(uint32_t bits) { return int(bits) - 0x4B400000; }
+
+// Low bytes of 16 bit patterns -> 16 wire-ordered bytes, three byte permutes per word.
+template <int WordBytes>
+__device__ __forceinline__ uint4 pack16_low_bytes(const uint32_t (&b)[16]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t e0 = b[4 * j], e1 = b[4 * j + 1], e2 = b[4 * j + 2], e3 = b[4 * j + 3];
+        if constexpr (WordBytes == 2) {   // memory bytes: e1 e0 e3 e2
+            w[j] = __byte_perm(__byte_perm(e1, e0, 0x0040), __byte_perm(e3, e2, 0x0040), 0x5410);
+        } else {                          // memory bytes: e3 e2 e1 e0
+            w[j] = __byte_perm(__byte_perm(e3, e2, 0x0040), __byte_perm(e1, e0, 0x0040), 0x5410);
+        }
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// 16 wire-ordered int8 codes -> their values as floats: flip the sign bit of every
+// byte, drop the byte into the mantissa of 2^23 and subtract 2^23 + 128 (exact).
+template <int WordBytes>
+__device__ __forceinline__ void unpack16_i8_fast(uint4 v, float (&out)[16]) {
+    const uint32_t w[4] = {v.x ^ 0x80808080u, v.y ^ 0x80808080u, v.z ^ 0x80808080u, v.w ^ 0x80808080u};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int pos = WordBytes == 2 ? (e ^ 1) : (3 - e);
+            out[4 * j + e] = __uint_as_float(__byte_perm(w[j], 0x4B000000u, 0x7540 | pos)) - 8388736.0f;
+        }
+    }
 }
 
 // Packs 16 int4 codes into 8 wire-ordered bytes (two 32-bit halves).

@@ -82,18 +82,21 @@ __device__ __forceinline__ uint4 encode16(const float (&vals)[16], float stored_
     constexpr int lim = BIT == 8 ? 127 : 7;
     const float safe = fmaxf(stored_scale, 1.0e-6f);
     const float mul = float(lim) / safe;
-    int q[16];
+    uint32_t b[16];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) q[i] = quant_rn(vals[i], mul, lim);
+    for (int i = 0; i < 16; ++i) b[i] = quant_bits<lim>(vals[i], mul);
     if (decoded != nullptr) {
         // this rank's own quantization error, one rounding: fma(-code, step, value)
         const float step = stored_scale / float(lim);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) (*decoded)[i] = __fmaf_rn(-float(q[i]), step, vals[i]);
+        for (int i = 0; i < 16; ++i) (*decoded)[i] = __fmaf_rn(-float(code_of_bits(b[i])), step, vals[i]);
     }
     if constexpr (BIT == 8) {
-        return pack16_i8<sizeof(T)>(q);
+        return pack16_low_bytes<sizeof(T)>(b);
     } else {
+        int q[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) q[i] = int(b[i]);
         const uint2 h = pack16_i4<sizeof(T)>(q);
         return make_uint4(h.x, h.y, 0, 0);
     }
@@ -103,7 +106,7 @@ __device__ __forceinline__ uint4 encode16(const float (&vals)[16], float stored_
 template <typename T, int BIT>
 __device__ __forceinline__ void codes16(uint4 codes, float (&out)[16]) {
     if constexpr (BIT == 8) {
-        unpack16_i8<sizeof(T)>(codes, out);
+        unpack16_i8_fast<sizeof(T)>(codes, out);
     } else {
         int c[16];
         unpack16_i4<sizeof(T)>(make_uint2(codes.x, codes.y), c);
@@ -116,7 +119,7 @@ __device__ __forceinline__ void codes16(uint4 codes, float (&out)[16]) {
 // quant_push
 // ---------------------------------------------------------------------------
 template <typename T, int G, int BIT>
-__global__ void __launch_bounds__(kThreads) quant_push_kernel(const LbcQuantPush p) {
+__global__ void __launch_bounds__(kThreads, 4) quant_push_kernel(const LbcQuantPush p) {
     constexpr int lanes = G / kElemsPerThread;
     constexpr int VB = G * BIT / 8;                 // value bytes per group
     constexpr int MB = sizeof(T);                   // scale bytes per group
@@ -192,7 +195,7 @@ __global__ void __launch_bounds__(kThreads) quant_push_kernel(const LbcQuantPush
 // reduce
 // ---------------------------------------------------------------------------
 template <typename T, int G, int BIT>
-__global__ void __launch_bounds__(kThreads) reduce_kernel(const LbcReduce p) {
+__global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) {
     constexpr int lanes = G / kElemsPerThread;
     constexpr int VB = G * BIT / 8;
     constexpr int MB = sizeof(T);
