@@ -1,0 +1,197 @@
+"""Compressed all-reduce sweep (algBW vs size) on 2/4/8 GPUs of one node.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port 29511 benchmarks/allreduce_sweep.py [--min-mib 1 --max-mib 1024] [--with-reference]
+
+One bf16 gradient tensor per size (x2 steps), values N(0, 1e-3) with 0.1 %
+outliers x100, int8 group-64 payload with error feedback.  Arms: this library
+(one-stage and two-stage fused paths), NCCL bf16 all-reduce, and optionally the
+unmodified reference's `compressed_all_reduce` (strategy all_gather) from
+baseline/_ref.  Every sample is timed on the device with CUDA events after an
+L2 flush and a barrier; the reported time is the max over ranks of each rank's
+median.  algBW = tensor bytes / time.  The roofline of a fused path is the
+slower of its HBM traffic at the measured copy bandwidth and its NVLink traffic
+at the measured 770 GB/s per direction.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+LINK_GBS = 770.0
+
+
+def hbm_peak() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def roofline_us(nbytes: int, world: int, stages: int, error_feedback: bool, hbm_gbs: float) -> dict:
+    c = 66.0 / 128.0
+    payload = c * nbytes
+    ef = 2 if error_feedback else 0  # extra tensor-sized reads+writes per kernel that touches the residual
+    if stages == 2:
+        hbm = (1 + ef) * nbytes + payload          # K1: read grad (+residual, +prepared), payload lands in HBM
+        hbm += 2 * payload                         # K2: read W slots of the shard, requantized shard lands in HBM
+        hbm += payload + (1 + ef) * nbytes         # K3: read payload (+prepared), write result (+residual)
+        link = 2 * payload * (world - 1) / world
+    else:
+        hbm = (1 + ef) * nbytes + world * payload  # K1: as above, W payloads land in HBM
+        hbm += world * payload + (1 + ef) * nbytes  # reduce: read W payloads (+prepared), write result (+residual)
+        link = payload * (world - 1)
+    t_hbm = hbm / (hbm_gbs * 1e9) * 1e6
+    t_link = link / (LINK_GBS * 1e9) * 1e6
+    return {"t_hbm_us": t_hbm, "t_link_us": t_link, "roofline_us": max(t_hbm, t_link)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--min-mib", type=float, default=1)
+    ap.add_argument("--max-mib", type=float, default=1024)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--with-reference", action="store_true")
+    ap.add_argument("--out", default="gpurun_out/allreduce_sweep.json")
+    args = ap.parse_args()
+
+    import torch
+    import torch.distributed as dist
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if world == 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29512")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    from lowbit_comm_b200 import CompressionConfig
+    from lowbit_comm_b200.parallel.communicator import Communicator
+    from lowbit_comm_b200.utils.timing import L2Flusher
+
+    cfg = CompressionConfig()
+    hbm_gbs, peak_kind = hbm_peak()
+    flush = L2Flusher(dev)
+    max_numel = int(args.max_mib * 1024 * 1024 // 2)
+    from lowbit_comm_b200.parallel.fused import FusedWorkspace
+
+    arena = FusedWorkspace.required_bytes(world, "bf16", cfg, 1 << (max_numel - 1).bit_length(), True) + (256 << 20)
+    comm = Communicator(None, arena_bytes=arena)
+    comm.workspace(torch.empty(max_numel, dtype=torch.bfloat16, device=dev), cfg, "bf16")  # largest first
+
+    ref = None
+    if args.with_reference:
+        try:
+            sys.path.insert(0, os.path.join(ROOT, "baseline"))
+            import reference_env
+
+            reference_env.activate(need_cuda_extension=True)
+            from ccdl_comm.collectives import compressed_all_reduce as ref_all_reduce
+            from ccdl_comm.config import CompressionConfig as RefConfig
+
+            ref = (ref_all_reduce, RefConfig(bit=8, group_size=64, topk=0))
+        except Exception as exc:  # noqa: BLE001
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}))
+
+    def measure(fn) -> float:
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        samples = []
+        for _ in range(args.iters):
+            flush()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            samples.append(a.elapsed_time(b))
+        t = torch.tensor([statistics.median(samples)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    rows = []
+    mib = args.min_mib
+    while mib <= args.max_mib:
+        n = int(mib * 1024 * 1024 // 2)
+        gen = torch.Generator(device=dev).manual_seed(1000 + rank)
+        x = torch.randn(n, generator=gen, device=dev) * 1e-3
+        mask = torch.rand(n, generator=gen, device=dev) < 1e-3
+        x = torch.where(mask, x * 100, x).to(torch.bfloat16)
+        exact = x.float().clone()
+        dist.all_reduce(exact)
+        exact /= world
+        nbytes = n * 2
+        residual = torch.zeros_like(x)
+        work = x.clone()
+
+        def ours(stages):
+            def run():
+                comm.all_reduce(x, out=work, config=cfg, op="mean",
+                                strategy="all_gather" if stages == 1 else "reduce_scatter", residual=residual)
+            return run
+
+        for stages in ((1, 2) if world > 1 else (1,)):
+            residual.zero_()
+            t = measure(ours(stages))
+            comm.check_status()
+            residual.zero_()
+            ours(stages)()
+            torch.cuda.synchronize()
+            rel = ((work.float() - exact).norm() / exact.norm()).item()
+            roof = roofline_us(nbytes, world, stages, True, hbm_gbs)
+            rows.append({"impl": f"ours_{stages}stage", "mib": mib, "world": world, "ms": t,
+                         "algbw_gbs": nbytes / (t * 1e-3) / 1e9, "rel_l2": rel, **roof,
+                         "roofline_frac": roof["roofline_us"] / (t * 1e3), "peak_kind": peak_kind})
+        nccl_buf = x.clone()
+
+        def nccl():
+            dist.all_reduce(nccl_buf, op=dist.ReduceOp.AVG)
+
+        t = measure(nccl)
+        rows.append({"impl": "nccl_bf16", "mib": mib, "world": world, "ms": t,
+                     "algbw_gbs": nbytes / (t * 1e-3) / 1e9})
+        if ref is not None and mib <= 256:
+            ref_fn, ref_cfg = ref
+
+            def reference():
+                return ref_fn(x, config=ref_cfg, op="mean", strategy="all_gather")
+
+            try:
+                t = measure(reference)
+                out = reference()
+                torch.cuda.synchronize()
+                rel = ((out.float() - exact).norm() / exact.norm()).item()
+                rows.append({"impl": "reference_all_gather", "mib": mib, "world": world, "ms": t,
+                             "algbw_gbs": nbytes / (t * 1e-3) / 1e9, "rel_l2": rel})
+            except Exception as exc:  # noqa: BLE001
+                rows.append({"impl": "reference_all_gather", "mib": mib, "world": world,
+                             "error": f"{type(exc).__name__}: {exc}"[:200]})
+        if rank == 0:
+            for r in rows[-4:]:
+                if r["mib"] == mib:
+                    print(json.dumps(r), flush=True)
+        del x, work, residual, nccl_buf, exact, mask
+        torch.cuda.empty_cache()
+        mib *= 2
+    if rank == 0:
+        os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+        json.dump(rows, open(args.out, "w"), indent=1)
+    comm.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,146 @@
+"""Child-process body of the multi-GPU tests: one process per GPU, NCCL rendezvous on
+127.0.0.1, results checked against the torch oracle computed from every rank's seed."""
+
+import os
+import sys
+import traceback
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def _inputs(world, n, dtype, seed):
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    return [(torch.randn(n, generator=g) * 1e-2 * (r + 1)).to(dtype) for r in range(world)]
+
+
+def collectives_case(rank: int, world: int) -> None:
+    import torch
+
+    from lowbit_comm_b200 import CompressionConfig
+    from lowbit_comm_b200.ops import oracle
+    from lowbit_comm_b200.parallel.collectives import (compressed_all_gather, compressed_all_reduce,
+                                                        compressed_hierarchical_all_reduce,
+                                                        compressed_reduce_scatter_shard)
+    from lowbit_comm_b200.parallel.communicator import get_communicator
+    from lowbit_comm_b200.parallel.fused import geometry
+
+    cfg = CompressionConfig()
+    dt, name = torch.bfloat16, "bf16"
+    comm = get_communicator(None)
+    for step, n in enumerate((64 * 8 * world, 100_003, 1, 3_000_017)):
+        xs = _inputs(world, n, dt, seed=step)
+        payloads = [oracle.encode(x, cfg) for x in xs]
+        y, _ = oracle.reduce_mean(payloads, n, cfg, name)
+        two = oracle.decode(oracle.encode(y, cfg), n, cfg, name)
+        for strategy, want in (("all_gather", y), ("reduce_scatter", two)):
+            mine = xs[rank].cuda()
+            got = compressed_all_reduce(mine, config=cfg, op="mean", strategy=strategy)
+            torch.cuda.synchronize()
+            assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), (strategy, n, rank)
+        work = compressed_all_reduce(xs[rank].cuda(), config=cfg, strategy="reduce_scatter", async_op=True)
+        got = work.wait()
+        torch.cuda.current_stream().synchronize()
+        assert torch.equal(got.cpu().view(torch.uint8), two.view(torch.uint8)), ("async", n, rank)
+        geo = geometry(n, world, name, cfg)
+        shard = compressed_reduce_scatter_shard(xs[rank].cuda(), config=cfg, op="mean")
+        torch.cuda.synchronize()
+        padded = torch.zeros(geo.shard_numel * world, dtype=dt)
+        padded[:n] = y
+        want = padded[rank * geo.shard_numel:(rank + 1) * geo.shard_numel]
+        assert shard.shard_index == rank and shard.transport == "fused_peer_scatter"
+        assert torch.equal(shard.shard.cpu().view(torch.uint8), want.view(torch.uint8)), ("shard", n, rank)
+        outs = compressed_all_gather(xs[rank].cuda(), config=cfg)
+        torch.cuda.synchronize()
+        for s in range(world):
+            assert torch.equal(outs[s].cpu().view(torch.uint8),
+                               oracle.decode(payloads[s], n, cfg, name).view(torch.uint8)), ("gather", n, rank, s)
+    if world >= 4 and world % 2 == 0:
+        n = 200_000
+        xs = _inputs(world, n, dt, seed=77)
+        got = compressed_hierarchical_all_reduce(xs[rank].cuda(), config=cfg, op="mean", local_group_size=world // 2)
+        torch.cuda.synchronize()
+        exact = torch.stack([x.float() for x in xs]).mean(0)
+        rel = ((got.float().cpu() - exact).norm() / exact.norm()).item()
+        assert rel < 0.03, rel
+    comm.check_status()
+    assert comm.stats["peer_ops"] > 0 and comm.stats["torch_ops"] == 0, comm.stats
+
+
+def ddp_case(rank: int, world: int) -> None:
+    import torch
+    from torch.nn.parallel import DistributedDataParallel as DDP
+
+    from lowbit_comm_b200 import CompressionConfig, create_ddp_comm_hook
+    from lowbit_comm_b200.models import GPT2, GPT2Config
+
+    def run(with_hook: bool):
+        torch.manual_seed(7)
+        cfg = GPT2Config.tiny()
+        model = GPT2(cfg).to(device="cuda", dtype=torch.bfloat16)
+        ddp = DDP(model, device_ids=[torch.cuda.current_device()], gradient_as_bucket_view=True)
+        hook = None
+        if with_hook:
+            hook = create_ddp_comm_hook(CompressionConfig(target="ddp_gradient_bucket"), strategy="auto")
+            ddp.register_comm_hook(state=None, hook=hook)
+        opt = torch.optim.SGD(ddp.parameters(), lr=0.05)
+        gen = torch.Generator().manual_seed(100 + rank)
+        losses = []
+        for _ in range(8):
+            tok = torch.randint(0, cfg.vocab_size, (4, cfg.seq_len + 1), generator=gen).cuda()
+            loss = ddp(tok[:, :-1], tok[:, 1:])
+            loss.backward()
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            losses.append(loss.item())
+        params = torch.cat([p.detach().float().reshape(-1) for p in ddp.parameters()])
+        return losses, params, hook
+
+    base_losses, base_params, _ = run(False)
+    losses, params, hook = run(True)
+    assert hook.gpu_launches() > 0
+    hook.peer_engine.group.check_status()
+    gathered = [torch.empty_like(params) for _ in range(world)]
+    import torch.distributed as dist
+
+    dist.all_gather(gathered, params)
+    for other in gathered:
+        assert torch.equal(other, params), "ranks diverged"
+    drift = ((params - base_params).norm() / base_params.norm()).item()
+    assert drift < 2e-2, drift
+    assert abs(losses[-1] - base_losses[-1]) < 0.05 * abs(base_losses[-1]) + 0.05, (losses[-1], base_losses[-1])
+    state = hook.state_dict()
+    assert state["feedback"]["residuals"], "error-feedback residuals must be checkpointable"
+
+
+def main() -> None:
+    import torch
+    import torch.distributed as dist
+
+    case = sys.argv[1]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    try:
+        {"collectives": collectives_case, "ddp": ddp_case}[case](rank, world)
+        dist.barrier()
+        if rank == 0:
+            print(f"MULTIRANK-OK {case} world={world}")
+    except BaseException:
+        traceback.print_exc()
+        sys.stdout.flush()
+        os._exit(1)
+    finally:
+        try:
+            from lowbit_comm_b200.parallel.communicator import shutdown_communicators
+
+            shutdown_communicators()
+        except Exception:  # noqa: BLE001
+            pass
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

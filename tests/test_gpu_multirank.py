@@ -1,0 +1,39 @@
+"""Real multi-GPU runs of the fused collectives and the DDP hook (one process per GPU).
+
+Skipped on a single-GPU box: kernels of different ranks that wait on one another
+must never share a GPU.  NVLS is switched off in NCCL and the fused kernels use
+plain peer loads and stores, so a failing rank cannot leave multicast state behind.
+"""
+
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _gpu_count() -> int:
+    import torch
+
+    return torch.cuda.device_count()
+
+
+def _launch(case: str, world: int) -> None:
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29400 + world + (7 if case == "ddp" else 0)),
+           os.path.join(ROOT, "tests", "multirank_worker.py"), case]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    tail = (proc.stdout + proc.stderr)[-4000:]
+    assert proc.returncode == 0 and f"MULTIRANK-OK {case}" in proc.stdout, tail
+
+
+@pytest.mark.parametrize("case", ["collectives", "ddp"])
+def test_multirank(case):
+    count = _gpu_count()
+    if count < 2:
+        pytest.skip("needs at least two GPUs")
+    _launch(case, min(count, 8) if count in (2, 4, 8) else 2)
