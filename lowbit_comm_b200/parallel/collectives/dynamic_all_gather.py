@@ -1,0 +1,173 @@
+"""Compressed all-gather of tensors whose shapes differ across ranks.
+
+Parity: ccdl_comm/collectives/dynamic_all_gather.py:12-82 (one-shot) and
+ccdl_comm/cuda/dynamic_gather_executor.py:30-506 (compiled executor with a fixed
+cross-rank shape class capacity, `object_v1` pickle metadata or `tensor_v1`
+16 x int64 packets, `auto` = tensor_v1, LRU executor cache, zero-element bypass).
+Payloads are padded to the capacity of the shape class, gathered with one
+collective, trimmed and decoded.
+"""
+
+from __future__ import annotations
+
+from collections import OrderedDict
+from collections.abc import Callable
+from importlib import import_module
+from typing import Any
+
+from ...config import CompressionConfig
+from ...core.info import ExecutionCounters, ExecutionInfo
+from ...ops import codec
+from ...ops.oracle import TORCH_DTYPES
+from ...ops.sizing import estimate_quantized_size
+from ..metadata_packet import FLAG_EMPTY, PACKET_WORDS, MetadataPacket, decode_all
+
+METADATA_PROTOCOLS = ("object_v1", "tensor_v1", "auto")
+
+
+def _numel(shape) -> int:
+    total = 1
+    for d in shape:
+        total *= int(d)
+    return total
+
+
+class CudaDynamicGatherExecutor:
+    def __init__(self, *, shape_class: tuple[int, ...], config: CompressionConfig, dtype: str, group: Any | None = None,
+                 extension_status: Any | None = None, metadata_protocol: str = "object_v1",
+                 import_module_fn: Callable[[str], Any] = import_module) -> None:
+        if metadata_protocol not in METADATA_PROTOCOLS:
+            raise ValueError(f"metadata_protocol must be one of {METADATA_PROTOCOLS}")
+        if dtype not in TORCH_DTYPES:
+            raise ValueError(f"unsupported dtype {dtype!r}")
+        self.shape_class = tuple(int(d) for d in shape_class)
+        self.config, self.dtype, self.group = config, dtype, group
+        self._status = extension_status
+        self.protocol = "tensor_v1" if metadata_protocol == "auto" else metadata_protocol
+        self._importer = import_module_fn
+        self.capacity_numel = _numel(self.shape_class)
+        est = estimate_quantized_size(self.capacity_numel, dtype=dtype, config=config)
+        self.capacity_bytes = est.quantized_bytes
+        self.execution_info = ExecutionInfo(
+            requested_strategy="dynamic_all_gather", executed_strategy="dynamic_all_gather", backend="cuda",
+            fallback_used=False, fallback_reason=None, stage_names=("metadata", "payload"),
+            original_bytes=est.original_bytes, compressed_bytes=max(est.quantized_bytes, 0),
+            compression_ratio=est.compression_ratio or 1.0, workspace_cache_hit=False, async_capable=False,
+            fast_path="cuda_dynamic_all_gather",
+            details={"shape_class": self.shape_class, "metadata_protocol": self.protocol})
+        self.execution_counters = ExecutionCounters()
+        self.host_sync_count = 0
+
+    def _kw(self) -> dict:
+        return {} if self.group is None else {"group": self.group}
+
+    def _gather_metadata(self, dist, torch, local: MetadataPacket, device) -> list[MetadataPacket]:
+        world = dist.get_world_size(**self._kw())
+        if self.protocol == "object_v1":
+            objs: list[Any] = [None] * world
+            dist.all_gather_object(objs, {"shape": local.shape, "dtype": local.dtype,
+                                          "payload_numel": local.payload_numel, "flags": local.flags}, **self._kw())
+            return [MetadataPacket(tuple(o["shape"]), o["dtype"], int(o["payload_numel"]), int(o["flags"])) for o in objs]
+        words = torch.tensor(local.encode(), dtype=torch.int64)
+        if device.type == "cuda":
+            words = words.pin_memory().to(device, non_blocking=True)
+        gathered = torch.empty(world * PACKET_WORDS, dtype=torch.int64, device=device)
+        dist.all_gather_into_tensor(gathered, words, **self._kw())
+        self.host_sync_count += 1
+        return decode_all(gathered.tolist(), world)
+
+    def run(self, tensor: Any) -> list[Any]:
+        torch = self._importer("torch")
+        dist = self._importer("torch.distributed")
+        self.execution_counters._record_run()
+        try:
+            if codec.resolve_dtype("auto", tensor) != self.dtype:
+                raise TypeError(f"executor was compiled for {self.dtype}")
+            n = tensor.numel()
+            if n > self.capacity_numel:
+                raise ValueError(f"tensor has {n} elements, the shape class holds {self.capacity_numel}")
+            device = tensor.device
+            payload_bytes = estimate_quantized_size(n, dtype=self.dtype, config=self.config).quantized_bytes
+            local = MetadataPacket(tuple(tensor.shape), self.dtype, payload_bytes, FLAG_EMPTY if n == 0 else 0)
+            send = torch.zeros(self.capacity_bytes, dtype=torch.uint8, device=device)
+            if n:  # zero-element tensors never reach a kernel
+                codec.quantize_tensor(tensor.contiguous(), self.config, extension_status=self._status,
+                                      output=send[:payload_bytes])
+            metas = self._gather_metadata(dist, torch, local, device)
+            slots = [torch.empty_like(send) for _ in metas]
+            dist.all_gather(slots, send, **self._kw())
+            outs = []
+            for meta, slot in zip(metas, slots):
+                if meta.dtype != self.dtype:
+                    raise TypeError("ranks disagree on the dtype of a dynamic all-gather")
+                if meta.numel == 0:
+                    outs.append(torch.empty(meta.shape, dtype=TORCH_DTYPES[self.dtype], device=device))
+                    continue
+                if meta.payload_numel > self.capacity_bytes:
+                    raise ValueError("a rank's payload exceeds the compiled shape class")
+                outs.append(codec.dequantize_tensor(slot[:meta.payload_numel], meta.shape, self.config,
+                                                    dtype=self.dtype, extension_status=self._status))
+            self.execution_counters._record_completed()
+            return outs
+        except BaseException:
+            self.execution_counters._record_failed()
+            raise
+
+
+class DynamicGatherExecutorCache:
+    def __init__(self, max_entries: int = 16) -> None:
+        self._max = max_entries
+        self._items: "OrderedDict[tuple, CudaDynamicGatherExecutor]" = OrderedDict()
+
+    def get_or_create(self, key: tuple, factory: Callable[[], CudaDynamicGatherExecutor]):
+        hit = self._items.get(key)
+        if hit is not None:
+            self._items.move_to_end(key)
+            return hit
+        made = factory()
+        self._items[key] = made
+        while len(self._items) > self._max:
+            self._items.popitem(last=False)
+        return made
+
+    def __len__(self) -> int:
+        return len(self._items)
+
+
+_DEFAULT_CACHE = DynamicGatherExecutorCache()
+
+
+def compile_dynamic_all_gather(*, shape_class, config: CompressionConfig, dtype: str, group: Any | None = None,
+                               extension_status: Any | None = None, cache: DynamicGatherExecutorCache | None = None,
+                               metadata_protocol: str = "object_v1", **kw) -> CudaDynamicGatherExecutor:
+    key = (tuple(shape_class), config, dtype, id(group), metadata_protocol)
+
+    def build():
+        return CudaDynamicGatherExecutor(shape_class=tuple(shape_class), config=config, dtype=dtype, group=group,
+                                         extension_status=extension_status, metadata_protocol=metadata_protocol, **kw)
+
+    return build() if cache is None else cache.get_or_create(key, build)
+
+
+def compressed_all_gather_dynamic(tensor: Any, *, config: CompressionConfig, dtype: str = "auto",
+                                  extension_status: Any | None = None, group: Any | None = None,
+                                  compiled_executor: CudaDynamicGatherExecutor | None = None,
+                                  metadata_protocol: str = "auto") -> list[Any]:
+    """One-shot form: agrees on the largest element count first, then gathers."""
+
+    if compiled_executor is not None:
+        return compiled_executor.run(tensor)
+    dist = import_module("torch.distributed")
+    torch = import_module("torch")
+    name = codec.resolve_dtype(dtype, tensor)
+    kw = {} if group is None else {"group": group}
+    biggest = torch.tensor([tensor.numel()], dtype=torch.int64, device=tensor.device)
+    dist.all_reduce(biggest, op=dist.ReduceOp.MAX, **kw)
+    capacity = max(int(biggest.item()), 1)
+    executor = compile_dynamic_all_gather(shape_class=(capacity,), config=config, dtype=name, group=group,
+                                          extension_status=extension_status, cache=_DEFAULT_CACHE,
+                                          metadata_protocol=metadata_protocol)
+    return executor.run(tensor)
+
+
+qall_gather_dyn = compressed_all_gather_dynamic

@@ -55,7 +55,7 @@ def compile_collective(sample: object | None, *, collective: str, group: object 
         from ..backend_cuda import register_cuda_backends
 
         reg = BackendRegistry()
-        register_cuda_backends(reg)
+        register_cuda_backends(reg, allow_cpu=not context.device.startswith("cuda"))
     return compile_plan(active, context, registry=reg)
 
 

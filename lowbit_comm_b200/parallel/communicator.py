@@ -240,7 +240,7 @@ class Communicator:
     def _torch_reduce_scatter(self, tensor, config, op, name):
         torch = import_module("torch")
         flat = tensor.reshape(-1)
-        plan = GroupShardPlan.build(flat.numel(), self.world_size, config.group_size, 1)
+        plan = GroupShardPlan.build(flat.numel(), self.world_size, config.group_size, 8)  # same geometry as the fused path
         padded = torch.nn.functional.pad(flat, (0, plan.padded_numel - flat.numel()))
         chunks = [padded[r * plan.shard_numel:(r + 1) * plan.shard_numel].contiguous() for r in range(self.world_size)]
         sent = [codec.quantize_tensor(c, config, extension_status=self._status) for c in chunks]

@@ -1,0 +1,1 @@
+"""Benchmark and diagnostics helpers (timing, result schema, gates, roofline, tracing)."""

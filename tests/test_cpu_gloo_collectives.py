@@ -1,0 +1,122 @@
+"""Real gloo ranks on CPU through the public collectives: the transports' host-side logic end to end."""
+
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _inputs(world, n, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [(torch.randn(n, generator=g) * 0.01 * (r + 1)).to(torch.bfloat16) for r in range(world)]
+
+
+def _worker(rank: int, world: int, port: int) -> None:
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import lowbit_comm_b200 as lbc
+        from lowbit_comm_b200.ops import oracle
+        from lowbit_comm_b200.parallel.backend_cuda import compile_cuda_shortcut
+
+        cfg = lbc.CompressionConfig()
+        n = 64 * 37 + 11
+        xs = _inputs(world, n)
+        payloads = [oracle.encode(x, cfg) for x in xs]
+        one, _ = oracle.reduce_mean(payloads, n, cfg, "bf16")
+        got = lbc.compressed_all_reduce(xs[rank].clone(), config=cfg, strategy="all_gather")
+        assert torch.equal(got.view(torch.uint8), one.view(torch.uint8))
+        exact = torch.stack([x.float() for x in xs]).mean(0)
+        for strategy in ("reduce_scatter", "topology", "auto", "hierarchical"):
+            if strategy == "hierarchical" and world < 4:
+                continue
+            got = lbc.compressed_all_reduce(xs[rank].clone(), config=cfg, strategy=strategy)
+            assert ((got.float() - exact).norm() / exact.norm()).item() < 0.03, strategy
+        work = lbc.compressed_all_reduce(xs[rank].clone(), config=cfg, strategy="all_gather", async_op=True)
+        assert torch.equal(work.wait().view(torch.uint8), one.view(torch.uint8)) and work.query()
+        summed = lbc.compressed_all_reduce(xs[rank].clone(), config=cfg, op="sum")
+        assert ((summed.float() - exact * world).norm() / (exact * world).norm()).item() < 0.03
+
+        shard = lbc.compressed_reduce_scatter_shard(xs[rank], config=cfg)
+        assert shard.shard_index == rank and shard.world_size == world and shard.original_numel == n
+        lo, valid = shard.shard_offset, shard.valid_numel
+        assert valid == 0 or (shard.shard[:valid].float() - exact[lo:lo + valid]).abs().max() < 2e-3
+        assert shard.shard[valid:].abs().sum() == 0 and shard.is_padding_only == (valid == 0)  # padding is zero
+        out = torch.empty(shard.shard_numel, dtype=torch.bfloat16)
+        again = lbc.compressed_reduce_scatter_shard(xs[rank], config=cfg, out=out)
+        assert again.shard.data_ptr() == out.data_ptr() and again.metadata["caller_owned_output"]
+        with pytest.raises(ValueError):
+            lbc.compressed_reduce_scatter_shard(xs[rank], config=cfg, out=torch.empty(3, dtype=torch.bfloat16))
+        full = lbc.compressed_reduce_scatter(xs[rank], config=cfg)
+        assert ((full.float() - exact).norm() / exact.norm()).item() < 0.03
+
+        parts = lbc.compressed_all_gather(xs[rank], config=cfg)
+        for r in range(world):
+            assert torch.equal(parts[r], oracle.decode(payloads[r], n, cfg, "bf16"))
+        topk = lbc.CompressionConfig(topk=2)
+        parts = lbc.compressed_all_gather(xs[rank], config=topk)
+        assert torch.equal(parts[(rank + 1) % world], oracle.decode(oracle.encode(xs[(rank + 1) % world], topk), n, topk, "bf16"))
+
+        ragged = torch.full((rank + 1, 3), float(rank), dtype=torch.float32)
+        for protocol in ("object_v1", "tensor_v1"):
+            got = lbc.compressed_all_gather_dynamic(ragged, config=cfg, metadata_protocol=protocol)
+            assert [tuple(t.shape) for t in got] == [(r + 1, 3) for r in range(world)]
+            assert all(torch.allclose(t, torch.full_like(t, float(r)), atol=0.02) for r, t in enumerate(got))
+        empty = lbc.compressed_all_gather_dynamic(torch.empty(0, 4) if rank == 0 else ragged, config=cfg)
+        assert tuple(empty[0].shape) == (0, 4)
+
+        peer = (rank + 1) % world
+        src = (rank - 1) % world
+        recv = torch.empty(n, dtype=torch.bfloat16)
+        w_recv = lbc.iqrecv(recv, src, config=cfg)
+        lbc.qsend(xs[rank], peer, config=cfg)
+        assert torch.equal(w_recv.wait(), oracle.decode(payloads[src], n, cfg, "bf16"))
+        assert w_recv.execution_info.fast_path == "cuda_compiled_recv"
+
+        t = torch.full((4,), float(rank + 1))
+        assert lbc.all_reduce(t, op="sum").wait().tolist() == [world * (world + 1) / 2] * 4
+        gathered = lbc.all_gather(torch.tensor([float(rank)])).wait()
+        assert [g.item() for g in gathered] == list(range(world))
+        b = torch.tensor([float(rank)])
+        lbc.broadcast(b, src=1).wait()
+        assert b.item() == 1.0
+        lbc.barrier().wait()
+        assert lbc.native_collectives()[0] == "all_reduce" and len(lbc.native_collectives()) == 9
+        compiled = lbc.compile_collective(t, collective="all_reduce", op="max")
+        assert compiled.execution_info.fast_path == "cuda_native_nccl"
+        assert compiled.run(torch.tensor([float(rank)])).wait().item() == world - 1
+
+        plan = compile_cuda_shortcut(xs[rank], collective="reduce_scatter", strategy="compressed", output_layout="shard",
+                                     config=cfg)
+        assert compile_cuda_shortcut(xs[rank], collective="reduce_scatter", strategy="compressed", output_layout="shard",
+                                     config=cfg) is plan
+        lease = plan.executor.acquire_output()
+        work = plan.run(xs[rank], out=lease)
+        result = work.wait()
+        assert result.shard.data_ptr() == lease.buffer.data_ptr() and work.execution_info.fast_path == "torch_fallback"
+        lease.release_after(result.shard)
+        assert plan.executor.workspace_stats.in_flight_bytes == 0
+        auto = compile_cuda_shortcut(xs[rank], collective="all_reduce", strategy="auto", output_layout="full", config=cfg)
+        assert auto.execution_info.requested_strategy == "auto"
+        assert auto.execution_info.details["strategy_policy_id"] == "b200-nvlink5-v1"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("world", (2, 4))
+def test_public_collectives_over_gloo(world):
+    mp.start_processes(_worker, args=(world, _free_port()), nprocs=world, join=True, start_method="spawn")

@@ -1,0 +1,185 @@
+"""DDP hook logic with hand-written fakes instead of a cluster: one simulated rank, fabricated peers."""
+
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from lowbit_comm_b200 import CompressionConfig, create_ddp_comm_hook
+from lowbit_comm_b200.ops import codec
+from lowbit_comm_b200.ops.error_feedback import ErrorFeedbackState
+from lowbit_comm_b200.parallel.ddp_hook import AsyncBucketPipeline, DDPBucketProcessor
+from lowbit_comm_b200.parallel.payload import CompressedPayload, GatheredPayloads, payload_buffer
+
+
+class FakeBucket:
+    def __init__(self, tensor, index=0):
+        self._t, self._i = tensor, index
+
+    def buffer(self):
+        return self._t
+
+    def index(self):
+        return self._i
+
+
+class FakeFuture:
+    def __init__(self):
+        self.value, self.error = None, None
+
+    def set_result(self, v):
+        self.value = v
+
+    def set_exception(self, e):
+        self.error = e
+
+
+def mirrored_gather(world):
+    """Every fabricated peer sent the same payload as this rank."""
+
+    calls = []
+
+    def gather(payload):
+        calls.append(payload)
+        return GatheredPayloads(tuple(payload for _ in range(world)))
+
+    gather.calls = calls
+    return gather
+
+
+def test_all_gather_strategy_with_error_feedback_matches_manual_math():
+    cfg = CompressionConfig()
+    gather = mirrored_gather(3)
+    feedback = ErrorFeedbackState()
+    hook = create_ddp_comm_hook(cfg, strategy="all_gather", all_gather=gather, error_feedback=feedback,
+                                future_factory=FakeFuture)
+    grad = (torch.randn(1000) * 0.01).to(torch.bfloat16)
+    out = hook(None, FakeBucket(grad.clone(), 7)).value
+    expect = codec.dequantize_tensor(codec.quantize_tensor(grad, cfg), grad.shape, cfg, dtype="bf16")
+    assert torch.equal(out, expect) and len(gather.calls) == 1
+    res1 = feedback.get(7).clone()
+    assert (res1.float() - (grad.float() - expect.float())).abs().max() < 1e-3
+    hook(None, FakeBucket(grad.clone(), 7))            # second step: the residual is added before quantization
+    prepared = (grad.float() + res1.float()).to(torch.bfloat16)
+    sent = payload_buffer(gather.calls[1])
+    assert torch.equal(sent, codec.quantize_tensor(prepared, cfg))
+    assert hook._ccdl_effective_strategy == "all_gather" and hook._ccdl_strategy_plan.requested_strategy == "all_gather"
+    assert hook.stats["buckets"] == 2 and hook.stats["torch"] == 2
+    state = hook.state_dict()
+    assert 7 in state["feedback"]["residuals"] and state["policy"]["steps"][7] == 2
+
+
+def test_small_bucket_bypass_and_policies():
+    seen = []
+    hook = create_ddp_comm_hook(CompressionConfig(), strategy="all_gather", all_gather=mirrored_gather(2),
+                                min_compress_numel=100, bypass_all_reduce=lambda t, op: seen.append(op) or t * 2,
+                                future_factory=FakeFuture)
+    small = torch.ones(10)
+    assert torch.equal(hook(None, FakeBucket(small)).value, small * 2) and seen == ["mean"]
+    assert hook.stats["bypassed"] == 1
+    feedback = ErrorFeedbackState()
+    no_ef = create_ddp_comm_hook(CompressionConfig(error_feedback=False), strategy="all_gather",
+                                 all_gather=mirrored_gather(2), error_feedback=feedback, future_factory=FakeFuture)
+    no_ef(None, FakeBucket(torch.randn(128), 1))
+    assert feedback.get(1) is None
+
+
+def test_injected_codec_path_and_byte_sum_transport():
+    log = []
+
+    def quantize(t, cfg):
+        log.append("q")
+        return CompressedPayload(t * 2, tuple(t.shape), "fp32")
+
+    def dequantize(p, shape, cfg, dtype):
+        log.append("dq")
+        return payload_buffer(p) / 2
+
+    hook = create_ddp_comm_hook(CompressionConfig(error_feedback=False), strategy="all_gather", quantize=quantize,
+                                dequantize=dequantize, all_gather=mirrored_gather(4), future_factory=FakeFuture)
+    g = torch.arange(8, dtype=torch.float32)
+    assert torch.allclose(hook(None, FakeBucket(g)).value, g) and log == ["q", "dq", "dq", "dq", "dq"]
+    proc = DDPBucketProcessor(config=CompressionConfig(), quantize=quantize, dequantize=dequantize,
+                              all_reduce=lambda payload, op: payload)
+    assert torch.allclose(proc.process(FakeBucket(g, 3), dtype="fp32"), g)
+    summed = create_ddp_comm_hook(CompressionConfig(error_feedback=False), strategy="all_reduce", quantize=quantize,
+                                  dequantize=dequantize, all_reduce=lambda payload, op: payload, future_factory=FakeFuture)
+    assert torch.allclose(summed(None, FakeBucket(g)).value, g)
+
+
+def test_async_pipeline_orders_steps_and_reports_errors():
+    order = []
+
+    class Work:
+        def wait(self):
+            order.append("wait")
+            return GatheredPayloads((torch.ones(2),))
+
+        def get_future(self):
+            class F:
+                def then(_, cb):
+                    order.append("then")
+                    cb(None)
+            return F()
+
+    class Completion:
+        def wait(self):
+            order.append("stream-wait")
+
+        def synchronize(self):
+            order.append("host-sync")
+
+    class Manager:
+        def record_for(self, t, stream=None):
+            order.append("record")
+            return Completion()
+
+    fut = FakeFuture()
+    AsyncBucketPipeline(gather_work=Work(), future=fut, dequantize_reduce=lambda g: order.append("reduce") or g.payloads[0],
+                        update_feedback=lambda r: order.append("feedback"), advance_policy=lambda: order.append("advance"),
+                        completion_manager=Manager(), synchronize_completion=False).run()
+    assert order == ["then", "wait", "reduce", "feedback", "advance", "record", "stream-wait"]
+    assert torch.equal(fut.value, torch.ones(2))
+    bad = FakeFuture()
+    AsyncBucketPipeline(gather_work=Work(), future=bad, completion_manager=Manager(),
+                        dequantize_reduce=lambda g: (_ for _ in ()).throw(RuntimeError("decode failed"))).run()
+    assert isinstance(bad.error, RuntimeError) and bad.value is None
+
+
+def test_async_gather_strategy_uses_the_injected_async_transport():
+    cfg = CompressionConfig()
+
+    class Work:
+        def __init__(self, payload):
+            self.payload = payload
+
+        def wait(self):
+            return GatheredPayloads((self.payload, self.payload))
+
+        def get_future(self):
+            return None
+
+    hook = create_ddp_comm_hook(cfg, strategy="all_gather", async_gather=True, async_error_feedback=True,
+                                async_all_gather=lambda buf: Work(buf), future_factory=FakeFuture,
+                                synchronize_async_feedback_completion=False)
+    grad = (torch.randn(256) * 0.01).to(torch.float16)
+    fut = hook(None, FakeBucket(grad.clone(), 0))
+    expect = codec.dequantize_tensor(codec.quantize_tensor(grad, cfg), grad.shape, cfg, dtype="fp16")
+    assert torch.equal(fut.value, expect) and hook.feedback.get(0) is not None
+
+
+def test_argument_validation_and_annotations():
+    with pytest.raises(ValueError):
+        create_ddp_comm_hook(CompressionConfig(), transport="carrier-pigeon")
+    with pytest.raises(ValueError):
+        create_ddp_comm_hook(CompressionConfig(), topology_method="moebius")
+    with pytest.raises(ValueError):
+        create_ddp_comm_hook(CompressionConfig(), ef_mode="psychic")
+    hook = create_ddp_comm_hook(CompressionConfig(), annotation_provider=lambda: {"bucket": int, "return": str})
+    assert hook.__annotations__ == {"bucket": int, "return": str} and hook.__name__ == "hook"
+
+
+def test_package_import_is_torch_free():
+    code = "import sys, lowbit_comm_b200 as l; l.CompressionConfig(); l.CompileCache(); assert 'torch' not in sys.modules"
+    subprocess.run([sys.executable, "-c", code], check=True, cwd=str(__import__("pathlib").Path(__file__).parents[1]))
