@@ -60,6 +60,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--with-reference", action="store_true")
+    ap.add_argument("--phases", action="store_true", help="also time K1/K2/K3 separately (Python launch path)")
     ap.add_argument("--out", default="gpurun_out/allreduce_sweep.json")
     args = ap.parse_args()
 
@@ -152,9 +153,22 @@ def main() -> None:
             torch.cuda.synchronize()
             rel = ((work.float() - exact).norm() / exact.norm()).item()
             roof = roofline_us(nbytes, world, stages, True, hbm_gbs)
+            phases = None
+            if args.phases:
+                from lowbit_comm_b200.utils.tracing import PhaseTimer
+
+                ws = comm.workspace(x, cfg, "bf16")
+                ws.phase_timer = PhaseTimer()
+                for _ in range(5):
+                    flush()
+                    dist.barrier()
+                    ours(stages)()
+                phases = ws.phase_timer.summary()
+                ws.phase_timer = None
             rows.append({"impl": f"ours_{stages}stage", "mib": mib, "world": world, "ms": t,
                          "algbw_gbs": nbytes / (t * 1e-3) / 1e9, "rel_l2": rel, **roof,
-                         "roofline_frac": roof["roofline_us"] / (t * 1e3), "peak_kind": peak_kind})
+                         "roofline_frac": roof["roofline_us"] / (t * 1e3), "peak_kind": peak_kind,
+                         "phases_ms": phases})
         nccl_buf = x.clone()
 
         def nccl():

@@ -15,6 +15,7 @@
 #include <tuple>
 #include <vector>
 
+#include "fused_plan.h"
 #include "lbc_api.h"
 #include "peer_memory.h"
 #include "work.h"
@@ -327,4 +328,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("memset_async", &memset_async);
 
     lbc::bind_work(m);
+    lbc::bind_fused_plan(m);
 }

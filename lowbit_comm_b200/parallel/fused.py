@@ -116,6 +116,20 @@ class FusedWorkspace:
             self._ensure_gather()
         self.channel = group.new_channel()
         self.launches = 0
+        self.phase_timer = None   # set to a utils.tracing.PhaseTimer to time K1/K2/K3 separately
+        # Real process groups launch through the native plan (one binding crossing per collective);
+        # emulated single-GPU groups keep the Python path so that launches can be interleaved by phase.
+        self._native = None
+        self._build_native()
+
+    def _build_native(self) -> None:
+        group = self.group
+        if group.process_group is None or not hasattr(self.ext, "FusedAllReducePlan"):
+            return
+        self._native = self.ext.FusedAllReducePlan(
+            _DTYPE_CODE[self.dtype], self.config.group_size, self.config.bit, group.rank, list(group.peer_ptrs),
+            list(self.rs_off), self.ag_off, list(self.gather_off or []), self.shard_stride, self.gather_stride,
+            self.channel, group.timeout_ns, group.status_device, self.max_blocks, self.max_numel)
 
     @staticmethod
     def required_bytes(world_size: int, dtype: str, config: CompressionConfig, max_numel: int,
@@ -131,6 +145,8 @@ class FusedWorkspace:
         if self.gather_off is None:
             size = self.group.world_size * self.gather_stride
             self.gather_off = [self.group.alloc(size), self.group.alloc(size)]
+            if getattr(self, "_native", None) is not None:
+                self._build_native()
         return self.gather_off
 
     # -- helpers ---------------------------------------------------------------
@@ -218,17 +234,41 @@ class FusedWorkspace:
         if geo.numel == 0:
             return x if out is None else out
         if stages == 1:
+            self._ensure_gather()
+        if self._native is not None and self.phase_timer is None:
+            import torch as _torch
+
+            self.launches += self._native.all_reduce(
+                flat.data_ptr(), out_flat.data_ptr(), 0 if res is None else res.data_ptr(), geo.numel, stages, scale,
+                bool(update_residual), ef_mode == "local", epoch, _torch.cuda.current_stream(x.device).cuda_stream)
+            return x if out is None else out
+        timer = self.phase_timer
+        if timer is not None:
+            timer.mark("start")
+        if stages == 1:
             self._k1_broadcast(flat, res, prepared_out, local_out, geo, epoch, parity)
+            if timer is not None:
+                timer.mark("k1_quant_push")
             region = self.gather_off[parity]
             src = [self.group.local_ptr + region + r * self.gather_stride for r in range(self.group.world_size)]
             self.ext.reduce(src, geo.full_groups, 0, False, geo.numel, self._code, geo.group_size, self.config.bit,
                             scale, out_flat, False, res if want_ref else None, res if want_ref else None, [], 0, 0,
                             None, self.group.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch), self.max_blocks)
             self.launches += 1
+            if timer is not None:
+                timer.mark("k2_reduce_all")
         else:
             self._k1_scatter(flat, res, prepared_out, local_out, geo, epoch, parity)
+            if timer is not None:
+                timer.mark("k1_quant_push")
             self._k2_reduce(geo, epoch, parity, scale, None, True)
+            if timer is not None:
+                timer.mark("k2_reduce_requant_push")
             self._k3_gather(geo, epoch, out_flat, res if want_ref else None, res if want_ref else None)
+            if timer is not None:
+                timer.mark("k3_gather_decode")
+        if timer is not None:
+            timer.flush()
         return x if out is None else out
 
     def reduce_scatter(self, x: torch.Tensor, out_shard: torch.Tensor, *, residual: torch.Tensor | None = None,
