@@ -76,6 +76,31 @@ __device__ __forceinline__ float load_scale(const uint8_t* p) {
         return *reinterpret_cast<const float*>(p);
 }
 
+// Scales of planar payloads are written as 16-byte vectors, eight (fp32: four) groups at a
+// time: one thread per group storing 2 or 4 bytes turns into one partial-sector write per
+// group, which over NVLink costs a whole packet each and was measured to halve the push rate.
+// The warp parks its scales in shared memory and a few lanes write them out.  Conditions
+// (checked once per kernel): planar layout, layout and group offsets multiples of 8 groups,
+// 16-byte aligned destinations; an 8-group unit then never straddles two shards.
+struct ScaleStage {
+    unsigned char bytes[kThreads / 32][32 * 4];
+};
+
+template <typename T>
+__device__ __forceinline__ void park_scale(ScaleStage& stage, int group_in_warp, float stored) {
+    unsigned char* slot = stage.bytes[threadIdx.x >> 5] + group_in_warp * sizeof(T);
+    if constexpr (sizeof(T) == 2)
+        *reinterpret_cast<uint16_t*>(slot) = Src<T>::down(stored);
+    else
+        *reinterpret_cast<float*>(slot) = stored;
+}
+
+__device__ __forceinline__ bool dsts_aligned16(uint8_t* const* dst, int n) {
+    uintptr_t bits = 0;
+    for (int d = 0; d < n; ++d) bits |= reinterpret_cast<uintptr_t>(dst[d]);
+    return (bits & 15) == 0;
+}
+
 // Quantizes 16 rounded values with the group's stored scale; returns packed codes.
 template <typename T, int BIT>
 __device__ __forceinline__ uint4 encode16(const float (&vals)[16], float stored_scale, float (*decoded)[16]) {
@@ -136,6 +161,10 @@ __global__ void __launch_bounds__(kThreads, 4) quant_push_kernel(const LbcQuantP
     const bool p_vec = prep == nullptr || (reinterpret_cast<uintptr_t>(prep) & 31) == 0;
     const bool l_vec = lef == nullptr || (reinterpret_cast<uintptr_t>(lef) & 31) == 0;
 
+    __shared__ __align__(16) ScaleStage stage;
+    const bool vec_scales = p.mode != LBC_PUSH_COMPACT_LOCAL && (p.layout_groups & 7) == 0 &&
+                            (p.group_offset & 7) == 0 && (p.shard_groups & 7) == 0 && dsts_aligned16(p.dst, p.num_dst);
+
     // Chunks are rounded up to a whole warp so that the shuffles stay convergent.
     const int64_t chunk_span = (num_chunks + 31) / 32 * 32;
     for (int64_t chunk = int64_t(blockIdx.x) * kThreads + threadIdx.x; chunk < chunk_span;
@@ -160,32 +189,53 @@ __global__ void __launch_bounds__(kThreads, 4) quant_push_kernel(const LbcQuantP
 #pragma unroll
         for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
         amax = group_max<G>(amax);
-        if (!live) continue;
         float stored = amax;
         if constexpr (sizeof(T) == 2) stored = Src<T>::up(Src<T>::down(amax));
-        if (prep != nullptr) store16<T>(prep, first, n, p_vec, v);
-        float dq[16];
-        const uint4 codes = encode16<T, BIT>(v, stored, lef != nullptr ? &dq : nullptr);
-        if (lef != nullptr) store16<T>(lef, first, n, l_vec, dq);
         const int64_t g = chunk / lanes;
         const int lane = int(chunk - g * lanes);
-        if (p.mode == LBC_PUSH_COMPACT_LOCAL) {
-            uint8_t* rec = p.dst[0] + g * (VB + MB);
-            store_codes(rec + lane * CB, codes, CB);
-            if (lane == 0) store_scale<T>(rec + VB, stored);
-        } else if (p.mode == LBC_PUSH_SCATTER) {
-            const int64_t d = g / p.shard_groups;
-            const int64_t gl = g - d * p.shard_groups;
-            uint8_t* base = p.dst[d];
-            store_codes(base + gl * VB + lane * CB, codes, CB);
-            if (lane == 0) store_scale<T>(base + p.layout_groups * VB + gl * MB, stored);
-        } else {
-            const int64_t gl = p.group_offset + g;
-            for (int d = 0; d < p.num_dst; ++d) {
+        if (live) {
+            if (prep != nullptr) store16<T>(prep, first, n, p_vec, v);
+            float dq[16];
+            const uint4 codes = encode16<T, BIT>(v, stored, lef != nullptr ? &dq : nullptr);
+            if (lef != nullptr) store16<T>(lef, first, n, l_vec, dq);
+            if (p.mode == LBC_PUSH_COMPACT_LOCAL) {
+                uint8_t* rec = p.dst[0] + g * (VB + MB);
+                store_codes(rec + lane * CB, codes, CB);
+                if (lane == 0) store_scale<T>(rec + VB, stored);
+            } else if (p.mode == LBC_PUSH_SCATTER) {
+                const int64_t d = g / p.shard_groups;
+                const int64_t gl = g - d * p.shard_groups;
                 uint8_t* base = p.dst[d];
                 store_codes(base + gl * VB + lane * CB, codes, CB);
-                if (lane == 0) store_scale<T>(base + p.layout_groups * VB + gl * MB, stored);
+                if (!vec_scales && lane == 0) store_scale<T>(base + p.layout_groups * VB + gl * MB, stored);
+            } else {
+                const int64_t gl = p.group_offset + g;
+                for (int d = 0; d < p.num_dst; ++d) {
+                    uint8_t* base = p.dst[d];
+                    store_codes(base + gl * VB + lane * CB, codes, CB);
+                    if (!vec_scales && lane == 0) store_scale<T>(base + p.layout_groups * VB + gl * MB, stored);
+                }
             }
+        }
+        if (vec_scales) {
+            const int wlane = threadIdx.x & 31;
+            if (lane == 0) park_scale<T>(stage, wlane / lanes, stored);   // dead groups park a zero
+            __syncwarp();
+            constexpr int groups_per_vec = 16 / MB;
+            constexpr int vecs_per_warp = (32 / lanes) / groups_per_vec;
+            const int64_t gv = (chunk - wlane) / lanes + int64_t(wlane) * groups_per_vec;  // first group of my vector
+            if (wlane < vecs_per_warp && gv < num_groups) {
+                const uint4 sv = *reinterpret_cast<const uint4*>(stage.bytes[threadIdx.x >> 5] + wlane * 16);
+                if (p.mode == LBC_PUSH_SCATTER) {
+                    const int64_t d = gv / p.shard_groups;
+                    const int64_t gl = gv - d * p.shard_groups;
+                    st16(p.dst[d] + p.layout_groups * VB + gl * MB, sv);
+                } else {
+                    const int64_t gl = p.group_offset + gv;
+                    for (int d = 0; d < p.num_dst; ++d) st16(p.dst[d] + p.layout_groups * VB + gl * MB, sv);
+                }
+            }
+            __syncwarp();
         }
     }
     grid_signal(p.signal);
@@ -215,6 +265,9 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
     const bool r_vec = rout == nullptr || (reinterpret_cast<uintptr_t>(rout) & 31) == 0;
     const int R = p.num_src;
     const int64_t rec = p.compact ? (VB + MB) : VB;
+    __shared__ __align__(16) ScaleStage stage;
+    const bool vec_scales = p.num_dst > 0 && (p.dst_layout_groups & 7) == 0 && (p.dst_group_offset & 7) == 0 &&
+                            dsts_aligned16(p.dst, p.num_dst);
 
     for (int64_t chunk = int64_t(blockIdx.x) * kThreads + threadIdx.x; chunk < chunk_span;
          chunk += int64_t(gridDim.x) * kThreads) {
@@ -271,16 +324,30 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
 #pragma unroll
             for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(acc[i]));
             amax = group_max<G>(amax);
+            float stored = amax;
+            if constexpr (sizeof(T) == 2) stored = Src<T>::up(Src<T>::down(amax));
             if (live) {
-                float stored = amax;
-                if constexpr (sizeof(T) == 2) stored = Src<T>::up(Src<T>::down(amax));
                 const uint4 codes = encode16<T, BIT>(acc, stored, nullptr);
                 const int64_t gl = p.dst_group_offset + g;
                 for (int d = 0; d < p.num_dst; ++d) {
                     uint8_t* base = p.dst[d];
                     store_codes(base + gl * VB + lane * CB, codes, CB);
-                    if (lane == 0) store_scale<T>(base + p.dst_layout_groups * VB + gl * MB, stored);
+                    if (!vec_scales && lane == 0) store_scale<T>(base + p.dst_layout_groups * VB + gl * MB, stored);
                 }
+            }
+            if (vec_scales) {
+                const int wlane = threadIdx.x & 31;
+                if (lane == 0) park_scale<T>(stage, wlane / lanes, live ? stored : 0.0f);
+                __syncwarp();
+                constexpr int groups_per_vec = 16 / MB;
+                constexpr int vecs_per_warp = (32 / lanes) / groups_per_vec;
+                const int64_t gv = (chunk - wlane) / lanes + int64_t(wlane) * groups_per_vec;
+                if (wlane < vecs_per_warp && gv < num_groups) {
+                    const uint4 sv = *reinterpret_cast<const uint4*>(stage.bytes[threadIdx.x >> 5] + wlane * 16);
+                    const int64_t gl = p.dst_group_offset + gv;
+                    for (int d = 0; d < p.num_dst; ++d) st16(p.dst[d] + p.dst_layout_groups * VB + gl * MB, sv);
+                }
+                __syncwarp();
             }
         }
     }

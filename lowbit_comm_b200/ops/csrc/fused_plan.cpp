@@ -95,8 +95,9 @@ class FusedAllReducePlan {
                 r.residual_out = reinterpret_cast<void*>(residual);
             }
             fill_wait(r.wait, kPhaseRS, epoch);
+            gate(r.wait, stream);
             check(lbc_reduce(&r, stream), "reduce(one stage)");
-            return 2;
+            return 3;
         }
 
         q.mode = LBC_PUSH_SCATTER;
@@ -121,6 +122,7 @@ class FusedAllReducePlan {
         k2.dst_group_offset = rank_ * shard_groups;
         fill_signal(k2.signal, kPhaseAG, epoch);
         fill_wait(k2.wait, kPhaseRS, epoch);
+        gate(k2.wait, stream);
         check(lbc_reduce(&k2, stream), "reduce(shard)");
 
         LbcReduce k3 = base_reduce(numel, 1.0);
@@ -133,11 +135,18 @@ class FusedAllReducePlan {
             k3.residual_out = reinterpret_cast<void*>(residual);
         }
         fill_wait(k3.wait, kPhaseAG, epoch);
+        gate(k3.wait, stream);
         check(lbc_reduce(&k3, stream), "reduce(gather)");
-        return 3;
+        return 5;
     }
 
   private:
+    // A one-block kernel does the (bounded) waiting, so that a rank that is ahead of its peers
+    // parks 256 threads instead of filling every SM with spinning blocks while its own backward
+    // pass still needs them; the reduce kernel that follows finds its flags already set.
+    void gate(const LbcWait& wait, cudaStream_t stream) const {
+        check(lbc_wait_signal(&wait, nullptr, stream), "wait_signal");
+    }
     uintptr_t flags_addr(int rank, int phase) const {
         return peers_[rank] + static_cast<uintptr_t>((channel_ * kNumPhases + phase) * kFlagSlots) * 4;
     }

@@ -151,7 +151,9 @@ class Communicator:
 
         torch = import_module("torch")
         if not async_op:
-            return torch.cuda.stream(torch.cuda.current_stream(tensor.device)), None
+            import contextlib
+
+            return contextlib.nullcontext(), None
         from .completion import comm_stream
 
         side = comm_stream(tensor.device)

@@ -50,6 +50,10 @@ def _round_up(value: int, align: int) -> int:
     return -(-value // align) * align
 
 
+def _current_stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
 @dataclass(frozen=True)
 class FusedGeometry:
     numel: int
@@ -102,6 +106,7 @@ class FusedWorkspace:
         self.max_numel = int(max_numel)
         self.max_blocks = int(max_blocks)
         self.ext = group._ext
+        self._torch_dtype = oracle.TORCH_DTYPES[dtype]
         cap = geometry(self.max_numel, group.world_size, dtype, config)
         self.cap = cap
         W = group.world_size
@@ -184,6 +189,8 @@ class FusedWorkspace:
         src = [g.local_ptr + self.rs_off[parity] + r * self.shard_stride for r in range(g.world_size)]
         dst = [g.addr(d, self.ag_off) for d in range(g.world_size)] if broadcast else []
         signal = g.signal_all(self.channel, PHASE_ALL_GATHER, epoch) if broadcast else None
+        self.ext.wait_signal(g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch), None)
+        self.launches += 1
         self.ext.reduce(src, geo.shard_groups, 0, False, geo.shard_valid_numel(me), self._code, geo.group_size,
                         self.config.bit, scale, out, False, None, None, dst, geo.total_groups,
                         me * geo.shard_groups, signal, g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch),
@@ -192,6 +199,8 @@ class FusedWorkspace:
 
     def _k3_gather(self, geo: FusedGeometry, epoch: int, out, prepared, residual_out):
         g = self.group
+        self.ext.wait_signal(g.wait_all(self.channel, PHASE_ALL_GATHER, epoch), None)
+        self.launches += 1
         self.ext.reduce([g.local_ptr + self.ag_off], geo.total_groups, 0, False, geo.numel, self._code,
                         geo.group_size, self.config.bit, 1.0, out, False, prepared, residual_out, [], 0, 0, None,
                         g.wait_all(self.channel, PHASE_ALL_GATHER, epoch), self.max_blocks)
@@ -218,13 +227,28 @@ class FusedWorkspace:
         rank's own quantization error.
         """
 
+        if stages is None:
+            stages = 1 if self.group.world_size <= 2 else 2
+        scale = self._scale(op)
+        if self._native is not None and self.phase_timer is None:
+            # hot path: one binding crossing; geometry is recomputed natively
+            n = x.numel()
+            if n > self.max_numel or x.dtype != self._torch_dtype or not x.is_contiguous():
+                self._geom(x)  # raises the precise error
+            if n == 0:
+                return x if out is None else out
+            if stages == 1:
+                self._ensure_gather()
+            epoch = self.group.next_epoch(self.channel)
+            target = x if out is None else out
+            self.launches += self._native.all_reduce(
+                x.data_ptr(), target.data_ptr(), 0 if residual is None else residual.data_ptr(), n, stages, scale,
+                bool(update_residual), ef_mode == "local", epoch, _current_stream_ptr(x.device))
+            return target
         geo = self._geom(x)
         flat = x.reshape(-1)
         out_flat = flat if out is None else out.reshape(-1)
         res = None if residual is None else residual.reshape(-1)
-        if stages is None:
-            stages = 1 if self.group.world_size <= 2 else 2
-        scale = self._scale(op)
         epoch = self.group.next_epoch(self.channel)
         parity = epoch & 1
         want_ref = res is not None and update_residual and ef_mode == "reference"
@@ -235,13 +259,6 @@ class FusedWorkspace:
             return x if out is None else out
         if stages == 1:
             self._ensure_gather()
-        if self._native is not None and self.phase_timer is None:
-            import torch as _torch
-
-            self.launches += self._native.all_reduce(
-                flat.data_ptr(), out_flat.data_ptr(), 0 if res is None else res.data_ptr(), geo.numel, stages, scale,
-                bool(update_residual), ef_mode == "local", epoch, _torch.cuda.current_stream(x.device).cuda_stream)
-            return x if out is None else out
         timer = self.phase_timer
         if timer is not None:
             timer.mark("start")
@@ -251,6 +268,8 @@ class FusedWorkspace:
                 timer.mark("k1_quant_push")
             region = self.gather_off[parity]
             src = [self.group.local_ptr + region + r * self.gather_stride for r in range(self.group.world_size)]
+            self.ext.wait_signal(self.group.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch), None)
+            self.launches += 1
             self.ext.reduce(src, geo.full_groups, 0, False, geo.numel, self._code, geo.group_size, self.config.bit,
                             scale, out_flat, False, res if want_ref else None, res if want_ref else None, [], 0, 0,
                             None, self.group.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch), self.max_blocks)
@@ -308,6 +327,8 @@ class FusedWorkspace:
             return outs
         self._k1_broadcast(x.reshape(-1), None, None, None, geo, epoch, parity)
         region = self.gather_off[parity]
+        self.ext.wait_signal(g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch), None)
+        self.launches += 1
         for r, out in enumerate(outs):
             wait = g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch) if r == 0 else None
             self.ext.reduce([g.local_ptr + region + r * self.gather_stride], geo.full_groups, 0, False, geo.numel,
