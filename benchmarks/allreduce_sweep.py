@@ -60,6 +60,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--with-reference", action="store_true")
+    ap.add_argument("--variants", action="store_true", help="time every push/reduce kernel variant")
     ap.add_argument("--phases", action="store_true", help="also time K1/K2/K3 separately (Python launch path)")
     ap.add_argument("--out", default="gpurun_out/allreduce_sweep.json")
     args = ap.parse_args()
@@ -144,7 +145,16 @@ def main() -> None:
                                 strategy="all_gather" if stages == 1 else "reduce_scatter", residual=residual)
             return run
 
-        for stages in ((1, 2) if world > 1 else (1,)):
+        from lowbit_comm_b200.ops.loader import require_extension
+
+        ext = require_extension()
+        combos = [(1, False)]
+        if args.variants:
+            combos = [(0, False), (1, False), (2, False), (1, True), (2, True)]
+        for stages, (push_variant, reduce_bulk) in [(s, c) for s in ((1, 2) if world > 1 else (1,)) for c in combos]:
+            if stages == 1 and reduce_bulk:
+                continue
+            ext.set_push_variant(push_variant, reduce_bulk)
             residual.zero_()
             t = measure(ours(stages))
             comm.check_status()
@@ -165,10 +175,12 @@ def main() -> None:
                     ours(stages)()
                 phases = ws.phase_timer.summary()
                 ws.phase_timer = None
-            rows.append({"impl": f"ours_{stages}stage", "mib": mib, "world": world, "ms": t,
+            tag = f"_p{push_variant}r{int(reduce_bulk)}" if args.variants else ""
+            rows.append({"impl": f"ours_{stages}stage{tag}", "mib": mib, "world": world, "ms": t,
                          "algbw_gbs": nbytes / (t * 1e-3) / 1e9, "rel_l2": rel, **roof,
                          "roofline_frac": roof["roofline_us"] / (t * 1e3), "peak_kind": peak_kind,
                          "phases_ms": phases})
+        ext.set_push_variant(1, False)
         nccl_buf = x.clone()
 
         def nccl():
@@ -194,7 +206,7 @@ def main() -> None:
                 rows.append({"impl": "reference_all_gather", "mib": mib, "world": world,
                              "error": f"{type(exc).__name__}: {exc}"[:200]})
         if rank == 0:
-            for r in rows[-4:]:
+            for r in rows[-12:]:
                 if r["mib"] == mib:
                     print(json.dumps(r), flush=True)
         del x, work, residual, nccl_buf, exact, mask

@@ -363,6 +363,28 @@ __device__ __forceinline__ bool block_wait(const WaitSpec& w) {
     return ok != 0;
 }
 
+// ---------------------------------------------------------------------------
+// bulk asynchronous stores (TMA engine): shared memory -> global memory, own or a peer's.
+// The copy engine moves the tile, so a back-pressured NVLink write does not stall the SM's
+// load/store pipeline the way per-thread peer stores do.  No multicast, no tensor map: plain
+// `cp.async.bulk` with 16-byte aligned addresses and sizes.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void fence_smem_to_async_proxy() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
+                 "r"(smem_addr(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// At most one committed group may still be reading shared memory afterwards.
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+// Every committed group has completed its writes.
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // Called by every thread after its last remote store.
 __device__ __forceinline__ void grid_signal(const SignalSpec& s) {
     if (s.num_remote <= 0) return;

@@ -242,6 +242,155 @@ __global__ void __launch_bounds__(kThreads, 4) quant_push_kernel(const LbcQuantP
 }
 
 // ---------------------------------------------------------------------------
+// quant_push through the bulk-store engine (scatter and broadcast modes)
+// ---------------------------------------------------------------------------
+// A block quantizes one tile (256 threads x 16 elements) into shared memory, then one thread
+// hands the tile's codes and scales to the copy engine, once per destination.  Two tile
+// buffers alternate, so the engine drains tile i while the block quantizes tile i + 1.
+// Tiles are dealt out shard-interleaved: consecutive tiles (and therefore the blocks running
+// at any instant) target different ranks, and the rotation by the sender's rank keeps the W
+// senders from converging on one receiver.
+struct PushTile {
+    unsigned char codes[2][kThreads * 16];
+    unsigned char scales[2][kThreads * 4];   // up to 256 groups (G = 16) of 4-byte scales
+};
+
+template <typename T, int G, int BIT, bool kBulk>
+__global__ void __launch_bounds__(kThreads, 3) quant_push_tiled_kernel(const LbcQuantPush p) {
+    constexpr int lanes = G / kElemsPerThread;
+    constexpr int VB = G * BIT / 8;
+    constexpr int MB = sizeof(T);
+    constexpr int CB = kElemsPerThread * BIT / 8;
+    constexpr int tile_groups = kThreads / lanes;
+    const T* x = static_cast<const T*>(p.x);
+    const T* res = static_cast<const T*>(p.residual);
+    T* prep = static_cast<T*>(p.prepared_out);
+    T* lef = static_cast<T*>(p.local_ef_out);
+    const int64_t n = p.numel;
+    const int64_t num_groups = (n + G - 1) / G;
+    const bool x_vec = (reinterpret_cast<uintptr_t>(x) & 31) == 0;
+    const bool r_vec = res == nullptr || (reinterpret_cast<uintptr_t>(res) & 31) == 0;
+    const bool p_vec = prep == nullptr || (reinterpret_cast<uintptr_t>(prep) & 31) == 0;
+    const bool l_vec = lef == nullptr || (reinterpret_cast<uintptr_t>(lef) & 31) == 0;
+    const bool scatter = p.mode == LBC_PUSH_SCATTER;
+    // scatter: one destination per shard; broadcast: one "shard" that holds every group
+    const int64_t span_groups = scatter ? p.shard_groups : (num_groups + 7) / 8 * 8;
+    const int shards = scatter ? int((num_groups + p.shard_groups - 1) / p.shard_groups) : 1;
+    const int64_t tiles_per_shard = (span_groups + tile_groups - 1) / tile_groups;
+    const int64_t num_tiles = tiles_per_shard * shards;
+    const int rot = p.signal.my_slot;   // this rank's index: staggers the senders
+
+    __shared__ __align__(128) PushTile tile;
+    int buf = 0;
+    for (int64_t vt = blockIdx.x; vt < num_tiles; vt += gridDim.x, buf ^= 1) {
+        const int shard = int((vt + rot) % shards);
+        const int64_t k = vt / shards;
+        const int64_t gl0 = k * tile_groups;                       // first group of the tile inside its shard
+        const int64_t shard_first = int64_t(shard) * span_groups;   // first group of the shard in the tensor
+        int64_t live_groups = min(span_groups, num_groups - shard_first) - gl0;
+        live_groups = max(int64_t(0), min(int64_t(tile_groups), live_groups));
+        const int gl = int(threadIdx.x) / lanes;                    // my group inside the tile
+        const int lane = int(threadIdx.x) - gl * lanes;
+        const bool live = gl < live_groups;
+        const int64_t first = ((shard_first + gl0) * lanes + threadIdx.x) * kElemsPerThread;
+        float v[16];
+        if (live) {
+            load16<T>(x, first, n, x_vec, v, true);
+            if (res != nullptr) {
+                float r[16];
+                load16<T>(res, first, n, r_vec, r, prep != res);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[i] += r[i];
+                round16<T>(v);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0.0f;
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        amax = group_max<G>(amax);
+        float stored = amax;
+        if constexpr (sizeof(T) == 2) stored = Src<T>::up(Src<T>::down(amax));
+        float dq[16];
+        const uint4 codes = encode16<T, BIT>(v, stored, (live && lef != nullptr) ? &dq : nullptr);
+        if (live) {
+            if (prep != nullptr) store16<T>(prep, first, n, p_vec, v);
+            if (lef != nullptr) store16<T>(lef, first, n, l_vec, dq);
+        }
+        const int64_t copy_groups = (live_groups + 7) / 8 * 8;   // layouts are padded to 8 groups
+        if constexpr (kBulk) {
+            // the engine may still be reading this buffer for the tile issued two iterations ago
+            if (threadIdx.x == 0) bulk_wait_read_1();
+            __syncthreads();
+            if constexpr (BIT == 8)
+                *reinterpret_cast<uint4*>(tile.codes[buf] + threadIdx.x * CB) = codes;
+            else
+                *reinterpret_cast<uint2*>(tile.codes[buf] + threadIdx.x * CB) = make_uint2(codes.x, codes.y);
+            if (lane == 0) {
+                if constexpr (sizeof(T) == 2)
+                    *reinterpret_cast<uint16_t*>(tile.scales[buf] + gl * MB) = Src<T>::down(stored);
+                else
+                    *reinterpret_cast<float*>(tile.scales[buf] + gl * MB) = stored;
+            }
+            fence_smem_to_async_proxy();
+            __syncthreads();
+            if (threadIdx.x == 0 && live_groups > 0) {
+                const uint32_t value_bytes = uint32_t(copy_groups * VB);
+                const uint32_t scale_bytes = uint32_t(copy_groups * MB);
+                if (scatter) {
+                    uint8_t* base = p.dst[shard];
+                    bulk_store(base + gl0 * VB, tile.codes[buf], value_bytes);
+                    bulk_store(base + p.layout_groups * VB + gl0 * MB, tile.scales[buf], scale_bytes);
+                } else {
+                    const int64_t g_dst = p.group_offset + gl0;
+                    for (int d = 0; d < p.num_dst; ++d) {
+                        const int dd = (d + rot) % p.num_dst;
+                        uint8_t* base = p.dst[dd];
+                        bulk_store(base + g_dst * VB, tile.codes[buf], value_bytes);
+                        bulk_store(base + p.layout_groups * VB + g_dst * MB, tile.scales[buf], scale_bytes);
+                    }
+                }
+            }
+            if (threadIdx.x == 0) bulk_commit();
+        } else {
+            // per-thread stores of the codes, scales gathered through shared memory into 16-byte vectors
+            const int64_t g_dst = (scatter ? 0 : p.group_offset) + gl0;
+            if (live) {
+                if (scatter) {
+                    store_codes(p.dst[shard] + (g_dst + gl) * VB + lane * CB, codes, CB);
+                } else {
+                    for (int d = 0; d < p.num_dst; ++d) {
+                        const int dd = (d + rot) % p.num_dst;
+                        store_codes(p.dst[dd] + (g_dst + gl) * VB + lane * CB, codes, CB);
+                    }
+                }
+            }
+            __syncthreads();   // the previous tile's scale vectors have been read
+            if (lane == 0) {
+                if constexpr (sizeof(T) == 2)
+                    *reinterpret_cast<uint16_t*>(tile.scales[0] + gl * MB) = Src<T>::down(stored);
+                else
+                    *reinterpret_cast<float*>(tile.scales[0] + gl * MB) = stored;
+            }
+            __syncthreads();
+            if (int64_t(threadIdx.x) * 16 < copy_groups * MB) {
+                const uint4 sv = *reinterpret_cast<const uint4*>(tile.scales[0] + threadIdx.x * 16);
+                if (scatter) {
+                    st16(p.dst[shard] + p.layout_groups * VB + g_dst * MB + threadIdx.x * 16, sv);
+                } else {
+                    for (int d = 0; d < p.num_dst; ++d)
+                        st16(p.dst[(d + rot) % p.num_dst] + p.layout_groups * VB + g_dst * MB + threadIdx.x * 16, sv);
+                }
+            }
+        }
+    }
+    if (kBulk && threadIdx.x == 0) bulk_wait_all();
+    grid_signal(p.signal);
+}
+
+// ---------------------------------------------------------------------------
 // reduce
 // ---------------------------------------------------------------------------
 template <typename T, int G, int BIT>
@@ -259,7 +408,6 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
     const int64_t n = p.numel;
     const int64_t num_groups = (n + G - 1) / G;
     const int64_t num_chunks = num_groups * lanes;
-    const int64_t chunk_span = (num_chunks + 31) / 32 * 32;
     const bool o_vec = out == nullptr || (reinterpret_cast<uintptr_t>(out) & 31) == 0;
     const bool p_vec = prep == nullptr || (reinterpret_cast<uintptr_t>(prep) & 31) == 0;
     const bool r_vec = rout == nullptr || (reinterpret_cast<uintptr_t>(rout) & 31) == 0;
@@ -268,6 +416,12 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
     __shared__ __align__(16) ScaleStage stage;
     const bool vec_scales = p.num_dst > 0 && (p.dst_layout_groups & 7) == 0 && (p.dst_group_offset & 7) == 0 &&
                             dsts_aligned16(p.dst, p.num_dst);
+    const bool bulk = vec_scales && p.bulk_store != 0;   // requantized tiles leave through the copy engine
+    __shared__ __align__(128) PushTile tile;
+    int buf = 0;
+    // whole warps keep the shuffles convergent; the bulk path also has block-wide barriers in the loop
+    const int64_t span_unit = bulk ? kThreads : 32;
+    const int64_t chunk_span = (num_chunks + span_unit - 1) / span_unit * span_unit;
 
     for (int64_t chunk = int64_t(blockIdx.x) * kThreads + threadIdx.x; chunk < chunk_span;
          chunk += int64_t(gridDim.x) * kThreads) {
@@ -326,7 +480,39 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
             amax = group_max<G>(amax);
             float stored = amax;
             if constexpr (sizeof(T) == 2) stored = Src<T>::up(Src<T>::down(amax));
-            if (live) {
+            if (bulk) {
+                // tile of this block iteration -> shared memory -> one bulk store per destination
+                const uint4 codes = encode16<T, BIT>(acc, stored, nullptr);
+                const int64_t g0 = (chunk - threadIdx.x) / lanes;
+                const int tg = int(threadIdx.x) / lanes;
+                int64_t live_groups = max(int64_t(0), min(int64_t(kThreads / lanes), num_groups - g0));
+                if (threadIdx.x == 0) bulk_wait_read_1();
+                __syncthreads();
+                if constexpr (BIT == 8)
+                    *reinterpret_cast<uint4*>(tile.codes[buf] + threadIdx.x * CB) = codes;
+                else
+                    *reinterpret_cast<uint2*>(tile.codes[buf] + threadIdx.x * CB) = make_uint2(codes.x, codes.y);
+                if (lane == 0) {
+                    if constexpr (sizeof(T) == 2)
+                        *reinterpret_cast<uint16_t*>(tile.scales[buf] + tg * MB) = Src<T>::down(live ? stored : 0.0f);
+                    else
+                        *reinterpret_cast<float*>(tile.scales[buf] + tg * MB) = live ? stored : 0.0f;
+                }
+                fence_smem_to_async_proxy();
+                __syncthreads();
+                if (threadIdx.x == 0 && live_groups > 0) {
+                    const int64_t copy_groups = (live_groups + 7) / 8 * 8;
+                    const int64_t g_dst = p.dst_group_offset + g0;
+                    for (int d = 0; d < p.num_dst; ++d) {
+                        uint8_t* base = p.dst[(d + p.signal.my_slot) % p.num_dst];
+                        bulk_store(base + g_dst * VB, tile.codes[buf], uint32_t(copy_groups * VB));
+                        bulk_store(base + p.dst_layout_groups * VB + g_dst * MB, tile.scales[buf],
+                                   uint32_t(copy_groups * MB));
+                    }
+                }
+                if (threadIdx.x == 0) bulk_commit();
+                buf ^= 1;
+            } else if (live) {
                 const uint4 codes = encode16<T, BIT>(acc, stored, nullptr);
                 const int64_t gl = p.dst_group_offset + g;
                 for (int d = 0; d < p.num_dst; ++d) {
@@ -335,7 +521,7 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
                     if (!vec_scales && lane == 0) store_scale<T>(base + p.dst_layout_groups * VB + gl * MB, stored);
                 }
             }
-            if (vec_scales) {
+            if (vec_scales && !bulk) {
                 const int wlane = threadIdx.x & 31;
                 if (lane == 0) park_scale<T>(stage, wlane / lanes, live ? stored : 0.0f);
                 __syncwarp();
@@ -351,6 +537,7 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
             }
         }
     }
+    if (bulk && threadIdx.x == 0) bulk_wait_all();
     grid_signal(p.signal);
 }
 
@@ -456,13 +643,37 @@ static cudaError_t dispatch(const P* p, cudaStream_t stream) {
     return cudaErrorInvalidValue;
 }
 
+// The bulk-store kernel needs 16-byte aligned destinations and layouts padded to 8 groups;
+// the collectives guarantee both, the local codec entry points (arbitrary payload tensors) do not.
+// Push variants (identical payload layout, so ranks may even differ):
+//   0 classic grid-stride kernel   1 shard-interleaved tiles, per-thread stores   2 tiles + bulk stores
+static int g_push_variant = 1;
+static int g_reduce_bulk = 0;
+
+static bool tiled_path_ok(const LbcQuantPush* p) {
+    if (p->num_dst <= 0) return false;
+    if (p->mode != LBC_PUSH_SCATTER && p->mode != LBC_PUSH_BROADCAST) return false;
+    if ((p->layout_groups & 7) != 0 || (p->group_offset & 7) != 0) return false;
+    if (p->mode == LBC_PUSH_SCATTER && (p->shard_groups & 7) != 0) return false;
+    for (int d = 0; d < p->num_dst; ++d)
+        if ((reinterpret_cast<uintptr_t>(p->dst[d]) & 15) != 0) return false;
+    return true;
+}
+
 template <typename T, int G, int BIT>
 struct QuantPushLauncher {
     static cudaError_t run(const LbcQuantPush* p, cudaStream_t stream) {
         const int64_t groups = (p->numel + G - 1) / G;
         if (groups == 0 && p->signal.num_remote == 0) return cudaSuccess;
         const int grid = grid_for(groups * (G / kElemsPerThread), p->max_blocks);
-        quant_push_kernel<T, G, BIT><<<grid, kThreads, 0, stream>>>(*p);
+        const int variant = tiled_path_ok(p) ? g_push_variant : 0;
+        if (variant == 2) {
+            quant_push_tiled_kernel<T, G, BIT, true><<<grid, kThreads, 0, stream>>>(*p);
+        } else if (variant == 1) {
+            quant_push_tiled_kernel<T, G, BIT, false><<<grid, kThreads, 0, stream>>>(*p);
+        } else {
+            quant_push_kernel<T, G, BIT><<<grid, kThreads, 0, stream>>>(*p);
+        }
         return cudaGetLastError();
     }
 };
@@ -473,7 +684,9 @@ struct ReduceLauncher {
         const int64_t groups = (p->numel + G - 1) / G;
         if (groups == 0 && p->signal.num_remote == 0 && p->wait.flags == nullptr) return cudaSuccess;
         const int grid = grid_for(groups * (G / kElemsPerThread), p->max_blocks);
-        reduce_kernel<T, G, BIT><<<grid, kThreads, 0, stream>>>(*p);
+        LbcReduce launch = *p;
+        launch.bulk_store = g_reduce_bulk;
+        reduce_kernel<T, G, BIT><<<grid, kThreads, 0, stream>>>(launch);
         return cudaGetLastError();
     }
 };
@@ -483,6 +696,11 @@ struct ReduceLauncher {
 extern "C" {
 
 int lbc_default_max_blocks(void) { return lbc::default_max_blocks(); }
+
+void lbc_set_push_variant(int push_variant, int reduce_bulk) {
+    lbc::g_push_variant = push_variant < 0 ? 0 : (push_variant > 2 ? 2 : push_variant);
+    lbc::g_reduce_bulk = reduce_bulk != 0;
+}
 
 cudaError_t lbc_quant_push(const LbcQuantPush* p, cudaStream_t stream) {
     if (p == nullptr || p->numel < 0 || p->num_dst < 0 || p->num_dst > LBC_MAX_RANKS) return cudaErrorInvalidValue;

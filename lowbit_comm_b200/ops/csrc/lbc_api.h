@@ -83,6 +83,7 @@ typedef struct {
     LbcSignal signal;
     LbcWait wait;
     int max_blocks;
+    int bulk_store;            // set by the launcher: requantized tiles leave through bulk stores
 } LbcReduce;
 
 cudaError_t lbc_quant_push(const LbcQuantPush* p, cudaStream_t stream);
@@ -126,6 +127,10 @@ cudaError_t lbc_push_bytes(const uint8_t* src, int64_t nbytes, uint8_t* const* d
 cudaError_t lbc_wait_signal(const LbcWait* wait, const LbcSignal* signal, cudaStream_t stream);
 
 int lbc_default_max_blocks(void);
+// How quantized tiles reach their destinations: push_variant 0 classic grid-stride kernel,
+// 1 shard-interleaved tiles with per-thread stores, 2 tiles handed to the bulk-store engine;
+// reduce_bulk selects bulk stores for the requantize-and-broadcast stage.
+void lbc_set_push_variant(int push_variant, int reduce_bulk);
 
 #ifdef __cplusplus
 }
