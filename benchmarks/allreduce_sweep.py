@@ -60,6 +60,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--with-reference", action="store_true")
+    ap.add_argument("--chunk-mib", type=float, default=None, help="pipeline chunk size (0 = no pipelining)")
     ap.add_argument("--variants", action="store_true", help="time every push/reduce kernel variant")
     ap.add_argument("--phases", action="store_true", help="also time K1/K2/K3 separately (Python launch path)")
     ap.add_argument("--out", default="gpurun_out/allreduce_sweep.json")
@@ -89,7 +90,9 @@ def main() -> None:
 
     arena = FusedWorkspace.required_bytes(world, "bf16", cfg, 1 << (max_numel - 1).bit_length(), True) + (256 << 20)
     comm = Communicator(None, arena_bytes=arena)
-    comm.workspace(torch.empty(max_numel, dtype=torch.bfloat16, device=dev), cfg, "bf16")  # largest first
+    big = comm.workspace(torch.empty(max_numel, dtype=torch.bfloat16, device=dev), cfg, "bf16")  # largest first
+    if args.chunk_mib is not None:
+        big.set_chunking(int(max(args.chunk_mib, 1e-3) * (1 << 20)), 1 if args.chunk_mib == 0 else 8)
 
     ref = None
     if args.with_reference:

@@ -4,11 +4,21 @@
 // registry per call; its executors walk Python schedules per step,
 // cuda/transports/pipelined_ring.py:205-282).  Here the per-call host work is a
 // handful of integer operations: measured launch gaps, not kernels, dominated
-// small buckets when the three launches were issued from Python.
+// small buckets when the launches were issued from Python.
+//
+// Large tensors are cut into chunks that flow through the three phases on three
+// streams (push on the caller's stream, reduce and gather on two side streams), so
+// the NVLink-bound phases of one chunk overlap the HBM-bound phases of its
+// neighbours.  Every chunk is a complete small all-reduce with its own receive
+// regions and its own flag channel; a one-block gate kernel in front of every
+// waiting kernel does the (bounded) waiting, so no stream can fill the GPU with
+// spinning blocks.  The side streams are joined back into the caller's stream at
+// the end, which keeps the region-reuse argument of the single-stream version.
 #include "fused_plan.h"
 
 #include <ATen/cuda/CUDAContext.h>
 
+#include <algorithm>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -23,31 +33,54 @@ namespace {
 
 constexpr int kPhaseRS = 0, kPhaseAG = 1;
 constexpr int kNumPhases = 4, kFlagSlots = 16;
-constexpr int64_t kCounterOffset = 64 * kNumPhases * kFlagSlots * 4;
 constexpr int64_t kAlignGroups = 8;
+constexpr int kMaxChunks = 8;
 
 int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
 
 void check(cudaError_t err, const char* what) {
     if (err != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(err));
 }
 
+struct Regions {        // byte offsets inside every rank's arena, for one chunk
+    int64_t rs, ag, gather;
+    int64_t shard_stride, gather_stride;
+    int channel;
+};
+
 class FusedAllReducePlan {
   public:
     FusedAllReducePlan(int dtype, int group_size, int bit, int rank, std::vector<uintptr_t> peer_ptrs,
-                       std::vector<int64_t> rs_off, int64_t ag_off, std::vector<int64_t> gather_off,
-                       int64_t shard_stride, int64_t gather_stride, int channel, unsigned long long timeout_ns,
-                       uintptr_t status_device, int max_blocks, int64_t max_numel)
+                       std::vector<int64_t> rs_off, int64_t rs_bytes, int64_t ag_off, int64_t ag_bytes,
+                       std::vector<int64_t> gather_off, int64_t gather_bytes, std::vector<int> channels,
+                       int64_t counter_offset, unsigned long long timeout_ns, uintptr_t status_device, int max_blocks,
+                       int64_t max_numel)
         : dtype_(dtype), group_(group_size), bit_(bit), rank_(rank), peers_(std::move(peer_ptrs)),
-          rs_off_(std::move(rs_off)), ag_off_(ag_off), gather_off_(std::move(gather_off)),
-          shard_stride_(shard_stride), gather_stride_(gather_stride), channel_(channel), timeout_ns_(timeout_ns),
-          status_(status_device), max_blocks_(max_blocks), max_numel_(max_numel) {
+          rs_off_(std::move(rs_off)), rs_bytes_(rs_bytes), ag_off_(ag_off), ag_bytes_(ag_bytes),
+          gather_off_(std::move(gather_off)), gather_bytes_(gather_bytes), channels_(std::move(channels)),
+          counter_offset_(counter_offset), timeout_ns_(timeout_ns), status_(status_device), max_blocks_(max_blocks),
+          max_numel_(max_numel) {
         world_ = static_cast<int>(peers_.size());
         if (world_ < 1 || world_ > LBC_MAX_RANKS) throw std::invalid_argument("bad world size");
         if (rank_ < 0 || rank_ >= world_) throw std::invalid_argument("bad rank");
         if (rs_off_.size() != 2) throw std::invalid_argument("two reduce-scatter regions are required");
-        value_bytes_ = group_ * bit_ / 8;
-        scale_bytes_ = dtype_ == LBC_FP32 ? 4 : 2;
+        if (channels_.empty()) throw std::invalid_argument("at least one flag channel is required");
+        group_bytes_ = group_ * bit_ / 8 + (dtype_ == LBC_FP32 ? 4 : 2);
+        elem_bytes_ = dtype_ == LBC_FP32 ? 4 : 2;
+    }
+
+    ~FusedAllReducePlan() {
+        for (auto& s : side_) {
+            if (s.stream != nullptr) cudaStreamDestroy(s.stream);
+            if (s.done != nullptr) cudaEventDestroy(s.done);
+        }
+        if (start_ != nullptr) cudaEventDestroy(start_);
+    }
+
+    void set_chunking(int64_t min_chunk_bytes, int max_chunks) {
+        min_chunk_bytes_ = std::max<int64_t>(min_chunk_bytes, 4096);
+        max_chunks_ = std::max(1, std::min(max_chunks, std::min<int>(kMaxChunks, static_cast<int>(channels_.size()))));
     }
 
     // Enqueues the collective on `stream`; returns the number of kernels launched.
@@ -55,15 +88,82 @@ class FusedAllReducePlan {
                    bool update_residual, bool ef_local, unsigned int epoch, uintptr_t stream_ptr) {
         if (numel < 0 || numel > max_numel_) throw std::invalid_argument("numel exceeds the workspace capacity");
         if (numel == 0) return 0;
+        if (stages == 1 && gather_off_.size() != 2) throw std::invalid_argument("this plan has no gather region");
         cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
         const int parity = static_cast<int>(epoch & 1u);
-        const int64_t groups = ceil_div(numel, group_);
-        int64_t shard_groups = ceil_div(groups, world_);
-        shard_groups = ceil_div(shard_groups, kAlignGroups) * kAlignGroups;
-        const int64_t full_groups = ceil_div(groups, kAlignGroups) * kAlignGroups;
+        // chunk boundaries keep every chunk's shards whole multiples of eight groups
+        const int64_t unit = int64_t(group_) * kAlignGroups * world_;
+        int chunks = static_cast<int>(std::min<int64_t>(max_chunks_, (numel * elem_bytes_) / min_chunk_bytes_));
+        chunks = std::max(1, chunks);
+        const int64_t chunk_numel = round_up(ceil_div(numel, chunks), unit);
+        chunks = static_cast<int>(ceil_div(numel, chunk_numel));
+        const bool piped = chunks > 1;
+        cudaStream_t s_reduce = stream, s_gather = stream;
+        if (piped) {
+            ensure_side_streams();
+            check(cudaEventRecord(start_, stream), "cudaEventRecord(start)");
+            for (auto& s : side_) check(cudaStreamWaitEvent(s.stream, start_, 0), "cudaStreamWaitEvent(start)");
+            s_reduce = side_[0].stream;
+            s_gather = stages == 1 ? side_[0].stream : side_[1].stream;
+        }
+        int launches = 0;
+        int64_t rs_cursor = 0, ag_cursor = 0, gather_cursor = 0;
+        for (int c = 0; c < chunks; ++c) {
+            const int64_t first = c * chunk_numel;
+            const int64_t n = std::min(chunk_numel, numel - first);
+            const int64_t groups = ceil_div(n, group_);
+            const int64_t shard_groups = round_up(ceil_div(groups, world_), kAlignGroups);
+            const int64_t full_groups = round_up(groups, kAlignGroups);
+            Regions r;
+            r.channel = channels_[c];
+            r.shard_stride = round_up(shard_groups * group_bytes_, 256);
+            r.gather_stride = round_up(full_groups * group_bytes_, 256);
+            r.rs = rs_off_[parity] + rs_cursor;
+            r.ag = ag_off_ + ag_cursor;
+            r.gather = stages == 1 ? gather_off_[parity] + gather_cursor : 0;
+            rs_cursor += r.shard_stride * world_;
+            ag_cursor += round_up(shard_groups * world_ * group_bytes_, 256);
+            gather_cursor += r.gather_stride * world_;
+            if (stages != 1 && (rs_cursor > rs_bytes_ || ag_cursor > ag_bytes_))
+                throw std::runtime_error("chunked regions exceed the workspace");
+            if (stages == 1 && gather_cursor > gather_bytes_) throw std::runtime_error("chunked regions exceed the workspace");
+            const uintptr_t off = static_cast<uintptr_t>(first) * elem_bytes_;
+            launches += one_chunk(x + off, out + off, residual == 0 ? 0 : residual + off, n, stages, scale,
+                                  update_residual, ef_local, epoch, r, shard_groups, full_groups, stream, s_reduce,
+                                  s_gather);
+        }
+        if (piped) {
+            const int used = stages == 1 ? 1 : 2;
+            for (int i = 0; i < used; ++i) {
+                check(cudaEventRecord(side_[i].done, side_[i].stream), "cudaEventRecord(done)");
+                check(cudaStreamWaitEvent(stream, side_[i].done, 0), "cudaStreamWaitEvent(done)");
+            }
+        }
+        return launches;
+    }
+
+  private:
+    struct Side {
+        cudaStream_t stream = nullptr;
+        cudaEvent_t done = nullptr;
+    };
+
+    void ensure_side_streams() {
+        if (start_ != nullptr) return;
+        int lo = 0, hi = 0;
+        check(cudaDeviceGetStreamPriorityRange(&lo, &hi), "cudaDeviceGetStreamPriorityRange");
+        for (auto& s : side_) {
+            check(cudaStreamCreateWithPriority(&s.stream, cudaStreamNonBlocking, hi), "cudaStreamCreateWithPriority");
+            check(cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming), "cudaEventCreateWithFlags");
+        }
+        check(cudaEventCreateWithFlags(&start_, cudaEventDisableTiming), "cudaEventCreateWithFlags");
+    }
+
+    int one_chunk(uintptr_t x, uintptr_t out, uintptr_t residual, int64_t numel, int stages, double scale,
+                  bool update_residual, bool ef_local, unsigned int epoch, const Regions& r, int64_t shard_groups,
+                  int64_t full_groups, cudaStream_t s_push, cudaStream_t s_reduce, cudaStream_t s_gather) const {
         const bool want_ref = residual != 0 && update_residual && !ef_local;
         const bool want_local = residual != 0 && update_residual && ef_local;
-
         LbcQuantPush q{};
         q.dtype = dtype_;
         q.group_size = group_;
@@ -75,28 +175,27 @@ class FusedAllReducePlan {
         q.numel = numel;
         q.num_dst = world_;
         q.max_blocks = max_blocks_;
-        fill_signal(q.signal, kPhaseRS, epoch);
+        fill_signal(q.signal, r.channel, kPhaseRS, epoch);
 
         if (stages == 1) {
-            if (gather_off_.size() != 2) throw std::invalid_argument("this plan has no gather region");
             q.mode = LBC_PUSH_BROADCAST;
             q.layout_groups = full_groups;
             for (int d = 0; d < world_; ++d)
-                q.dst[d] = reinterpret_cast<uint8_t*>(peers_[d] + gather_off_[parity] + rank_ * gather_stride_);
-            check(lbc_quant_push(&q, stream), "quant_push(broadcast)");
-            LbcReduce r = base_reduce(numel, scale);
-            r.num_src = world_;
+                q.dst[d] = reinterpret_cast<uint8_t*>(peers_[d] + r.gather + rank_ * r.gather_stride);
+            check(lbc_quant_push(&q, s_push), "quant_push(broadcast)");
+            LbcReduce k = base_reduce(numel, scale);
+            k.num_src = world_;
             for (int s = 0; s < world_; ++s)
-                r.src[s] = reinterpret_cast<const uint8_t*>(peers_[rank_] + gather_off_[parity] + s * gather_stride_);
-            r.layout_groups = full_groups;
-            r.out = reinterpret_cast<void*>(out);
+                k.src[s] = reinterpret_cast<const uint8_t*>(peers_[rank_] + r.gather + s * r.gather_stride);
+            k.layout_groups = full_groups;
+            k.out = reinterpret_cast<void*>(out);
             if (want_ref) {
-                r.prepared = reinterpret_cast<const void*>(residual);
-                r.residual_out = reinterpret_cast<void*>(residual);
+                k.prepared = reinterpret_cast<const void*>(residual);
+                k.residual_out = reinterpret_cast<void*>(residual);
             }
-            fill_wait(r.wait, kPhaseRS, epoch);
-            gate(r.wait, stream);
-            check(lbc_reduce(&r, stream), "reduce(one stage)");
+            fill_wait(k.wait, r.channel, kPhaseRS, epoch);
+            gate(k.wait, s_reduce);
+            check(lbc_reduce(&k, s_reduce), "reduce(one stage)");
             return 3;
         }
 
@@ -104,62 +203,61 @@ class FusedAllReducePlan {
         q.shard_groups = shard_groups;
         q.layout_groups = shard_groups;
         for (int d = 0; d < world_; ++d)
-            q.dst[d] = reinterpret_cast<uint8_t*>(peers_[d] + rs_off_[parity] + rank_ * shard_stride_);
-        check(lbc_quant_push(&q, stream), "quant_push(scatter)");
+            q.dst[d] = reinterpret_cast<uint8_t*>(peers_[d] + r.rs + rank_ * r.shard_stride);
+        check(lbc_quant_push(&q, s_push), "quant_push(scatter)");
 
         const int64_t shard_numel = shard_groups * group_;
         const int64_t lo = rank_ * shard_numel;
-        int64_t valid = (numel < lo + shard_numel ? numel : lo + shard_numel) - lo;
-        if (valid < 0) valid = 0;
+        const int64_t valid = std::max<int64_t>(0, std::min(numel, lo + shard_numel) - lo);
         LbcReduce k2 = base_reduce(valid, scale);
         k2.num_src = world_;
         for (int s = 0; s < world_; ++s)
-            k2.src[s] = reinterpret_cast<const uint8_t*>(peers_[rank_] + rs_off_[parity] + s * shard_stride_);
+            k2.src[s] = reinterpret_cast<const uint8_t*>(peers_[rank_] + r.rs + s * r.shard_stride);
         k2.layout_groups = shard_groups;
         k2.num_dst = world_;
-        for (int d = 0; d < world_; ++d) k2.dst[d] = reinterpret_cast<uint8_t*>(peers_[d] + ag_off_);
+        for (int d = 0; d < world_; ++d) k2.dst[d] = reinterpret_cast<uint8_t*>(peers_[d] + r.ag);
         k2.dst_layout_groups = shard_groups * world_;
         k2.dst_group_offset = rank_ * shard_groups;
-        fill_signal(k2.signal, kPhaseAG, epoch);
-        fill_wait(k2.wait, kPhaseRS, epoch);
-        gate(k2.wait, stream);
-        check(lbc_reduce(&k2, stream), "reduce(shard)");
+        fill_signal(k2.signal, r.channel, kPhaseAG, epoch);
+        fill_wait(k2.wait, r.channel, kPhaseRS, epoch);
+        gate(k2.wait, s_reduce);
+        check(lbc_reduce(&k2, s_reduce), "reduce(shard)");
 
         LbcReduce k3 = base_reduce(numel, 1.0);
         k3.num_src = 1;
-        k3.src[0] = reinterpret_cast<const uint8_t*>(peers_[rank_] + ag_off_);
+        k3.src[0] = reinterpret_cast<const uint8_t*>(peers_[rank_] + r.ag);
         k3.layout_groups = shard_groups * world_;
         k3.out = reinterpret_cast<void*>(out);
         if (want_ref) {
             k3.prepared = reinterpret_cast<const void*>(residual);
             k3.residual_out = reinterpret_cast<void*>(residual);
         }
-        fill_wait(k3.wait, kPhaseAG, epoch);
-        gate(k3.wait, stream);
-        check(lbc_reduce(&k3, stream), "reduce(gather)");
+        fill_wait(k3.wait, r.channel, kPhaseAG, epoch);
+        gate(k3.wait, s_gather);
+        check(lbc_reduce(&k3, s_gather), "reduce(gather)");
         return 5;
     }
 
-  private:
     // A one-block kernel does the (bounded) waiting, so that a rank that is ahead of its peers
     // parks 256 threads instead of filling every SM with spinning blocks while its own backward
     // pass still needs them; the reduce kernel that follows finds its flags already set.
     void gate(const LbcWait& wait, cudaStream_t stream) const {
         check(lbc_wait_signal(&wait, nullptr, stream), "wait_signal");
     }
-    uintptr_t flags_addr(int rank, int phase) const {
-        return peers_[rank] + static_cast<uintptr_t>((channel_ * kNumPhases + phase) * kFlagSlots) * 4;
+    uintptr_t flags_addr(int rank, int channel, int phase) const {
+        return peers_[rank] + static_cast<uintptr_t>((channel * kNumPhases + phase) * kFlagSlots) * 4;
     }
-    void fill_signal(LbcSignal& s, int phase, unsigned int epoch) const {
+    void fill_signal(LbcSignal& s, int channel, int phase, unsigned int epoch) const {
         s.num_remote = world_;
-        for (int d = 0; d < world_; ++d) s.remote_flags[d] = reinterpret_cast<unsigned int*>(flags_addr(d, phase));
+        for (int d = 0; d < world_; ++d)
+            s.remote_flags[d] = reinterpret_cast<unsigned int*>(flags_addr(d, channel, phase));
         s.my_slot = rank_;
         s.epoch = epoch;
-        s.block_counter = reinterpret_cast<unsigned int*>(peers_[rank_] + kCounterOffset +
-                                                          static_cast<uintptr_t>(channel_ * kNumPhases + phase) * 4);
+        s.block_counter = reinterpret_cast<unsigned int*>(peers_[rank_] + counter_offset_ +
+                                                          static_cast<uintptr_t>(channel * kNumPhases + phase) * 4);
     }
-    void fill_wait(LbcWait& w, int phase, unsigned int epoch) const {
-        w.flags = reinterpret_cast<const unsigned int*>(flags_addr(rank_, phase));
+    void fill_wait(LbcWait& w, int channel, int phase, unsigned int epoch) const {
+        w.flags = reinterpret_cast<const unsigned int*>(flags_addr(rank_, channel, phase));
         w.count = world_;
         w.epoch = epoch;
         w.timeout_ns = timeout_ns_;
@@ -180,27 +278,34 @@ class FusedAllReducePlan {
     int dtype_, group_, bit_, rank_, world_ = 1;
     std::vector<uintptr_t> peers_;
     std::vector<int64_t> rs_off_;
-    int64_t ag_off_;
+    int64_t rs_bytes_, ag_off_, ag_bytes_;
     std::vector<int64_t> gather_off_;
-    int64_t shard_stride_, gather_stride_;
-    int channel_;
+    int64_t gather_bytes_;
+    std::vector<int> channels_;
+    int64_t counter_offset_;
     unsigned long long timeout_ns_;
     uintptr_t status_;
     int max_blocks_;
     int64_t max_numel_;
-    int value_bytes_ = 0, scale_bytes_ = 0;
+    int64_t group_bytes_ = 66, elem_bytes_ = 2;
+    int64_t min_chunk_bytes_ = int64_t(8) << 20;
+    int max_chunks_ = 1;
+    Side side_[2];
+    cudaEvent_t start_ = nullptr;
 };
 
 }  // namespace
 
 void bind_fused_plan(py::module_& m) {
     py::class_<FusedAllReducePlan>(m, "FusedAllReducePlan")
-        .def(py::init<int, int, int, int, std::vector<uintptr_t>, std::vector<int64_t>, int64_t, std::vector<int64_t>,
-                      int64_t, int64_t, int, unsigned long long, uintptr_t, int, int64_t>(),
+        .def(py::init<int, int, int, int, std::vector<uintptr_t>, std::vector<int64_t>, int64_t, int64_t, int64_t,
+                      std::vector<int64_t>, int64_t, std::vector<int>, int64_t, unsigned long long, uintptr_t, int,
+                      int64_t>(),
              py::arg("dtype"), py::arg("group_size"), py::arg("bit"), py::arg("rank"), py::arg("peer_ptrs"),
-             py::arg("rs_off"), py::arg("ag_off"), py::arg("gather_off"), py::arg("shard_stride"),
-             py::arg("gather_stride"), py::arg("channel"), py::arg("timeout_ns"), py::arg("status_device"),
-             py::arg("max_blocks"), py::arg("max_numel"))
+             py::arg("rs_off"), py::arg("rs_bytes"), py::arg("ag_off"), py::arg("ag_bytes"), py::arg("gather_off"),
+             py::arg("gather_bytes"), py::arg("channels"), py::arg("counter_offset"), py::arg("timeout_ns"),
+             py::arg("status_device"), py::arg("max_blocks"), py::arg("max_numel"))
+        .def("set_chunking", &FusedAllReducePlan::set_chunking, py::arg("min_chunk_bytes"), py::arg("max_chunks"))
         .def("all_reduce", &FusedAllReducePlan::all_reduce, py::arg("x"), py::arg("out"), py::arg("residual"),
              py::arg("numel"), py::arg("stages"), py::arg("scale"), py::arg("update_residual"), py::arg("ef_local"),
              py::arg("epoch"), py::arg("stream"));

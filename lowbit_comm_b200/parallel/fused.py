@@ -44,10 +44,17 @@ from ..ops.sizing import dtype_bytes
 from .peer_memory import PHASE_ALL_GATHER, PHASE_REDUCE_SCATTER, PeerGroup
 
 ALIGN_GROUPS = 8
+MAX_CHUNKS = 8          # pipeline depth of the native launcher (one flag channel per chunk)
 
 
 def _round_up(value: int, align: int) -> int:
     return -(-value // align) * align
+
+
+def _chunk_slack(world_size: int, config: CompressionConfig) -> int:
+    """Extra elements of capacity: every chunk of a pipelined call rounds its regions up separately."""
+
+    return 2 * MAX_CHUNKS * world_size * ALIGN_GROUPS * config.group_size + MAX_CHUNKS * 256 * 8
 
 
 def _current_stream_ptr(device) -> int:
@@ -107,7 +114,7 @@ class FusedWorkspace:
         self.max_blocks = int(max_blocks)
         self.ext = group._ext
         self._torch_dtype = oracle.TORCH_DTYPES[dtype]
-        cap = geometry(self.max_numel, group.world_size, dtype, config)
+        cap = geometry(self.max_numel + _chunk_slack(group.world_size, config), group.world_size, dtype, config)
         self.cap = cap
         W = group.world_size
         self.shard_stride = _round_up(max(cap.shard_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
@@ -119,27 +126,40 @@ class FusedWorkspace:
         self.gather_off: list[int] | None = None
         if with_gather_region or (with_gather_region is None and W <= 2):
             self._ensure_gather()
-        self.channel = group.new_channel()
+        self.channels = [group.new_channel() for _ in range(MAX_CHUNKS)]
+        self.channel = self.channels[0]
         self.launches = 0
         self.phase_timer = None   # set to a utils.tracing.PhaseTimer to time K1/K2/K3 separately
         # Real process groups launch through the native plan (one binding crossing per collective);
         # emulated single-GPU groups keep the Python path so that launches can be interleaved by phase.
         self._native = None
+        self.min_chunk_bytes, self.max_chunks = 8 << 20, MAX_CHUNKS
         self._build_native()
 
     def _build_native(self) -> None:
         group = self.group
         if group.process_group is None or not hasattr(self.ext, "FusedAllReducePlan"):
             return
+        from .peer_memory import COUNTER_OFFSET
+
         self._native = self.ext.FusedAllReducePlan(
             _DTYPE_CODE[self.dtype], self.config.group_size, self.config.bit, group.rank, list(group.peer_ptrs),
-            list(self.rs_off), self.ag_off, list(self.gather_off or []), self.shard_stride, self.gather_stride,
-            self.channel, group.timeout_ns, group.status_device, self.max_blocks, self.max_numel)
+            list(self.rs_off), self.rs_bytes, self.ag_off, self.ag_bytes, list(self.gather_off or []),
+            group.world_size * self.gather_stride, list(self.channels), COUNTER_OFFSET, group.timeout_ns,
+            group.status_device, self.max_blocks, self.max_numel)
+        self._native.set_chunking(self.min_chunk_bytes, self.max_chunks)
+
+    def set_chunking(self, min_chunk_bytes: int, max_chunks: int = MAX_CHUNKS) -> None:
+        """Tensors of at least 2 x `min_chunk_bytes` are pipelined in up to `max_chunks` chunks."""
+
+        self.min_chunk_bytes, self.max_chunks = int(min_chunk_bytes), int(max_chunks)
+        if self._native is not None:
+            self._native.set_chunking(self.min_chunk_bytes, self.max_chunks)
 
     @staticmethod
     def required_bytes(world_size: int, dtype: str, config: CompressionConfig, max_numel: int,
                        with_gather_region: bool) -> int:
-        cap = geometry(max_numel, world_size, dtype, config)
+        cap = geometry(max_numel + _chunk_slack(world_size, config), world_size, dtype, config)
         shard = _round_up(max(cap.shard_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
         total = 2 * world_size * shard + _round_up(max(cap.total_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
         if with_gather_region:

@@ -6,9 +6,9 @@ arena mean the same thing on every rank (symmetric allocation), so a kernel can
 address "my slot in rank d's receive region" as `peer_base[d] + offset`.
 
 Arena layout:
-  [0, 16 KiB)      flags[channel][phase][source rank]  (uint32 epochs, written by peers)
-  [16, 20 KiB)     block counters[channel][phase]      (local scratch of the signalling kernels)
-  [64 KiB, ...)    data regions handed out by `alloc`
+  [0, 64 KiB)      flags[channel][phase][source rank]  (uint32 epochs, written by peers)
+  [64, 68 KiB)     block counters[channel][phase]      (local scratch of the signalling kernels)
+  [128 KiB, ...)   data regions handed out by `alloc`
 
 The reference has no counterpart (its payloads travel through torch.distributed
 calls, ccdl_comm/communication/torch_transport.py:61-188).
@@ -24,12 +24,12 @@ import torch
 from ..exceptions import AsyncCommunicationError, CCDLUnavailableError
 from ..ops.loader import require_extension
 
-MAX_CHANNELS = 64
+MAX_CHANNELS = 256
 NUM_PHASES = 4
 MAX_RANKS = 16
 FLAG_BYTES = MAX_CHANNELS * NUM_PHASES * MAX_RANKS * 4
 COUNTER_OFFSET = FLAG_BYTES
-DATA_OFFSET = 64 * 1024
+DATA_OFFSET = 128 * 1024
 DEFAULT_TIMEOUT_NS = 20_000_000_000  # 20 s: far above any real skew, far below a watchdog
 
 PHASE_REDUCE_SCATTER, PHASE_ALL_GATHER, PHASE_P2P_DATA, PHASE_P2P_ACK = range(NUM_PHASES)

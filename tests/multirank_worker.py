@@ -37,6 +37,8 @@ def collectives_case(rank: int, world: int) -> None:
         two = oracle.decode(oracle.encode(y, cfg), n, cfg, name)
         for strategy, want in (("all_gather", y), ("reduce_scatter", two)):
             mine = xs[rank].cuda()
+            if n > 50_000:  # small chunks: the pipelined multi-stream launcher runs with up to 8 chunks
+                comm.workspace(mine, cfg, name).set_chunking(1 << 17, 8)
             got = compressed_all_reduce(mine, config=cfg, op="mean", strategy=strategy)
             torch.cuda.synchronize()
             assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), (strategy, n, rank)
