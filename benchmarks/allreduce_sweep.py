@@ -151,13 +151,15 @@ def main() -> None:
         from lowbit_comm_b200.ops.loader import require_extension
 
         ext = require_extension()
-        combos = [(1, False)]
+        combos = [(1, False, 0)]
         if args.variants:
-            combos = [(0, False), (1, False), (2, False), (1, True), (2, True)]
-        for stages, (push_variant, reduce_bulk) in [(s, c) for s in ((1, 2) if world > 1 else (1,)) for c in combos]:
-            if stages == 1 and reduce_bulk:
+            combos = [(0, False, 0), (1, False, 0), (2, False, 0), (1, True, 0), (1, False, 296), (1, True, 296),
+                      (1, False, 592)]
+        for stages, (push_variant, reduce_bulk, k2_blocks) in [(s, c) for s in ((1, 2) if world > 1 else (1,))
+                                                               for c in combos]:
+            if stages == 1 and (reduce_bulk or k2_blocks):
                 continue
-            ext.set_push_variant(push_variant, reduce_bulk)
+            ext.set_push_variant(push_variant, reduce_bulk, k2_blocks)
             residual.zero_()
             t = measure(ours(stages))
             comm.check_status()
@@ -178,12 +180,12 @@ def main() -> None:
                     ours(stages)()
                 phases = ws.phase_timer.summary()
                 ws.phase_timer = None
-            tag = f"_p{push_variant}r{int(reduce_bulk)}" if args.variants else ""
+            tag = f"_p{push_variant}r{int(reduce_bulk)}b{k2_blocks}" if args.variants else ""
             rows.append({"impl": f"ours_{stages}stage{tag}", "mib": mib, "world": world, "ms": t,
                          "algbw_gbs": nbytes / (t * 1e-3) / 1e9, "rel_l2": rel, **roof,
                          "roofline_frac": roof["roofline_us"] / (t * 1e3), "peak_kind": peak_kind,
                          "phases_ms": phases})
-        ext.set_push_variant(1, False)
+        ext.set_push_variant(1, False, 0)
         nccl_buf = x.clone()
 
         def nccl():

@@ -309,8 +309,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("signal") = py::none(), py::arg("max_blocks") = 0);
     m.def("wait_signal", &wait_signal, py::arg("wait") = py::none(), py::arg("signal") = py::none());
     m.def("default_max_blocks", [] { return lbc_default_max_blocks(); });
-    m.def("set_push_variant", [](int push, bool reduce_bulk) { lbc_set_push_variant(push, reduce_bulk ? 1 : 0); },
-          py::arg("push_variant"), py::arg("reduce_bulk") = false);
+    m.def("set_push_variant",
+          [](int push, bool reduce_bulk, int reduce_push_blocks) {
+              lbc_set_push_variant(push, reduce_bulk ? 1 : 0, reduce_push_blocks);
+          },
+          py::arg("push_variant"), py::arg("reduce_bulk") = false, py::arg("reduce_push_blocks") = 0);
 
     m.def("arena_alloc", &lbc::arena_alloc);
     m.def("arena_free", &lbc::arena_free);

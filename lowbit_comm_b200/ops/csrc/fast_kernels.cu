@@ -649,6 +649,7 @@ static cudaError_t dispatch(const P* p, cudaStream_t stream) {
 //   0 classic grid-stride kernel   1 shard-interleaved tiles, per-thread stores   2 tiles + bulk stores
 static int g_push_variant = 1;
 static int g_reduce_bulk = 0;
+static int g_reduce_push_blocks = 0;   // grid cap of reduce kernels that also push (0 = default)
 
 static bool tiled_path_ok(const LbcQuantPush* p) {
     if (p->num_dst <= 0) return false;
@@ -683,7 +684,9 @@ struct ReduceLauncher {
     static cudaError_t run(const LbcReduce* p, cudaStream_t stream) {
         const int64_t groups = (p->numel + G - 1) / G;
         if (groups == 0 && p->signal.num_remote == 0 && p->wait.flags == nullptr) return cudaSuccess;
-        const int grid = grid_for(groups * (G / kElemsPerThread), p->max_blocks);
+        int cap = p->max_blocks;
+        if (p->num_dst > 0 && g_reduce_push_blocks > 0 && (cap == 0 || cap > g_reduce_push_blocks)) cap = g_reduce_push_blocks;
+        const int grid = grid_for(groups * (G / kElemsPerThread), cap);
         LbcReduce launch = *p;
         launch.bulk_store = g_reduce_bulk;
         reduce_kernel<T, G, BIT><<<grid, kThreads, 0, stream>>>(launch);
@@ -697,9 +700,10 @@ extern "C" {
 
 int lbc_default_max_blocks(void) { return lbc::default_max_blocks(); }
 
-void lbc_set_push_variant(int push_variant, int reduce_bulk) {
+void lbc_set_push_variant(int push_variant, int reduce_bulk, int reduce_push_blocks) {
     lbc::g_push_variant = push_variant < 0 ? 0 : (push_variant > 2 ? 2 : push_variant);
     lbc::g_reduce_bulk = reduce_bulk != 0;
+    lbc::g_reduce_push_blocks = reduce_push_blocks < 0 ? 0 : reduce_push_blocks;
 }
 
 cudaError_t lbc_quant_push(const LbcQuantPush* p, cudaStream_t stream) {

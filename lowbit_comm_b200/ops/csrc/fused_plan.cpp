@@ -128,6 +128,7 @@ class FusedAllReducePlan {
                 throw std::runtime_error("chunked regions exceed the workspace");
             if (stages == 1 && gather_cursor > gather_bytes_) throw std::runtime_error("chunked regions exceed the workspace");
             const uintptr_t off = static_cast<uintptr_t>(first) * elem_bytes_;
+            grid_cap_ = max_blocks_;
             launches += one_chunk(x + off, out + off, residual == 0 ? 0 : residual + off, n, stages, scale,
                                   update_residual, ef_local, epoch, r, shard_groups, full_groups, stream, s_reduce,
                                   s_gather);
@@ -174,7 +175,7 @@ class FusedAllReducePlan {
         q.local_ef_out = want_local ? reinterpret_cast<void*>(residual) : nullptr;
         q.numel = numel;
         q.num_dst = world_;
-        q.max_blocks = max_blocks_;
+        q.max_blocks = grid_cap_;
         fill_signal(q.signal, r.channel, kPhaseRS, epoch);
 
         if (stages == 1) {
@@ -271,7 +272,7 @@ class FusedAllReducePlan {
         r.bit = bit_;
         r.numel = numel;
         r.scale = static_cast<float>(scale);
-        r.max_blocks = max_blocks_;
+        r.max_blocks = grid_cap_;
         return r;
     }
 
@@ -290,6 +291,7 @@ class FusedAllReducePlan {
     int64_t group_bytes_ = 66, elem_bytes_ = 2;
     int64_t min_chunk_bytes_ = int64_t(8) << 20;
     int max_chunks_ = 1;
+    mutable int grid_cap_ = 0;
     Side side_[2];
     cudaEvent_t start_ = nullptr;
 };

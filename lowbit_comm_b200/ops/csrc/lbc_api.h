@@ -129,8 +129,9 @@ cudaError_t lbc_wait_signal(const LbcWait* wait, const LbcSignal* signal, cudaSt
 int lbc_default_max_blocks(void);
 // How quantized tiles reach their destinations: push_variant 0 classic grid-stride kernel,
 // 1 shard-interleaved tiles with per-thread stores, 2 tiles handed to the bulk-store engine;
-// reduce_bulk selects bulk stores for the requantize-and-broadcast stage.
-void lbc_set_push_variant(int push_variant, int reduce_bulk);
+// reduce_bulk selects bulk stores for the requantize-and-broadcast stage; reduce_push_blocks caps the
+// grid of that stage (0 = default) so that every block amortises its closing system-scope fence.
+void lbc_set_push_variant(int push_variant, int reduce_bulk, int reduce_push_blocks);
 
 #ifdef __cplusplus
 }

@@ -133,7 +133,10 @@ class FusedWorkspace:
         # Real process groups launch through the native plan (one binding crossing per collective);
         # emulated single-GPU groups keep the Python path so that launches can be interleaved by phase.
         self._native = None
-        self.min_chunk_bytes, self.max_chunks = 8 << 20, MAX_CHUNKS
+        # Chunk pipelining is off by default: measured on 2 x B200 it was slower than the plain sequence
+        # (persistent grids of neighbouring chunks do not interleave; one-tile blocks pay a system-scope
+        # fence each).  `set_chunking` turns it on for experiments.
+        self.min_chunk_bytes, self.max_chunks = 16 << 20, 1
         self._build_native()
 
     def _build_native(self) -> None:
