@@ -63,6 +63,8 @@ def main() -> None:
     ap.add_argument("--chunk-mib", type=float, default=None, help="pipeline chunk size (0 = no pipelining)")
     ap.add_argument("--variants", action="store_true", help="time every push/reduce kernel variant")
     ap.add_argument("--phases", action="store_true", help="also time K1/K2/K3 separately (Python launch path)")
+    ap.add_argument("--multicast", action="store_true",
+                    help="arenas from the symmetric-memory allocator: broadcasts use multimem stores")
     ap.add_argument("--out", default="gpurun_out/allreduce_sweep.json")
     args = ap.parse_args()
 
@@ -89,6 +91,8 @@ def main() -> None:
     from lowbit_comm_b200.parallel.fused import FusedWorkspace
 
     arena = FusedWorkspace.required_bytes(world, "bf16", cfg, 1 << (max_numel - 1).bit_length(), True) + (256 << 20)
+    if args.multicast:
+        os.environ["LBC_MULTICAST"] = "1"
     comm = Communicator(None, arena_bytes=arena)
     big = comm.workspace(torch.empty(max_numel, dtype=torch.bfloat16, device=dev), cfg, "bf16")  # largest first
     if args.chunk_mib is not None:
@@ -127,6 +131,9 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    multicast_on = bool(comm.peer_group is not None and comm.peer_group.multicast_ptr)
+    if rank == 0:
+        print(json.dumps({"multicast_arena": multicast_on}), flush=True)
     rows = []
     mib = args.min_mib
     while mib <= args.max_mib:
@@ -151,13 +158,13 @@ def main() -> None:
         from lowbit_comm_b200.ops.loader import require_extension
 
         ext = require_extension()
-        combos = [(1, False, 0)]
+        combos = [(1, True, 0)]
         if args.variants:
-            combos = [(0, False, 0), (1, False, 0), (2, False, 0), (1, True, 0), (1, False, 296), (1, True, 296),
-                      (1, False, 592)]
+            combos = [(0, True, 0), (1, True, 0), (2, True, 0), (1, False, 0), (1, False, -1), (1, True, -1),
+                      (1, True, 592)]
         for stages, (push_variant, reduce_bulk, k2_blocks) in [(s, c) for s in ((1, 2) if world > 1 else (1,))
                                                                for c in combos]:
-            if stages == 1 and (reduce_bulk or k2_blocks):
+            if stages == 1 and (not reduce_bulk or k2_blocks):
                 continue
             ext.set_push_variant(push_variant, reduce_bulk, k2_blocks)
             residual.zero_()
@@ -184,8 +191,8 @@ def main() -> None:
             rows.append({"impl": f"ours_{stages}stage{tag}", "mib": mib, "world": world, "ms": t,
                          "algbw_gbs": nbytes / (t * 1e-3) / 1e9, "rel_l2": rel, **roof,
                          "roofline_frac": roof["roofline_us"] / (t * 1e3), "peak_kind": peak_kind,
-                         "phases_ms": phases})
-        ext.set_push_variant(1, False, 0)
+                         "phases_ms": phases, "multicast": multicast_on})
+        ext.set_push_variant(1, True, 0)
         nccl_buf = x.clone()
 
         def nccl():

@@ -100,7 +100,7 @@ int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 void quant_push(const at::Tensor& x, const std::optional<at::Tensor>& residual,
                 const std::optional<at::Tensor>& prepared_out, const std::optional<at::Tensor>& local_ef_out,
                 const Ptrs& dst, int mode, int64_t shard_groups, int64_t layout_groups, int64_t group_offset,
-                int group_size, int bit, const SignalArg& signal, int max_blocks) {
+                int group_size, int bit, const SignalArg& signal, int max_blocks, uintptr_t mc_dst) {
     check_dense(x, "input");
     c10::cuda::CUDAGuard guard(x.device());
     LbcQuantPush p{};
@@ -131,6 +131,8 @@ void quant_push(const at::Tensor& x, const std::optional<at::Tensor>& residual,
     p.group_offset = group_offset;
     p.signal = make_signal(signal);
     p.max_blocks = max_blocks;
+    TORCH_CHECK(mc_dst == 0 || mode == LBC_PUSH_BROADCAST, "a multicast destination needs broadcast mode");
+    p.mc_dst = reinterpret_cast<uint8_t*>(mc_dst);
     cuda_check(lbc_quant_push(&p, at::cuda::getCurrentCUDAStream()), "lbc_quant_push");
 }
 
@@ -138,7 +140,7 @@ void reduce(const Ptrs& src, int64_t layout_groups, int64_t group_offset, bool c
             int group_size, int bit, double scale, const std::optional<at::Tensor>& out, bool accumulate,
             const std::optional<at::Tensor>& prepared, const std::optional<at::Tensor>& residual_out, const Ptrs& dst,
             int64_t dst_layout_groups, int64_t dst_group_offset, const SignalArg& signal, const WaitArg& wait,
-            int max_blocks) {
+            int max_blocks, uintptr_t mc_dst) {
     LbcReduce p{};
     p.dtype = dtype;
     p.group_size = group_size;
@@ -178,6 +180,8 @@ void reduce(const Ptrs& src, int64_t layout_groups, int64_t group_offset, bool c
     p.signal = make_signal(signal);
     p.wait = make_wait(wait);
     p.max_blocks = max_blocks;
+    TORCH_CHECK(mc_dst == 0 || p.num_dst > 0, "a multicast destination needs the unicast destinations too");
+    p.mc_dst = reinterpret_cast<uint8_t*>(mc_dst);
     cuda_check(lbc_reduce(&p, at::cuda::getCurrentCUDAStream()), "lbc_reduce");
 }
 
@@ -295,12 +299,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("quant_push", &quant_push, py::arg("x"), py::arg("residual"), py::arg("prepared_out"),
           py::arg("local_ef_out"), py::arg("dst"), py::arg("mode"), py::arg("shard_groups"), py::arg("layout_groups"),
           py::arg("group_offset"), py::arg("group_size"), py::arg("bit"), py::arg("signal") = py::none(),
-          py::arg("max_blocks") = 0);
+          py::arg("max_blocks") = 0, py::arg("mc_dst") = 0);
     m.def("reduce", &reduce, py::arg("src"), py::arg("layout_groups"), py::arg("group_offset"), py::arg("compact"),
           py::arg("numel"), py::arg("dtype"), py::arg("group_size"), py::arg("bit"), py::arg("scale"), py::arg("out"),
           py::arg("accumulate"), py::arg("prepared"), py::arg("residual_out"), py::arg("dst"),
           py::arg("dst_layout_groups"), py::arg("dst_group_offset"), py::arg("signal") = py::none(),
-          py::arg("wait") = py::none(), py::arg("max_blocks") = 0);
+          py::arg("wait") = py::none(), py::arg("max_blocks") = 0, py::arg("mc_dst") = 0);
     m.def("quant_general", &quant_general);
     m.def("dequant_general", &dequant_general);
     m.def("error_feedback_update", &error_feedback_update);

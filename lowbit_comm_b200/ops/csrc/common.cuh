@@ -339,21 +339,30 @@ __device__ __forceinline__ bool block_wait(const WaitSpec& w) {
             for (;;) {
                 seen = ld_acquire_sys(f);
                 if (int(seen - w.epoch) >= 0) break;
-                if ((++spins & 63u) == 0 && global_ns() - t0 > w.timeout_ns) {
-                    ok = 0;
-                    // plain stores: the status word may live in mapped host memory, where
-                    // device atomics are not guaranteed; any timed-out thread's report will do
+                if ((++spins & 63u) == 0) {
                     volatile DeviceStatus* st = static_cast<volatile DeviceStatus*>(w.status);
-                    if (st != nullptr) {
-                        st->phase = w.phase;
-                        st->peer = threadIdx.x;
-                        st->seen = seen;
-                        st->expected = w.epoch;
-                        __threadfence_system();
-                        st->code = 1u;
-                        __threadfence_system();
+                    // an earlier wait of this group already ran out: give up at once, so that the
+                    // kernels queued behind a failed collective drain quickly
+                    const bool failed_before = st != nullptr && st->code != 0u;
+                    if (failed_before) {
+                        ok = 0;
+                        break;
                     }
-                    break;
+                    if (global_ns() - t0 > w.timeout_ns) {
+                        ok = 0;
+                        // plain stores: the status word may live in mapped host memory, where
+                        // device atomics are not guaranteed; any timed-out thread's report will do
+                        if (st != nullptr) {
+                            st->phase = w.phase;
+                            st->peer = threadIdx.x;
+                            st->seen = seen;
+                            st->expected = w.epoch;
+                            __threadfence_system();
+                            st->code = 1u;
+                            __threadfence_system();
+                        }
+                        break;
+                    }
                 }
                 __nanosleep(64);
             }
@@ -386,6 +395,20 @@ __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // Called by every thread after its last remote store.
+// Stores through an NVLink multicast address: the switch writes the same bytes into the mapped
+// region of every GPU of the multicast group (this GPU included), so one store leaves the SM
+// instead of one per destination.  The data moves through .f32 registers bit for bit.
+__device__ __forceinline__ void multimem_st16(void* mc_addr, uint4 v) {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+__device__ __forceinline__ void multimem_st8(void* mc_addr, uint2 v) {
+    asm volatile("multimem.st.weak.global.v2.f32 [%0], {%1, %2};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y))
+                 : "memory");
+}
+
 __device__ __forceinline__ void grid_signal(const SignalSpec& s) {
     if (s.num_remote <= 0) return;
     __threadfence_system();

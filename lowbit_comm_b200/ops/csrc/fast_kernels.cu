@@ -164,6 +164,7 @@ __global__ void __launch_bounds__(kThreads, 4) quant_push_kernel(const LbcQuantP
     __shared__ __align__(16) ScaleStage stage;
     const bool vec_scales = p.mode != LBC_PUSH_COMPACT_LOCAL && (p.layout_groups & 7) == 0 &&
                             (p.group_offset & 7) == 0 && (p.shard_groups & 7) == 0 && dsts_aligned16(p.dst, p.num_dst);
+    const bool mcast = vec_scales && p.mode == LBC_PUSH_BROADCAST && p.mc_dst != nullptr;
 
     // Chunks are rounded up to a whole warp so that the shuffles stay convergent.
     const int64_t chunk_span = (num_chunks + 31) / 32 * 32;
@@ -210,10 +211,17 @@ __global__ void __launch_bounds__(kThreads, 4) quant_push_kernel(const LbcQuantP
                 if (!vec_scales && lane == 0) store_scale<T>(base + p.layout_groups * VB + gl * MB, stored);
             } else {
                 const int64_t gl = p.group_offset + g;
-                for (int d = 0; d < p.num_dst; ++d) {
-                    uint8_t* base = p.dst[d];
-                    store_codes(base + gl * VB + lane * CB, codes, CB);
-                    if (!vec_scales && lane == 0) store_scale<T>(base + p.layout_groups * VB + gl * MB, stored);
+                if (mcast) {
+                    if constexpr (CB == 16)
+                        multimem_st16(p.mc_dst + gl * VB + lane * CB, codes);
+                    else
+                        multimem_st8(p.mc_dst + gl * VB + lane * CB, make_uint2(codes.x, codes.y));
+                } else {
+                    for (int d = 0; d < p.num_dst; ++d) {
+                        uint8_t* base = p.dst[d];
+                        store_codes(base + gl * VB + lane * CB, codes, CB);
+                        if (!vec_scales && lane == 0) store_scale<T>(base + p.layout_groups * VB + gl * MB, stored);
+                    }
                 }
             }
         }
@@ -232,7 +240,11 @@ __global__ void __launch_bounds__(kThreads, 4) quant_push_kernel(const LbcQuantP
                     st16(p.dst[d] + p.layout_groups * VB + gl * MB, sv);
                 } else {
                     const int64_t gl = p.group_offset + gv;
-                    for (int d = 0; d < p.num_dst; ++d) st16(p.dst[d] + p.layout_groups * VB + gl * MB, sv);
+                    if (mcast) {
+                        multimem_st16(p.mc_dst + p.layout_groups * VB + gl * MB, sv);
+                    } else {
+                        for (int d = 0; d < p.num_dst; ++d) st16(p.dst[d] + p.layout_groups * VB + gl * MB, sv);
+                    }
                 }
             }
             __syncwarp();
@@ -360,6 +372,11 @@ __global__ void __launch_bounds__(kThreads, 3) quant_push_tiled_kernel(const Lbc
             if (live) {
                 if (scatter) {
                     store_codes(p.dst[shard] + (g_dst + gl) * VB + lane * CB, codes, CB);
+                } else if (p.mc_dst != nullptr) {
+                    if constexpr (CB == 16)
+                        multimem_st16(p.mc_dst + (g_dst + gl) * VB + lane * CB, codes);
+                    else
+                        multimem_st8(p.mc_dst + (g_dst + gl) * VB + lane * CB, make_uint2(codes.x, codes.y));
                 } else {
                     for (int d = 0; d < p.num_dst; ++d) {
                         const int dd = (d + rot) % p.num_dst;
@@ -379,6 +396,8 @@ __global__ void __launch_bounds__(kThreads, 3) quant_push_tiled_kernel(const Lbc
                 const uint4 sv = *reinterpret_cast<const uint4*>(tile.scales[0] + threadIdx.x * 16);
                 if (scatter) {
                     st16(p.dst[shard] + p.layout_groups * VB + g_dst * MB + threadIdx.x * 16, sv);
+                } else if (p.mc_dst != nullptr) {
+                    multimem_st16(p.mc_dst + p.layout_groups * VB + g_dst * MB + threadIdx.x * 16, sv);
                 } else {
                     for (int d = 0; d < p.num_dst; ++d)
                         st16(p.dst[(d + rot) % p.num_dst] + p.layout_groups * VB + g_dst * MB + threadIdx.x * 16, sv);
@@ -416,7 +435,10 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
     __shared__ __align__(16) ScaleStage stage;
     const bool vec_scales = p.num_dst > 0 && (p.dst_layout_groups & 7) == 0 && (p.dst_group_offset & 7) == 0 &&
                             dsts_aligned16(p.dst, p.num_dst);
-    const bool bulk = vec_scales && p.bulk_store != 0;   // requantized tiles leave through the copy engine
+    // requantized tiles leave through the copy engine (a multicast destination takes precedence)
+    const bool bulk = vec_scales && p.bulk_store != 0 && p.mc_dst == nullptr;
+    // multicast: one multimem store per vector, replicated by the switch into every rank's region
+    const bool mcast = vec_scales && !bulk && p.mc_dst != nullptr && (CB == 16 || CB == 8);
     __shared__ __align__(128) PushTile tile;
     int buf = 0;
     // whole warps keep the shuffles convergent; the bulk path also has block-wide barriers in the loop
@@ -515,10 +537,18 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
             } else if (live) {
                 const uint4 codes = encode16<T, BIT>(acc, stored, nullptr);
                 const int64_t gl = p.dst_group_offset + g;
-                for (int d = 0; d < p.num_dst; ++d) {
-                    uint8_t* base = p.dst[d];
-                    store_codes(base + gl * VB + lane * CB, codes, CB);
-                    if (!vec_scales && lane == 0) store_scale<T>(base + p.dst_layout_groups * VB + gl * MB, stored);
+                if (mcast) {
+                    if constexpr (CB == 16)
+                        multimem_st16(p.mc_dst + gl * VB + lane * CB, codes);
+                    else
+                        multimem_st8(p.mc_dst + gl * VB + lane * CB, make_uint2(codes.x, codes.y));
+                } else {
+                    for (int d = 0; d < p.num_dst; ++d) {
+                        uint8_t* base = p.dst[d];
+                        store_codes(base + gl * VB + lane * CB, codes, CB);
+                        if (!vec_scales && lane == 0)
+                            store_scale<T>(base + p.dst_layout_groups * VB + gl * MB, stored);
+                    }
                 }
             }
             if (vec_scales && !bulk) {
@@ -531,7 +561,12 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
                 if (wlane < vecs_per_warp && gv < num_groups) {
                     const uint4 sv = *reinterpret_cast<const uint4*>(stage.bytes[threadIdx.x >> 5] + wlane * 16);
                     const int64_t gl = p.dst_group_offset + gv;
-                    for (int d = 0; d < p.num_dst; ++d) st16(p.dst[d] + p.dst_layout_groups * VB + gl * MB, sv);
+                    if (mcast) {
+                        multimem_st16(p.mc_dst + p.dst_layout_groups * VB + gl * MB, sv);
+                    } else {
+                        for (int d = 0; d < p.num_dst; ++d)
+                            st16(p.dst[d] + p.dst_layout_groups * VB + gl * MB, sv);
+                    }
                 }
                 __syncwarp();
             }
@@ -648,8 +683,10 @@ static cudaError_t dispatch(const P* p, cudaStream_t stream) {
 // Push variants (identical payload layout, so ranks may even differ):
 //   0 classic grid-stride kernel   1 shard-interleaved tiles, per-thread stores   2 tiles + bulk stores
 static int g_push_variant = 1;
-static int g_reduce_bulk = 0;
-static int g_reduce_push_blocks = 0;   // grid cap of reduce kernels that also push (0 = default)
+// Defaults from the 8 x B200 sweep (64-256 MiB): bulk stores and two blocks per SM for the
+// requantize-and-broadcast stage were 4-8 % faster than per-thread stores on the full grid.
+static int g_reduce_bulk = 1;
+static int g_reduce_push_blocks = 0;   // grid cap of reduce kernels that also push: 0 = two per SM, < 0 = none
 
 static bool tiled_path_ok(const LbcQuantPush* p) {
     if (p->num_dst <= 0) return false;
@@ -685,7 +722,10 @@ struct ReduceLauncher {
         const int64_t groups = (p->numel + G - 1) / G;
         if (groups == 0 && p->signal.num_remote == 0 && p->wait.flags == nullptr) return cudaSuccess;
         int cap = p->max_blocks;
-        if (p->num_dst > 0 && g_reduce_push_blocks > 0 && (cap == 0 || cap > g_reduce_push_blocks)) cap = g_reduce_push_blocks;
+        if (p->num_dst > 0 && g_reduce_push_blocks >= 0) {
+            const int push_cap = g_reduce_push_blocks > 0 ? g_reduce_push_blocks : default_max_blocks() / 4;
+            if (cap == 0 || cap > push_cap) cap = push_cap;
+        }
         const int grid = grid_for(groups * (G / kElemsPerThread), cap);
         LbcReduce launch = *p;
         launch.bulk_store = g_reduce_bulk;
@@ -703,13 +743,15 @@ int lbc_default_max_blocks(void) { return lbc::default_max_blocks(); }
 void lbc_set_push_variant(int push_variant, int reduce_bulk, int reduce_push_blocks) {
     lbc::g_push_variant = push_variant < 0 ? 0 : (push_variant > 2 ? 2 : push_variant);
     lbc::g_reduce_bulk = reduce_bulk != 0;
-    lbc::g_reduce_push_blocks = reduce_push_blocks < 0 ? 0 : reduce_push_blocks;
+    lbc::g_reduce_push_blocks = reduce_push_blocks;
 }
 
 cudaError_t lbc_quant_push(const LbcQuantPush* p, cudaStream_t stream) {
     if (p == nullptr || p->numel < 0 || p->num_dst < 0 || p->num_dst > LBC_MAX_RANKS) return cudaErrorInvalidValue;
     if (p->signal.num_remote < 0 || p->signal.num_remote > LBC_MAX_RANKS) return cudaErrorInvalidValue;
     if (p->mode == LBC_PUSH_SCATTER && p->shard_groups <= 0) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(p->mc_dst) & 15) != 0) return cudaErrorInvalidValue;
+    if (p->mc_dst != nullptr && p->mode != LBC_PUSH_BROADCAST) return cudaErrorInvalidValue;
     return lbc::dispatch<lbc::QuantPushLauncher>(p, stream);
 }
 
@@ -718,6 +760,7 @@ cudaError_t lbc_reduce(const LbcReduce* p, cudaStream_t stream) {
     if (p->num_dst < 0 || p->num_dst > LBC_MAX_RANKS) return cudaErrorInvalidValue;
     if (p->signal.num_remote < 0 || p->signal.num_remote > LBC_MAX_RANKS) return cudaErrorInvalidValue;
     if (p->wait.count < 0 || p->wait.count > lbc::kThreads) return cudaErrorInvalidValue;
+    if ((reinterpret_cast<uintptr_t>(p->mc_dst) & 15) != 0) return cudaErrorInvalidValue;
     return lbc::dispatch<lbc::ReduceLauncher>(p, stream);
 }
 

@@ -83,6 +83,9 @@ class FusedAllReducePlan {
         max_chunks_ = std::max(1, std::min(max_chunks, std::min<int>(kMaxChunks, static_cast<int>(channels_.size()))));
     }
 
+    // Base of the NVLink multicast mapping of the arenas (0 = none): broadcasts then leave this GPU once.
+    void set_multicast(uintptr_t mc_base) { mc_base_ = mc_base; }
+
     // Enqueues the collective on `stream`; returns the number of kernels launched.
     int all_reduce(uintptr_t x, uintptr_t out, uintptr_t residual, int64_t numel, int stages, double scale,
                    bool update_residual, bool ef_local, unsigned int epoch, uintptr_t stream_ptr) {
@@ -183,6 +186,7 @@ class FusedAllReducePlan {
             q.layout_groups = full_groups;
             for (int d = 0; d < world_; ++d)
                 q.dst[d] = reinterpret_cast<uint8_t*>(peers_[d] + r.gather + rank_ * r.gather_stride);
+            if (mc_base_ != 0) q.mc_dst = reinterpret_cast<uint8_t*>(mc_base_ + r.gather + rank_ * r.gather_stride);
             check(lbc_quant_push(&q, s_push), "quant_push(broadcast)");
             LbcReduce k = base_reduce(numel, scale);
             k.num_src = world_;
@@ -217,6 +221,7 @@ class FusedAllReducePlan {
         k2.layout_groups = shard_groups;
         k2.num_dst = world_;
         for (int d = 0; d < world_; ++d) k2.dst[d] = reinterpret_cast<uint8_t*>(peers_[d] + r.ag);
+        if (mc_base_ != 0) k2.mc_dst = reinterpret_cast<uint8_t*>(mc_base_ + r.ag);
         k2.dst_layout_groups = shard_groups * world_;
         k2.dst_group_offset = rank_ * shard_groups;
         fill_signal(k2.signal, r.channel, kPhaseAG, epoch);
@@ -288,6 +293,7 @@ class FusedAllReducePlan {
     uintptr_t status_;
     int max_blocks_;
     int64_t max_numel_;
+    uintptr_t mc_base_ = 0;
     int64_t group_bytes_ = 66, elem_bytes_ = 2;
     int64_t min_chunk_bytes_ = int64_t(8) << 20;
     int max_chunks_ = 1;
@@ -308,6 +314,7 @@ void bind_fused_plan(py::module_& m) {
              py::arg("gather_bytes"), py::arg("channels"), py::arg("counter_offset"), py::arg("timeout_ns"),
              py::arg("status_device"), py::arg("max_blocks"), py::arg("max_numel"))
         .def("set_chunking", &FusedAllReducePlan::set_chunking, py::arg("min_chunk_bytes"), py::arg("max_chunks"))
+        .def("set_multicast", &FusedAllReducePlan::set_multicast, py::arg("mc_base"))
         .def("all_reduce", &FusedAllReducePlan::all_reduce, py::arg("x"), py::arg("out"), py::arg("residual"),
              py::arg("numel"), py::arg("stages"), py::arg("scale"), py::arg("update_residual"), py::arg("ef_local"),
              py::arg("epoch"), py::arg("stream"));

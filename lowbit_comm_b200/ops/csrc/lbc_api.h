@@ -61,6 +61,7 @@ typedef struct {
     int64_t group_offset;      // broadcast: index of group 0 inside the destination layout
     LbcSignal signal;
     int max_blocks;            // 0 = library default
+    uint8_t* mc_dst;           // broadcast only: NVLink multicast alias of dst[*] (one store reaches every rank)
 } LbcQuantPush;
 
 typedef struct {
@@ -84,6 +85,7 @@ typedef struct {
     LbcWait wait;
     int max_blocks;
     int bulk_store;            // set by the launcher: requantized tiles leave through bulk stores
+    uint8_t* mc_dst;           // optional NVLink multicast alias of dst[*]: one multimem store reaches every rank
 } LbcReduce;
 
 cudaError_t lbc_quant_push(const LbcQuantPush* p, cudaStream_t stream);
@@ -130,7 +132,8 @@ int lbc_default_max_blocks(void);
 // How quantized tiles reach their destinations: push_variant 0 classic grid-stride kernel,
 // 1 shard-interleaved tiles with per-thread stores, 2 tiles handed to the bulk-store engine;
 // reduce_bulk selects bulk stores for the requantize-and-broadcast stage; reduce_push_blocks caps the
-// grid of that stage (0 = default) so that every block amortises its closing system-scope fence.
+// grid of that stage (0 = two blocks per SM, negative = no cap) so that every block amortises its
+// closing system-scope fence.
 void lbc_set_push_variant(int push_variant, int reduce_bulk, int reduce_push_blocks);
 
 #ifdef __cplusplus

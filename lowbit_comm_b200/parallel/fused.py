@@ -151,6 +151,7 @@ class FusedWorkspace:
             group.world_size * self.gather_stride, list(self.channels), COUNTER_OFFSET, group.timeout_ns,
             group.status_device, self.max_blocks, self.max_numel)
         self._native.set_chunking(self.min_chunk_bytes, self.max_chunks)
+        self._native.set_multicast(group.multicast_ptr)
 
     def set_chunking(self, min_chunk_bytes: int, max_chunks: int = MAX_CHUNKS) -> None:
         """Tensors of at least 2 x `min_chunk_bytes` are pipelined in up to `max_chunks` chunks."""
@@ -217,7 +218,7 @@ class FusedWorkspace:
         self.ext.reduce(src, geo.shard_groups, 0, False, geo.shard_valid_numel(me), self._code, geo.group_size,
                         self.config.bit, scale, out, False, None, None, dst, geo.total_groups,
                         me * geo.shard_groups, signal, g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch),
-                        self.max_blocks)
+                        self.max_blocks, g.multicast_addr(self.ag_off) if broadcast else 0)
         self.launches += 1
 
     def _k3_gather(self, geo: FusedGeometry, epoch: int, out, prepared, residual_out):
@@ -235,7 +236,8 @@ class FusedWorkspace:
         dst = [g.addr(d, region + me * self.gather_stride) for d in range(g.world_size)]
         self.ext.quant_push(x, residual, prepared_out, local_ef_out, dst, self.ext.PUSH_BROADCAST, 0,
                             geo.full_groups, 0, geo.group_size, self.config.bit,
-                            g.signal_all(self.channel, PHASE_REDUCE_SCATTER, epoch), self.max_blocks)
+                            g.signal_all(self.channel, PHASE_REDUCE_SCATTER, epoch), self.max_blocks,
+                            g.multicast_addr(region + me * self.gather_stride))
         self.launches += 1
 
     # -- collectives -------------------------------------------------------------

@@ -10,12 +10,22 @@ Arena layout:
   [64, 68 KiB)     block counters[channel][phase]      (local scratch of the signalling kernels)
   [128 KiB, ...)   data regions handed out by `alloc`
 
+Two ways to obtain the arenas.  The default is `cudaMalloc` + CUDA IPC.  With
+`multicast=True` (or LBC_MULTICAST=1) the arena comes from torch's symmetric
+memory allocator, which additionally binds the arenas of all ranks to one
+NVLink multicast object: a `multimem.st` through `multicast_ptr + offset`
+writes the same bytes at `offset` of every rank's arena (the NVSwitch
+replicates them), so a broadcast leaves the sending GPU once instead of W - 1
+times.  torch only does the allocation and the handle exchange; every kernel
+that touches the memory is this library's.
+
 The reference has no counterpart (its payloads travel through torch.distributed
 calls, ccdl_comm/communication/torch_transport.py:61-188).
 """
 
 from __future__ import annotations
 
+import os
 import threading
 from typing import Any
 
@@ -44,7 +54,7 @@ class PeerGroup:
 
     def __init__(self, *, rank: int, world_size: int, device: torch.device, nbytes: int, peer_ptrs: list[int],
                  ext: Any, owner: bool, process_group: Any = None, opened: list[int] | None = None,
-                 timeout_ns: int = DEFAULT_TIMEOUT_NS) -> None:
+                 timeout_ns: int = DEFAULT_TIMEOUT_NS, multicast_ptr: int = 0, keepalive: Any = None) -> None:
         if world_size > MAX_RANKS:
             raise CCDLUnavailableError(f"peer groups support at most {MAX_RANKS} ranks")
         self.rank = rank
@@ -53,6 +63,8 @@ class PeerGroup:
         self.nbytes = nbytes
         self.peer_ptrs = list(peer_ptrs)
         self.local_ptr = self.peer_ptrs[rank]
+        self.multicast_ptr = int(multicast_ptr)   # 0: no multicast mapping, broadcasts use W unicast stores
+        self._keepalive = keepalive               # symmetric-memory tensor + handle backing the arena
         self.process_group = process_group
         self.timeout_ns = timeout_ns
         self._ext = ext
@@ -69,8 +81,12 @@ class PeerGroup:
     # -- construction -------------------------------------------------------
     @classmethod
     def create(cls, process_group: Any, nbytes: int, device: torch.device | None = None, *,
-               timeout_ns: int = DEFAULT_TIMEOUT_NS) -> "PeerGroup":
-        """Collective: every rank of `process_group` (one node) calls this."""
+               timeout_ns: int = DEFAULT_TIMEOUT_NS, multicast: bool | None = None) -> "PeerGroup":
+        """Collective: every rank of `process_group` (one node) calls this.
+
+        `multicast=None` reads LBC_MULTICAST (default off); when the multicast
+        arena cannot be set up on every rank, all ranks fall back to CUDA IPC.
+        """
 
         import torch.distributed as dist
 
@@ -79,6 +95,14 @@ class PeerGroup:
         rank = dist.get_rank(process_group)
         world = dist.get_world_size(process_group)
         nbytes = _round_up(max(nbytes, DATA_OFFSET + 4096), 2 << 20)
+        if timeout_ns == DEFAULT_TIMEOUT_NS and os.environ.get("LBC_WAIT_TIMEOUT_MS"):
+            timeout_ns = max(1, int(os.environ["LBC_WAIT_TIMEOUT_MS"])) * 1_000_000
+        if multicast is None:
+            multicast = os.environ.get("LBC_MULTICAST", "0").lower() in ("1", "true", "on", "yes")
+        if multicast and world > 1:
+            made = cls._create_symmetric(process_group, nbytes, device, ext, rank, world, timeout_ns)
+            if made is not None:
+                return made
         with torch.cuda.device(device):
             local = ext.arena_alloc(nbytes)
             handle = ext.ipc_get_handle(local) if world > 1 else b""
@@ -99,6 +123,47 @@ class PeerGroup:
         dist.barrier(group=process_group)
         return cls(rank=rank, world_size=world, device=device, nbytes=nbytes, peer_ptrs=ptrs, ext=ext, owner=True,
                    process_group=process_group, opened=opened, timeout_ns=timeout_ns)
+
+    @classmethod
+    def _create_symmetric(cls, process_group: Any, nbytes: int, device: torch.device, ext: Any, rank: int,
+                          world: int, timeout_ns: int) -> "PeerGroup | None":
+        """Arena from torch's symmetric-memory allocator, with the NVLink multicast mapping.
+
+        Returns None (on every rank alike) when any rank could not get a
+        multicast pointer; the caller then uses the IPC arena.
+        """
+
+        import torch.distributed as dist
+
+        tensor = handle = None
+        error = ""
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            pg = process_group if process_group is not None else dist.group.WORLD
+            with torch.cuda.device(device):
+                tensor = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+                handle = symm_mem.rendezvous(tensor, pg)
+                tensor.zero_()
+                torch.cuda.synchronize(device)
+            ok = int(handle.multicast_ptr) != 0 and len(handle.buffer_ptrs) == world
+            if not ok:
+                error = "no multicast pointer"
+        except Exception as exc:  # noqa: BLE001 - any failure means "use the IPC arena"
+            ok = False
+            error = f"{type(exc).__name__}: {exc}"
+        votes: list[Any] = [None] * world
+        dist.all_gather_object(votes, bool(ok), group=process_group)
+        if not all(votes):
+            if rank == 0 and os.environ.get("LBC_DEBUG"):
+                print(f"[lowbit_comm_b200] multicast arena unavailable ({error or 'a peer failed'}); using CUDA IPC")
+            del tensor, handle
+            return None
+        dist.barrier(group=process_group)
+        return cls(rank=rank, world_size=world, device=device, nbytes=nbytes,
+                   peer_ptrs=[int(p) for p in handle.buffer_ptrs], ext=ext, owner=False,
+                   process_group=process_group, opened=[], timeout_ns=timeout_ns,
+                   multicast_ptr=int(handle.multicast_ptr), keepalive=(tensor, handle))
 
     @classmethod
     def loopback(cls, world_size: int, nbytes: int, device: torch.device | None = None, *,
@@ -144,6 +209,11 @@ class PeerGroup:
     # -- addresses ----------------------------------------------------------
     def addr(self, rank: int, offset: int) -> int:
         return self.peer_ptrs[rank] + offset
+
+    def multicast_addr(self, offset: int) -> int:
+        """Multicast alias of `offset` in every rank's arena (0 when there is no multicast mapping)."""
+
+        return self.multicast_ptr + offset if self.multicast_ptr else 0
 
     def flags_addr(self, rank: int, channel: int, phase: int) -> int:
         return self.peer_ptrs[rank] + ((channel * NUM_PHASES + phase) * MAX_RANKS) * 4
@@ -216,6 +286,9 @@ class PeerGroup:
         self._ext.status_free(self.status_host)
         if self._owner and free_arena and self.process_group is not None:
             self._ext.arena_free(self.local_ptr)
+        # Every collective ends with a wait for all ranks' last stores, so once this rank's stream has
+        # drained nobody is still writing into its arena; dropping the symmetric tensor unmaps it.
+        self._keepalive = None
 
     @staticmethod
     def close_loopback(groups: list["PeerGroup"]) -> None:

@@ -117,6 +117,29 @@ def ddp_case(rank: int, world: int) -> None:
     assert state["feedback"]["residuals"], "error-feedback residuals must be checkpointable"
 
 
+def _exit_barrier(world: int, limit_s: float = 120.0) -> None:
+    """No rank leaves (and unmaps its arena) before every rank has drained its GPU work: with a
+    multicast arena a store that reaches an unmapped replica would fault the other GPUs."""
+
+    import time
+
+    import torch
+    import torch.distributed as dist
+
+    try:
+        torch.cuda.synchronize()
+    except Exception:  # noqa: BLE001
+        pass
+    try:
+        store = dist.distributed_c10d._get_default_store()
+        store.add("lbc_exit_barrier", 1)
+        t0 = time.time()
+        while int(store.add("lbc_exit_barrier", 0)) < world and time.time() - t0 < limit_s:
+            time.sleep(0.05)
+    except Exception:  # noqa: BLE001
+        time.sleep(5.0)
+
+
 def main() -> None:
     import torch
     import torch.distributed as dist
@@ -127,12 +150,17 @@ def main() -> None:
     dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
     try:
         {"collectives": collectives_case, "ddp": ddp_case}[case](rank, world)
-        dist.barrier()
+        _exit_barrier(world)
         if rank == 0:
-            print(f"MULTIRANK-OK {case} world={world}")
+            from lowbit_comm_b200.parallel.communicator import get_communicator
+
+            group = get_communicator(None).peer_group
+            mc = bool(group is not None and group.multicast_ptr)
+            print(f"MULTIRANK-OK {case} world={world} multicast={int(mc)}")
     except BaseException:
         traceback.print_exc()
         sys.stdout.flush()
+        _exit_barrier(world)
         os._exit(1)
     finally:
         try:

@@ -84,6 +84,38 @@ def test_all_reduce_matches_oracle(ext, world, dtype, bit, group, stages):
         PeerGroup.close_loopback(groups)
 
 
+@pytest.mark.parametrize("push_variant,reduce_bulk,push_blocks",
+                         [(0, False, -1), (0, True, 0), (1, False, 0), (1, True, -1), (2, False, 3), (2, True, 0)])
+@pytest.mark.parametrize("dtype,bit,group", [("bf16", 8, 64), ("fp32", 4, 32)])
+def test_every_push_variant_writes_the_same_bytes(ext, push_variant, reduce_bulk, push_blocks, dtype, bit, group):
+    """Classic, shard-interleaved and bulk-store pushes (and both broadcast forms of the reduce
+    stage, with and without a grid cap) must be indistinguishable to the consumer."""
+
+    cfg = CompressionConfig(bit=bit, group_size=group, allow_experimental=True)
+    world, max_numel = 4, 300_000
+    groups, wss = _make(world, dtype, cfg, max_numel)
+    ext.set_push_variant(push_variant, reduce_bulk, push_blocks)
+    try:
+        for step, n in enumerate((world * group * 8, 70_001, max_numel)):
+            xs = _inputs(world, n, dtype, seed=step)
+            rs = _inputs(world, n, dtype, seed=50 + step)
+            for stages, expected in ((1, _expected_one_stage), (2, _expected_two_stage)):
+                dev_x = [x.cuda() for x in xs]
+                dev_r = [r.cuda() for r in rs]
+                run_loopback(wss, "all_reduce", [(dev_x[r],) for r in range(world)],
+                             [{"residual": dev_r[r]} for r in range(world)], stages=stages)
+                want = expected(xs, rs, cfg, dtype)
+                for r in range(world):
+                    assert torch.equal(dev_x[r].cpu().view(torch.uint8), want[0].view(torch.uint8)), (n, stages, r)
+                    assert torch.equal(dev_r[r].cpu().view(torch.uint8), want[1][r].view(torch.uint8)), (n, stages, r)
+        torch.cuda.synchronize()
+        for g in groups:
+            g.check_status()
+    finally:
+        ext.set_push_variant(1, True, 0)
+        PeerGroup.close_loopback(groups)
+
+
 @pytest.mark.parametrize("world", (2, 4, 8))
 def test_reduce_scatter_and_all_gather(ext, world):
     cfg = CompressionConfig()
