@@ -4,6 +4,11 @@ int8 group-64 hook (both error-feedback rules), same seeds, same synthetic data.
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port 29531 benchmarks/loss_curve.py [--model gpt2-small --steps 60 --batch 8]
 
+Two controls put the gap in context: `nccl_bf16_noise` multiplies every gradient element by
+(1 + 0.017 * N(0, 1)) before the NCCL all-reduce (the relative error of int8 group-64 payloads,
+without its structure), and `reference_hook` registers the unmodified reference's own hook
+(`--with-reference`, needs baseline/_ref) on the same model.
+
 The data is learnable (token t+1 = (a * token t + b) mod V with 10 % noise), so the loss falls
 during the run and a broken gradient path shows up as a diverging curve.  The reference compares
 20-50-step synthetic training losses against DDP the same way
@@ -41,6 +46,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=60)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--lr", type=float, default=6e-4)
+    ap.add_argument("--with-reference", action="store_true")
     ap.add_argument("--out", default="gpurun_out/loss_curve.json")
     args = ap.parse_args()
 
@@ -68,7 +74,23 @@ def main() -> None:
         model = GPT2(mcfg).to(device=dev, dtype=torch.bfloat16)
         ddp = DDP(model, device_ids=[local], bucket_cap_mb=25, gradient_as_bucket_view=True)
         hook = None
-        if arm != "nccl_bf16":
+        if arm == "nccl_bf16_noise":
+            def noisy(state, bucket):
+                buf = bucket.buffer()
+                buf.mul_(1 + 0.017 * torch.randn_like(buf))
+                fut = dist.all_reduce(buf, op=dist.ReduceOp.AVG, async_op=True).get_future()
+                return fut.then(lambda f: f.value()[0])
+
+            ddp.register_comm_hook(state=None, hook=noisy)
+        elif arm == "reference_hook":
+            from ccdl_comm.communication import create_ddp_comm_hook as ref_factory
+            from ccdl_comm.config import CompressionConfig as RefConfig
+
+            rcfg = RefConfig(bit=8, group_size=64, topk=0, error_feedback=True, target="ddp_gradient_bucket")
+            ddp.register_comm_hook(state=None, hook=ref_factory(rcfg, dtype="auto", strategy="all_gather",
+                                                                reduce="mean", async_gather=True,
+                                                                async_error_feedback=True))
+        elif arm != "nccl_bf16":
             cfg = CompressionConfig(bit=8, group_size=64, topk=0, error_feedback=True, target="ddp_gradient_bucket")
             hook = create_ddp_comm_hook(cfg, strategy="auto", reduce="mean", ef_mode=arm.split(":")[1])
             ddp.register_comm_hook(state=None, hook=hook)
@@ -87,8 +109,19 @@ def main() -> None:
         torch.cuda.empty_cache()
         return losses
 
+    arms = ["nccl_bf16", "nccl_bf16_noise", "int8_g64:reference", "int8_g64:local"]
+    if args.with_reference:
+        try:
+            sys.path.insert(0, os.path.join(ROOT, "baseline"))
+            import reference_env
+
+            reference_env.activate(need_cuda_extension=True)
+            arms.append("reference_hook")
+        except Exception as exc:  # noqa: BLE001
+            if rank == 0:
+                print(json.dumps({"arm": "reference_hook", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}))
     curves = {}
-    for arm in ("nccl_bf16", "int8_g64:reference", "int8_g64:local"):
+    for arm in arms:
         curves[arm] = run(arm)
         if rank == 0:
             print(json.dumps({"arm": arm, "world": world, "model": args.model,

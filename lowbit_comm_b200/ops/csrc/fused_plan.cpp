@@ -84,7 +84,13 @@ class FusedAllReducePlan {
     }
 
     // Base of the NVLink multicast mapping of the arenas (0 = none): broadcasts then leave this GPU once.
-    void set_multicast(uintptr_t mc_base) { mc_base_ = mc_base; }
+    // The requantize-and-broadcast stage of the two-stage path uses it only on request: measured on
+    // 8 GPUs its multicast form was slower above 64 MiB (the replica for the sender itself also
+    // arrives over NVLink, so every GPU receives W/W instead of (W-1)/W of the payload).
+    void set_multicast(uintptr_t mc_base, bool in_reduce_stage) {
+        mc_base_ = mc_base;
+        mc_reduce_ = in_reduce_stage;
+    }
 
     // Enqueues the collective on `stream`; returns the number of kernels launched.
     int all_reduce(uintptr_t x, uintptr_t out, uintptr_t residual, int64_t numel, int stages, double scale,
@@ -221,7 +227,7 @@ class FusedAllReducePlan {
         k2.layout_groups = shard_groups;
         k2.num_dst = world_;
         for (int d = 0; d < world_; ++d) k2.dst[d] = reinterpret_cast<uint8_t*>(peers_[d] + r.ag);
-        if (mc_base_ != 0) k2.mc_dst = reinterpret_cast<uint8_t*>(mc_base_ + r.ag);
+        if (mc_base_ != 0 && mc_reduce_) k2.mc_dst = reinterpret_cast<uint8_t*>(mc_base_ + r.ag);
         k2.dst_layout_groups = shard_groups * world_;
         k2.dst_group_offset = rank_ * shard_groups;
         fill_signal(k2.signal, r.channel, kPhaseAG, epoch);
@@ -294,6 +300,7 @@ class FusedAllReducePlan {
     int max_blocks_;
     int64_t max_numel_;
     uintptr_t mc_base_ = 0;
+    bool mc_reduce_ = false;
     int64_t group_bytes_ = 66, elem_bytes_ = 2;
     int64_t min_chunk_bytes_ = int64_t(8) << 20;
     int max_chunks_ = 1;
@@ -314,7 +321,7 @@ void bind_fused_plan(py::module_& m) {
              py::arg("gather_bytes"), py::arg("channels"), py::arg("counter_offset"), py::arg("timeout_ns"),
              py::arg("status_device"), py::arg("max_blocks"), py::arg("max_numel"))
         .def("set_chunking", &FusedAllReducePlan::set_chunking, py::arg("min_chunk_bytes"), py::arg("max_chunks"))
-        .def("set_multicast", &FusedAllReducePlan::set_multicast, py::arg("mc_base"))
+        .def("set_multicast", &FusedAllReducePlan::set_multicast, py::arg("mc_base"), py::arg("in_reduce_stage") = false)
         .def("all_reduce", &FusedAllReducePlan::all_reduce, py::arg("x"), py::arg("out"), py::arg("residual"),
              py::arg("numel"), py::arg("stages"), py::arg("scale"), py::arg("update_residual"), py::arg("ef_local"),
              py::arg("epoch"), py::arg("stream"));

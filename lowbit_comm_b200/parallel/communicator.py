@@ -217,7 +217,9 @@ class Communicator:
     def _torch_all_reduce(self, tensor, config, op, stages, name, out, residual, update_residual):
         torch = import_module("torch")
         prepared = tensor if residual is None else (tensor.float() + residual.float()).to(tensor.dtype)
-        stages = stages or (1 if self.world_size <= 2 else 2)
+        from .fused import default_stages
+
+        stages = stages or default_stages(self.world_size, tensor.numel() * tensor.element_size())
         shape = tuple(tensor.shape)
         gather = make_torch_all_gather(group=self.process_group)
         if stages == 1:

@@ -32,6 +32,7 @@ ccdl_comm/collectives/all_reduce.py:158-271).
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -100,6 +101,20 @@ def geometry(numel: int, world_size: int, dtype: str, config: CompressionConfig)
                          dtype_bytes(dtype), plan.shard_groups, plan.num_groups)
 
 
+def default_stages(world_size: int, nbytes: int, multicast: bool = False) -> int:
+    """One-stage (every rank reduces W payloads) or two-stage (scatter, reduce, gather) all-reduce.
+
+    Measured on 8 x B200 (bf16, int8 group 64): one stage wins while launches and signal round
+    trips dominate, up to 4 MiB with unicast stores and up to 8 MiB when the broadcast leaves
+    through the NVLink multicast mapping; above that the (W - 1) payloads per rank lose to the
+    2 (W - 1) / W of the two-stage path.  Two ranks move the same bytes either way.
+    """
+
+    if world_size <= 2:
+        return 1
+    return 1 if nbytes <= ((8 << 20) if multicast else (4 << 20)) else 2
+
+
 class FusedWorkspace:
     """Symmetric regions + channel for tensors of up to `max_numel` elements."""
 
@@ -137,6 +152,9 @@ class FusedWorkspace:
         # (persistent grids of neighbouring chunks do not interleave; one-tile blocks pay a system-scope
         # fence each).  `set_chunking` turns it on for experiments.
         self.min_chunk_bytes, self.max_chunks = 16 << 20, 1
+        # multimem stores serve the one-stage broadcast; the two-stage broadcast keeps unicast stores (faster
+        # above 64 MiB on 8 GPUs) unless this is set before the first collective
+        self.multicast_in_reduce_stage = os.environ.get("LBC_MULTICAST_REDUCE", "0") == "1"
         self._build_native()
 
     def _build_native(self) -> None:
@@ -151,7 +169,7 @@ class FusedWorkspace:
             group.world_size * self.gather_stride, list(self.channels), COUNTER_OFFSET, group.timeout_ns,
             group.status_device, self.max_blocks, self.max_numel)
         self._native.set_chunking(self.min_chunk_bytes, self.max_chunks)
-        self._native.set_multicast(group.multicast_ptr)
+        self._native.set_multicast(group.multicast_ptr, self.multicast_in_reduce_stage)
 
     def set_chunking(self, min_chunk_bytes: int, max_chunks: int = MAX_CHUNKS) -> None:
         """Tensors of at least 2 x `min_chunk_bytes` are pipelined in up to `max_chunks` chunks."""
@@ -218,7 +236,8 @@ class FusedWorkspace:
         self.ext.reduce(src, geo.shard_groups, 0, False, geo.shard_valid_numel(me), self._code, geo.group_size,
                         self.config.bit, scale, out, False, None, None, dst, geo.total_groups,
                         me * geo.shard_groups, signal, g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch),
-                        self.max_blocks, g.multicast_addr(self.ag_off) if broadcast else 0)
+                        self.max_blocks,
+                        g.multicast_addr(self.ag_off) if broadcast and self.multicast_in_reduce_stage else 0)
         self.launches += 1
 
     def _k3_gather(self, geo: FusedGeometry, epoch: int, out, prepared, residual_out):
@@ -253,7 +272,8 @@ class FusedWorkspace:
         """
 
         if stages is None:
-            stages = 1 if self.group.world_size <= 2 else 2
+            stages = default_stages(self.group.world_size, x.numel() * x.element_size(),
+                                    bool(self.group.multicast_ptr))
         scale = self._scale(op)
         if self._native is not None and self.phase_timer is None:
             # hot path: one binding crossing; geometry is recomputed natively

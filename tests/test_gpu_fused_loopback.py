@@ -116,6 +116,34 @@ def test_every_push_variant_writes_the_same_bytes(ext, push_variant, reduce_bulk
         PeerGroup.close_loopback(groups)
 
 
+@pytest.mark.parametrize("world,stages", [(2, 1), (4, 2), (8, 2)])
+@pytest.mark.parametrize("dtype", ("bf16", "fp32"))
+def test_local_error_feedback_mode(ext, world, stages, dtype):
+    """ef_mode="local": the residual becomes this rank's own quantization error, over several steps."""
+
+    cfg = CompressionConfig()
+    n = 64 * 777 + 5
+    groups, wss = _make(world, dtype, cfg, n)
+    try:
+        residual_ref = [torch.zeros(n, dtype=DT[dtype]) for _ in range(world)]
+        dev_r = [r.cuda() for r in residual_ref]
+        for step in range(3):
+            xs = _inputs(world, n, dtype, seed=300 + step)
+            dev_x = [x.cuda() for x in xs]
+            run_loopback(wss, "all_reduce", [(dev_x[r],) for r in range(world)],
+                         [{"residual": dev_r[r], "ef_mode": "local"} for r in range(world)], stages=stages)
+            prepared = [oracle.prepare(x, r) for x, r in zip(xs, residual_ref)]
+            payloads = [oracle.encode(p, cfg) for p in prepared]
+            y, _ = oracle.reduce_mean(payloads, n, cfg, dtype)
+            want = y if stages == 1 else oracle.decode(oracle.encode(y, cfg), n, cfg, dtype)
+            residual_ref = [oracle.local_error(p, q, cfg) for p, q in zip(prepared, payloads)]
+            for r in range(world):
+                assert torch.equal(dev_x[r].cpu().view(torch.uint8), want.view(torch.uint8)), (step, r)
+                assert torch.equal(dev_r[r].cpu().view(torch.uint8), residual_ref[r].view(torch.uint8)), (step, r)
+    finally:
+        PeerGroup.close_loopback(groups)
+
+
 @pytest.mark.parametrize("world", (2, 4, 8))
 def test_reduce_scatter_and_all_gather(ext, world):
     cfg = CompressionConfig()
