@@ -191,7 +191,7 @@ def main() -> None:
             rows.append({"impl": f"ours_{stages}stage{tag}", "mib": mib, "world": world, "ms": t,
                          "algbw_gbs": nbytes / (t * 1e-3) / 1e9, "rel_l2": rel, **roof,
                          "roofline_frac": roof["roofline_us"] / (t * 1e3), "peak_kind": peak_kind,
-                         "phases_ms": phases, "multicast": multicast_on})
+                         "phases_ms": phases, "multicast": multicast_on, "chunk_mib": args.chunk_mib})
         ext.set_push_variant(1, True, 0)
         nccl_buf = x.clone()
 

@@ -832,8 +832,9 @@ cudaError_t lbc_wait_signal(const LbcWait* wait, const LbcSignal* signal, cudaSt
     lbc::WaitSignalArgs a{};
     if (wait != nullptr) a.wait = *wait;
     if (signal != nullptr) a.signal = *signal;
-    if (a.wait.count < 0 || a.wait.count > lbc::kThreads) return cudaErrorInvalidValue;
-    lbc::wait_signal_kernel<<<1, lbc::kThreads, 0, stream>>>(a);
+    if (a.wait.count < 0 || a.wait.count > 32) return cudaErrorInvalidValue;
+    // one warp: it fits beside the resident blocks of a persistent kernel of another stream
+    lbc::wait_signal_kernel<<<1, 32, 0, stream>>>(a);
     return cudaGetLastError();
 }
 

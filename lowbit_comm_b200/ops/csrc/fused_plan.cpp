@@ -14,6 +14,12 @@
 // waiting kernel does the (bounded) waiting, so no stream can fill the GPU with
 // spinning blocks.  The side streams are joined back into the caller's stream at
 // the end, which keeps the region-reuse argument of the single-stream version.
+//
+// A variant that staged the payload locally and let the copy engines deliver it (peer-to-peer
+// cudaMemcpyAsync on a copy stream, flags raised by a one-warp kernel behind the copies) was
+// measured on 2 x B200 and dropped: with both directions busy the engines moved the payload at
+// about 420 GB/s, slower than the kernels' own peer stores (about 560 GB/s), e.g. 256 MiB in
+// 0.60-0.67 ms against 0.45 ms.
 #include "fused_plan.h"
 
 #include <ATen/cuda/CUDAContext.h>
@@ -249,6 +255,7 @@ class FusedAllReducePlan {
         check(lbc_reduce(&k3, s_gather), "reduce(gather)");
         return 5;
     }
+
 
     // A one-block kernel does the (bounded) waiting, so that a rank that is ahead of its peers
     // parks 256 threads instead of filling every SM with spinning blocks while its own backward

@@ -37,11 +37,22 @@ def collectives_case(rank: int, world: int) -> None:
         two = oracle.decode(oracle.encode(y, cfg), n, cfg, name)
         for strategy, want in (("all_gather", y), ("reduce_scatter", two)):
             mine = xs[rank].cuda()
+            ws = comm.workspace(mine, cfg, name)
             if n > 50_000:  # small chunks: the pipelined multi-stream launcher runs with up to 8 chunks
-                comm.workspace(mine, cfg, name).set_chunking(1 << 17, 8)
+                ws.set_chunking(1 << 17, 8)
             got = compressed_all_reduce(mine, config=cfg, op="mean", strategy=strategy)
             torch.cuda.synchronize()
             assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), (strategy, n, rank)
+            # with error feedback (residual starts at zero, so prepared == input)
+            residual = torch.zeros_like(mine)
+            got = ws.all_reduce(xs[rank].cuda(), residual=residual, op="mean",
+                                stages=1 if strategy == "all_gather" else 2)
+            torch.cuda.synchronize()
+            assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), (strategy, n, "ef")
+            reduced32 = (oracle.reduce_mean(payloads, n, cfg, name)[1] if strategy == "all_gather"
+                         else oracle.decode_fp32(oracle.encode(y, cfg), n, cfg, name))
+            want_res = oracle.residual_update(xs[rank], reduced32)
+            assert torch.equal(residual.cpu().view(torch.uint8), want_res.view(torch.uint8)), (strategy, n, "residual")
         work = compressed_all_reduce(xs[rank].cuda(), config=cfg, strategy="reduce_scatter", async_op=True)
         got = work.wait()
         torch.cuda.current_stream().synchronize()
