@@ -63,6 +63,8 @@ def main() -> None:
     ap.add_argument("--chunk-mib", type=float, default=None, help="pipeline chunk size (0 = no pipelining)")
     ap.add_argument("--variants", action="store_true", help="time every push/reduce kernel variant")
     ap.add_argument("--phases", action="store_true", help="also time K1/K2/K3 separately (Python launch path)")
+    ap.add_argument("--gather", choices=("pull", "push"), default=None,
+                    help="two-stage gather: peer loads by the decode kernel (pull) or peer stores by the reduce kernel")
     ap.add_argument("--multicast", action="store_true",
                     help="arenas from the symmetric-memory allocator: broadcasts use multimem stores")
     ap.add_argument("--out", default="gpurun_out/allreduce_sweep.json")
@@ -95,6 +97,8 @@ def main() -> None:
         os.environ["LBC_MULTICAST"] = "1"
     comm = Communicator(None, arena_bytes=arena)
     big = comm.workspace(torch.empty(max_numel, dtype=torch.bfloat16, device=dev), cfg, "bf16")  # largest first
+    if args.gather is not None:
+        big.set_gather_mode(args.gather)
     if args.chunk_mib is not None:
         big.set_chunking(int(max(args.chunk_mib, 1e-3) * (1 << 20)), 1 if args.chunk_mib == 0 else 8)
 
@@ -191,7 +195,8 @@ def main() -> None:
             rows.append({"impl": f"ours_{stages}stage{tag}", "mib": mib, "world": world, "ms": t,
                          "algbw_gbs": nbytes / (t * 1e-3) / 1e9, "rel_l2": rel, **roof,
                          "roofline_frac": roof["roofline_us"] / (t * 1e3), "peak_kind": peak_kind,
-                         "phases_ms": phases, "multicast": multicast_on, "chunk_mib": args.chunk_mib})
+                         "phases_ms": phases, "multicast": multicast_on, "chunk_mib": args.chunk_mib,
+                         "gather": "pull" if big.pull_gather else "push"})
         ext.set_push_variant(1, True, 0)
         nccl_buf = x.clone()
 

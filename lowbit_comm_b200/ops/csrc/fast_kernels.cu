@@ -268,7 +268,7 @@ struct PushTile {
 };
 
 template <typename T, int G, int BIT, bool kBulk>
-__global__ void __launch_bounds__(kThreads, 3) quant_push_tiled_kernel(const LbcQuantPush p) {
+__global__ void __launch_bounds__(kThreads, kBulk ? 3 : 4) quant_push_tiled_kernel(const LbcQuantPush p) {
     constexpr int lanes = G / kElemsPerThread;
     constexpr int VB = G * BIT / 8;
     constexpr int MB = sizeof(T);
@@ -292,7 +292,10 @@ __global__ void __launch_bounds__(kThreads, 3) quant_push_tiled_kernel(const Lbc
     const int64_t num_tiles = tiles_per_shard * shards;
     const int rot = p.signal.my_slot;   // this rank's index: staggers the senders
 
-    __shared__ __align__(128) PushTile tile;
+    // the bulk form stages whole tiles for the copy engine; the per-thread form only parks scales per warp
+    __shared__ __align__(128) unsigned char tile_raw[kBulk ? sizeof(PushTile) : 16];
+    PushTile& tile = *reinterpret_cast<PushTile*>(tile_raw);
+    __shared__ __align__(16) ScaleStage stage;
     int buf = 0;
     for (int64_t vt = blockIdx.x; vt < num_tiles; vt += gridDim.x, buf ^= 1) {
         const int shard = int((vt + rot) % shards);
@@ -384,25 +387,25 @@ __global__ void __launch_bounds__(kThreads, 3) quant_push_tiled_kernel(const Lbc
                     }
                 }
             }
-            __syncthreads();   // the previous tile's scale vectors have been read
-            if (lane == 0) {
-                if constexpr (sizeof(T) == 2)
-                    *reinterpret_cast<uint16_t*>(tile.scales[0] + gl * MB) = Src<T>::down(stored);
-                else
-                    *reinterpret_cast<float*>(tile.scales[0] + gl * MB) = stored;
-            }
-            __syncthreads();
-            if (int64_t(threadIdx.x) * 16 < copy_groups * MB) {
-                const uint4 sv = *reinterpret_cast<const uint4*>(tile.scales[0] + threadIdx.x * 16);
+            // scales: every warp gathers the scales of its own groups into 16-byte vectors
+            const int wlane = threadIdx.x & 31;
+            if (lane == 0) park_scale<T>(stage, wlane / lanes, stored);   // dead groups park a zero
+            __syncwarp();
+            constexpr int groups_per_vec = 16 / MB;
+            constexpr int vecs_per_warp = (32 / lanes) / groups_per_vec;
+            const int gvl = (int(threadIdx.x) >> 5) * (32 / lanes) + wlane * groups_per_vec;   // in-tile group
+            if (wlane < vecs_per_warp && gvl < copy_groups) {
+                const uint4 sv = *reinterpret_cast<const uint4*>(stage.bytes[threadIdx.x >> 5] + wlane * 16);
+                const int64_t off = p.layout_groups * VB + (g_dst + gvl) * MB;
                 if (scatter) {
-                    st16(p.dst[shard] + p.layout_groups * VB + g_dst * MB + threadIdx.x * 16, sv);
+                    st16(p.dst[shard] + off, sv);
                 } else if (p.mc_dst != nullptr) {
-                    multimem_st16(p.mc_dst + p.layout_groups * VB + g_dst * MB + threadIdx.x * 16, sv);
+                    multimem_st16(p.mc_dst + off, sv);
                 } else {
-                    for (int d = 0; d < p.num_dst; ++d)
-                        st16(p.dst[(d + rot) % p.num_dst] + p.layout_groups * VB + g_dst * MB + threadIdx.x * 16, sv);
+                    for (int d = 0; d < p.num_dst; ++d) st16(p.dst[(d + rot) % p.num_dst] + off, sv);
                 }
             }
+            __syncwarp();
         }
     }
     if (kBulk && threadIdx.x == 0) bulk_wait_all();
@@ -456,10 +459,21 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
 #pragma unroll
         for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
         if (live) {
-            const int64_t voff = gs * rec + lane * CB;
-            const int64_t soff = p.compact ? gs * rec + VB : p.layout_groups * VB + gs * MB;
+            int64_t voff = gs * rec + lane * CB;
+            int64_t soff = p.compact ? gs * rec + VB : p.layout_groups * VB + gs * MB;
+            int first_src = 0, last_src = R;
+            if (p.src_shard_groups > 0) {
+                // gather mode: the group lives in exactly one source, the owner's reduced shard,
+                // which may be a peer's memory (the payload then crosses NVLink as this kernel's loads)
+                const int64_t owner = gs / p.src_shard_groups;
+                const int64_t gl = gs - owner * p.src_shard_groups;
+                first_src = int(owner);
+                last_src = first_src + 1;
+                voff = gl * VB + lane * CB;
+                soff = p.src_shard_groups * VB + gl * MB;
+            }
 #pragma unroll 4
-            for (int r = 0; r < R; ++r) {
+            for (int r = first_src; r < last_src; ++r) {
                 const uint8_t* base = p.src[r];
                 const uint4 codes = load_codes(base + voff, CB);
                 const float s = load_scale<T>(base + soff);
@@ -761,6 +775,11 @@ cudaError_t lbc_reduce(const LbcReduce* p, cudaStream_t stream) {
     if (p->signal.num_remote < 0 || p->signal.num_remote > LBC_MAX_RANKS) return cudaErrorInvalidValue;
     if (p->wait.count < 0 || p->wait.count > lbc::kThreads) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(p->mc_dst) & 15) != 0) return cudaErrorInvalidValue;
+    if (p->src_shard_groups < 0 || (p->src_shard_groups > 0 && p->compact)) return cudaErrorInvalidValue;
+    if (p->src_shard_groups > 0 && p->numel > 0) {
+        const int64_t groups = (p->numel + p->group_size - 1) / p->group_size;
+        if ((p->group_offset + groups - 1) / p->src_shard_groups >= p->num_src) return cudaErrorInvalidValue;
+    }
     return lbc::dispatch<lbc::ReduceLauncher>(p, stream);
 }
 

@@ -98,6 +98,11 @@ class FusedAllReducePlan {
         mc_reduce_ = in_reduce_stage;
     }
 
+    // Gather stage by peer loads (default): the decode kernel reads every rank's reduced shard from
+    // that rank's memory, so the second NVLink crossing hides behind decode and error feedback.
+    // Off: the reduce stage stores its shard into every rank's gather region.
+    void set_pull_gather(bool on) { pull_gather_ = on; }
+
     // Enqueues the collective on `stream`; returns the number of kernels launched.
     int all_reduce(uintptr_t x, uintptr_t out, uintptr_t residual, int64_t numel, int stages, double scale,
                    bool update_residual, bool ef_local, unsigned int epoch, uintptr_t stream_ptr) {
@@ -231,20 +236,36 @@ class FusedAllReducePlan {
         for (int s = 0; s < world_; ++s)
             k2.src[s] = reinterpret_cast<const uint8_t*>(peers_[rank_] + r.rs + s * r.shard_stride);
         k2.layout_groups = shard_groups;
-        k2.num_dst = world_;
-        for (int d = 0; d < world_; ++d) k2.dst[d] = reinterpret_cast<uint8_t*>(peers_[d] + r.ag);
-        if (mc_base_ != 0 && mc_reduce_) k2.mc_dst = reinterpret_cast<uint8_t*>(mc_base_ + r.ag);
-        k2.dst_layout_groups = shard_groups * world_;
-        k2.dst_group_offset = rank_ * shard_groups;
+        if (pull_gather_) {
+            // the reduced shard stays in this rank's own gather region as a self-contained payload;
+            // peers fetch it from there with the loads of their decode kernel
+            k2.num_dst = 1;
+            k2.dst[0] = reinterpret_cast<uint8_t*>(peers_[rank_] + r.ag);
+            k2.dst_layout_groups = shard_groups;
+            k2.dst_group_offset = 0;
+        } else {
+            k2.num_dst = world_;
+            for (int d = 0; d < world_; ++d) k2.dst[d] = reinterpret_cast<uint8_t*>(peers_[d] + r.ag);
+            if (mc_base_ != 0 && mc_reduce_) k2.mc_dst = reinterpret_cast<uint8_t*>(mc_base_ + r.ag);
+            k2.dst_layout_groups = shard_groups * world_;
+            k2.dst_group_offset = rank_ * shard_groups;
+        }
         fill_signal(k2.signal, r.channel, kPhaseAG, epoch);
         fill_wait(k2.wait, r.channel, kPhaseRS, epoch);
         gate(k2.wait, s_reduce);
         check(lbc_reduce(&k2, s_reduce), "reduce(shard)");
 
         LbcReduce k3 = base_reduce(numel, 1.0);
-        k3.num_src = 1;
-        k3.src[0] = reinterpret_cast<const uint8_t*>(peers_[rank_] + r.ag);
-        k3.layout_groups = shard_groups * world_;
+        if (pull_gather_) {
+            k3.num_src = world_;
+            for (int s = 0; s < world_; ++s) k3.src[s] = reinterpret_cast<const uint8_t*>(peers_[s] + r.ag);
+            k3.src_shard_groups = shard_groups;
+            k3.layout_groups = shard_groups;
+        } else {
+            k3.num_src = 1;
+            k3.src[0] = reinterpret_cast<const uint8_t*>(peers_[rank_] + r.ag);
+            k3.layout_groups = shard_groups * world_;
+        }
         k3.out = reinterpret_cast<void*>(out);
         if (want_ref) {
             k3.prepared = reinterpret_cast<const void*>(residual);
@@ -308,6 +329,7 @@ class FusedAllReducePlan {
     int64_t max_numel_;
     uintptr_t mc_base_ = 0;
     bool mc_reduce_ = false;
+    bool pull_gather_ = true;
     int64_t group_bytes_ = 66, elem_bytes_ = 2;
     int64_t min_chunk_bytes_ = int64_t(8) << 20;
     int max_chunks_ = 1;
@@ -329,6 +351,7 @@ void bind_fused_plan(py::module_& m) {
              py::arg("status_device"), py::arg("max_blocks"), py::arg("max_numel"))
         .def("set_chunking", &FusedAllReducePlan::set_chunking, py::arg("min_chunk_bytes"), py::arg("max_chunks"))
         .def("set_multicast", &FusedAllReducePlan::set_multicast, py::arg("mc_base"), py::arg("in_reduce_stage") = false)
+        .def("set_pull_gather", &FusedAllReducePlan::set_pull_gather, py::arg("on"))
         .def("all_reduce", &FusedAllReducePlan::all_reduce, py::arg("x"), py::arg("out"), py::arg("residual"),
              py::arg("numel"), py::arg("stages"), py::arg("scale"), py::arg("update_residual"), py::arg("ef_local"),
              py::arg("epoch"), py::arg("stream"));

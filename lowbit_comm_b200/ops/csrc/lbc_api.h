@@ -71,6 +71,8 @@ typedef struct {
     int64_t layout_groups;     // groups in every source layout
     int64_t group_offset;      // first group to read inside the source layout
     int compact;               // sources use the per-group record layout
+    int64_t src_shard_groups;  // > 0: gather mode, group g is read from src[g / src_shard_groups] only (every
+                               // source is a planar payload of src_shard_groups groups: a peer's reduced shard)
     int64_t numel;             // elements to produce
     float scale;               // applied to the fp32 sum (1/W for a mean)
     void* out;                 // optional T[numel]

@@ -155,6 +155,11 @@ class FusedWorkspace:
         # multimem stores serve the one-stage broadcast; the two-stage broadcast keeps unicast stores (faster
         # above 64 MiB on 8 GPUs) unless this is set before the first collective
         self.multicast_in_reduce_stage = os.environ.get("LBC_MULTICAST_REDUCE", "0") == "1"
+        # Gather stage of the two-stage path: True = every rank's decode kernel loads the reduced shards
+        # from their owners' memory (the NVLink crossing hides behind decode + error feedback; measured
+        # 600 GB/s per GPU with the local work fully overlapped); False = the reduce stage stores its shard
+        # into every rank's gather region.
+        self.pull_gather = os.environ.get("LBC_GATHER", "pull") != "push"
         self._build_native()
 
     def _build_native(self) -> None:
@@ -170,6 +175,16 @@ class FusedWorkspace:
             group.status_device, self.max_blocks, self.max_numel)
         self._native.set_chunking(self.min_chunk_bytes, self.max_chunks)
         self._native.set_multicast(group.multicast_ptr, self.multicast_in_reduce_stage)
+        self._native.set_pull_gather(self.pull_gather)
+
+    def set_gather_mode(self, mode: str) -> None:
+        """"pull" (default) or "push": how the reduced shards reach the other ranks (see `pull_gather`)."""
+
+        if mode not in ("pull", "push"):
+            raise ValueError("gather mode must be 'pull' or 'push'")
+        self.pull_gather = mode == "pull"
+        if self._native is not None:
+            self._native.set_pull_gather(self.pull_gather)
 
     def set_chunking(self, min_chunk_bytes: int, max_chunks: int = MAX_CHUNKS) -> None:
         """Tensors of at least 2 x `min_chunk_bytes` are pipelined in up to `max_chunks` chunks."""
@@ -229,24 +244,33 @@ class FusedWorkspace:
     def _k2_reduce(self, geo: FusedGeometry, epoch: int, parity: int, scale: float, out, broadcast: bool):
         g, me = self.group, self.group.rank
         src = [g.local_ptr + self.rs_off[parity] + r * self.shard_stride for r in range(g.world_size)]
-        dst = [g.addr(d, self.ag_off) for d in range(g.world_size)] if broadcast else []
         signal = g.signal_all(self.channel, PHASE_ALL_GATHER, epoch) if broadcast else None
+        dst, dst_layout, dst_offset, mc = [], geo.total_groups, me * geo.shard_groups, 0
+        if broadcast and self.pull_gather:
+            # the reduced shard stays here as a self-contained payload; peers load it in their K3
+            dst, dst_layout, dst_offset = [g.local_ptr + self.ag_off], geo.shard_groups, 0
+        elif broadcast:
+            dst = [g.addr(d, self.ag_off) for d in range(g.world_size)]
+            mc = g.multicast_addr(self.ag_off) if self.multicast_in_reduce_stage else 0
         self.ext.wait_signal(g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch), None)
         self.launches += 1
         self.ext.reduce(src, geo.shard_groups, 0, False, geo.shard_valid_numel(me), self._code, geo.group_size,
-                        self.config.bit, scale, out, False, None, None, dst, geo.total_groups,
-                        me * geo.shard_groups, signal, g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch),
-                        self.max_blocks,
-                        g.multicast_addr(self.ag_off) if broadcast and self.multicast_in_reduce_stage else 0)
+                        self.config.bit, scale, out, False, None, None, dst, dst_layout, dst_offset, signal,
+                        g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch), self.max_blocks, mc)
         self.launches += 1
 
     def _k3_gather(self, geo: FusedGeometry, epoch: int, out, prepared, residual_out):
         g = self.group
         self.ext.wait_signal(g.wait_all(self.channel, PHASE_ALL_GATHER, epoch), None)
         self.launches += 1
-        self.ext.reduce([g.local_ptr + self.ag_off], geo.total_groups, 0, False, geo.numel, self._code,
-                        geo.group_size, self.config.bit, 1.0, out, False, prepared, residual_out, [], 0, 0, None,
-                        g.wait_all(self.channel, PHASE_ALL_GATHER, epoch), self.max_blocks)
+        if self.pull_gather:
+            src, layout, shard_groups = [g.addr(r, self.ag_off) for r in range(g.world_size)], geo.shard_groups, \
+                geo.shard_groups
+        else:
+            src, layout, shard_groups = [g.local_ptr + self.ag_off], geo.total_groups, 0
+        self.ext.reduce(src, layout, 0, False, geo.numel, self._code, geo.group_size, self.config.bit, 1.0, out,
+                        False, prepared, residual_out, [], 0, 0, None,
+                        g.wait_all(self.channel, PHASE_ALL_GATHER, epoch), self.max_blocks, 0, shard_groups)
         self.launches += 1
 
     def _k1_broadcast(self, x, residual, prepared_out, local_ef_out, geo: FusedGeometry, epoch: int, parity: int):

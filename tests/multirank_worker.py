@@ -43,16 +43,20 @@ def collectives_case(rank: int, world: int) -> None:
             got = compressed_all_reduce(mine, config=cfg, op="mean", strategy=strategy)
             torch.cuda.synchronize()
             assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), (strategy, n, rank)
-            # with error feedback (residual starts at zero, so prepared == input)
-            residual = torch.zeros_like(mine)
-            got = ws.all_reduce(xs[rank].cuda(), residual=residual, op="mean",
-                                stages=1 if strategy == "all_gather" else 2)
-            torch.cuda.synchronize()
-            assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), (strategy, n, "ef")
+            # with error feedback (residual starts at zero, so prepared == input); the gather stage both as
+            # peer loads by the decode kernel and as peer stores by the reduce kernel
             reduced32 = (oracle.reduce_mean(payloads, n, cfg, name)[1] if strategy == "all_gather"
                          else oracle.decode_fp32(oracle.encode(y, cfg), n, cfg, name))
             want_res = oracle.residual_update(xs[rank], reduced32)
-            assert torch.equal(residual.cpu().view(torch.uint8), want_res.view(torch.uint8)), (strategy, n, "residual")
+            for gather in ("push", "pull"):
+                ws.set_gather_mode(gather)
+                residual = torch.zeros_like(mine)
+                got = ws.all_reduce(xs[rank].cuda(), residual=residual, op="mean",
+                                    stages=1 if strategy == "all_gather" else 2)
+                torch.cuda.synchronize()
+                assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), (strategy, n, gather, "ef")
+                assert torch.equal(residual.cpu().view(torch.uint8), want_res.view(torch.uint8)), \
+                    (strategy, n, gather, "residual")
         work = compressed_all_reduce(xs[rank].cuda(), config=cfg, strategy="reduce_scatter", async_op=True)
         got = work.wait()
         torch.cuda.current_stream().synchronize()

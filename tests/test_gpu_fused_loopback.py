@@ -99,15 +99,18 @@ def test_every_push_variant_writes_the_same_bytes(ext, push_variant, reduce_bulk
         for step, n in enumerate((world * group * 8, 70_001, max_numel)):
             xs = _inputs(world, n, dtype, seed=step)
             rs = _inputs(world, n, dtype, seed=50 + step)
-            for stages, expected in ((1, _expected_one_stage), (2, _expected_two_stage)):
+            for stages, expected, gather in ((1, _expected_one_stage, "pull"), (2, _expected_two_stage, "pull"),
+                                             (2, _expected_two_stage, "push")):
+                for ws in wss:
+                    ws.set_gather_mode(gather)
                 dev_x = [x.cuda() for x in xs]
                 dev_r = [r.cuda() for r in rs]
                 run_loopback(wss, "all_reduce", [(dev_x[r],) for r in range(world)],
                              [{"residual": dev_r[r]} for r in range(world)], stages=stages)
                 want = expected(xs, rs, cfg, dtype)
                 for r in range(world):
-                    assert torch.equal(dev_x[r].cpu().view(torch.uint8), want[0].view(torch.uint8)), (n, stages, r)
-                    assert torch.equal(dev_r[r].cpu().view(torch.uint8), want[1][r].view(torch.uint8)), (n, stages, r)
+                    assert torch.equal(dev_x[r].cpu().view(torch.uint8), want[0].view(torch.uint8)), (n, stages, gather, r)
+                    assert torch.equal(dev_r[r].cpu().view(torch.uint8), want[1][r].view(torch.uint8)), (n, stages, gather, r)
         torch.cuda.synchronize()
         for g in groups:
             g.check_status()
