@@ -140,7 +140,7 @@ void reduce(const Ptrs& src, int64_t layout_groups, int64_t group_offset, bool c
             int group_size, int bit, double scale, const std::optional<at::Tensor>& out, bool accumulate,
             const std::optional<at::Tensor>& prepared, const std::optional<at::Tensor>& residual_out, const Ptrs& dst,
             int64_t dst_layout_groups, int64_t dst_group_offset, const SignalArg& signal, const WaitArg& wait,
-            int max_blocks, uintptr_t mc_dst, int64_t src_shard_groups) {
+            int max_blocks, uintptr_t mc_dst, int64_t src_shard_groups, int first_src) {
     LbcReduce p{};
     p.dtype = dtype;
     p.group_size = group_size;
@@ -161,6 +161,7 @@ void reduce(const Ptrs& src, int64_t layout_groups, int64_t group_offset, bool c
                     "source groups do not fit the source layout");
     }
     p.src_shard_groups = src_shard_groups;
+    p.first_src = src_shard_groups > 0 ? first_src : 0;
     p.layout_groups = layout_groups;
     p.group_offset = group_offset;
     p.compact = compact ? 1 : 0;
@@ -312,7 +313,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("accumulate"), py::arg("prepared"), py::arg("residual_out"), py::arg("dst"),
           py::arg("dst_layout_groups"), py::arg("dst_group_offset"), py::arg("signal") = py::none(),
           py::arg("wait") = py::none(), py::arg("max_blocks") = 0, py::arg("mc_dst") = 0,
-          py::arg("src_shard_groups") = 0);
+          py::arg("src_shard_groups") = 0, py::arg("first_src") = 0);
     m.def("quant_general", &quant_general);
     m.def("dequant_general", &dequant_general);
     m.def("error_feedback_update", &error_feedback_update);

@@ -448,8 +448,15 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
     const int64_t span_unit = bulk ? kThreads : 32;
     const int64_t chunk_span = (num_chunks + span_unit - 1) / span_unit * span_unit;
 
-    for (int64_t chunk = int64_t(blockIdx.x) * kThreads + threadIdx.x; chunk < chunk_span;
-         chunk += int64_t(gridDim.x) * kThreads) {
+    // gather mode: rotate the sweep (by whole warps) so that it starts at shard `first_src`
+    int64_t rotation = 0;
+    if (p.src_shard_groups > 0 && p.first_src > 0 && p.num_dst == 0)
+        rotation = (int64_t(p.first_src) * p.src_shard_groups * lanes / 32 * 32) % chunk_span;
+
+    for (int64_t it = int64_t(blockIdx.x) * kThreads + threadIdx.x; it < chunk_span;
+         it += int64_t(gridDim.x) * kThreads) {
+        int64_t chunk = it + rotation;
+        if (chunk >= chunk_span) chunk -= chunk_span;
         const bool live = chunk < num_chunks;
         const int64_t first = chunk * kElemsPerThread;
         const int64_t g = chunk / lanes;
@@ -776,6 +783,7 @@ cudaError_t lbc_reduce(const LbcReduce* p, cudaStream_t stream) {
     if (p->wait.count < 0 || p->wait.count > lbc::kThreads) return cudaErrorInvalidValue;
     if ((reinterpret_cast<uintptr_t>(p->mc_dst) & 15) != 0) return cudaErrorInvalidValue;
     if (p->src_shard_groups < 0 || (p->src_shard_groups > 0 && p->compact)) return cudaErrorInvalidValue;
+    if (p->first_src < 0 || p->first_src > LBC_MAX_RANKS) return cudaErrorInvalidValue;
     if (p->src_shard_groups > 0 && p->numel > 0) {
         const int64_t groups = (p->numel + p->group_size - 1) / p->group_size;
         if ((p->group_offset + groups - 1) / p->src_shard_groups >= p->num_src) return cudaErrorInvalidValue;

@@ -260,6 +260,7 @@ class FusedAllReducePlan {
             k3.num_src = world_;
             for (int s = 0; s < world_; ++s) k3.src[s] = reinterpret_cast<const uint8_t*>(peers_[s] + r.ag);
             k3.src_shard_groups = shard_groups;
+            k3.first_src = rank_;
             k3.layout_groups = shard_groups;
         } else {
             k3.num_src = 1;

@@ -73,6 +73,8 @@ typedef struct {
     int compact;               // sources use the per-group record layout
     int64_t src_shard_groups;  // > 0: gather mode, group g is read from src[g / src_shard_groups] only (every
                                // source is a planar payload of src_shard_groups groups: a peer's reduced shard)
+    int first_src;             // gather mode: the sweep over the groups starts at this source's shard, so that
+                               // ranks that start at their own index never read from the same peer at once
     int64_t numel;             // elements to produce
     float scale;               // applied to the fp32 sum (1/W for a mean)
     void* out;                 // optional T[numel]

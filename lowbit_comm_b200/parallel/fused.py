@@ -270,7 +270,8 @@ class FusedWorkspace:
             src, layout, shard_groups = [g.local_ptr + self.ag_off], geo.total_groups, 0
         self.ext.reduce(src, layout, 0, False, geo.numel, self._code, geo.group_size, self.config.bit, 1.0, out,
                         False, prepared, residual_out, [], 0, 0, None,
-                        g.wait_all(self.channel, PHASE_ALL_GATHER, epoch), self.max_blocks, 0, shard_groups)
+                        g.wait_all(self.channel, PHASE_ALL_GATHER, epoch), self.max_blocks, 0, shard_groups,
+                        g.rank if shard_groups else 0)
         self.launches += 1
 
     def _k1_broadcast(self, x, residual, prepared_out, local_ef_out, geo: FusedGeometry, epoch: int, parity: int):
