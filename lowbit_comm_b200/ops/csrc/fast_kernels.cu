@@ -743,13 +743,13 @@ struct ReduceLauncher {
         const int64_t groups = (p->numel + G - 1) / G;
         if (groups == 0 && p->signal.num_remote == 0 && p->wait.flags == nullptr) return cudaSuccess;
         int cap = p->max_blocks;
-        if (p->num_dst > 0 && g_reduce_push_blocks >= 0) {
+        if (p->num_dst > 1 && g_reduce_push_blocks >= 0) {   // several destinations: peers are among them
             const int push_cap = g_reduce_push_blocks > 0 ? g_reduce_push_blocks : default_max_blocks() / 4;
             if (cap == 0 || cap > push_cap) cap = push_cap;
         }
         const int grid = grid_for(groups * (G / kElemsPerThread), cap);
         LbcReduce launch = *p;
-        launch.bulk_store = g_reduce_bulk;
+        launch.bulk_store = p->num_dst > 1 ? g_reduce_bulk : 0;   // a single (local) destination takes plain stores
         reduce_kernel<T, G, BIT><<<grid, kThreads, 0, stream>>>(launch);
         return cudaGetLastError();
     }
