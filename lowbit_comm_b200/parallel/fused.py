@@ -4,26 +4,31 @@ One `FusedWorkspace` owns symmetric receive regions inside a `PeerGroup` arena
 and one signal channel.  Its methods only enqueue kernels on the current CUDA
 stream; nothing here synchronises with the host.
 
-Two-stage all-reduce (W >= 3 by default), per rank:
+Two-stage all-reduce (W >= 3 above a few MiB), per rank:
   K1 quant_push/scatter : x (+residual) -> int8 groups; group g goes to the rank
                           owning shard g // shard_groups, into that rank's RS
                           region slot [me]; then signals RS[me] on every rank
   K2 reduce             : waits RS[0..W); dequantizes the W slots of its shard,
-                          sums in fp32, scales, requantizes and writes the shard
-                          into every rank's AG region; then signals AG[me]
-  K3 reduce             : waits AG[0..W); decodes the AG region (a planar payload
-                          of the whole tensor) into `out`; updates the residual
-One-stage all-reduce (W <= 2): K1 broadcasts the whole payload to every rank's
-gather region slot [me]; one reduce kernel sums the W slots.
+                          sums in fp32, scales, requantizes the shard into its OWN
+                          AG region (a self-contained payload); then signals AG[me]
+  K3 reduce (gather)    : waits AG[0..W); loads shard s from rank s's AG region
+                          (peer loads over NVLink), decodes into `out`; updates the
+                          residual
+(`set_gather_mode("push")`: K2 stores its shard into every rank's AG region instead
+and K3 reads only local memory.)
+One-stage all-reduce (W <= 2, small tensors): K1 broadcasts the whole payload to
+every rank's gather region slot [me]; one reduce kernel sums the W slots.
 
 Why reuse of the regions is safe without extra barriers: all ranks enqueue the
 same kernel sequence on one in-order stream.  K3(t) of a rank finishes only
 after every peer's K2(t) signalled, so by the time the rank's K1(t+1) overwrites
-a peer's RS slot that peer has finished reading it; K2(t+1) writes peers' AG
-regions only after every peer's K1(t+1) signalled, which those peers enqueue
-after their K3(t).  Regions that are read by a kernel not followed by such a
-barrier (gather region, RS region used by reduce-scatter alone) are double
-buffered by epoch parity, which the same argument makes sufficient.
+a peer's RS slot that peer has finished reading it.  A rank overwrites its own AG
+region in K2(t+1), which waits for every peer's K1(t+1) signal, and a peer enqueues
+K1(t+1) after its K3(t), the kernel that read this rank's AG region (push mode: the
+same argument with "writes the peers' AG regions").  Regions that are read by a
+kernel not followed by such a barrier (gather region, RS region used by
+reduce-scatter alone) are double buffered by epoch parity, which the same argument
+makes sufficient.
 
 This replaces the reference's quantize -> NCCL all_to_all / all_gather ->
 dequantize chains (ccdl_comm/communication/reduce_scatter_transport.py:186-377,
