@@ -109,15 +109,17 @@ def geometry(numel: int, world_size: int, dtype: str, config: CompressionConfig)
 def default_stages(world_size: int, nbytes: int, multicast: bool = False) -> int:
     """One-stage (every rank reduces W payloads) or two-stage (scatter, reduce, gather) all-reduce.
 
-    Measured on 8 x B200 (bf16, int8 group 64): one stage wins while launches and signal round
-    trips dominate, up to 4 MiB with unicast stores and up to 8 MiB when the broadcast leaves
-    through the NVLink multicast mapping; above that the (W - 1) payloads per rank lose to the
-    2 (W - 1) / W of the two-stage path.  Two ranks move the same bytes either way.
+    Measured on B200 (bf16, int8 group 64): one stage wins while launches and signal round trips
+    dominate; the crossover sits near 16-32 MiB on 4 GPUs and 8 MiB on 8 GPUs, i.e. where the
+    tensor is about 64 MiB / W (twice that when the broadcast leaves through the NVLink multicast
+    mapping).  Above it the (W - 1) payloads per rank lose to the 2 (W - 1) / W of the two-stage
+    path.  Two ranks move the same bytes either way.
     """
 
     if world_size <= 2:
         return 1
-    return 1 if nbytes <= ((8 << 20) if multicast else (4 << 20)) else 2
+    budget = (128 << 20) if multicast else (64 << 20)
+    return 1 if nbytes * world_size <= budget else 2
 
 
 class FusedWorkspace:
