@@ -94,8 +94,11 @@ class CudaStrategyTable:
         """Rules for sm_100 / bf16+fp16 / W in {2,4,8}; `measured` overrides the recorded speed-ups
         (keys `(layout, world)` -> speed-up over the NCCL bf16 full all-reduce)."""
 
-        recorded = {("full", 2): 1.0, ("full", 4): 1.0, ("full", 8): 1.0,
-                    ("shard", 2): 1.5, ("shard", 4): 1.5, ("shard", 8): 1.5}
+        # Recorded on this pool's B200s (bf16, int8 group 64, error feedback on; profiles/allreduce_sweep_b200.md).
+        # full: NCCL bf16 all-reduce time / best fused path at 256 MiB.  shard: NCCL *full* all-reduce time /
+        # (K1 + K2) of the two-stage path at 64 MiB, the baseline the reference's own table uses for shards.
+        recorded = {("full", 2): 1.20, ("full", 4): 1.25, ("full", 8): 1.17,
+                    ("shard", 2): 1.5, ("shard", 4): 1.5, ("shard", 8): 1.7}
         recorded.update(measured or {})
         rules = []
         for (layout, world), speedup in recorded.items():
@@ -109,9 +112,12 @@ class CudaStrategyTable:
                 elif world <= 2:
                     rules.append(CudaStrategyRule(min_numel=262_144, max_numel=1 << 31, strategy="all_gather", **common))
                 else:
-                    rules.append(CudaStrategyRule(min_numel=262_144, max_numel=2_097_151, strategy="all_gather", **common))
-                    rules.append(CudaStrategyRule(min_numel=2_097_152, max_numel=1 << 31, strategy="reduce_scatter",
+                    # one stage while tensor bytes x W <= 64 MiB (measured crossover: 16 MiB on 4 GPUs, 8 MiB on 8)
+                    one_stage_max = (64 << 20) // (2 * world)
+                    rules.append(CudaStrategyRule(min_numel=262_144, max_numel=one_stage_max, strategy="all_gather",
                                                   **common))
+                    rules.append(CudaStrategyRule(min_numel=one_stage_max + 1, max_numel=1 << 31,
+                                                  strategy="reduce_scatter", **common))
         return cls(tuple(rules))
 
     def select(self, plan: CommunicationPlan, context: CompileContext) -> StrategyChoice:
