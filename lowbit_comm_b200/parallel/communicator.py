@@ -85,6 +85,7 @@ class Communicator:
         self.max_blocks = max_blocks
         self._status = extension_status
         self.peer_group = None
+        self.mailbox = None   # PeerMailbox after enable_peer_mailbox()
         self._peer_failed: str | None = None
         self._workspaces: dict[tuple, Any] = {}
         self._subcomms: dict[tuple, Any] = {}
@@ -124,6 +125,24 @@ class Communicator:
                 self._peer_failed = str(exc)
                 raise
         return self.peer_group
+
+    def enable_peer_mailbox(self, capacity_bytes: int, device: Any = None):
+        """Collective over the group: reserves one payload slot per source rank in every arena, after which
+        `iqsend` / `iqrecv` between any two ranks move their payload with the quantize kernel's own peer
+        stores (`PeerMailbox`) instead of an NCCL send/receive pair.  Every rank must call it, in the same
+        order relative to other collectives (the arenas are allocated symmetrically)."""
+
+        from .p2p import PeerMailbox
+
+        if self.mailbox is None:
+            if device is None:
+                import torch
+
+                device = torch.device("cuda", torch.cuda.current_device())
+            need = int(capacity_bytes) * self.world_size + (1 << 20)
+            group = self._ensure_peer_group(device, need)
+            self.mailbox = PeerMailbox(group, capacity_bytes=int(capacity_bytes))
+        return self.mailbox
 
     def workspace(self, tensor: Any, config: CompressionConfig, dtype: str):
         """Fused workspace able to hold `tensor` (capacity grows in powers of two)."""

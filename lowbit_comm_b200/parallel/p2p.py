@@ -12,6 +12,11 @@ Two transports:
   receiver's decode kernel waits (bounded), decodes and acknowledges, and the
   next send to the same peer first waits (bounded) for that acknowledgement.
   Messages between a pair are matched by order, so this path needs tag 0.
+  Mailbox operations are kernels on the caller's current stream, in call order:
+  a rank that both sends and receives in one step posts its sends first (a
+  receive kernel waits on the device for the peer's send, and a send queued
+  behind it on the same stream could not start), or uses two streams.  It is
+  enabled per group with `Communicator.enable_peer_mailbox`, a collective call.
 """
 
 from __future__ import annotations
@@ -24,7 +29,7 @@ from typing import Any
 from ..config import CompressionConfig
 from ..core.info import ExecutionCounters, ExecutionInfo
 from ..core.work import CompletionWork, bind_execution_work
-from ..exceptions import TorchDistributedUnavailableError
+from ..exceptions import TorchDistributedUnavailableError, UnsupportedCollective
 from ..ops import codec
 from ..ops.sizing import estimate_quantized_size
 from .peer_memory import PHASE_P2P_ACK, PHASE_P2P_DATA, PeerGroup
@@ -208,9 +213,48 @@ def compile_qrecv(tensor: Any, src: int | None = None, *, config: CompressionCon
     return CudaP2PExecutor(direction="recv", peer=src, tensor=tensor, config=config, **kw)
 
 
+def _mailbox_for(tensor: Any, peer: int | None, config: CompressionConfig, group: Any | None, tag: int,
+                 dtype: str, transport: str) -> PeerMailbox | None:
+    """The group's peer mailbox when this message can use it, else None ("peer" insists and raises)."""
+
+    if transport not in ("auto", "peer", "torch"):
+        raise ValueError("transport must be 'auto', 'peer' or 'torch'")
+    if transport == "torch":
+        return None
+    reason = None
+    mailbox = None
+    if not bool(getattr(tensor, "is_cuda", False)):
+        reason = "the tensor is not on a CUDA device"
+    elif peer is None or tag != 0:
+        reason = "the mailbox needs an explicit peer and tag 0"
+    elif not codec.is_fast_profile(config):
+        reason = "the mailbox serves linear / top-k 0 / deterministic profiles"
+    else:
+        from .communicator import _REGISTRY
+
+        comm = _REGISTRY.get(id(group) if group is not None else 0)
+        mailbox = None if comm is None or comm.closed else comm.mailbox
+        if mailbox is None:
+            reason = "Communicator.enable_peer_mailbox() was not called for this group"
+        else:
+            need = estimate_quantized_size(tensor.numel(), dtype=codec.resolve_dtype(dtype, tensor),
+                                           config=config).quantized_bytes
+            if need > mailbox.capacity:
+                mailbox, reason = None, f"payload of {need} bytes exceeds the mailbox capacity"
+    if mailbox is None and transport == "peer":
+        raise UnsupportedCollective("p2p:peer", reason=reason or "peer mailbox unavailable")
+    return mailbox
+
+
 def iqsend(tensor: Any, dst: int, *, config: CompressionConfig, group: Any | None = None, tag: int = 0,
            dtype: str = "auto", extension_status: Any | None = None, compiled_executor: CudaP2PExecutor | None = None,
-           **kw):
+           transport: str = "auto", **kw):
+    """Quantized send.  transport="auto" uses the group's peer mailbox when one was enabled and the message
+    qualifies, else a torch.distributed send of the payload (the reference's only form,
+    ccdl_comm/communication/point_to_point.py)."""
+
+    if compiled_executor is None and "mailbox" not in kw:
+        kw["mailbox"] = _mailbox_for(tensor, dst, config, group, tag, dtype, transport)
     executor = compiled_executor or compile_qsend(tensor, dst, config=config, group=group, tag=tag, dtype=dtype,
                                                   extension_status=extension_status, **kw)
     return executor.run(tensor)
@@ -218,7 +262,9 @@ def iqsend(tensor: Any, dst: int, *, config: CompressionConfig, group: Any | Non
 
 def iqrecv(tensor: Any, src: int | None = None, *, config: CompressionConfig, group: Any | None = None, tag: int = 0,
            dtype: str = "auto", extension_status: Any | None = None, compiled_executor: CudaP2PExecutor | None = None,
-           **kw):
+           transport: str = "auto", **kw):
+    if compiled_executor is None and "mailbox" not in kw:
+        kw["mailbox"] = _mailbox_for(tensor, src, config, group, tag, dtype, transport)
     executor = compiled_executor or compile_qrecv(tensor, src, config=config, group=group, tag=tag, dtype=dtype,
                                                   extension_status=extension_status, **kw)
     return executor.run(tensor)

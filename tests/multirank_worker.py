@@ -82,6 +82,23 @@ def collectives_case(rank: int, world: int) -> None:
         exact = torch.stack([x.float() for x in xs]).mean(0)
         rel = ((got.float().cpu() - exact).norm() / exact.norm()).item()
         assert rel < 0.03, rel
+    # quantized point-to-point through the peer mailboxes: a ring, three rounds (the second and third
+    # sends first wait for the receiver's acknowledgement of the previous message)
+    import lowbit_comm_b200 as lbc
+
+    comm.enable_peer_mailbox(1 << 20)
+    n, nxt, prv = 50_001, (rank + 1) % world, (rank - 1) % world
+    for it in range(3):
+        xs = _inputs(world, n, dt, seed=200 + it)
+        recv = torch.empty(n, dtype=dt, device="cuda")
+        sent = lbc.iqsend(xs[rank].cuda(), nxt, config=cfg, transport="peer")
+        work = lbc.iqrecv(recv, prv, config=cfg, transport="peer")
+        sent.wait()
+        got = work.wait()
+        torch.cuda.synchronize()
+        want = oracle.decode(oracle.encode(xs[prv], cfg), n, cfg, name)
+        assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), ("mailbox", it, rank)
+        assert work.execution_info.fast_path == "cuda_peer_mailbox_recv"
     comm.check_status()
     assert comm.stats["peer_ops"] > 0 and comm.stats["torch_ops"] == 0, comm.stats
 

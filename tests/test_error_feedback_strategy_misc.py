@@ -141,3 +141,29 @@ def test_plugin_and_capability():
     assert not caps.available and caps.reason == "no gpu"
     live = CapabilityReport(available=True, cuda=True, quantize=True, compressed_collectives=True).to_backend_capabilities()
     assert live.available and "reduce_scatter" in live.collectives and 8 in live.bits
+
+
+def test_p2p_transport_selection_rules():
+    import torch
+
+    from lowbit_comm_b200 import CompressionConfig
+    from lowbit_comm_b200.exceptions import UnsupportedCollective
+    from lowbit_comm_b200.parallel.p2p import _mailbox_for
+
+    cfg = CompressionConfig()
+    t = torch.zeros(128, dtype=torch.bfloat16)
+    assert _mailbox_for(t, 1, cfg, None, 0, "auto", "torch") is None
+    assert _mailbox_for(t, 1, cfg, None, 0, "auto", "auto") is None      # CPU tensor: torch.distributed send
+    with pytest.raises(UnsupportedCollective):
+        _mailbox_for(t, 1, cfg, None, 0, "auto", "peer")                 # insisting on the mailbox fails loudly
+    with pytest.raises(ValueError):
+        _mailbox_for(t, 1, cfg, None, 0, "auto", "carrier-pigeon")
+
+
+def test_default_stage_rule():
+    from lowbit_comm_b200.parallel.fused import default_stages
+
+    assert default_stages(2, 1 << 30) == 1
+    assert default_stages(8, 4 << 20) == 1 and default_stages(8, 8 << 20) == 1 and default_stages(8, 16 << 20) == 2
+    assert default_stages(4, 16 << 20) == 1 and default_stages(4, 32 << 20) == 2
+    assert default_stages(8, 16 << 20, multicast=True) == 1
