@@ -1,6 +1,6 @@
 """Single-GPU microbenchmark of the codec and fused kernels (HBM roofline check).
 
-Usage: python benchmarks/kernel_bench.py [--mib 64] [--out gpurun_out/kernel_bench.json]
+Usage: python benchmarks/kernel_bench.py [--mib 64 256] [--worlds 1 2 8] [--profile] [--out FILE]
 Every kernel is timed with CUDA events after warm-up with an L2 flush between
 iterations; bandwidth = algorithmic bytes / median time, reported as a fraction
 of the measured copy bandwidth in MEASURED_PEAKS.json (fallback 6650 GB/s).

@@ -6,7 +6,8 @@
 // handful of integer operations: measured launch gaps, not kernels, dominated
 // small buckets when the launches were issued from Python.
 //
-// Large tensors are cut into chunks that flow through the three phases on three
+// Optionally (`set_chunking`; off by default because it measured slower: persistent grids of
+// neighbouring chunks do not interleave) large tensors are cut into chunks that flow through the three phases on three
 // streams (push on the caller's stream, reduce and gather on two side streams), so
 // the NVLink-bound phases of one chunk overlap the HBM-bound phases of its
 // neighbours.  Every chunk is a complete small all-reduce with its own receive
@@ -14,6 +15,9 @@
 // waiting kernel does the (bounded) waiting, so no stream can fill the GPU with
 // spinning blocks.  The side streams are joined back into the caller's stream at
 // the end, which keeps the region-reuse argument of the single-stream version.
+//
+// A one-warp gate kernel sits in front of every waiting kernel also without chunking: a rank
+// that is ahead of its peers parks 32 threads instead of filling its SMs with spinning blocks.
 //
 // A variant that staged the payload locally and let the copy engines deliver it (peer-to-peer
 // cudaMemcpyAsync on a copy stream, flags raised by a one-warp kernel behind the copies) was
