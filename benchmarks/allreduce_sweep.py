@@ -65,6 +65,8 @@ def main() -> None:
     ap.add_argument("--phases", action="store_true", help="also time K1/K2/K3 separately (Python launch path)")
     ap.add_argument("--gather", choices=("pull", "push"), default=None,
                     help="two-stage gather: peer loads by the decode kernel (pull) or peer stores by the reduce kernel")
+    ap.add_argument("--gather-order", type=int, choices=(0, 1), default=None,
+                    help="pull gather: 1 = tiles round-robin over the owners (default), 0 = linear sweep")
     ap.add_argument("--multicast", action="store_true",
                     help="arenas from the symmetric-memory allocator: broadcasts use multimem stores")
     ap.add_argument("--out", default="gpurun_out/allreduce_sweep.json")
@@ -97,6 +99,10 @@ def main() -> None:
         os.environ["LBC_MULTICAST"] = "1"
     comm = Communicator(None, arena_bytes=arena)
     big = comm.workspace(torch.empty(max_numel, dtype=torch.bfloat16, device=dev), cfg, "bf16")  # largest first
+    if args.gather_order is not None:
+        from lowbit_comm_b200.ops.loader import require_extension as _req
+
+        _req().set_gather_order(args.gather_order)
     if args.gather is not None:
         big.set_gather_mode(args.gather)
     if args.chunk_mib is not None:

@@ -328,6 +328,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           },
           py::arg("push_variant"), py::arg("reduce_bulk") = false, py::arg("reduce_push_blocks") = 0);
 
+    m.def("set_gather_order", [](int order) { lbc_set_gather_order(order); }, py::arg("order"));
     m.def("arena_alloc", &lbc::arena_alloc);
     m.def("arena_free", &lbc::arena_free);
     m.def("ipc_get_handle", [](uintptr_t p) { return py::bytes(lbc::ipc_get_handle(p)); });

@@ -452,16 +452,34 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
     const int64_t span_unit = bulk ? kThreads : 32;
     const int64_t chunk_span = (num_chunks + span_unit - 1) / span_unit * span_unit;
 
-    // gather mode: rotate the sweep (by whole warps) so that it starts at shard `first_src`
+    // Gather mode without destinations (the decode stage of the two-stage all-reduce): the sweep is dealt
+    // out in 256-thread tiles that walk the shards round-robin, starting at shard `first_src`.  At any
+    // instant the blocks of this GPU then read from all owners at once, and ranks that start at their own
+    // index load every owner evenly even when they run skewed in time (gather_order 1).  gather_order 0
+    // keeps the linear sweep, rotated to start at `first_src`: one owner at a time.
+    const bool by_tiles = p.src_shard_groups > 0 && p.num_dst == 0 && p.group_offset == 0 && p.gather_order == 1;
+    const int64_t shard_chunks = p.src_shard_groups * lanes;
+    const int64_t tiles_per_shard = by_tiles ? (shard_chunks + kThreads - 1) / kThreads : 0;
+    const int64_t loop_span = by_tiles ? tiles_per_shard * R * kThreads : chunk_span;
     int64_t rotation = 0;
-    if (p.src_shard_groups > 0 && p.first_src > 0 && p.num_dst == 0)
-        rotation = (int64_t(p.first_src) * p.src_shard_groups * lanes / 32 * 32) % chunk_span;
+    if (!by_tiles && p.src_shard_groups > 0 && p.first_src > 0 && p.num_dst == 0)
+        rotation = (int64_t(p.first_src) * shard_chunks / 32 * 32) % chunk_span;
 
-    for (int64_t it = int64_t(blockIdx.x) * kThreads + threadIdx.x; it < chunk_span;
+    for (int64_t it = int64_t(blockIdx.x) * kThreads + threadIdx.x; it < loop_span;
          it += int64_t(gridDim.x) * kThreads) {
-        int64_t chunk = it + rotation;
-        if (chunk >= chunk_span) chunk -= chunk_span;
-        const bool live = chunk < num_chunks;
+        int64_t chunk;
+        bool inside = true;
+        if (by_tiles) {
+            const int64_t tile = it / kThreads;                    // block-uniform
+            const int64_t owner = (tile + p.first_src) % R;
+            const int64_t within = (tile / R) * kThreads + threadIdx.x;
+            inside = within < shard_chunks;
+            chunk = owner * shard_chunks + within;
+        } else {
+            chunk = it + rotation;
+            if (chunk >= chunk_span) chunk -= chunk_span;
+        }
+        const bool live = inside && chunk < num_chunks;
         const int64_t first = chunk * kElemsPerThread;
         const int64_t g = chunk / lanes;
         const int lane = int(chunk - g * lanes);
@@ -711,6 +729,7 @@ static int g_push_variant = 1;
 // Defaults from the 8 x B200 sweep (64-256 MiB): bulk stores and two blocks per SM for the
 // requantize-and-broadcast stage were 4-8 % faster than per-thread stores on the full grid.
 static int g_reduce_bulk = 1;
+static int g_gather_order = 1;          // decode stage of the all-reduce: 1 = tiles round-robin over the owners, 0 = linear sweep
 static int g_reduce_push_blocks = 0;   // grid cap of reduce kernels that also push: 0 = two per SM, < 0 = none
 
 static bool tiled_path_ok(const LbcQuantPush* p) {
@@ -753,6 +772,7 @@ struct ReduceLauncher {
         }
         const int grid = grid_for(groups * (G / kElemsPerThread), cap);
         LbcReduce launch = *p;
+        launch.gather_order = g_gather_order;
         launch.bulk_store = p->num_dst > 1 ? g_reduce_bulk : 0;   // a single (local) destination takes plain stores
         reduce_kernel<T, G, BIT><<<grid, kThreads, 0, stream>>>(launch);
         return cudaGetLastError();
@@ -770,6 +790,8 @@ void lbc_set_push_variant(int push_variant, int reduce_bulk, int reduce_push_blo
     lbc::g_reduce_bulk = reduce_bulk != 0;
     lbc::g_reduce_push_blocks = reduce_push_blocks;
 }
+
+void lbc_set_gather_order(int order) { lbc::g_gather_order = order != 0; }
 
 cudaError_t lbc_quant_push(const LbcQuantPush* p, cudaStream_t stream) {
     if (p == nullptr || p->numel < 0 || p->num_dst < 0 || p->num_dst > LBC_MAX_RANKS) return cudaErrorInvalidValue;

@@ -88,6 +88,7 @@ typedef struct {
     LbcSignal signal;
     LbcWait wait;
     int max_blocks;
+    int gather_order;          // set by the launcher: 1 = gather-mode tiles walk the sources round-robin
     int bulk_store;            // set by the launcher: requantized tiles leave through bulk stores
     uint8_t* mc_dst;           // optional NVLink multicast alias of dst[*]: one multimem store reaches every rank
 } LbcReduce;
@@ -139,6 +140,8 @@ int lbc_default_max_blocks(void);
 // grid of that stage (0 = two blocks per SM, negative = no cap) so that every block amortises its
 // closing system-scope fence.
 void lbc_set_push_variant(int push_variant, int reduce_bulk, int reduce_push_blocks);
+// Gather-mode decode: 1 (default) deals 256-thread tiles round-robin over the source shards, 0 sweeps linearly.
+void lbc_set_gather_order(int order);
 
 #ifdef __cplusplus
 }

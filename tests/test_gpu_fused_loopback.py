@@ -119,6 +119,33 @@ def test_every_push_variant_writes_the_same_bytes(ext, push_variant, reduce_bulk
         PeerGroup.close_loopback(groups)
 
 
+@pytest.mark.parametrize("order", (0, 1))
+@pytest.mark.parametrize("world", (3, 8))
+@pytest.mark.parametrize("dtype,bit,group", [("bf16", 8, 64), ("fp16", 4, 16), ("fp32", 8, 32)])
+def test_gather_sweep_orders(ext, order, world, dtype, bit, group):
+    """The decode stage may walk the owners' shards linearly or tile by tile round-robin; same result."""
+
+    cfg = CompressionConfig(bit=bit, group_size=group, allow_experimental=True)
+    max_numel = 200_000
+    groups, wss = _make(world, dtype, cfg, max_numel)
+    ext.set_gather_order(order)
+    try:
+        for step, n in enumerate((world * group * 8, 12_345, 1, max_numel, group * 8 * world * 31 + 5)):
+            xs = _inputs(world, n, dtype, seed=400 + step)
+            rs = _inputs(world, n, dtype, seed=500 + step)
+            dev_x = [x.cuda() for x in xs]
+            dev_r = [r.cuda() for r in rs]
+            run_loopback(wss, "all_reduce", [(dev_x[r],) for r in range(world)],
+                         [{"residual": dev_r[r]} for r in range(world)], stages=2)
+            want = _expected_two_stage(xs, rs, cfg, dtype)
+            for r in range(world):
+                assert torch.equal(dev_x[r].cpu().view(torch.uint8), want[0].view(torch.uint8)), (n, r)
+                assert torch.equal(dev_r[r].cpu().view(torch.uint8), want[1][r].view(torch.uint8)), (n, r)
+    finally:
+        ext.set_gather_order(1)
+        PeerGroup.close_loopback(groups)
+
+
 @pytest.mark.parametrize("world,stages", [(2, 1), (4, 2), (8, 2)])
 @pytest.mark.parametrize("dtype", ("bf16", "fp32"))
 def test_local_error_feedback_mode(ext, world, stages, dtype):
