@@ -133,7 +133,7 @@ def main() -> None:
     args = parse_args()
     # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; the only stdout line of this
     # program is the JSON result, so the banner level is lowered to warnings.
-    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":   # unset: a system nccl.conf may ask for it
         os.environ["NCCL_DEBUG"] = "WARN"
     if args.impl == "reference":
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
