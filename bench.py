@@ -131,10 +131,9 @@ def build_model(name: str, impl: str):
 
 def main() -> None:
     args = parse_args()
-    # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; the only stdout line of this
-    # program is the JSON result, so the banner level is lowered to warnings.
-    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":   # unset: a system nccl.conf may ask for it
-        os.environ["NCCL_DEBUG"] = "WARN"
+    # NCCL writes its version banner and warnings to stdout by default; the only stdout line of this
+    # program is the JSON result, so NCCL's log goes to stderr.
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     if args.impl == "reference":
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
         import reference_env
