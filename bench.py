@@ -134,6 +134,8 @@ def main() -> None:
     # NCCL writes its version banner and warnings to stdout by default; the only stdout line of this
     # program is the JSON result, so NCCL's log goes to stderr.
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":   # NCCL honours the log file only above VERSION
+        os.environ["NCCL_DEBUG"] = "WARN"
     if args.impl == "reference":
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
         import reference_env

@@ -208,7 +208,7 @@ class FusedWorkspace:
         total = 2 * world_size * shard + _round_up(max(cap.total_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
         if with_gather_region:
             total += 2 * world_size * _round_up(max(cap.full_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
-        return total + 8 * 256
+        return total + 32 * 256   # rounding and canaries of the five regions
 
     def _ensure_gather(self) -> list[int]:
         if self.gather_off is None:

@@ -31,7 +31,7 @@ from typing import Any
 
 import torch
 
-from ..exceptions import AsyncCommunicationError, CCDLUnavailableError
+from ..exceptions import AsyncCommunicationError, CCDLError, CCDLUnavailableError
 from ..ops.loader import require_extension
 
 MAX_CHANNELS = 256
@@ -40,6 +40,7 @@ MAX_RANKS = 16
 FLAG_BYTES = MAX_CHANNELS * NUM_PHASES * MAX_RANKS * 4
 COUNTER_OFFSET = FLAG_BYTES
 DATA_OFFSET = 128 * 1024
+CANARY_BYTES, CANARY_VALUE = 256, 0xA5
 DEFAULT_TIMEOUT_NS = 20_000_000_000  # 20 s: far above any real skew, far below a watchdog
 
 PHASE_REDUCE_SCATTER, PHASE_ALL_GATHER, PHASE_P2P_DATA, PHASE_P2P_ACK = range(NUM_PHASES)
@@ -71,6 +72,7 @@ class PeerGroup:
         self._owner = owner
         self._opened = list(opened or [])
         self._cursor = DATA_OFFSET
+        self._canaries: list[int] = []
         self._epochs = [0] * MAX_CHANNELS
         self._channels_used = 0
         self._lock = threading.Lock()
@@ -185,15 +187,32 @@ class PeerGroup:
 
     # -- symmetric allocation ----------------------------------------------
     def alloc(self, nbytes: int, align: int = 256) -> int:
-        """Reserve `nbytes`; returns the offset (identical on every rank)."""
+        """Reserve `nbytes`; returns the offset (identical on every rank).
+
+        Every region is followed by a 256-byte canary (0xA5) in this rank's own arena; `check_canaries`
+        finds any kernel, local or remote, that wrote past the end of a region.
+        """
 
         with self._lock:
             start = _round_up(self._cursor, align)
-            if start + nbytes > self.nbytes:
+            end = _round_up(start + nbytes, 256)
+            if end + CANARY_BYTES > self.nbytes:
                 raise CCDLUnavailableError(
                     f"peer arena exhausted: need {nbytes} bytes at {start}, arena has {self.nbytes}")
-            self._cursor = start + nbytes
+            self._cursor = end + CANARY_BYTES
+            self._canaries.append(end)
+            with torch.cuda.device(self.device):
+                self._ext.memset_async(self.local_ptr + end, CANARY_VALUE, CANARY_BYTES)
             return start
+
+    def check_canaries(self) -> None:
+        """Raises when a canary behind one of this rank's regions was overwritten (synchronises the device)."""
+
+        torch.cuda.synchronize(self.device)
+        for offset in self._canaries:
+            view = self.local_view(offset, CANARY_BYTES)
+            if not bool((view == CANARY_VALUE).all().item()):
+                raise CCDLError(f"rank {self.rank}: the canary at arena offset {offset} was overwritten")
 
     def new_channel(self) -> int:
         with self._lock:
@@ -291,12 +310,23 @@ class PeerGroup:
         self._keepalive = None
 
     @staticmethod
-    def close_loopback(groups: list["PeerGroup"]) -> None:
+    def close_loopback(groups: list["PeerGroup"], *, check: bool = True) -> None:
+        """Frees the emulated ranks' arenas; with `check` it first verifies every canary."""
+
         if not groups:
             return
         torch.cuda.synchronize(groups[0].device)
+        problem = None
+        if check:
+            for g in groups:
+                try:
+                    g.check_canaries()
+                except CCDLError as exc:
+                    problem = problem or exc
         for g in groups:
             g._closed = True
             g._ext.status_free(g.status_host)
         for ptr in groups[0].peer_ptrs:
             groups[0]._ext.arena_free(ptr)
+        if problem is not None:
+            raise problem

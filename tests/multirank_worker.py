@@ -100,6 +100,7 @@ def collectives_case(rank: int, world: int) -> None:
         assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), ("mailbox", it, rank)
         assert work.execution_info.fast_path == "cuda_peer_mailbox_recv"
     comm.check_status()
+    comm.peer_group.check_canaries()   # nobody, local or remote, wrote past the end of a region of this arena
     assert comm.stats["peer_ops"] > 0 and comm.stats["torch_ops"] == 0, comm.stats
 
 

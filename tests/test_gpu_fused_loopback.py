@@ -223,3 +223,22 @@ def test_bounded_wait_reports_status_instead_of_hanging(ext):
         assert torch.ones(4, device="cuda").sum().item() == 4
     finally:
         PeerGroup.close_loopback(groups)
+
+
+def test_canaries_catch_a_write_past_a_region(ext):
+    """Every arena region is followed by a canary; an overrun (here: a deliberate host-side memset through
+    the arena's own tensor view, no kernel misbehaves) is reported by `check_canaries`."""
+
+    from lowbit_comm_b200.exceptions import CCDLError
+
+    groups = PeerGroup.loopback(2, 1 << 20)
+    try:
+        off = groups[0].alloc(1000)
+        groups[1].alloc(1000)
+        groups[0].check_canaries()
+        groups[0].local_view(off, 1024 + 8)[-1] = 0     # region rounded up to 1024 bytes, then the canary
+        with pytest.raises(CCDLError):
+            groups[0].check_canaries()
+        groups[1].check_canaries()
+    finally:
+        PeerGroup.close_loopback(groups, check=False)
