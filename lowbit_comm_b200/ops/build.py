@@ -38,8 +38,33 @@ def cuda_sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
+HOST_SOURCE = "host_codec.cpp"       # plain C++ (no torch, no CUDA): its own small library
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-fno-fast-math"]
+
+
 def cxx_sources() -> list[Path]:
-    return sorted(CSRC.glob("*.cpp"))
+    return sorted(p for p in CSRC.glob("*.cpp") if p.name != HOST_SOURCE)
+
+
+def host_library_path() -> Path:
+    return HERE / "_lbc_host.so"
+
+
+def build_host_library(*, force: bool = False, verbose: bool = False) -> Path:
+    """Compile the CPU implementation of the wire format (`csrc/host_codec.cpp`) with g++."""
+
+    src, target = CSRC / HOST_SOURCE, host_library_path()
+    obj_dir = HERE / "build"
+    obj_dir.mkdir(exist_ok=True)
+    stamp = obj_dir / "host_fingerprint.json"
+    h = hashlib.sha256(src.read_bytes())
+    h.update(" ".join(HOST_FLAGS).encode())
+    fp = h.hexdigest()
+    if not force and target.exists() and stamp.exists() and json.loads(stamp.read_text()).get("fp") == fp:
+        return target
+    _run(["g++", *HOST_FLAGS, str(src), "-o", str(target)], verbose)
+    stamp.write_text(json.dumps({"fp": fp}))
+    return target
 
 
 def _cuda_home() -> Path:
@@ -114,3 +139,4 @@ def build_extension(*, force: bool = False, verbose: bool = False, ptxas_info: b
 if __name__ == "__main__":
     out = build_extension(force="--force" in sys.argv, verbose="-v" in sys.argv, ptxas_info="--ptxas" in sys.argv)
     print(out)
+    print(build_host_library(force="--force" in sys.argv, verbose="-v" in sys.argv))

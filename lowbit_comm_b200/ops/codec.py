@@ -15,7 +15,7 @@ from typing import Any, Sequence
 import torch
 
 from ..config import CompressionConfig
-from . import oracle
+from . import host_codec, oracle
 from .loader import CudaExtensionStatus, require_extension
 from .sizing import estimate_quantized_size
 
@@ -115,6 +115,11 @@ def quantize_tensor(tensor: torch.Tensor, config: CompressionConfig, *,
         prep = None if prepared_out is None else prepared_out.detach().reshape(-1)
         _cuda_quantize(ext, flat, output, res, prep, config)
         return output
+    prep = None if prepared_out is None else prepared_out.detach().reshape(-1)
+    if (host_codec.serves(config) and output.is_contiguous() and (res is None or res.is_contiguous())
+            and (prep is None or prep.is_contiguous())):
+        host_codec.quantize(flat, config, name, output, res, prep)   # C++ twin of the oracle, bit-identical
+        return output
     noise = None
     if config.stochastic:
         noise = torch.rand(est.padded_numel) - 0.5
@@ -182,6 +187,8 @@ def dequantize_tensor(buffer: torch.Tensor, shape, config: CompressionConfig, *,
         else:
             ext.dequant_general(buffer, flat, config.group_size, config.bit, config.topk,
                                 _QUANT_CODE[config.quant_type], config.compact, accumulate)
+    elif host_codec.serves(config) and flat.is_contiguous() and buffer.is_contiguous():
+        host_codec.dequantize(buffer.reshape(-1), numel, config, name, flat, accumulate)
     elif accumulate:
         flat.copy_(oracle.decode_accumulate(buffer, flat, config))
     else:
@@ -221,6 +228,14 @@ def _reduce_into(buffers: Sequence[torch.Tensor], flat_out: torch.Tensor, config
             ext.error_feedback_update(prepared.reshape(-1), flat_out, residual.reshape(-1))
         return
     if is_fast_profile(config):
+        prep_flat = None if prepared is None else prepared.reshape(-1)
+        res_flat = None if residual is None else residual.reshape(-1)
+        if (host_codec.serves(config) and flat_out.is_contiguous() and all(b.is_contiguous() for b in buffers)
+                and (res_flat is None or (res_flat.is_contiguous() and prep_flat.is_contiguous()))):
+            inv = float(torch.tensor(1.0, dtype=torch.float32) / torch.tensor(float(divisor), dtype=torch.float32))
+            host_codec.reduce([b.reshape(-1) for b in buffers], numel, config, name, inv, flat_out, prep_flat,
+                              res_flat)
+            return
         y, y32 = oracle.reduce_mean(buffers, numel, config, name, divisor)
         if residual is not None:
             residual.reshape(-1).copy_(oracle.residual_update(prepared, y32))

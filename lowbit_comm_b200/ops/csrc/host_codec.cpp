@@ -1,0 +1,282 @@
+// Host (CPU) implementation of the wire format: plain C++17, no CUDA, no torch.
+//
+// Two jobs.  (1) The CPU / gloo configuration quantizes and decodes gradient
+// buckets with it instead of composing a dozen torch ops per call.  (2) It is a
+// second, independently written statement of the format: the tests require it
+// to agree bit for bit with the torch oracle (ops/oracle.py) that the sm_100a
+// kernels are checked against.
+//
+// Scope: the production profile family (linear, top-k 0, deterministic
+// rounding; int8 and int4; groups of 16, 32, 64; fp16, bf16 and fp32 sources;
+// planar and compact layouts).  Math as in the reference's kernels
+// (csrc/quantization/quant_pack_kernel.cu:25-163, dequant_kernel.cuh:15-44,
+// dequant_reduce_kernel.cu:38-221): scale = group abs-max stored in the source
+// dtype, q = clamp(rint(p * (L / max(s, 1e-6))), -L, L), decode q * (s / L),
+// fused reduce with one fused multiply-add per payload.
+//
+// Build with -ffp-contract=off: every product and sum below is a separate
+// fp32 rounding except the explicit fmaf.
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+
+namespace {
+
+enum DType { kFP16 = 0, kBF16 = 1, kFP32 = 2 };
+
+inline uint32_t bits_of(float f) {
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    return u;
+}
+inline float float_of(uint32_t u) {
+    float f;
+    std::memcpy(&f, &u, 4);
+    return f;
+}
+
+// ---- fp16 / bf16 <-> fp32, round to nearest even -----------------------------
+inline float half_to_float(uint16_t h) {
+    const uint32_t sign = uint32_t(h & 0x8000u) << 16;
+    const uint32_t exp = (h >> 10) & 0x1Fu;
+    uint32_t man = h & 0x3FFu;
+    if (exp == 0) {
+        if (man == 0) return float_of(sign);
+        int e = -1;                       // subnormal: normalise
+        do {
+            ++e;
+            man <<= 1;
+        } while ((man & 0x400u) == 0);
+        return float_of(sign | uint32_t(127 - 15 - e) << 23 | (man & 0x3FFu) << 13);
+    }
+    if (exp == 31) return float_of(sign | 0x7F800000u | man << 13);
+    return float_of(sign | (exp + 112u) << 23 | man << 13);
+}
+
+inline uint16_t float_to_half(float f) {
+    uint32_t x = bits_of(f);
+    const uint16_t sign = uint16_t((x >> 16) & 0x8000u);
+    x &= 0x7FFFFFFFu;
+    if (x >= 0x7F800000u) return uint16_t(sign | (x > 0x7F800000u ? 0x7E00u : 0x7C00u));
+    if (x >= 0x477FF000u) return uint16_t(sign | 0x7C00u);       // >= 65520 rounds to infinity
+    if (x < 0x38800000u) {                                      // below the smallest normal half
+        if (x < 0x33000000u) return sign;                       // < 2^-25 rounds to zero
+        const uint32_t shift = 126u - (x >> 23);                // 14 ... 24
+        const uint32_t man = (x & 0x7FFFFFu) | 0x800000u;
+        uint32_t r = man >> shift;
+        const uint32_t rem = man & ((1u << shift) - 1u), halfway = 1u << (shift - 1);
+        if (rem > halfway || (rem == halfway && (r & 1u))) ++r;
+        return uint16_t(sign | r);
+    }
+    uint32_t r = (x - 0x38000000u) >> 13;
+    const uint32_t rem = x & 0x1FFFu;
+    if (rem > 0x1000u || (rem == 0x1000u && (r & 1u))) ++r;     // may carry into the exponent: still right
+    return uint16_t(sign | r);
+}
+
+inline float bf16_to_float(uint16_t b) { return float_of(uint32_t(b) << 16); }
+
+inline uint16_t float_to_bf16(float f) {
+    const uint32_t x = bits_of(f);
+    if ((x & 0x7FFFFFFFu) > 0x7F800000u) return uint16_t((x >> 16) | 0x0040u);   // quiet NaN
+    return uint16_t((x + 0x7FFFu + ((x >> 16) & 1u)) >> 16);
+}
+
+template <int DT> struct Src;
+template <> struct Src<kFP16> {
+    using T = uint16_t;
+    static float up(T v) { return half_to_float(v); }
+    static T down(float v) { return float_to_half(v); }
+};
+template <> struct Src<kBF16> {
+    using T = uint16_t;
+    static float up(T v) { return bf16_to_float(v); }
+    static T down(float v) { return float_to_bf16(v); }
+};
+template <> struct Src<kFP32> {
+    using T = uint32_t;
+    static float up(T v) { return float_of(v); }
+    static T down(float v) { return bits_of(v); }
+};
+
+struct Layout {
+    int64_t groups, value_bytes, meta_bytes;
+    bool compact;
+    const uint8_t* values(const uint8_t* base, int64_t g) const {
+        return compact ? base + g * (value_bytes + meta_bytes) : base + g * value_bytes;
+    }
+    const uint8_t* meta(const uint8_t* base, int64_t g) const {
+        return compact ? base + g * (value_bytes + meta_bytes) + value_bytes
+                       : base + groups * value_bytes + g * meta_bytes;
+    }
+    uint8_t* values(uint8_t* base, int64_t g) const { return const_cast<uint8_t*>(values((const uint8_t*)base, g)); }
+    uint8_t* meta(uint8_t* base, int64_t g) const { return const_cast<uint8_t*>(meta((const uint8_t*)base, g)); }
+};
+
+inline Layout layout_of(int64_t numel, int group, int bit, int word, bool compact) {
+    return Layout{(numel + group - 1) / group, int64_t(group) * bit / 8, int64_t(word), compact};
+}
+
+// Position of natural byte `e` of a group's value bytes: words are as wide as the source element
+// and hold their bytes most-significant first.
+inline int wire_pos(int e, int word) { return (e / word) * word + (word - 1 - e % word); }
+
+inline int signed_code(const uint8_t* values, int i, int bit, int word) {
+    if (bit == 8) return int(int8_t(values[wire_pos(i, word)]));
+    const uint8_t byte = values[wire_pos(i / 2, word)];
+    const int field = (i % 2 == 0) ? (byte >> 4) : (byte & 15);
+    return field >= 8 ? field - 16 : field;
+}
+
+template <int DT>
+int quantize(int group, int bit, bool compact, const void* x_, const void* res_, void* prep_, int64_t numel,
+             uint8_t* out) {
+    using S = Src<DT>;
+    using T = typename S::T;
+    const T* x = static_cast<const T*>(x_);
+    const T* res = static_cast<const T*>(res_);
+    T* prep = static_cast<T*>(prep_);
+    const int word = int(sizeof(T));
+    const Layout lay = layout_of(numel, group, bit, word, compact);
+    const float lim = bit == 8 ? 127.0f : 7.0f;
+    float p[64];
+    for (int64_t g = 0; g < lay.groups; ++g) {
+        const int64_t first = g * group;
+        float amax = 0.0f;
+        for (int i = 0; i < group; ++i) {
+            const int64_t idx = first + i;
+            float v = 0.0f;
+            if (idx < numel) {
+                v = S::up(x[idx]);
+                if (res != nullptr) v = S::up(S::down(v + S::up(res[idx])));   // prepared, rounded to T first
+                if (prep != nullptr) prep[idx] = S::down(v);
+            }
+            p[i] = v;
+            const float a = std::fabs(v);
+            if (a > amax) amax = a;
+        }
+        const T stored = S::down(amax);                 // exact: amax is a T value
+        const float safe = std::fmax(S::up(stored), 1e-6f);
+        const float mul = lim / safe;
+        uint8_t* values = lay.values(out, g);
+        for (int i = 0; i < group; i += (bit == 8 ? 1 : 2)) {
+            auto code = [&](float v) {
+                float q = std::nearbyintf(v * mul);
+                q = q < -lim ? -lim : (q > lim ? lim : q);
+                return int(q);
+            };
+            if (bit == 8) {
+                values[wire_pos(i, word)] = uint8_t(code(p[i]) & 255);
+            } else {
+                values[wire_pos(i / 2, word)] = uint8_t(((code(p[i]) & 15) << 4) | (code(p[i + 1]) & 15));
+            }
+        }
+        std::memcpy(lay.meta(out, g), &stored, sizeof(T));
+    }
+    return 0;
+}
+
+template <int DT>
+int dequantize(int group, int bit, bool compact, const uint8_t* payload, int64_t numel, void* out_, bool accumulate) {
+    using S = Src<DT>;
+    using T = typename S::T;
+    T* out = static_cast<T*>(out_);
+    const int word = int(sizeof(T));
+    const Layout lay = layout_of(numel, group, bit, word, compact);
+    const float lim = bit == 8 ? 127.0f : 7.0f;
+    for (int64_t g = 0; g < lay.groups; ++g) {
+        T stored;
+        std::memcpy(&stored, lay.meta(payload, g), sizeof(T));
+        const float step = S::up(stored) / lim;
+        const uint8_t* values = lay.values(payload, g);
+        for (int i = 0; i < group; ++i) {
+            const int64_t idx = g * group + i;
+            if (idx >= numel) break;
+            const T y = S::down(float(signed_code(values, i, bit, word)) * step);
+            out[idx] = accumulate ? S::down(S::up(out[idx]) + S::up(y)) : y;
+        }
+    }
+    return 0;
+}
+
+template <int DT>
+int reduce(int group, int bit, bool compact, const uint8_t* const* payloads, int num, int64_t numel, float scale,
+           void* out_, const void* prep_, void* res_out_) {
+    using S = Src<DT>;
+    using T = typename S::T;
+    T* out = static_cast<T*>(out_);
+    const T* prep = static_cast<const T*>(prep_);
+    T* res_out = static_cast<T*>(res_out_);
+    const int word = int(sizeof(T));
+    const Layout lay = layout_of(numel, group, bit, word, compact);
+    const float lim = bit == 8 ? 127.0f : 7.0f;
+    float acc[64];
+    for (int64_t g = 0; g < lay.groups; ++g) {
+        for (int i = 0; i < group; ++i) acc[i] = 0.0f;
+        for (int r = 0; r < num; ++r) {
+            T stored;
+            std::memcpy(&stored, lay.meta(payloads[r], g), sizeof(T));
+            const float step = S::up(stored) / lim;
+            const uint8_t* values = lay.values(payloads[r], g);
+            for (int i = 0; i < group; ++i)
+                acc[i] = std::fmaf(float(signed_code(values, i, bit, word)), step, acc[i]);   // one rounding
+        }
+        for (int i = 0; i < group; ++i) {
+            const int64_t idx = g * group + i;
+            if (idx >= numel) break;
+            const float y32 = acc[i] * scale;
+            if (res_out != nullptr) res_out[idx] = S::down(S::up(prep[idx]) - y32);   // may alias prep
+            if (out != nullptr) out[idx] = S::down(y32);
+        }
+    }
+    return 0;
+}
+
+bool bad_profile(int dtype, int group, int bit) {
+    return dtype < 0 || dtype > 2 || (group != 16 && group != 32 && group != 64) || (bit != 8 && bit != 4);
+}
+
+}  // namespace
+
+extern "C" {
+
+int lbc_host_abi_version(void) { return 1; }
+
+int lbc_host_quantize(int dtype, int group, int bit, int compact, const void* x, const void* residual,
+                      void* prepared_out, int64_t numel, uint8_t* out) {
+    if (bad_profile(dtype, group, bit) || numel < 0 || (numel > 0 && (x == nullptr || out == nullptr))) return 1;
+    switch (dtype) {
+        case kFP16: return quantize<kFP16>(group, bit, compact != 0, x, residual, prepared_out, numel, out);
+        case kBF16: return quantize<kBF16>(group, bit, compact != 0, x, residual, prepared_out, numel, out);
+        default: return quantize<kFP32>(group, bit, compact != 0, x, residual, prepared_out, numel, out);
+    }
+}
+
+int lbc_host_dequantize(int dtype, int group, int bit, int compact, const uint8_t* payload, int64_t numel, void* out,
+                        int accumulate) {
+    if (bad_profile(dtype, group, bit) || numel < 0 || (numel > 0 && (payload == nullptr || out == nullptr))) return 1;
+    switch (dtype) {
+        case kFP16: return dequantize<kFP16>(group, bit, compact != 0, payload, numel, out, accumulate != 0);
+        case kBF16: return dequantize<kBF16>(group, bit, compact != 0, payload, numel, out, accumulate != 0);
+        default: return dequantize<kFP32>(group, bit, compact != 0, payload, numel, out, accumulate != 0);
+    }
+}
+
+// out = T(sum_r decode_fp32(payload_r) * scale); optionally residual_out = T(float(prepared) - that fp32 value).
+int lbc_host_reduce(int dtype, int group, int bit, int compact, const uint8_t* const* payloads, int num, int64_t numel,
+                    float scale, void* out, const void* prepared, void* residual_out) {
+    if (bad_profile(dtype, group, bit) || numel < 0 || num < 1 || payloads == nullptr) return 1;
+    if ((prepared == nullptr) != (residual_out == nullptr)) return 1;
+    switch (dtype) {
+        case kFP16: return reduce<kFP16>(group, bit, compact != 0, payloads, num, numel, scale, out, prepared, residual_out);
+        case kBF16: return reduce<kBF16>(group, bit, compact != 0, payloads, num, numel, scale, out, prepared, residual_out);
+        default: return reduce<kFP32>(group, bit, compact != 0, payloads, num, numel, scale, out, prepared, residual_out);
+    }
+}
+
+// Element conversions, exported so that the tests can check them exhaustively.
+float lbc_host_half_to_float(uint16_t h) { return half_to_float(h); }
+uint16_t lbc_host_float_to_half(float f) { return float_to_half(f); }
+uint16_t lbc_host_float_to_bf16(float f) { return float_to_bf16(f); }
+
+}  // extern "C"
