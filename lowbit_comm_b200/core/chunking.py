@@ -95,3 +95,24 @@ class GroupShardPlan:
     def shard_valid_groups(self, rank: int) -> int:
         lo = rank * self.shard_groups
         return max(0, min(self.num_groups, lo + self.shard_groups) - lo)
+
+
+def hierarchy_groups(ranks: list[int] | tuple[int, ...], local_group_size: int) -> tuple[list[list[int]], list[list[int]]]:
+    """Contiguous two-level grouping of `ranks` (global ranks of one process group, in group order).
+
+    Returns (local groups, inter groups): `len(ranks) / L` local groups of L consecutive ranks, and L inter
+    groups that hold the ranks with the same position in every local group.  Rank r sits in local group
+    r // L with local rank r % L, and in inter group r % L with inter rank r // L.  This is the membership
+    rule of the reference's hierarchical stages (ccdl_comm/communication/hierarchical_transport.py:178-215;
+    cuda/transports/hierarchical.py:184-265), e.g. 8 ranks as 2 x 4: full -> 4-rank shard -> 2-rank
+    all-reduce of the shard -> 4-rank restore.
+    """
+
+    L = int(local_group_size)
+    world = len(ranks)
+    if L <= 0 or world == 0 or world % L != 0:
+        raise ValueError(f"{world} ranks cannot be split into local groups of {L}")
+    nodes = world // L
+    local = [[ranks[node * L + i] for i in range(L)] for node in range(nodes)]
+    inter = [[ranks[node * L + lane] for node in range(nodes)] for lane in range(L)]
+    return local, inter

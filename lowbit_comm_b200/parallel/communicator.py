@@ -381,15 +381,15 @@ class Communicator:
             return self._subcomms[key]
         dist = _dist()
         base = list(range(self.world_size)) if self.process_group is None else dist.get_process_group_ranks(self.process_group)
-        nodes = self.world_size // L
+        from ..core.chunking import hierarchy_groups
+
+        local_groups, inter_groups = hierarchy_groups(base, L)
         local_pg = inter_pg = None
-        for node in range(nodes):
-            ranks = [base[node * L + i] for i in range(L)]
+        for node, ranks in enumerate(local_groups):
             pg = dist.new_group(ranks)
             if self.rank // L == node:
                 local_pg = pg
-        for lane in range(L):
-            ranks = [base[node * L + lane] for node in range(nodes)]
+        for lane, ranks in enumerate(inter_groups):
             pg = dist.new_group(ranks)
             if self.rank % L == lane:
                 inter_pg = pg

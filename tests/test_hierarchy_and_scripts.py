@@ -1,0 +1,73 @@
+"""Two-level grouping without hardware (8 ranks as 2 x 4, every rank's view), and contract checks on
+the benchmark scripts' pure helpers (flags and formulas stay stable without running a GPU)."""
+
+import importlib.util
+import os
+import sys
+
+import pytest
+
+from lowbit_comm_b200.core.chunking import GroupShardPlan, hierarchy_groups
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _load(path, name):
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, path))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+@pytest.mark.parametrize("rank", range(8))
+def test_two_by_four_membership_from_every_rank(rank):
+    local, inter = hierarchy_groups(list(range(8)), 4)
+    assert local == [[0, 1, 2, 3], [4, 5, 6, 7]] and inter == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    mine_local, mine_inter = local[rank // 4], inter[rank % 4]
+    assert rank in mine_local and rank in mine_inter
+    assert mine_local.index(rank) == rank % 4 and mine_inter.index(rank) == rank // 4   # group-local ranks
+    assert len(mine_local) == 4 and len(mine_inter) == 2                              # 4 -> 2 -> 4
+    # full -> shard (1/4 of the tensor) -> inter all-reduce of that shard -> full: the shard every member of
+    # an inter group holds is the same slice, so their all-reduce is well defined
+    plan = GroupShardPlan.build(1_000_003, 4, 64)
+    lo = (rank % 4) * plan.shard_numel
+    for peer in mine_inter:
+        assert (peer % 4) * plan.shard_numel == lo
+
+
+def test_grouping_follows_the_order_of_the_given_ranks_and_rejects_ragged_splits():
+    local, inter = hierarchy_groups([8, 9, 10, 11, 12, 13], 3)       # a sub-group with global ranks 8..13
+    assert local == [[8, 9, 10], [11, 12, 13]] and inter == [[8, 11], [9, 12], [10, 13]]
+    with pytest.raises(ValueError):
+        hierarchy_groups(list(range(6)), 4)
+    with pytest.raises(ValueError):
+        hierarchy_groups([], 2)
+
+
+def test_sweep_roofline_formula():
+    sweep = _load("benchmarks/allreduce_sweep.py", "allreduce_sweep_script")
+    nbytes = 256 << 20
+    two = sweep.roofline_us(nbytes, 8, 2, True, 6552.3)
+    one = sweep.roofline_us(nbytes, 8, 1, True, 6552.3)
+    payload = nbytes * 66 / 128
+    assert two["t_link_us"] == pytest.approx(2 * payload * 7 / 8 / 770e9 * 1e6)
+    assert one["t_link_us"] == pytest.approx(payload * 7 / 770e9 * 1e6)
+    assert two["roofline_us"] == max(two["t_hbm_us"], two["t_link_us"]) and one["t_link_us"] > two["t_link_us"]
+    # two-stage HBM bytes: 2 x (tensor x 3 + payload) for K1 and K3, 2 payloads for K2
+    assert two["t_hbm_us"] == pytest.approx((6 * nbytes + 4 * payload) / 6552.3e9 * 1e6)
+
+
+def test_bench_contract_flags_and_defaults(monkeypatch):
+    bench = _load("bench.py", "bench_script")
+    monkeypatch.setattr(sys, "argv", ["bench.py"])
+    args = bench.parse_args()
+    assert (args.gpus, args.impl, args.model) == (1, "ours", "gpt2-small") and args.warmup >= 3 and args.steps > 0
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--gpus", "8", "--steps", "7", "--warmup", "4", "--impl", "reference"])
+    args = bench.parse_args()
+    assert (args.gpus, args.steps, args.warmup, args.impl) == (8, 7, 4, "reference")
+    src = open(os.path.join(ROOT, "bench.py")).read()
+    for key in ('"metric"', '"value"', '"unit"', '"n_gpus"', '"ms_per_step"', '"higher_is_better"', '"scaling"',
+                '"vs_baseline"', '"dtype"', '"data"', '"config"', '"e2e"', '"h2d_bytes_per_step"',
+                '"d2h_bytes_per_step"', '"gpu_launches"', '"clocks"'):
+        assert key in src, key
