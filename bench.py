@@ -107,6 +107,8 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--ef-mode", choices=("reference", "local"), default="reference")
     ap.add_argument("--ref-strategy", default="all_gather")
     ap.add_argument("--bucket-mb", type=int, default=None)
+    ap.add_argument("--hook-max-blocks", type=int, default=0,
+                    help="grid cap of the hook's kernels (0 = library default: the full persistent grid)")
     return ap.parse_args()
 
 
@@ -172,7 +174,8 @@ def main() -> None:
         from lowbit_comm_b200 import CompressionConfig, create_ddp_comm_hook
 
         cfg = CompressionConfig(bit=8, group_size=64, topk=0, error_feedback=True, target="ddp_gradient_bucket")
-        hook = create_ddp_comm_hook(cfg, strategy=args.strategy, reduce="mean", ef_mode=args.ef_mode)
+        hook = create_ddp_comm_hook(cfg, strategy=args.strategy, reduce="mean", ef_mode=args.ef_mode,
+                                    max_blocks=args.hook_max_blocks)
         ddp.register_comm_hook(state=None, hook=hook)
     elif args.impl == "reference":
         try:
