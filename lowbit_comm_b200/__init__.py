@@ -12,7 +12,7 @@ from importlib import import_module
 from .abi import CCDL_CORE_ABI, NATIVE_WORK_ABI_VERSION
 from .capability import CapabilityReport, detect
 from .config import CompressionConfig
-from .core import (BackendCapabilities, BackendKey, BackendRegistry, BoundCollectiveWork, ChunkPlan,
+from .core import (AutoStrategySelector, BackendCapabilities, BackendKey, BackendRegistry, BoundCollectiveWork, ChunkPlan,
                    CollectiveWork, CommunicationBackend, CommunicationPlan, CommunicationStage, CompileCache,
                    CompileCacheKey, CompileContext, CompiledCommunicationPlan, CompiledExecutor, CompletionWork,
                    ExecutionCounters, ExecutionCounterSnapshot, ExecutionInfo, GroupShardPlan, ImmediateWork,
