@@ -3,9 +3,12 @@
 from .all_gather import compressed_all_gather
 from .all_reduce import compressed_all_reduce
 from .hierarchical import compressed_hierarchical_all_reduce
-from .native import (all_gather, all_reduce, all_to_all, barrier, broadcast, compile_collective, context_from_tensor,
-                     gather, native_collectives, reduce, reduce_scatter, scatter)
 from .reduce_scatter import compressed_reduce_scatter, compressed_reduce_scatter_shard
+
+# last: importing the submodules above binds their names (all_gather, all_reduce, reduce_scatter) in this
+# package; the pass-through functions of the same names must win
+from .native import (all_gather, all_reduce, all_to_all, barrier, broadcast, compile_collective, context_from_tensor,  # noqa: E402,I001
+                     gather, native_collectives, reduce, reduce_scatter, scatter)
 
 
 def __getattr__(name):
