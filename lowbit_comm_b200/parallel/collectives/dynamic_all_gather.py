@@ -35,7 +35,8 @@ def _numel(shape) -> int:
 class CudaDynamicGatherExecutor:
     def __init__(self, *, shape_class: tuple[int, ...], config: CompressionConfig, dtype: str, group: Any | None = None,
                  extension_status: Any | None = None, metadata_protocol: str = "object_v1",
-                 import_module_fn: Callable[[str], Any] = import_module) -> None:
+                 import_module_fn: Callable[[str], Any] = import_module, quantize: Callable[..., Any] | None = None,
+                 dequantize: Callable[..., Any] | None = None) -> None:
         if metadata_protocol not in METADATA_PROTOCOLS:
             raise ValueError(f"metadata_protocol must be one of {METADATA_PROTOCOLS}")
         if dtype not in TORCH_DTYPES:
@@ -45,6 +46,8 @@ class CudaDynamicGatherExecutor:
         self._status = extension_status
         self.protocol = "tensor_v1" if metadata_protocol == "auto" else metadata_protocol
         self._importer = import_module_fn
+        self._quantize = quantize or codec.quantize_tensor        # injectable, like the reference's transports
+        self._dequantize = dequantize or codec.dequantize_tensor
         self.capacity_numel = _numel(self.shape_class)
         est = estimate_quantized_size(self.capacity_numel, dtype=dtype, config=config)
         self.capacity_bytes = est.quantized_bytes
@@ -91,8 +94,8 @@ class CudaDynamicGatherExecutor:
             local = MetadataPacket(tuple(tensor.shape), self.dtype, payload_bytes, FLAG_EMPTY if n == 0 else 0)
             send = torch.zeros(self.capacity_bytes, dtype=torch.uint8, device=device)
             if n:  # zero-element tensors never reach a kernel
-                codec.quantize_tensor(tensor.contiguous(), self.config, extension_status=self._status,
-                                      output=send[:payload_bytes])
+                self._quantize(tensor.contiguous(), self.config, extension_status=self._status,
+                               output=send[:payload_bytes])
             metas = self._gather_metadata(dist, torch, local, device)
             slots = [torch.empty_like(send) for _ in metas]
             dist.all_gather(slots, send, **self._kw())
@@ -105,8 +108,8 @@ class CudaDynamicGatherExecutor:
                     continue
                 if meta.payload_numel > self.capacity_bytes:
                     raise ValueError("a rank's payload exceeds the compiled shape class")
-                outs.append(codec.dequantize_tensor(slot[:meta.payload_numel], meta.shape, self.config,
-                                                    dtype=self.dtype, extension_status=self._status))
+                outs.append(self._dequantize(slot[:meta.payload_numel], meta.shape, self.config,
+                                             dtype=self.dtype, extension_status=self._status))
             self.execution_counters._record_completed()
             return outs
         except BaseException:
@@ -152,21 +155,32 @@ def compile_dynamic_all_gather(*, shape_class, config: CompressionConfig, dtype:
 def compressed_all_gather_dynamic(tensor: Any, *, config: CompressionConfig, dtype: str = "auto",
                                   extension_status: Any | None = None, group: Any | None = None,
                                   compiled_executor: CudaDynamicGatherExecutor | None = None,
-                                  metadata_protocol: str = "auto") -> list[Any]:
-    """One-shot form: agrees on the largest element count first, then gathers."""
+                                  metadata_protocol: str = "auto",
+                                  import_module_fn: Callable[[str], Any] = import_module,
+                                  quantize: Callable[..., Any] | None = None,
+                                  dequantize: Callable[..., Any] | None = None) -> list[Any]:
+    """One-shot form: agrees on the largest element count first, then gathers.
+
+    `import_module_fn`, `quantize` and `dequantize` are injection points (a fake `torch.distributed`, a
+    recording codec), as in ccdl_comm/communication/dynamic_all_gather.py; injected codecs bypass the
+    executor cache.
+    """
 
     if compiled_executor is not None:
         return compiled_executor.run(tensor)
-    dist = import_module("torch.distributed")
-    torch = import_module("torch")
+    dist = import_module_fn("torch.distributed")
+    torch = import_module_fn("torch")
     name = codec.resolve_dtype(dtype, tensor)
     kw = {} if group is None else {"group": group}
     biggest = torch.tensor([tensor.numel()], dtype=torch.int64, device=tensor.device)
     dist.all_reduce(biggest, op=dist.ReduceOp.MAX, **kw)
     capacity = max(int(biggest.item()), 1)
+    injected = import_module_fn is not import_module or quantize is not None or dequantize is not None
     executor = compile_dynamic_all_gather(shape_class=(capacity,), config=config, dtype=name, group=group,
-                                          extension_status=extension_status, cache=_DEFAULT_CACHE,
-                                          metadata_protocol=metadata_protocol)
+                                          extension_status=extension_status,
+                                          cache=None if injected else _DEFAULT_CACHE,
+                                          metadata_protocol=metadata_protocol, import_module_fn=import_module_fn,
+                                          quantize=quantize, dequantize=dequantize)
     return executor.run(tensor)
 
 
