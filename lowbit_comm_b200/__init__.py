@@ -55,6 +55,13 @@ _LAZY = {
     "CudaWorkspacePool": ".parallel.workspace", "PeerGroup": ".parallel.peer_memory",
     "FusedWorkspace": ".parallel.fused",
     "plan_ddp_compression_strategy": ".parallel.strategy", "plan_bucket_fusion": ".parallel.bucket_fusion",
+    "make_torch_all_gather": ".parallel.torch_transport", "make_torch_all_reduce": ".parallel.torch_transport",
+    "make_torch_compressed_reduce_scatter_shard": ".parallel.transports",
+    "make_torch_compressed_reduce_scatter_all_gather": ".parallel.transports",
+    "make_native_topology_all_reduce": ".parallel.transports",
+    "make_native_topology_reduce_scatter_shard": ".parallel.transports",
+    "make_torch_hierarchical_all_reduce": ".parallel.transports",
+    "make_legacy_topology_all_reduce": ".parallel.transports",
 }
 
 
