@@ -1,7 +1,7 @@
 """Torch-free control plane (plans, registry, compiler, work objects)."""
 
 from .backend import AutoStrategySelector, BackendCapabilities, CommunicationBackend, StrategyChoice
-from .chunking import ChunkPlan, GroupShardPlan, hierarchy_groups
+from .chunking import ChunkPlan, ChunkRange, GroupShardPlan, compile_chunk_plan, hierarchy_groups
 from .compiler import CompileCache, ResolvedPlan, compile, default_registry, resolve_plan
 from .executor import CompileCacheKey, CompiledCommunicationPlan, CompiledExecutor, ObjectIdentity
 from .info import ExecutionCounters, ExecutionCounterSnapshot, ExecutionInfo

@@ -18,6 +18,27 @@ def _ceil_div(a: int, b: int) -> int:
 
 
 @dataclass(frozen=True)
+class ChunkRange:
+    """Half-open range of the flattened (padded) tensor owned by one destination rank."""
+
+    start: int
+    stop: int
+
+    def __post_init__(self) -> None:
+        for value, name in ((self.start, "chunk start"), (self.stop, "chunk stop")):
+            if isinstance(value, bool) or not isinstance(value, int):
+                raise TypeError(f"{name} must be an integer")
+        if self.start < 0:
+            raise ValueError("chunk start must be >= 0")
+        if self.stop < self.start:
+            raise ValueError("chunk stop must be >= start")
+
+    @property
+    def numel(self) -> int:
+        return self.stop - self.start
+
+
+@dataclass(frozen=True)
 class ChunkPlan:
     numel: int
     world_size: int
@@ -54,6 +75,35 @@ class ChunkPlan:
     def _check(self, chunk: int) -> None:
         if not 0 <= chunk < self.world_size:
             raise ValueError("chunk index out of range")
+
+    # the reference's field names (compressed_reduce_scatter.py:28-69)
+    @property
+    def original_numel(self) -> int:
+        return self.numel
+
+    @property
+    def chunks(self) -> tuple[ChunkRange, ...]:
+        return tuple(ChunkRange(*self.bounds(c)) for c in range(self.world_size))
+
+    @property
+    def owner_by_chunk(self) -> tuple[int, ...]:
+        return tuple(range(self.world_size))
+
+    def chunk_for_rank(self, rank: int) -> ChunkRange:
+        if isinstance(rank, bool) or not isinstance(rank, int):
+            raise TypeError("rank must be an integer")
+        if not 0 <= rank < self.world_size:
+            raise ValueError(f"rank must be in [0, {self.world_size})")
+        return ChunkRange(*self.bounds(rank))
+
+
+def compile_chunk_plan(*, original_numel: int, world_size: int) -> ChunkPlan:
+    """The reference's constructor name for `ChunkPlan.build`."""
+
+    for value, name in ((original_numel, "original_numel"), (world_size, "world_size")):
+        if isinstance(value, bool) or not isinstance(value, int):
+            raise TypeError(f"{name} must be an integer")
+    return ChunkPlan.build(original_numel, world_size)
 
 
 @dataclass(frozen=True)

@@ -19,6 +19,11 @@ class CompressedPayload:
     dtype: str
     metadata: Mapping[str, Any] = field(default_factory=dict)
 
+    def with_buffer(self, buffer: Any) -> "CompressedPayload":
+        """Same shape, dtype and metadata around another buffer (what a transport returns after moving it)."""
+
+        return CompressedPayload(buffer, self.shape, self.dtype, dict(self.metadata))
+
 
 @dataclass(frozen=True)
 class GatheredPayloads:
@@ -26,6 +31,10 @@ class GatheredPayloads:
 
     def __post_init__(self) -> None:
         object.__setattr__(self, "payloads", tuple(self.payloads))
+
+    @property
+    def world_size(self) -> int:
+        return len(self.payloads)
 
 
 def payload_buffer(payload: Any) -> Any:

@@ -120,6 +120,24 @@ class CudaStrategyTable:
                                                   strategy="reduce_scatter", **common))
         return cls(tuple(rules))
 
+    @classmethod
+    def from_task13_a6000(cls) -> "CudaStrategyTable":
+        """The reference's own table, for callers that ask for it by name: RTX A6000, fp16, 2 and 4 GPUs,
+        8 Mi - 32 Mi elements, `topology` for full output and `compressed` for shard output, with the
+        speed-ups its Task 13 report published (ccdl_comm/cuda/strategy_table.py:81-107).  Nothing on a B200
+        matches these rules; `for_b200` is the table the CUDA backend registers."""
+
+        published = {("full", 2): 1.6253136683796892, ("full", 4): 1.33102168223003,
+                     ("shard", 2): 2.855439327752976, ("shard", 4): 2.6032121073325847}
+        rules = tuple(
+            CudaStrategyRule(collective="all_reduce" if layout == "full" else "reduce_scatter", output_layout=layout,
+                             device_architecture="nvidia_rtx_a6000", world_size=world, dtype="fp16",
+                             compression=PRODUCTION_PROFILE, min_numel=8_388_608, max_numel=33_554_432,
+                             strategy="topology" if layout == "full" else "compressed", speedup=speedup,
+                             same_semantics_baseline=layout == "full")
+            for (layout, world), speedup in published.items())
+        return cls(rules, policy_id="cuda-task13-a6000-v1", evidence="tests/benchmarks/reports/task13_topology")
+
     def select(self, plan: CommunicationPlan, context: CompileContext) -> StrategyChoice:
         if not isinstance(plan, CommunicationPlan):
             raise TypeError("plan must be a CommunicationPlan")
@@ -137,7 +155,7 @@ class CudaStrategyTable:
                 same = rule.same_semantics_baseline
                 return StrategyChoice(
                     rule.strategy,
-                    f"B200 sweep matched all validated dimensions; observed speedup {rule.speedup:.2f}x",
+                    f"benchmark table {self.policy_id} matched all validated dimensions; observed speedup {rule.speedup:.2f}x",
                     self.policy_id, True, expected_speedup=rule.speedup if same else None,
                     observed_speedup=None if same else rule.speedup,
                     baseline=None if same else "nccl_bf16_full_output_reference", evidence=self.evidence,

@@ -236,3 +236,41 @@ def test_control_plane_never_imports_torch_or_backends():
                 assert "ops" not in name.split(".") and "csrc" not in name, (path.name, name)
                 if path.parent.name == "core":
                     assert "parallel" not in name.split("."), (path.name, name)
+
+
+def test_fused_payload_packer_schema_round_trip():
+    import torch
+
+    from lowbit_comm_b200.parallel.payload import CompressedPayload, GatheredPayloads
+    from lowbit_comm_b200.parallel.payload_packing import (FusedPayloadAllGather, FusedPayloadPacker, TensorFieldSchema,
+                                                          make_fused_payload_all_gather)
+
+    payload = CompressedPayload(torch.arange(128, dtype=torch.int8), (2, 64), "bf16",
+                                {"scales": torch.tensor([0.5, 2.0]), "original_numel": 128, "zeros": torch.zeros(3, dtype=torch.int16)})
+    packer = FusedPayloadPacker.from_payload(payload)
+    assert isinstance(packer.buffer_schema, TensorFieldSchema)
+    assert packer.buffer_schema.byte_count == 128 and packer.buffer_schema.offset == 0
+    assert [(f.name, f.offset, f.byte_count) for f in packer.metadata_schemas] == [("scales", 128, 8), ("zeros", 136, 6)]
+    assert packer.scalar_metadata == {"original_numel": 128} and packer.packed_bytes == 142
+    packed = packer.pack(payload)
+    assert packed.dtype == torch.uint8 and packed.numel() == 142
+    back = packer.unpack(packed, shape=(2, 64), dtype="bf16")
+    assert torch.equal(back.buffer, payload.buffer) and torch.equal(back.metadata["scales"], payload.metadata["scales"])
+    assert back.metadata["original_numel"] == 128 and back.shape == (2, 64) and back.dtype == "bf16"
+    with pytest.raises(ValueError):
+        packer.unpack(packed[:-1], shape=(2, 64), dtype="bf16")
+    with pytest.raises(ValueError):
+        packer.pack(payload.with_buffer(torch.zeros(64, dtype=torch.int8)))      # another buffer shape: schema mismatch
+    assert payload.with_buffer(packed).metadata["original_numel"] == 128
+
+    calls = []
+
+    def byte_all_gather(t):
+        calls.append(t.numel())
+        return GatheredPayloads((t, t.clone()))
+
+    fused = FusedPayloadAllGather(byte_all_gather, packer, (2, 64), "bf16")
+    got = fused(payload)
+    assert got.world_size == 2 and calls == [142] and torch.equal(got.payloads[1].metadata["scales"], payload.metadata["scales"])
+    transport = make_fused_payload_all_gather(byte_all_gather)
+    assert transport(payload).world_size == 2 and transport(payload).world_size == 2 and calls == [142, 142, 142]
