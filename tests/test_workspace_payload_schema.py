@@ -170,7 +170,7 @@ def test_payload_all_gather_variants():
 def test_metadata_packet_round_trip():
     pkt = MetadataPacket((3, 5, 7), "bf16", 1234)
     words = pkt.encode()
-    assert len(words) == PACKET_WORDS and words[:5] == [1, 3, 1, 1234, 0] and words[8:11] == [3, 5, 7]
+    assert len(words) == PACKET_WORDS and words[:5] == [1, 3, 2, 1234, 0] and words[8:11] == [3, 5, 7]
     assert MetadataPacket.decode(words) == pkt and pkt.numel == 105
     both = decode_all(words + MetadataPacket((), "fp32", 0, flags=1).encode(), 2)
     assert both[1].shape == () and both[1].flags == 1
@@ -274,3 +274,32 @@ def test_fused_payload_packer_schema_round_trip():
     assert got.world_size == 2 and calls == [142] and torch.equal(got.payloads[1].metadata["scales"], payload.metadata["scales"])
     transport = make_fused_payload_all_gather(byte_all_gather)
     assert transport(payload).world_size == 2 and transport(payload).world_size == 2 and calls == [142, 142, 142]
+
+
+def test_metadata_packet_function_interface():
+    import torch
+
+    from lowbit_comm_b200.parallel import metadata_packet as mp
+
+    packet = mp.encode_metadata_packet(shape=(3, 0, 5), dtype="bf16", payload_numel=99, torch=torch, device="cpu", flags=1)
+    assert packet.dtype == torch.int64 and packet.numel() == mp.METADATA_PACKET_NUMEL == 16
+    assert packet.tolist() == [1, 3, 2, 99, 1, 0, 0, 0, 3, 0, 5, 0, 0, 0, 0, 0]       # bf16 is code 2 on the wire
+    assert mp.decode_metadata_packet(packet) == {"protocol_version": 1, "shape": (3, 0, 5), "dtype": "bf16",
+                                                 "payload_numel": 99, "flags": 1}
+    reused = torch.zeros(16, dtype=torch.int64)
+    assert mp.write_metadata_packet(reused, shape=(7,), dtype="fp32", payload_numel=0) is reused
+    both = torch.cat([packet, reused])
+    decoded = mp.decode_metadata_packets(both, world_size=2)
+    assert [d["shape"] for d in decoded] == [(3, 0, 5), (7,)] and decoded[1]["dtype"] == "fp32"
+    bad = packet.clone()
+    bad[6] = 4                                            # a reserved word
+    with pytest.raises(RuntimeError):
+        mp.decode_metadata_packet(bad)
+    with pytest.raises(RuntimeError):
+        mp.decode_metadata_packets(both[:-1], world_size=2)
+    with pytest.raises(ValueError):
+        mp.write_metadata_packet(reused, shape=(1,) * 9, dtype="fp16", payload_numel=0)
+    with pytest.raises(TypeError):
+        mp.write_metadata_packet(reused, shape=(1.5,), dtype="fp16", payload_numel=0)
+    with pytest.raises(ValueError):
+        mp.write_metadata_packet(torch.zeros(8, dtype=torch.int64), shape=(1,), dtype="fp16", payload_numel=0)
