@@ -37,3 +37,31 @@ def ext():
     from lowbit_comm_b200.ops.loader import require_extension
 
     return require_extension()
+
+
+def spawn_ranks(worker, make_args, nprocs: int, attempts: int = 2) -> None:
+    """Run `worker(rank, *make_args(port))` as `nprocs` spawned processes rendezvousing on 127.0.0.1.
+
+    The free port is probed and released before the ranks bind it, so another process can take it in
+    between; a failed rendezvous is retried once on a fresh port (a genuine failure fails both times).
+    """
+
+    import socket
+
+    import torch.multiprocessing as mp
+
+    last = None
+    for _ in range(attempts):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        try:
+            mp.start_processes(worker, args=make_args(port), nprocs=nprocs, join=True, start_method="spawn")
+            return
+        except Exception as exc:  # noqa: BLE001
+            last = exc
+            text = str(exc)
+            if not any(k in text for k in ("Address already in use", "EADDRINUSE", "Connection refused",
+                                           "connect() timed out", "failed to connect")):
+                raise
+    raise last

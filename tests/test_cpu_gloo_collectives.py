@@ -1,21 +1,14 @@
 """Real gloo ranks on CPU through the public collectives: the transports' host-side logic end to end."""
 
 import os
-import socket
 import sys
 
 import pytest
 import torch
 import torch.distributed as dist
-import torch.multiprocessing as mp
+from conftest import spawn_ranks
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-
-
-def _free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
 
 
 def _inputs(world, n, seed=0):
@@ -119,4 +112,4 @@ def _worker(rank: int, world: int, port: int) -> None:
 @pytest.mark.timeout(600)
 @pytest.mark.parametrize("world", (2, 4))
 def test_public_collectives_over_gloo(world):
-    mp.start_processes(_worker, args=(world, _free_port()), nprocs=world, join=True, start_method="spawn")
+    spawn_ranks(_worker, lambda port: (world, port), world)

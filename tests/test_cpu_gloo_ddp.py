@@ -7,21 +7,14 @@ the test fast; `examples/cpu_gloo_mlp.py` runs the full 50 steps.
 """
 
 import os
-import socket
 import sys
 
 import pytest
 import torch
 import torch.distributed as dist
-import torch.multiprocessing as mp
+from conftest import spawn_ranks
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-
-
-def _free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
 
 
 def _worker(rank: int, world: int, port: int, mode: str, steps: int, out_dir: str) -> None:
@@ -73,8 +66,7 @@ def _worker(rank: int, world: int, port: int, mode: str, steps: int, out_dir: st
 
 
 def _run(mode: str, steps: int, out_dir: str) -> None:
-    mp.start_processes(_worker, args=(2, _free_port(), mode, steps, out_dir), nprocs=2, join=True,
-                       start_method="spawn")
+    spawn_ranks(_worker, lambda port: (2, port, mode, steps, out_dir), 2)
 
 
 @pytest.mark.timeout(600)

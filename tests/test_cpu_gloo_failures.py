@@ -8,22 +8,15 @@ cache that exception and raise it again on every later wait.
 import datetime
 import json
 import os
-import socket
 import sys
 import time
 
 import pytest
 import torch
 import torch.distributed as dist
-import torch.multiprocessing as mp
+from conftest import spawn_ranks
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-
-
-def _free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
 
 
 def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
@@ -70,8 +63,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str) -> None:
 @pytest.mark.timeout(180)
 def test_a_rank_that_left_turns_the_next_collective_into_an_error(tmp_path):
     world = 2
-    mp.start_processes(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True,
-                       start_method="spawn")
+    spawn_ranks(_worker, lambda port: (world, port, str(tmp_path)), world)
     report = json.load(open(tmp_path / "rank0.json"))
     assert report["outcome"] == "raised", report
     assert report["seconds"] < 60, report
