@@ -131,3 +131,15 @@ def _first_tensor(values: Sequence[Any]):
         if hasattr(v, "is_cuda"):
             return v
     return None
+
+
+def native_work_available(extension_status: Any) -> bool:
+    """Whether the extension carries the native work executor (`CudaExecutor` / `CompressedWork`) with the
+    ABI this package speaks (ccdl_comm/communication/cuda_completion.py:148-156)."""
+
+    from ..abi import NATIVE_WORK_ABI_VERSION
+
+    module = getattr(extension_status, "module", None)
+    return bool(getattr(extension_status, "available", False) and module is not None
+                and hasattr(module, "create_cuda_executor")
+                and getattr(module, "NATIVE_WORK_ABI_VERSION", None) == NATIVE_WORK_ABI_VERSION)

@@ -393,5 +393,51 @@ class ShardCommunicationWorkspaceCache:
         if key is None:
             self._items.clear()
         else:
-            for full in [f for f in self._items if f[0] == key]:
+            for full in [f for f in self._items if f[0][0] == key or f[0] == key]:
                 del self._items[full]
+
+    # The reference's three accessors (ccdl_comm/communication/workspace.py:105-170): one cached buffer per
+    # (bucket, role, index, world size, tensor signature); a changed signature allocates a new one.
+    @staticmethod
+    def _signature(tensor: Any) -> tuple:
+        return (str(getattr(tensor, "device", "")), str(getattr(tensor, "dtype", "")),
+                tuple(getattr(tensor, "shape", ())))
+
+    def get_quantized_chunk(self, bucket_key: Any, chunk_index: int, tensor: Any, config: Any, *, dtype: str,
+                            world_size: int) -> Any:
+        """uint8 payload buffer for chunk `chunk_index` of `tensor` (the send side of the all-to-all)."""
+
+        from ..ops.codec import allocate_quantized_buffer
+
+        key = (bucket_key, world_size, self._signature(tensor), dtype, config)
+        return self.get(key, "send", chunk_index, lambda: allocate_quantized_buffer(tensor, config, dtype=dtype))
+
+    def get_received_payload(self, bucket_key: Any, payload_template: Any, index: int, *, world_size: int,
+                             config: Any) -> Any:
+        """A buffer shaped like `payload_template` for the payload arriving from rank `index`."""
+
+        key = (bucket_key, world_size, self._signature(payload_template), config)
+        return self.get(key, "recv", index, lambda: payload_template.new_empty(payload_template.shape))
+
+    def get_reduced_shard(self, bucket_key: Any, tensor: Any, shape: tuple[int, ...], config: Any, *, dtype: str,
+                          world_size: int, rank: int) -> Any:
+        """The reduced shard of this rank, in the source dtype."""
+
+        key = (bucket_key, world_size, self._signature(tensor), tuple(shape), dtype, config)
+        return self.get(key, "reduced", rank, lambda: tensor.new_empty(tuple(shape)))
+
+
+def _allocate_torch_buffer(key: WorkspaceKey, stream: Any) -> Any:
+    import torch
+
+    dtype = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32, "uint8": torch.uint8,
+             "int64": torch.int64}.get(key.dtype, torch.uint8)
+    return torch.empty(key.shape_class, dtype=dtype, device=key.device)
+
+
+def create_torch_workspace_pool(*, max_cached_bytes: int | None = None,
+                                max_entries: int | None = None) -> CudaWorkspacePool:
+    """A pool whose misses allocate torch tensors lazily (ccdl_comm/cuda/workspace.py:444-455)."""
+
+    return CudaWorkspacePool(allocator=_allocate_torch_buffer, max_cached_bytes=max_cached_bytes,
+                             max_entries=max_entries)

@@ -303,3 +303,40 @@ def test_metadata_packet_function_interface():
         mp.write_metadata_packet(reused, shape=(1.5,), dtype="fp16", payload_numel=0)
     with pytest.raises(ValueError):
         mp.write_metadata_packet(torch.zeros(8, dtype=torch.int64), shape=(1,), dtype="fp16", payload_numel=0)
+
+
+def test_shard_workspace_cache_accessors_and_torch_pool():
+    import types
+
+    import torch
+
+    from lowbit_comm_b200 import CompressionConfig
+    from lowbit_comm_b200.parallel.completion import native_work_available
+    from lowbit_comm_b200.parallel.workspace import (ShardCommunicationWorkspaceCache, WorkspaceKey,
+                                                     create_torch_workspace_pool)
+
+    cfg = CompressionConfig()
+    cache = ShardCommunicationWorkspaceCache()
+    chunk = torch.zeros(640, dtype=torch.bfloat16)
+    a = cache.get_quantized_chunk("bucket0", 1, chunk, cfg, dtype="bf16", world_size=4)
+    assert a.dtype == torch.uint8 and a.numel() == 660
+    assert cache.get_quantized_chunk("bucket0", 1, chunk, cfg, dtype="bf16", world_size=4) is a        # cached
+    assert cache.get_quantized_chunk("bucket0", 2, chunk, cfg, dtype="bf16", world_size=4) is not a    # other chunk
+    assert cache.get_quantized_chunk("bucket0", 1, chunk[:320], cfg, dtype="bf16", world_size=4) is not a  # new shape
+    r = cache.get_received_payload("bucket0", a, 3, world_size=4, config=cfg)
+    assert r.shape == a.shape and r is cache.get_received_payload("bucket0", a, 3, world_size=4, config=cfg)
+    s = cache.get_reduced_shard("bucket0", chunk, (160,), cfg, dtype="bf16", world_size=4, rank=2)
+    assert s.shape == (160,) and s.dtype == torch.bfloat16
+    cache.clear("bucket0")
+    assert cache.get_reduced_shard("bucket0", chunk, (160,), cfg, dtype="bf16", world_size=4, rank=2) is not s
+
+    pool = create_torch_workspace_pool(max_entries=2)
+    key = WorkspaceKey("cuda", "reduce_scatter", "compressed", (128,), "uint8", 4, 8, 64, (), "send", device="cpu")
+    lease = pool.acquire(key, None)
+    assert lease.buffer.dtype == torch.uint8 and lease.buffer.numel() == 128
+
+    assert not native_work_available(types.SimpleNamespace(available=False, module=None))
+    fake = types.SimpleNamespace(create_cuda_executor=lambda: None, NATIVE_WORK_ABI_VERSION=1)
+    assert native_work_available(types.SimpleNamespace(available=True, module=fake))
+    fake.NATIVE_WORK_ABI_VERSION = 2
+    assert not native_work_available(types.SimpleNamespace(available=True, module=fake))
