@@ -103,25 +103,45 @@ def _clone(tensor: Any) -> Any:
 class DDPBucketProcessor:
     """Synchronous compensate -> compress -> all_reduce(payload) -> decompress -> update.
 
-    Only used when an `all_reduce` payload transport is injected
-    (parity: ccdl_comm/communication/ddp.py:33-97).
+    Without an `all_reduce` payload transport the bucket only makes the local quantize / dequantize round
+    trip (single-process use and tests).  Parity: ccdl_comm/communication/ddp.py:33-97.
     """
 
-    def __init__(self, *, config: CompressionConfig, quantize, dequantize, all_reduce,
+    def __init__(self, *, config: CompressionConfig, quantize, dequantize, all_reduce=None,
                  error_feedback: ErrorFeedbackState | None = None) -> None:
         self.config = config
+        self.quantize, self.dequantize, self.all_reduce = quantize, dequantize, all_reduce
         self.error_feedback = error_feedback or ErrorFeedbackState()
-        self._pipeline = CompressedAllReduce(
+        self._pipeline = None if all_reduce is None else CompressedAllReduce(
             config=config,
             compress=lambda t, c: coerce_payload(quantize(t, c), shape=tuple(t.shape), dtype="auto"),
             all_reduce=all_reduce, decompress=dequantize)
+
+    @classmethod
+    def from_cuda_codec(cls, config: CompressionConfig, *, extension_status: Any | None = None,
+                        error_feedback: ErrorFeedbackState | None = None) -> "DDPBucketProcessor":
+        """Processor over the package codec (the sm_100a kernels for CUDA buckets, the host codec otherwise)."""
+
+        from ..ops import codec
+
+        def quantize(tensor: Any, active: CompressionConfig) -> Any:
+            return codec.quantize_tensor(tensor, active, extension_status=extension_status)
+
+        def dequantize(payload: Any, shape: tuple[int, ...], active: CompressionConfig, dtype: str) -> Any:
+            return codec.dequantize_tensor(payload, shape, active, dtype=dtype, extension_status=extension_status)
+
+        return cls(config=config, quantize=quantize, dequantize=dequantize, error_feedback=error_feedback)
 
     def process(self, bucket: Any, *, dtype: str, reduce: str = "mean") -> Any:
         key = _bucket_key(bucket)
         original = bucket.buffer()
         use_ef = self.config.error_feedback
         prepared = self.error_feedback.compensate(key, original) if use_ef else original
-        restored = self._pipeline.run(prepared, shape=tuple(prepared.shape), dtype=dtype, reduce=reduce)
+        if self._pipeline is None:
+            payload = self.quantize(prepared, self.config)
+            restored = self.dequantize(payload, tuple(prepared.shape), self.config, dtype)
+        else:
+            restored = self._pipeline.run(prepared, shape=tuple(prepared.shape), dtype=dtype, reduce=reduce)
         if use_ef:
             self.error_feedback.update(key, original=prepared, transmitted=restored)
         return restored

@@ -183,3 +183,32 @@ def test_argument_validation_and_annotations():
 def test_package_import_is_torch_free():
     code = "import sys, lowbit_comm_b200 as l; l.CompressionConfig(); l.CompileCache(); assert 'torch' not in sys.modules"
     subprocess.run([sys.executable, "-c", code], check=True, cwd=str(__import__("pathlib").Path(__file__).parents[1]))
+
+
+def test_bucket_processor_from_cuda_codec_round_trips_locally():
+    import torch
+
+    from lowbit_comm_b200 import CompressionConfig
+    from lowbit_comm_b200.ops import oracle
+    from lowbit_comm_b200.parallel.ddp_hook import DDPBucketProcessor
+
+    class Bucket:
+        def __init__(self, t):
+            self._t = t
+
+        def buffer(self):
+            return self._t
+
+        def index(self):
+            return 0
+
+    cfg = CompressionConfig()
+    proc = DDPBucketProcessor.from_cuda_codec(cfg)
+    assert proc.all_reduce is None and callable(proc.quantize) and callable(proc.dequantize)
+    x = (torch.randn(64 * 9 + 5, generator=torch.Generator().manual_seed(2)) * 0.1).to(torch.bfloat16)
+    first = proc.process(Bucket(x.clone()), dtype="bf16")
+    want = oracle.decode(oracle.encode(x, cfg), x.numel(), cfg, "bf16")
+    assert torch.equal(first, want)
+    residual = proc.error_feedback.get(0) if proc.error_feedback.get(0) is not None else None
+    second = proc.process(Bucket(x.clone()), dtype="bf16")                       # second step: residual is added first
+    assert residual is None or not torch.equal(second, first) or torch.equal(residual, torch.zeros_like(residual))
