@@ -310,6 +310,31 @@ def register_cuda_backends(registry: BackendRegistry, *, extension_status: CudaE
         registry.register_strategy_selector(backend_name, (strategy_table or CudaStrategyTable.for_b200()).as_selector())
 
 
+def default_operation_factories() -> dict[OperationKey, Callable | None]:
+    """The (collective, strategy, output layout) keys the CUDA backend serves out of the box.  The reference
+    maps each key to a host-side operation builder (ccdl_comm/cuda/compiler.py:122-146); here one backend
+    object compiles all of them onto the communicator, so the values are None: a placeholder that callers
+    override per key to inject their own builder `(plan, context) -> executor`."""
+
+    return {key: None for key in CUDA_BACKEND_KEYS}
+
+
+def compile_cuda_plan(plan: CommunicationPlan, context: CompileContext,
+                      extension_status: CudaExtensionStatus | None = None, *,
+                      operation_factories: Mapping[OperationKey, Callable] | None = None, allow_cpu: bool = False):
+    """Compile one validated plan straight with the CUDA backend, without a registry
+    (ccdl_comm/cuda/compiler.py:82-119).  Entries of `operation_factories` that are None keep the built-in path."""
+
+    given = None
+    if operation_factories is not None:
+        given = {k: v for k, v in operation_factories.items() if v is not None} or None
+    backend = CudaCommunicationBackend(extension_status=extension_status, operation_factories=given,
+                                       allow_cpu=allow_cpu)
+    if given is not None:                      # injected builders add to the built-in keys, they do not replace them
+        backend._keys = tuple(dict.fromkeys((*CUDA_BACKEND_KEYS, *given)))
+    return backend.compile(plan, context)
+
+
 _SHORTCUT_LOCK = threading.Lock()
 _SHORTCUT_REGISTRIES: dict[tuple, BackendRegistry] = {}
 _SHORTCUT_CACHE = CompileCache(max_entries=256)

@@ -61,6 +61,14 @@ class CudaDynamicGatherExecutor:
         self.execution_counters = ExecutionCounters()
         self.host_sync_count = 0
 
+    @property
+    def metadata_protocol(self) -> str:
+        return self.protocol
+
+    @property
+    def metadata_protocol_version(self) -> int:
+        return 1
+
     def _kw(self) -> dict:
         return {} if self.group is None else {"group": self.group}
 

@@ -170,6 +170,12 @@ NATIVE_BUILDERS: dict[str, Callable] = {
 }
 NATIVE_COLLECTIVES = tuple(NATIVE_BUILDERS)
 
+# the reference's builder names (ccdl_comm/cuda/native_collectives.py:116-330): `(plan, context, dist) -> operation`
+build_native_all_reduce, build_native_all_gather, build_native_reduce_scatter = \
+    _b_all_reduce, _b_all_gather, _b_reduce_scatter
+build_native_all_to_all, build_native_broadcast, build_native_reduce = _b_all_to_all, _b_broadcast, _b_reduce
+build_native_gather, build_native_scatter, build_native_barrier = _b_gather, _b_scatter, _b_barrier
+
 
 class NativeCollectiveExecutor:
     def __init__(self, operation: Callable, execution_info: ExecutionInfo) -> None:
@@ -226,3 +232,6 @@ def compile_native_collective(plan: CommunicationPlan, context: CompileContext, 
         compression_ratio=1.0, workspace_cache_hit=False, async_capable=True, fast_path="cuda_native_nccl",
         details={"collective": plan.collective, "root": plan.root, "reduce_op": plan.reduce_op})
     return NativeCollectiveExecutor(builder(plan, context, active), info)
+
+
+CudaNativeCollectiveExecutor = NativeCollectiveExecutor   # the reference's class name

@@ -157,6 +157,13 @@ class CudaP2PExecutor:
     def metadata(self) -> P2PMetadata:
         return self._metadata
 
+    # the frozen endpoint description, under the reference's attribute names
+    direction = property(lambda self: self._direction)
+    peer = property(lambda self: self._peer)
+    group = property(lambda self: self._group)
+    tag = property(lambda self: self._tag)
+    config = property(lambda self: self._config)
+
     def _validate(self, tensor: Any) -> None:
         if tuple(tensor.shape) != self._shape:
             raise ValueError(f"tensor shape {tuple(tensor.shape)} does not match compiled shape {self._shape}")
@@ -203,6 +210,13 @@ class CudaP2PExecutor:
             return tensor
 
         return CompletionWork(tensor, handle=handle, complete=complete, resources=(payload, tensor))
+
+
+def compile_p2p_executor(*, direction: str, peer: int | None, tensor: Any, config: CompressionConfig,
+                         **kwargs: Any) -> CudaP2PExecutor:
+    """One immutable quantized point-to-point endpoint (ccdl_comm/cuda/p2p_executor.py:220-236)."""
+
+    return CudaP2PExecutor(direction=direction, peer=peer, tensor=tensor, config=config, **kwargs)
 
 
 def compile_qsend(tensor: Any, dst: int, *, config: CompressionConfig, **kw) -> CudaP2PExecutor:

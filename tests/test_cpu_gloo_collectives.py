@@ -102,6 +102,15 @@ def _worker(rank: int, world: int, port: int) -> None:
         assert result.shard.data_ptr() == lease.buffer.data_ptr() and work.execution_info.fast_path == "torch_fallback"
         lease.release_after(result.shard)
         assert plan.executor.workspace_stats.in_flight_bytes == 0
+        # the registry-free entry point with the reference's name
+        from lowbit_comm_b200.parallel.backend_cuda import compile_cuda_plan, default_operation_factories
+
+        assert ("all_reduce", "all_gather", "full") in default_operation_factories()
+        direct = compile_cuda_plan(lbc.CommunicationPlan(collective="all_reduce", strategy="all_gather", compression=cfg,
+                                                         async_op=False),
+                                   lbc.CompileContext(rank=rank, world_size=world, device="cpu", shape=(n,), dtype="bf16"),
+                                   allow_cpu=True)
+        assert torch.equal(direct.run(xs[rank].clone()).wait().view(torch.uint8), one.view(torch.uint8))
         auto = compile_cuda_shortcut(xs[rank], collective="all_reduce", strategy="auto", output_layout="full", config=cfg)
         assert auto.execution_info.requested_strategy == "auto"
         assert auto.execution_info.details["strategy_policy_id"] == "b200-nvlink5-v1"
