@@ -7,6 +7,9 @@ from .executor import CompileCacheKey, CompiledCommunicationPlan, CompiledExecut
 from .info import ExecutionCounters, ExecutionCounterSnapshot, ExecutionInfo
 from .plan import CommunicationPlan, CommunicationStage, CompileContext, WorkspacePolicy
 from .registry import BackendKey, BackendRegistry
+from .schedules import (DirectExchangeSchedule, PipelinedRingSchedule, RingAllGatherStep, RingReduceScatterStep,
+                        TreeEdge, TreeSchedule, compile_direct_exchange_schedule, compile_pipelined_ring_schedule,
+                        compile_tree_schedule)
 from .shard import ReducedShard
 from .work import (BoundCollectiveWork, CollectiveWork, CompletionWork, ImmediateWork,
                    bind_execution_work)

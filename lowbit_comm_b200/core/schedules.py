@@ -1,0 +1,180 @@
+"""Rank-local communication schedules as plain data (torch-free).
+
+The reference drives its ring, tree and hierarchical all-reduce from immutable schedules compiled once per
+(world size, rank): `PipelinedRingSchedule`, `TreeSchedule`, hierarchical stages
+(ccdl_comm/cuda/transports/pipelined_ring.py:14-120, 285-332; tree.py:15-75, 277-307).  On an NVSwitch
+node this library executes none of them hop by hop: every strategy name lands on the direct one-hop
+exchange of the fused kernels (`DirectExchangeSchedule` below states who writes to and reads from whom).
+The ring and tree schedules are still compiled here, with the reference's field names, for tools and
+callers that inspect them, and so that the topology definitions stay testable: `tests/test_schedules.py`
+executes them on integers and checks that they reduce and restore every chunk.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from .chunking import ChunkPlan, ChunkRange
+
+
+def _index(value: object, bound: int, name: str) -> int:
+    if isinstance(value, bool) or not isinstance(value, int):
+        raise TypeError(f"{name} must be an integer")
+    if not 0 <= value < bound:
+        raise ValueError(f"{name} must be in [0, {bound})")
+    return value
+
+
+def _plan(chunk_plan: object) -> ChunkPlan:
+    if not isinstance(chunk_plan, ChunkPlan):
+        raise TypeError("chunk_plan must be a ChunkPlan")
+    return chunk_plan
+
+
+# ---- ring ----------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class RingReduceScatterStep:
+    """Step s of the reduce-scatter: send one partially reduced chunk to the next rank, receive another from
+    the previous rank and add it.  `received_contributors` are the ranks already summed into what arrives."""
+
+    step_index: int
+    send_peer: int
+    recv_peer: int
+    send_chunk_owner: int
+    recv_chunk_owner: int
+    received_contributors: tuple[int, ...]
+    send_chunk: ChunkRange
+    recv_chunk: ChunkRange
+
+
+@dataclass(frozen=True)
+class RingAllGatherStep:
+    """Step s of the all-gather that follows: pass a finished chunk on, receive the one before it."""
+
+    step_index: int
+    send_peer: int
+    recv_peer: int
+    send_chunk_owner: int
+    recv_chunk_owner: int
+    send_chunk: ChunkRange
+    recv_chunk: ChunkRange
+
+
+@dataclass(frozen=True)
+class PipelinedRingSchedule:
+    chunk_plan: ChunkPlan
+    rank: int
+    steps: tuple[RingReduceScatterStep, ...]
+    gather_steps: tuple[RingAllGatherStep, ...]
+
+    @property
+    def local_chunk(self) -> ChunkRange:
+        """The shard this rank owns once the reduce-scatter is done."""
+
+        return self.chunk_plan.chunk_for_rank(self.rank)
+
+
+def compile_pipelined_ring_schedule(*, chunk_plan: ChunkPlan, rank: int) -> PipelinedRingSchedule:
+    """Ring over ranks 0..W-1, data flowing r -> r + 1.  In reduce-scatter step s rank r forwards the chunk
+    that will end at rank r - s - 1 and receives the one bound for r - s - 2, so after W - 1 steps it holds
+    the complete sum of chunk r; the all-gather then walks the finished chunks around the same way."""
+
+    plan = _plan(chunk_plan)
+    W = plan.world_size
+    r = _index(rank, W, "rank")
+    nxt, prv = (r + 1) % W, (r - 1) % W
+    steps, gathers = [], []
+    for s in range(W - 1):
+        out_owner, in_owner = (r - s - 1) % W, (r - s - 2) % W
+        steps.append(RingReduceScatterStep(
+            step_index=s, send_peer=nxt, recv_peer=prv, send_chunk_owner=out_owner, recv_chunk_owner=in_owner,
+            received_contributors=tuple((r - s - 1 + k) % W for k in range(s + 1)),
+            send_chunk=plan.chunk_for_rank(out_owner), recv_chunk=plan.chunk_for_rank(in_owner)))
+        g_out, g_in = (r - s) % W, (r - s - 1) % W
+        gathers.append(RingAllGatherStep(
+            step_index=s, send_peer=nxt, recv_peer=prv, send_chunk_owner=g_out, recv_chunk_owner=g_in,
+            send_chunk=plan.chunk_for_rank(g_out), recv_chunk=plan.chunk_for_rank(g_in)))
+    return PipelinedRingSchedule(plan, r, tuple(steps), tuple(gathers))
+
+
+# ---- tree ----------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class TreeEdge:
+    """Child-to-parent edge of the reduction tree; the broadcast uses it in the other direction."""
+
+    child_rank: int
+    parent_rank: int
+
+    def __post_init__(self) -> None:
+        if self.child_rank == self.parent_rank:
+            raise ValueError("child_rank and parent_rank must differ")
+
+
+@dataclass(frozen=True)
+class TreeSchedule:
+    chunk_plan: ChunkPlan
+    rank: int
+    root: int
+    parent: int | None
+    children: tuple[int, ...]
+    reduce_edges: tuple[TreeEdge, ...]
+    broadcast_edges: tuple[TreeEdge, ...]
+
+    @property
+    def local_chunk(self) -> ChunkRange:
+        return self.chunk_plan.chunk_for_rank(self.rank)
+
+
+def tree_edges(world_size: int, root: int = 0) -> tuple[TreeEdge, ...]:
+    """Heap-ordered binary tree over the ranks renumbered from `root`: position p hangs under (p - 1) // 2.
+    Edges come deepest position first, so replaying them in order reduces every subtree before its parent."""
+
+    if isinstance(world_size, bool) or not isinstance(world_size, int) or world_size <= 0:
+        raise ValueError("world_size must be a positive integer")
+    root = _index(root, world_size, "root")
+    at = [(root + p) % world_size for p in range(world_size)]
+    return tuple(TreeEdge(child_rank=at[p], parent_rank=at[(p - 1) // 2]) for p in range(world_size - 1, 0, -1))
+
+
+def compile_tree_schedule(*, chunk_plan: ChunkPlan, rank: int, root: int = 0) -> TreeSchedule:
+    plan = _plan(chunk_plan)
+    r = _index(rank, plan.world_size, "rank")
+    edges = tree_edges(plan.world_size, root)
+    parent = next((e.parent_rank for e in edges if e.child_rank == r), None)
+    children = tuple(e.child_rank for e in edges if e.parent_rank == r)
+    return TreeSchedule(plan, r, _index(root, plan.world_size, "root"), parent, children, edges,
+                        tuple(reversed(edges)))
+
+
+# ---- what the fused kernels do -------------------------------------------------------------------------
+@dataclass(frozen=True)
+class DirectExchangeSchedule:
+    """One-hop exchange of the two-stage fused all-reduce, from rank `rank`'s point of view.
+
+    scatter: this rank's quantize kernel stores shard d of its tensor into rank d's receive slot `rank`
+    (all d, its own included), in the order `scatter_order` (rotated by the rank, so no two senders start
+    at the same receiver); reduce: it sums the W slots of its own shard; gather: its decode kernel loads
+    the reduced shard s from rank s, in the order `gather_order`.
+    """
+
+    chunk_plan: ChunkPlan
+    rank: int
+    scatter_order: tuple[int, ...]
+    gather_order: tuple[int, ...]
+
+    @property
+    def local_chunk(self) -> ChunkRange:
+        return self.chunk_plan.chunk_for_rank(self.rank)
+
+    @property
+    def link_crossings(self) -> int:
+        """Times a byte of payload crosses NVLink per rank and direction: (W - 1) / W of it, twice."""
+
+        return 2
+
+
+def compile_direct_exchange_schedule(*, chunk_plan: ChunkPlan, rank: int) -> DirectExchangeSchedule:
+    plan = _plan(chunk_plan)
+    r = _index(rank, plan.world_size, "rank")
+    order = tuple((r + k) % plan.world_size for k in range(plan.world_size))
+    return DirectExchangeSchedule(plan, r, order, order)
