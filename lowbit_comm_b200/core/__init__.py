@@ -4,6 +4,8 @@ from .backend import AutoStrategySelector, BackendCapabilities, CommunicationBac
 from .chunking import ChunkPlan, ChunkRange, GroupShardPlan, compile_chunk_plan, hierarchy_groups
 from .compiler import CompileCache, ResolvedPlan, compile, default_registry, resolve_plan
 from .executor import CompileCacheKey, CompiledCommunicationPlan, CompiledExecutor, ObjectIdentity
+from .hierarchy import (CompiledStage, HierarchicalExecutor, StageExecution, canonical_hierarchical_stages,
+                        compile_hierarchical_stages)
 from .info import ExecutionCounters, ExecutionCounterSnapshot, ExecutionInfo
 from .plan import CommunicationPlan, CommunicationStage, CompileContext, WorkspacePolicy
 from .registry import BackendKey, BackendRegistry

@@ -195,6 +195,8 @@ class CudaCommunicationBackend:
         comm = self._communicator(context)
         info = self._info(plan, context)
         cfg, op, dtype = plan.compression, plan.reduce_op, normalize_dtype(context.dtype)
+        if plan.collective == "all_reduce" and plan.strategy == "hierarchical" and plan.stages:
+            return CudaAllReduceExecutor(self._staged_hierarchy(plan, context, dtype), info)
         if plan.collective == "all_reduce":
             strategy = plan.strategy
 
@@ -240,6 +242,56 @@ class CudaCommunicationBackend:
         return CompressedReduceScatterExecutor(shard_operation, info, shard_numel=shard_numel, pool=pool, key=wkey,
                                                completion_manager=CudaCompletionManager(extension_status=self._status),
                                                stream_provider=_current_stream_provider(context.device))
+
+    def _staged_hierarchy(self, plan: CommunicationPlan, context: CompileContext, dtype: str):
+        """A plan that spells out its three stages is compiled stage by stage (`core/hierarchy.py`); every stage
+        runs on the communicator of its own process group: fused kernels inside the local group for the
+        reduce-scatter and the gather, a compressed all-reduce of the shard between the groups."""
+
+        from importlib import import_module
+
+        from ..core.hierarchy import compile_hierarchical_stages
+
+        torch = import_module("torch")
+        dist = import_module("torch.distributed")
+        n = _numel(context.shape)
+        op = plan.reduce_op
+
+        def bind(stage, stage_context):
+            comm = self._communicator(stage_context)
+            cfg = stage.compression or plan.compression
+            if stage.collective == "reduce_scatter":
+                return lambda tensor: comm.reduce_scatter_shard(tensor, config=cfg, op=op, dtype=dtype).shard
+            if stage.collective == "all_reduce":
+                strategy = "auto" if stage.strategy in ("topology", "compressed") else stage.strategy
+
+                def inter(piece):
+                    if comm.world_size == 1:
+                        return piece
+                    return comm.all_reduce(piece, config=cfg, op=op, strategy=strategy, dtype=dtype)
+
+                return inter
+
+            def gather(piece):
+                if stage.strategy == "native_nccl":
+                    parts = [torch.empty_like(piece) for _ in range(comm.world_size)]
+                    kw = {} if stage_context.process_group is None else {"group": stage_context.process_group}
+                    dist.all_gather(parts, piece.contiguous(), **kw)
+                else:
+                    parts = comm.all_gather(piece, config=cfg, dtype=dtype)
+                return torch.cat([p.reshape(-1) for p in parts])[:n].reshape(context.shape)
+
+            return gather
+
+        chain = compile_hierarchical_stages(plan, context, operation_factory=bind,
+                                            group_factory=lambda ranks: dist.new_group(list(ranks)))
+
+        def operation(tensor):
+            _check_tensor(tensor, context)
+            work = chain.run(tensor)
+            return work if plan.async_op else work.wait()
+
+        return operation
 
     def _communicator(self, context: CompileContext):
         if self._communicator_factory is not None:
