@@ -6,9 +6,10 @@
 // to agree bit for bit with the torch oracle (ops/oracle.py) that the sm_100a
 // kernels are checked against.
 //
-// Scope: the production profile family (linear, top-k 0, deterministic
-// rounding; int8 and int4; groups of 16, 32, 64; fp16, bf16 and fp32 sources;
-// planar and compact layouts).  Math as in the reference's kernels
+// Scope: deterministic rounding; int8 and int4; groups of 16, 32, 64; fp16,
+// bf16 and fp32 sources; planar and compact layouts; top-k 0, 1 and 2; the
+// linear code and the four 4-bit code-books.  The fused multi-payload reduce
+// serves the production profile family (linear, top-k 0).  Math as in the reference's kernels
 // (csrc/quantization/quant_pack_kernel.cu:25-163, dequant_kernel.cuh:15-44,
 // dequant_reduce_kernel.cu:38-221): scale = group abs-max stored in the source
 // dtype, q = clamp(rint(p * (L / max(s, 1e-6))), -L, L), decode q * (s / L),
@@ -232,6 +233,169 @@ int reduce(int group, int bit, bool compact, const uint8_t* const* payloads, int
     return 0;
 }
 
+
+// ---- general profiles: top-k outliers and 4-bit code-books -------------------------------------------
+// Metadata words per group (each as wide as the source element): [scale] (+ [idx1 | idx2 << 8][top1][top2]).
+inline int meta_words(int topk) { return topk == 0 ? 1 : (topk == 1 ? 3 : 4); }
+
+// 15 code points in [-1, 1] plus +inf as the upper sentinel of the search (csrc/quantization/inner.cuh:9-96).
+const float kCodebooks[4][16] = {
+    {-1.0f, (float)-0.815410147, (float)-0.655160150, (float)-0.510228027, (float)-0.375324982, (float)-0.246951370,
+     (float)-0.122538030, 0.0f, (float)0.122538030, (float)0.246951370, (float)0.375324982, (float)0.510228027,
+     (float)0.655160150, (float)0.815410147, 1.0f, INFINITY},
+    {-1.0f, (float)-0.85714286, (float)-0.71428571, (float)-0.57142857, (float)-0.42857143, (float)-0.28571429,
+     (float)-0.14285714, 0.0f, (float)0.14285714, (float)0.28571429, (float)0.42857143, (float)0.57142857,
+     (float)0.71428571, (float)0.85714286, 1.0f, INFINITY},
+    {-1.0f, -0.5f, -0.25f, -0.125f, -0.0625f, -0.03125f, -0.015625f, 0.0f, 0.015625f, 0.03125f, 0.0625f, 0.125f,
+     0.25f, 0.5f, 1.0f, INFINITY},
+    {-1.0f, (float)-0.6666666666666666, -0.5f, (float)-0.3333333333333333, -0.25f, (float)-0.16666666666666666,
+     -0.125f, 0.0f, 0.125f, (float)0.16666666666666666, 0.25f, (float)0.3333333333333333, 0.5f,
+     (float)0.6666666666666666, 1.0f, INFINITY},
+};
+
+struct GeneralLayout {
+    int64_t groups, value_bytes, meta_bytes;
+    bool compact;
+    int64_t values_at(int64_t g) const { return compact ? g * (value_bytes + meta_bytes) : g * value_bytes; }
+    int64_t meta_at(int64_t g) const {
+        return compact ? g * (value_bytes + meta_bytes) + value_bytes : groups * value_bytes + g * meta_bytes;
+    }
+};
+
+template <int DT>
+int quantize_general(int group, int bit, int topk, int quant_type, bool compact, const void* x_, const void* res_,
+                     void* prep_, int64_t numel, uint8_t* out) {
+    using S = Src<DT>;
+    using T = typename S::T;
+    const T* x = static_cast<const T*>(x_);
+    const T* res = static_cast<const T*>(res_);
+    T* prep = static_cast<T*>(prep_);
+    const int word = int(sizeof(T));
+    const GeneralLayout lay{(numel + group - 1) / group, int64_t(group) * bit / 8, int64_t(meta_words(topk)) * word,
+                            compact};
+    const bool last_wins = DT == kFP32;       // tie rule of the reference kernels: fp32 keeps the last maximum
+    const float lim = bit == 8 ? 127.0f : 7.0f;
+    T raw[64];
+    float v[64];
+    for (int64_t g = 0; g < lay.groups; ++g) {
+        for (int i = 0; i < group; ++i) {
+            const int64_t idx = g * group + i;
+            T bits = S::down(0.0f);
+            if (idx < numel) {
+                bits = x[idx];
+                if (res != nullptr) bits = S::down(S::up(x[idx]) + S::up(res[idx]));
+                if (prep != nullptr) prep[idx] = bits;
+            }
+            raw[i] = bits;
+            v[i] = S::up(bits);
+        }
+        int top_idx[2] = {0, 0};
+        T top_val[2] = {S::down(0.0f), S::down(0.0f)};
+        bool taken[64] = {false};
+        for (int k = 0; k < topk; ++k) {
+            int best = -1;
+            float best_mag = -1.0f;
+            for (int i = 0; i < group; ++i) {
+                if (taken[i]) continue;
+                const float mag = std::fabs(v[i]);
+                if (mag > best_mag || (last_wins && mag == best_mag)) {
+                    best_mag = mag;
+                    best = i;
+                }
+            }
+            taken[best] = true;
+            top_idx[k] = best;
+            top_val[k] = raw[best];
+        }
+        float amax = 0.0f;
+        for (int i = 0; i < group; ++i) {
+            if (taken[i]) v[i] = 0.0f;
+            const float a = std::fabs(v[i]);
+            if (a > amax) amax = a;
+        }
+        const T stored = S::down(amax);
+        const float safe = std::fmax(S::up(stored), 1e-6f);
+        int codes[64];
+        if (quant_type == 0) {
+            const float mul = lim / safe;
+            for (int i = 0; i < group; ++i) {
+                float q = std::nearbyintf(v[i] * mul);
+                q = q < -lim ? -lim : (q > lim ? lim : q);
+                codes[i] = int(q) & (bit == 8 ? 255 : 15);
+            }
+        } else {
+            const float* table = kCodebooks[quant_type - 1];
+            for (int i = 0; i < group; ++i) {
+                const float t = v[i] / safe;
+                int low = 0;                                   // entries of table[0..15) that are <= t, minus one
+                while (low < 15 && table[low] <= t) ++low;
+                low = low - 1 < 0 ? 0 : (low - 1 > 14 ? 14 : low - 1);
+                const float gap = table[low + 1] - table[low];
+                codes[i] = low + ((t - table[low]) > gap / 2 ? 1 : 0);
+            }
+        }
+        uint8_t* values = out + lay.values_at(g);
+        if (bit == 8) {
+            for (int i = 0; i < group; ++i) values[wire_pos(i, word)] = uint8_t(codes[i]);
+        } else {
+            for (int i = 0; i < group; i += 2) values[wire_pos(i / 2, word)] = uint8_t((codes[i] << 4) | codes[i + 1]);
+        }
+        T meta[4] = {stored, T(0), T(0), T(0)};
+        if (topk >= 1) {
+            meta[1] = T(top_idx[0] | (topk == 2 ? top_idx[1] << 8 : 0));
+            meta[2] = top_val[0];
+            if (topk == 2) meta[3] = top_val[1];
+        }
+        std::memcpy(out + lay.meta_at(g), meta, size_t(meta_words(topk)) * sizeof(T));
+    }
+    return 0;
+}
+
+template <int DT>
+int dequantize_general(int group, int bit, int topk, int quant_type, bool compact, const uint8_t* payload,
+                       int64_t numel, void* out_, bool accumulate) {
+    using S = Src<DT>;
+    using T = typename S::T;
+    T* out = static_cast<T*>(out_);
+    const int word = int(sizeof(T));
+    const GeneralLayout lay{(numel + group - 1) / group, int64_t(group) * bit / 8, int64_t(meta_words(topk)) * word,
+                            compact};
+    const float lim = bit == 8 ? 127.0f : 7.0f;
+    for (int64_t g = 0; g < lay.groups; ++g) {
+        T meta[4] = {T(0), T(0), T(0), T(0)};
+        std::memcpy(meta, payload + lay.meta_at(g), size_t(meta_words(topk)) * sizeof(T));
+        const float scale = S::up(meta[0]);
+        const uint8_t* values = payload + lay.values_at(g);
+        T decoded[64];
+        for (int i = 0; i < group; ++i) {
+            if (quant_type == 0) {
+                decoded[i] = S::down(float(signed_code(values, i, bit, word)) * (scale / lim));
+            } else {
+                const uint8_t byte = values[wire_pos(i / 2, word)];
+                const int code = (i % 2 == 0) ? (byte >> 4) : (byte & 15);
+                decoded[i] = S::down(kCodebooks[quant_type - 1][code] * scale);
+            }
+        }
+        const uint32_t index_word = uint32_t(meta[1]) & 0xFFFFu;
+        for (int k = 0; k < topk; ++k) {
+            const int pos = int((index_word >> (8 * k)) & 0xFFu);
+            if (pos < group) decoded[pos] = meta[2 + k];      // outliers travel verbatim
+        }
+        for (int i = 0; i < group; ++i) {
+            const int64_t idx = g * group + i;
+            if (idx >= numel) break;
+            out[idx] = accumulate ? S::down(S::up(out[idx]) + S::up(decoded[i])) : decoded[i];
+        }
+    }
+    return 0;
+}
+
+bool bad_general(int dtype, int group, int bit, int topk, int quant_type) {
+    if (dtype < 0 || dtype > 2 || (group != 16 && group != 32 && group != 64) || (bit != 8 && bit != 4)) return true;
+    if (topk < 0 || topk > 2 || quant_type < 0 || quant_type > 4) return true;
+    return quant_type != 0 && bit != 4;       // the code-books are 4-bit
+}
+
 bool bad_profile(int dtype, int group, int bit) {
     return dtype < 0 || dtype > 2 || (group != 16 && group != 32 && group != 64) || (bit != 8 && bit != 4);
 }
@@ -240,7 +404,7 @@ bool bad_profile(int dtype, int group, int bit) {
 
 extern "C" {
 
-int lbc_host_abi_version(void) { return 1; }
+int lbc_host_abi_version(void) { return 2; }
 
 int lbc_host_quantize(int dtype, int group, int bit, int compact, const void* x, const void* residual,
                       void* prepared_out, int64_t numel, uint8_t* out) {
@@ -271,6 +435,36 @@ int lbc_host_reduce(int dtype, int group, int bit, int compact, const uint8_t* c
         case kFP16: return reduce<kFP16>(group, bit, compact != 0, payloads, num, numel, scale, out, prepared, residual_out);
         case kBF16: return reduce<kBF16>(group, bit, compact != 0, payloads, num, numel, scale, out, prepared, residual_out);
         default: return reduce<kFP32>(group, bit, compact != 0, payloads, num, numel, scale, out, prepared, residual_out);
+    }
+}
+
+// General profiles (top-k 0..2; quant_type 0 linear, 1 normal, 2 uniform, 3 e3m0, 4 e2m1; deterministic rounding).
+int lbc_host_quantize_general(int dtype, int group, int bit, int topk, int quant_type, int compact, const void* x,
+                              const void* residual, void* prepared_out, int64_t numel, uint8_t* out) {
+    if (bad_general(dtype, group, bit, topk, quant_type) || numel < 0 || (numel > 0 && (x == nullptr || out == nullptr)))
+        return 1;
+    switch (dtype) {
+        case kFP16:
+            return quantize_general<kFP16>(group, bit, topk, quant_type, compact != 0, x, residual, prepared_out, numel, out);
+        case kBF16:
+            return quantize_general<kBF16>(group, bit, topk, quant_type, compact != 0, x, residual, prepared_out, numel, out);
+        default:
+            return quantize_general<kFP32>(group, bit, topk, quant_type, compact != 0, x, residual, prepared_out, numel, out);
+    }
+}
+
+int lbc_host_dequantize_general(int dtype, int group, int bit, int topk, int quant_type, int compact,
+                                const uint8_t* payload, int64_t numel, void* out, int accumulate) {
+    if (bad_general(dtype, group, bit, topk, quant_type) || numel < 0 ||
+        (numel > 0 && (payload == nullptr || out == nullptr)))
+        return 1;
+    switch (dtype) {
+        case kFP16:
+            return dequantize_general<kFP16>(group, bit, topk, quant_type, compact != 0, payload, numel, out, accumulate != 0);
+        case kBF16:
+            return dequantize_general<kBF16>(group, bit, topk, quant_type, compact != 0, payload, numel, out, accumulate != 0);
+        default:
+            return dequantize_general<kFP32>(group, bit, topk, quant_type, compact != 0, payload, numel, out, accumulate != 0);
     }
 }
 

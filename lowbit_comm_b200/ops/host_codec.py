@@ -1,8 +1,8 @@
 """ctypes front end of the C++ host codec (`csrc/host_codec.cpp`, built as `_lbc_host.so`).
 
-The CPU side of the codec facade uses it for the fast profile family (linear,
-top-k 0, deterministic rounding) when the library has been built; everything
-else, and a tree without the library, goes through the torch oracle.  The two
+The CPU side of the codec facade uses it for every deterministic profile when
+the library has been built (the fused multi-payload reduce for linear / top-k 0);
+stochastic rounding, and a tree without the library, go through the torch oracle.  The two
 are required to agree bit for bit (tests/test_host_codec.py), which makes this
 an independent check of the oracle that the GPU kernels are tested against.
 """
@@ -39,13 +39,16 @@ def library() -> ctypes.CDLL | None:
             try:
                 lib = ctypes.CDLL(str(_LIB_PATH))
                 lib.lbc_host_abi_version.restype = ctypes.c_int
-                if lib.lbc_host_abi_version() == 1:
+                if lib.lbc_host_abi_version() == 2:
                     vp, i64, ci = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
                     lib.lbc_host_quantize.argtypes = [ci, ci, ci, ci, vp, vp, vp, i64, vp]
                     lib.lbc_host_dequantize.argtypes = [ci, ci, ci, ci, vp, i64, vp, ci]
                     lib.lbc_host_reduce.argtypes = [ci, ci, ci, ci, ctypes.POINTER(vp), ci, i64, ctypes.c_float, vp,
                                                     vp, vp]
-                    for fn in (lib.lbc_host_quantize, lib.lbc_host_dequantize, lib.lbc_host_reduce):
+                    lib.lbc_host_quantize_general.argtypes = [ci, ci, ci, ci, ci, ci, vp, vp, vp, i64, vp]
+                    lib.lbc_host_dequantize_general.argtypes = [ci, ci, ci, ci, ci, ci, vp, i64, vp, ci]
+                    for fn in (lib.lbc_host_quantize, lib.lbc_host_dequantize, lib.lbc_host_reduce,
+                               lib.lbc_host_quantize_general, lib.lbc_host_dequantize_general):
                         fn.restype = ci
                     lib.lbc_host_half_to_float.argtypes, lib.lbc_host_half_to_float.restype = \
                         [ctypes.c_uint16], ctypes.c_float
@@ -60,9 +63,17 @@ def library() -> ctypes.CDLL | None:
     return _lib
 
 
+_QUANT_CODE = {"linear": 0, "normal": 1, "uniform": 2, "e3m0": 3, "e2m1": 4}
+
+
 def serves(config: CompressionConfig) -> bool:
-    return (library() is not None and config.quant_type == "linear" and config.topk == 0
-            and not config.stochastic)
+    """Encode and decode: every deterministic profile (stochastic rounding stays with the torch oracle)."""
+
+    return library() is not None and not config.stochastic and config.quant_type in _QUANT_CODE
+
+
+def _fast(config: CompressionConfig) -> bool:
+    return config.quant_type == "linear" and config.topk == 0
 
 
 def _ptr(t: torch.Tensor | None) -> int | None:
@@ -89,8 +100,13 @@ def quantize(x: torch.Tensor, config: CompressionConfig, dtype: str, out: torch.
             _check(t, dtype, what)
             if t.numel() != n:
                 raise ValueError(f"{what} must have {n} elements")
-    rc = lib.lbc_host_quantize(_DTYPE_CODE[dtype], config.group_size, config.bit, int(config.compact), _ptr(x),
-                               _ptr(residual), _ptr(prepared_out), n, _ptr(out))
+    if _fast(config):
+        rc = lib.lbc_host_quantize(_DTYPE_CODE[dtype], config.group_size, config.bit, int(config.compact), _ptr(x),
+                                   _ptr(residual), _ptr(prepared_out), n, _ptr(out))
+    else:
+        rc = lib.lbc_host_quantize_general(_DTYPE_CODE[dtype], config.group_size, config.bit, config.topk,
+                                           _QUANT_CODE[config.quant_type], int(config.compact), _ptr(x),
+                                           _ptr(residual), _ptr(prepared_out), n, _ptr(out))
     if rc != 0:
         raise ValueError("host codec rejected the arguments")
     return out
@@ -105,8 +121,13 @@ def dequantize(payload: torch.Tensor, numel: int, config: CompressionConfig, dty
     _check(out, dtype, "output")
     if out.numel() != numel:
         raise ValueError("output has the wrong number of elements")
-    rc = lib.lbc_host_dequantize(_DTYPE_CODE[dtype], config.group_size, config.bit, int(config.compact),
-                                 _ptr(payload), numel, _ptr(out), int(accumulate))
+    if _fast(config):
+        rc = lib.lbc_host_dequantize(_DTYPE_CODE[dtype], config.group_size, config.bit, int(config.compact),
+                                     _ptr(payload), numel, _ptr(out), int(accumulate))
+    else:
+        rc = lib.lbc_host_dequantize_general(_DTYPE_CODE[dtype], config.group_size, config.bit, config.topk,
+                                             _QUANT_CODE[config.quant_type], int(config.compact), _ptr(payload),
+                                             numel, _ptr(out), int(accumulate))
     if rc != 0:
         raise ValueError("host codec rejected the arguments")
     return out
@@ -117,6 +138,8 @@ def reduce(payloads: list[torch.Tensor], numel: int, config: CompressionConfig, 
            residual_out: torch.Tensor | None = None) -> None:
     """out = T(fp32 sum of the decoded payloads * scale); residual_out = T(float(prepared) - that fp32 value)."""
 
+    if not _fast(config):
+        raise ValueError("the fused host reduce serves linear / top-k 0 profiles")
     lib = library()
     need = estimate_quantized_size(numel, dtype=dtype, config=config).quantized_bytes
     for p in payloads:

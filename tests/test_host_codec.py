@@ -101,6 +101,38 @@ def test_fused_reduce_matches_the_oracle(dtype, bit, group, count):
             assert torch.equal(_bits(residual), _bits(oracle.residual_update(xs[0], y32))), (n, divisor)
 
 
+@pytest.mark.parametrize("dtype", ("bf16", "fp16", "fp32"))
+@pytest.mark.parametrize("topk", (0, 1, 2))
+@pytest.mark.parametrize("bit,group,quant", [(8, 64, "linear"), (4, 32, "linear"), (4, 16, "normal"), (4, 64, "uniform"),
+                                             (4, 32, "e3m0"), (4, 64, "e2m1")])
+@pytest.mark.parametrize("compact", (False, True))
+def test_general_profiles_match_the_oracle(dtype, topk, bit, group, quant, compact):
+    if topk == 0 and quant == "linear":
+        pytest.skip("covered by the fast-path test")
+    cfg = CompressionConfig(bit=bit, group_size=group, topk=topk, quant_type=quant, compact=compact,
+                            allow_experimental=True)
+    for seed, n in enumerate((group, group * 9, group * 31 + 5)):
+        x = _inputs(n, dtype, seed)
+        if n > 8:
+            x[3] = x[2]                      # equal magnitudes inside a group: the tie rule of the top-k scan matters
+            x[6] = -x[2]
+        r = (_inputs(n, dtype, 300 + seed).float() * 1e-2).to(DT[dtype])
+        for residual in (None, r):
+            want = oracle.encode(x, cfg, residual=residual)
+            out = torch.empty_like(want)
+            prepared = torch.empty_like(x)
+            host_codec.quantize(x, cfg, dtype, out, residual, prepared)
+            assert torch.equal(out, want), (n, residual is not None)
+            assert torch.equal(_bits(prepared), _bits(oracle.prepare(x, residual)))
+            dec = torch.empty(n, dtype=DT[dtype])
+            host_codec.dequantize(want, n, cfg, dtype, dec)
+            assert torch.equal(_bits(dec), _bits(oracle.decode(want, n, cfg, dtype))), n
+            acc = (_inputs(n, dtype, 400 + seed).float() * 1e-3).to(DT[dtype])
+            expect = oracle.decode_accumulate(want, acc.clone(), cfg)
+            host_codec.dequantize(want, n, cfg, dtype, acc, accumulate=True)
+            assert torch.equal(_bits(acc), _bits(expect)), n
+
+
 def test_facade_uses_the_host_library_on_cpu():
     cfg = CompressionConfig()
     x = _inputs(5000, "bf16", 1)
@@ -109,7 +141,10 @@ def test_facade_uses_the_host_library_on_cpu():
     assert torch.equal(payload, oracle.encode(x, cfg))
     back = codec.dequantize_tensor(payload, x.shape, cfg, dtype="bf16")
     assert torch.equal(_bits(back), _bits(oracle.decode(payload, x.numel(), cfg, "bf16")))
-    assert not host_codec.serves(CompressionConfig(topk=1))          # the oracle serves everything else
+    assert host_codec.serves(CompressionConfig(topk=1))
+    assert not host_codec.serves(CompressionConfig(stochastic=True))  # the oracle keeps stochastic rounding
+    with pytest.raises(ValueError):
+        host_codec.reduce([payload], x.numel(), CompressionConfig(topk=1), "bf16", 1.0, torch.empty_like(x))
 
 
 def test_arguments_are_validated():
