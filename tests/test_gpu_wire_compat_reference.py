@@ -59,6 +59,17 @@ def test_payload_bytes_and_cross_decoding(ext, reference, dtype, bit, group, com
     a = codec.dequantize_tensor(theirs.reshape(-1).contiguous(), x.shape, ours_cfg, dtype=dtype)
     b = ref_codec.dequantize_tensor(mine, tuple(x.shape), ref_cfg, dtype=dtype, extension_status=status)
     torch.cuda.synchronize()
+    if topk > 0 and bit == 4 and group == 16 and not compact:
+        # Measured on B200: for this corner (planar layout, 4-bit, groups of 16, top-k outliers) the reference's
+        # decoder returns values unrelated to the input in the tail of the tensor, although its encoder's bytes
+        # equal ours and its compact-layout decoder agrees with ours.  Our decoder is held to the oracle here.
+        from lowbit_comm_b200.ops import oracle
+
+        want = oracle.decode(theirs.reshape(-1).cpu(), n, ours_cfg, dtype)
+        assert torch.equal(a.cpu().view(torch.uint8), want.view(torch.uint8)), "our decode differs from the oracle"
+        close = (a.float() - x.float()).abs().max().item() <= x.float().abs().max().item() / 7 + 1e-6
+        assert close, "our decode is not within one 4-bit step of the input"
+        return
     assert torch.equal(a.view(torch.uint8), b.reshape(x.shape).view(torch.uint8)), "decoded values differ"
 
 
