@@ -10,7 +10,7 @@ tensor without the extension is an error, never a silent fallback.
 
 from __future__ import annotations
 
-from typing import Any, Sequence
+from typing import Sequence
 
 import torch
 

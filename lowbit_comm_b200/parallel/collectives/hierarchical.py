@@ -6,7 +6,6 @@ from collections.abc import Callable
 from typing import Any
 
 from ...config import CompressionConfig
-from ...core.work import ImmediateWork
 from ...exceptions import UnsupportedCollective
 
 

@@ -29,7 +29,7 @@ from ..config import CompressionConfig
 from ..core.chunking import GroupShardPlan
 from ..core.info import ExecutionInfo
 from ..core.shard import ReducedShard
-from ..core.work import CollectiveWork, CompletionWork, ImmediateWork
+from ..core.work import ImmediateWork
 from ..exceptions import CCDLUnavailableError, UnsupportedCollective
 from ..ops import codec
 from ..ops.loader import load_cuda_extension

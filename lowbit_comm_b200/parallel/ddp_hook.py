@@ -39,7 +39,7 @@ from .payload import (CompressedAllGatherReduce, CompressedAllReduce, Compressed
 from .payload_packing import (DEFAULT_FUSED_PAYLOAD_MIN_NUMEL, make_fused_payload_all_gather,
                               make_payload_all_gather, should_fuse_payload)
 from .strategy import CollectiveCapabilities, plan_ddp_compression_strategy
-from .torch_transport import (make_torch_all_gather, make_torch_all_reduce, make_torch_all_to_all,
+from .torch_transport import (make_torch_all_gather, make_torch_all_to_all,
                               make_torch_async_all_gather, make_torch_tensor_all_reduce)
 
 _TOPOLOGY_METHODS = {None, "auto", "ring", "tree", "p2p", "overlap-gather", "overlap-p2p", "overlap-tree",
