@@ -187,6 +187,102 @@ class AsyncBucketPipeline:
             return None
 
 
+class AsyncShardPipeline:
+    """The reduced-shard counterpart of `AsyncBucketPipeline`: when the payload exchange (an all-to-all work
+    object) completes, reduce this rank's shard, run the feedback and policy callbacks, hand the workspace
+    leases back with the completion event of the shard, and complete the outer future with a `ReducedShard`
+    whose metadata says `async_completion`.  On failure the leases are still released, behind an event, and the
+    future carries the exception.  The object is itself work-like (`wait`, `query`, `get_future`, `then`).
+    Parity: ccdl_comm/communication/async_shard_pipeline.py:11-129.
+    """
+
+    def __init__(self, *, communication_work, future, reduce_shard, update_feedback=None, advance_policy=None,
+                 completion_manager=None, synchronize_completion: bool = False, resources=(),
+                 workspace_leases=()) -> None:
+        self.communication_work = communication_work
+        self.future = future
+        self.reduce_shard = reduce_shard
+        self.update_feedback = update_feedback
+        self.advance_policy = advance_policy
+        self.completion_manager = completion_manager or CudaCompletionManager()
+        self.synchronize_completion = synchronize_completion
+        self.resources = tuple(resources)          # buffers kept alive until completion
+        self._leases = list(workspace_leases)
+
+    def run(self) -> "AsyncShardPipeline":
+        getter = getattr(self.communication_work, "get_future", None)
+        inner = getter() if callable(getter) else None
+        if inner is not None and hasattr(inner, "then"):
+            inner.then(self._complete)
+        else:
+            self._complete()
+        return self
+
+    # -- work protocol --------------------------------------------------------------
+    def wait(self):
+        waiter = getattr(self.future, "wait", None)
+        if callable(waiter):
+            return waiter()
+        error = getattr(self.future, "exception", None)
+        if error is not None and not callable(error):
+            raise error
+        result = getattr(self.future, "result", None)
+        if result is None:
+            raise RuntimeError("asynchronous shard result is not complete")
+        return result
+
+    def query(self) -> bool:
+        done = getattr(self.future, "done", None)
+        if callable(done):
+            return bool(done())
+        return getattr(self.future, "result", None) is not None or getattr(self.future, "exception", None) is not None
+
+    def get_future(self):
+        return self.future
+
+    def then(self, callback):
+        chain = getattr(self.future, "then", None)
+        if not callable(chain):
+            raise AttributeError("underlying future does not support then()")
+        return chain(callback)
+
+    # -- completion -------------------------------------------------------------------
+    def _release(self, completion) -> None:
+        while self._leases:
+            self._leases.pop(0).release(completion=completion)
+
+    def _complete(self, _ignored: Any = None):
+        from dataclasses import replace
+
+        try:
+            received = self.communication_work.wait()
+            shard = self.reduce_shard(received)
+            shard = replace(shard, metadata={**dict(shard.metadata), "async_completion": True})
+            if self.update_feedback is not None:
+                self.update_feedback(shard)
+            if self.advance_policy is not None:
+                self.advance_policy()
+            completion = self.completion_manager.record_for(shard.shard)
+            completion.wait()
+            self._release(completion)
+            if self.synchronize_completion:
+                sync = getattr(completion, "synchronize", None)
+                if callable(sync):
+                    sync()
+            self.future.set_result(shard)
+            return shard
+        except BaseException as exc:  # noqa: BLE001 - the failure travels through the future
+            if self._leases:
+                fence = self.completion_manager.record_for(getattr(self._leases[0], "buffer", None))
+                fence.wait()
+                self._release(fence)
+            setter = getattr(self.future, "set_exception", None)
+            if callable(setter):
+                setter(exc)
+                return None
+            raise
+
+
 class _PeerEngine:
     """Lazily built peer group + fused workspaces for one hook."""
 

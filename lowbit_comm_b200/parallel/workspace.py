@@ -427,6 +427,90 @@ class ShardCommunicationWorkspaceCache:
         return self.get(key, "reduced", rank, lambda: tensor.new_empty(tuple(shape)))
 
 
+class CudaShardWorkspaceProvider:
+    """Binds the send / recv / reduced buffers of one reduced-shard executor to a `CudaWorkspacePool`.
+
+    `begin(stream=...)` opens a session for one collective call; every buffer the session hands out is an
+    exclusive lease of the pool, and `session.release(completion=...)` gives all of them back at once behind
+    the call's completion event.  Parity: ccdl_comm/cuda/workspace.py:418-581.  The fused peer path does not
+    need it (its buffers live in the peer arena); the torch.distributed path and external callers do.
+    """
+
+    def __init__(self, pool: CudaWorkspacePool, *, backend: str, collective: str, strategy: str, device: str,
+                 pool_reduced_output: bool = True) -> None:
+        if not isinstance(pool, CudaWorkspacePool):
+            raise TypeError("pool must be a CudaWorkspacePool")
+        self.pool = pool
+        self.backend, self.collective, self.strategy, self.device = backend, collective, strategy, device
+        self.pool_reduced_output = bool(pool_reduced_output)
+
+    def begin(self, *, stream: Any) -> "CudaShardWorkspaceSession":
+        return CudaShardWorkspaceSession(self, stream=stream)
+
+
+class CudaShardWorkspaceSession:
+    """Exclusive leases of one shard collective call; same accessor names as `ShardCommunicationWorkspaceCache`."""
+
+    def __init__(self, provider: CudaShardWorkspaceProvider, *, stream: Any) -> None:
+        self._provider, self._stream = provider, stream
+        self._leases: list[WorkspaceLease] = []
+
+    @property
+    def leases(self) -> tuple[WorkspaceLease, ...]:
+        return tuple(self._leases)
+
+    def _take(self, *, shape: tuple[int, ...], dtype: str, world_size: int, config: Any, chunk_config: tuple[int, ...],
+              kind: str) -> Any:
+        p = self._provider
+        key = WorkspaceKey(backend=p.backend, collective=p.collective, strategy=p.strategy, shape_class=tuple(shape),
+                           dtype=dtype, world_size=world_size, bit=config.bit, group_size=config.group_size,
+                           chunk_config=tuple(chunk_config), workspace_kind=kind, device=p.device)
+        lease = p.pool.acquire(key, self._stream)
+        self._leases.append(lease)
+        return lease.buffer
+
+    @staticmethod
+    def _payload_bytes(tensor: Any, dtype: str, config: Any) -> int:
+        from ..ops.sizing import estimate_quantized_size
+
+        return estimate_quantized_size(int(tensor.numel()), dtype=dtype, config=config).quantized_bytes
+
+    def get_quantized_chunk(self, bucket_key: Any, chunk_index: int, tensor: Any, config: Any, *, dtype: str,
+                            world_size: int) -> Any:
+        return self._take(shape=(self._payload_bytes(tensor, dtype, config),), dtype="uint8", world_size=world_size,
+                          config=config, chunk_config=(chunk_index, int(tensor.numel())), kind="send")
+
+    def get_received_payload(self, bucket_key: Any, payload_template: Any, index: int, *, world_size: int,
+                             config: Any) -> Any:
+        name = {"torch.uint8": "uint8"}.get(str(payload_template.dtype), str(payload_template.dtype))
+        return self._take(shape=tuple(payload_template.shape), dtype=name, world_size=world_size, config=config,
+                          chunk_config=(index,), kind="recv")
+
+    def get_received_tensor_payload(self, bucket_key: Any, index: int, tensor: Any, config: Any, *, dtype: str,
+                                    world_size: int) -> Any:
+        """Receive storage sized from the source chunk's metadata (no payload template needed)."""
+
+        return self._take(shape=(self._payload_bytes(tensor, dtype, config),), dtype="uint8", world_size=world_size,
+                          config=config, chunk_config=(index, int(tensor.numel())), kind="recv")
+
+    def get_reduced_shard(self, bucket_key: Any, tensor: Any, shape: tuple[int, ...], config: Any, *, dtype: str,
+                          world_size: int, rank: int) -> Any:
+        """The reduced shard, padded to whole groups; None when the provider leaves the output to the caller."""
+
+        if not self._provider.pool_reduced_output:
+            return None
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        padded = -(-numel // config.group_size) * config.group_size
+        return self._take(shape=(padded,), dtype=dtype, world_size=world_size, config=config, chunk_config=(rank,),
+                          kind="reduced")
+
+    def release(self, *, completion: Any) -> None:
+        while self._leases:
+            self._leases.pop(0).release(completion=completion)
+
+
 def _allocate_torch_buffer(key: WorkspaceKey, stream: Any) -> Any:
     import torch
 

@@ -212,3 +212,91 @@ def test_bucket_processor_from_cuda_codec_round_trips_locally():
     residual = proc.error_feedback.get(0) if proc.error_feedback.get(0) is not None else None
     second = proc.process(Bucket(x.clone()), dtype="bf16")                       # second step: residual is added first
     assert residual is None or not torch.equal(second, first) or torch.equal(residual, torch.zeros_like(residual))
+
+
+def test_async_shard_pipeline_releases_leases_and_marks_the_shard():
+    from lowbit_comm_b200 import ReducedShard
+    from lowbit_comm_b200.parallel.ddp_hook import AsyncShardPipeline
+
+    log = []
+
+    class Completion:
+        def __init__(self, of):
+            self.of = of
+
+        def wait(self):
+            log.append(("completion.wait", self.of))
+
+        def synchronize(self):
+            log.append(("completion.synchronize", self.of))
+
+    class Manager:
+        def record_for(self, tensor, stream=None):
+            log.append(("record_for", tensor))
+            return Completion(tensor)
+
+    class Lease:
+        def __init__(self, name):
+            self.name, self.buffer = name, f"buffer:{name}"
+
+        def release(self, *, completion):
+            log.append(("release", self.name, completion.of))
+
+    class InnerFuture:
+        def __init__(self):
+            self.callbacks = []
+
+        def then(self, cb):
+            self.callbacks.append(cb)
+
+    class Work:
+        def __init__(self, fail=False):
+            self.inner, self.fail = InnerFuture(), fail
+
+        def get_future(self):
+            return self.inner
+
+        def wait(self):
+            if self.fail:
+                raise RuntimeError("all_to_all failed")
+            return ["payload0", "payload1"]
+
+    class Future:
+        result = exception = None
+
+        def set_result(self, value):
+            self.result = value
+
+        def set_exception(self, exc):
+            self.exception = exc
+
+        def done(self):
+            return self.result is not None or self.exception is not None
+
+    def reduce_shard(received):
+        log.append(("reduce", tuple(received)))
+        return ReducedShard(shard="shard-tensor", shard_index=1, shard_numel=4, original_shape=(8,), original_numel=8,
+                            world_size=2, reduce="mean", metadata={"fused": True})
+
+    work, fut = Work(), Future()
+    pipe = AsyncShardPipeline(communication_work=work, future=fut, reduce_shard=reduce_shard,
+                              update_feedback=lambda s: log.append(("feedback", s.shard_index)),
+                              advance_policy=lambda: log.append(("advance",)), completion_manager=Manager(),
+                              synchronize_completion=True, resources=("keep",),
+                              workspace_leases=(Lease("send"), Lease("recv"))).run()
+    assert not pipe.query() and log == [] and pipe.resources == ("keep",)      # nothing happens before the exchange ends
+    work.inner.callbacks[0](None)
+    assert pipe.query() and pipe.get_future() is fut
+    shard = fut.result
+    assert shard.metadata == {"fused": True, "async_completion": True} and shard.shard == "shard-tensor"
+    assert log == [("reduce", ("payload0", "payload1")), ("feedback", 1), ("advance",), ("record_for", "shard-tensor"),
+                   ("completion.wait", "shard-tensor"), ("release", "send", "shard-tensor"),
+                   ("release", "recv", "shard-tensor"), ("completion.synchronize", "shard-tensor")]
+
+    log.clear()
+    work, fut = Work(fail=True), Future()
+    AsyncShardPipeline(communication_work=work, future=fut, reduce_shard=reduce_shard, completion_manager=Manager(),
+                       workspace_leases=(Lease("send"),)).run()
+    work.inner.callbacks[0](None)
+    assert isinstance(fut.exception, RuntimeError) and fut.result is None
+    assert log == [("record_for", "buffer:send"), ("completion.wait", "buffer:send"), ("release", "send", "buffer:send")]

@@ -340,3 +340,50 @@ def test_shard_workspace_cache_accessors_and_torch_pool():
     assert native_work_available(types.SimpleNamespace(available=True, module=fake))
     fake.NATIVE_WORK_ABI_VERSION = 2
     assert not native_work_available(types.SimpleNamespace(available=True, module=fake))
+
+
+def test_shard_workspace_session_leases_and_release():
+    import torch
+
+    from lowbit_comm_b200 import CompressionConfig
+    from lowbit_comm_b200.parallel.workspace import CudaShardWorkspaceProvider, create_torch_workspace_pool
+
+    class Completion:
+        def __init__(self, ready):
+            self.ready = ready
+
+        def query(self):
+            return self.ready
+
+    cfg = CompressionConfig()
+    pool = create_torch_workspace_pool()
+    provider = CudaShardWorkspaceProvider(pool, backend="cuda", collective="reduce_scatter", strategy="compressed",
+                                          device="cpu")
+    with pytest.raises(TypeError):
+        CudaShardWorkspaceProvider(object(), backend="cuda", collective="reduce_scatter", strategy="compressed", device="cpu")
+    chunk = torch.zeros(640, dtype=torch.bfloat16)
+    session = provider.begin(stream=None)
+    send = session.get_quantized_chunk("b0", 0, chunk, cfg, dtype="bf16", world_size=4)
+    recv = session.get_received_payload("b0", send, 2, world_size=4, config=cfg)
+    recv2 = session.get_received_tensor_payload("b0", 3, chunk, cfg, dtype="bf16", world_size=4)
+    reduced = session.get_reduced_shard("b0", chunk, (150,), cfg, dtype="bf16", world_size=4, rank=1)
+    assert send.dtype == torch.uint8 and send.numel() == 660 and recv.shape == send.shape and recv2.numel() == 660
+    assert reduced.dtype == torch.bfloat16 and reduced.numel() == 192            # padded to whole groups of 64
+    assert len(session.leases) == 4 and pool.stats.in_flight_bytes > 0
+    # a second session running at the same time gets other buffers
+    other = provider.begin(stream=None)
+    assert other.get_quantized_chunk("b0", 0, chunk, cfg, dtype="bf16", world_size=4).data_ptr() != send.data_ptr()
+    other.release(completion=Completion(True))
+    pending = Completion(False)
+    session.release(completion=pending)
+    assert session.leases == ()
+    third = provider.begin(stream=None)
+    again = third.get_quantized_chunk("b0", 0, chunk, cfg, dtype="bf16", world_size=4)
+    assert again.data_ptr() != send.data_ptr()           # not reusable while its completion is pending
+    pending.ready = True
+    fourth = provider.begin(stream=None)
+    reused = fourth.get_quantized_chunk("b0", 0, chunk, cfg, dtype="bf16", world_size=4)
+    assert reused.data_ptr() == send.data_ptr()          # its completion is ready now: the buffer comes back
+    no_out = CudaShardWorkspaceProvider(pool, backend="cuda", collective="reduce_scatter", strategy="compressed",
+                                        device="cpu", pool_reduced_output=False)
+    assert no_out.begin(stream=None).get_reduced_shard("b0", chunk, (150,), cfg, dtype="bf16", world_size=4, rank=0) is None
