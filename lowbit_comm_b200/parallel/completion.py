@@ -72,6 +72,56 @@ def comm_stream(device=None):
         return stream
 
 
+class CudaStreamWork:
+    """`with CudaStreamWork(torch=torch, async_op=True) as work:` runs the body on the communication stream
+    (ordered after the caller's current stream) and records an event when the body ends; `work.wait()` makes
+    the caller's current stream wait for that event (and waits on `handle` first when one was given), without
+    blocking the host.  With `async_op=False` the body runs on the current stream and is already ordered.
+    Parity: ccdl_comm/communication/cuda_completion.py:70-119.
+    """
+
+    def __init__(self, *, torch: Any, async_op: bool = False, handle: Any | None = None) -> None:
+        self.async_op, self.handle, self._torch = async_op, handle, torch
+        cuda = torch.cuda
+        self.stream = _shared_comm_stream(cuda) if async_op else cuda.current_stream()
+        self._guard = cuda.stream(self.stream)
+        self.event = None
+
+    def __enter__(self) -> "CudaStreamWork":
+        self.stream.wait_stream(self._torch.cuda.current_stream())
+        self._guard.__enter__()
+        return self
+
+    def __exit__(self, exc_type, exc_value, traceback) -> None:
+        self._guard.__exit__(exc_type, exc_value, traceback)
+        self.event = self._torch.cuda.Event()
+        self.event.record(self.stream)
+        if not self.async_op:
+            self.event.wait()
+
+    def wait(self) -> None:
+        waiter = getattr(self.handle, "wait", None)
+        if callable(waiter):
+            waiter()
+        if self.async_op and self.event is not None:
+            self.event.wait()
+
+    def query(self) -> bool:
+        if not self.async_op:
+            return True
+        return bool(self.event.query()) if self.event is not None else False
+
+
+_SHARED_COMM_STREAMS: dict[int, Any] = {}
+
+
+def _shared_comm_stream(cuda: Any) -> Any:
+    device = int(cuda.current_device())
+    if device not in _SHARED_COMM_STREAMS:
+        _SHARED_COMM_STREAMS[device] = cuda.Stream(device)
+    return _SHARED_COMM_STREAMS[device]
+
+
 class CudaCompletionManager:
     def __init__(self, *, extension_status=None, torch_module=None) -> None:
         self._status = extension_status

@@ -300,3 +300,77 @@ def test_async_shard_pipeline_releases_leases_and_marks_the_shard():
     work.inner.callbacks[0](None)
     assert isinstance(fut.exception, RuntimeError) and fut.result is None
     assert log == [("record_for", "buffer:send"), ("completion.wait", "buffer:send"), ("release", "send", "buffer:send")]
+
+
+def test_cuda_stream_work_orders_streams_without_host_waits():
+    from lowbit_comm_b200.parallel.completion import CudaStreamWork
+
+    log = []
+
+    class Stream:
+        def __init__(self, name):
+            self.name = name
+
+        def wait_stream(self, other):
+            log.append(("wait_stream", self.name, other.name))
+
+    class Event:
+        def record(self, stream):
+            log.append(("record", stream.name))
+
+        def wait(self):
+            log.append(("event.wait",))
+
+        def query(self):
+            return True
+
+    class Guard:
+        def __init__(self, stream):
+            self.stream = stream
+
+        def __enter__(self):
+            log.append(("enter", self.stream.name))
+
+        def __exit__(self, *a):
+            log.append(("exit", self.stream.name))
+
+    event_type, stream_type = Event, Stream
+
+    class Cuda:
+        Event = event_type
+        current = stream_type("compute")
+
+        @staticmethod
+        def current_stream():
+            return Cuda.current
+
+        @staticmethod
+        def current_device():
+            return 0
+
+        @staticmethod
+        def Stream(device):  # noqa: N802 - mirrors torch.cuda.Stream
+            return stream_type(f"comm{device}")
+
+        @staticmethod
+        def stream(s):
+            return Guard(s)
+
+    class Torch:
+        cuda = Cuda
+
+    class Handle:
+        def wait(self):
+            log.append(("handle.wait",))
+
+    with CudaStreamWork(torch=Torch, async_op=True, handle=Handle()) as work:
+        log.append(("body",))
+    assert log == [("wait_stream", "comm0", "compute"), ("enter", "comm0"), ("body",), ("exit", "comm0"),
+                   ("record", "comm0")]
+    assert work.query()
+    work.wait()
+    assert log[-2:] == [("handle.wait",), ("event.wait",)]
+    log.clear()
+    with CudaStreamWork(torch=Torch, async_op=False) as sync:
+        pass
+    assert sync.stream is Cuda.current and log[-1] == ("event.wait",) and sync.query()
