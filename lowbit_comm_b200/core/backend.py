@@ -1,19 +1,19 @@
-"""Backend capability records and the backend protocol.
+"""What a backend tells the compiler about itself, and the protocol it implements.
 
-Parity: ccdl_comm/backend.py:15-116.
+`BackendCapabilities` is the answer to "what can you do for this compile context?"; the compiler turns a
+mismatch into a rejection reason (`BackendCapabilities.why_not`).  `StrategyChoice` is the answer of an
+automatic strategy selector, with the evidence it rests on.  Field names follow the reference
+(ccdl_comm/backend.py:15-116).
 """
 
 from __future__ import annotations
 
 from collections.abc import Mapping
 from dataclasses import dataclass, field
-from types import MappingProxyType
 from typing import Protocol, runtime_checkable
 
-from ._checks import is_plain_int, need_text
+from ._checks import freeze, is_plain_int, need_text, need_texts, read_only, text_set, text_tuple
 from .plan import CommunicationPlan, CompileContext
-
-_STRING_SETS = ("collectives", "strategies", "dtypes", "output_layouts", "features")
 
 
 @dataclass(frozen=True)
@@ -36,22 +36,33 @@ class BackendCapabilities:
 
     def __post_init__(self) -> None:
         need_text(self.backend, "backend")
-        for attr in _STRING_SETS:
-            values = frozenset(getattr(self, attr))
-            if any(not isinstance(v, str) or not v.strip() for v in values):
-                raise ValueError(f"{attr} must contain non-empty strings")
-            object.__setattr__(self, attr, values)
         bits = frozenset(self.bits)
         if any(not is_plain_int(b) or b <= 0 for b in bits):
             raise ValueError("bits must contain positive integers")
-        object.__setattr__(self, "bits", bits)
-        notes = tuple(self.warnings)
-        if any(not isinstance(w, str) or not w.strip() for w in notes):
-            raise ValueError("warnings must contain non-empty strings")
-        object.__setattr__(self, "warnings", notes)
-        object.__setattr__(self, "details", MappingProxyType(dict(self.details)))
+        freeze(self, bits=bits, warnings=text_tuple(self.warnings, "warnings"), details=read_only(self.details),
+               **{name: text_set(getattr(self, name), name)
+                  for name in ("collectives", "strategies", "dtypes", "output_layouts", "features")})
         if not self.available and not (self.reason and self.reason.strip()):
             raise ValueError("reason is required when backend is unavailable")
+
+    def why_not(self, plan: CommunicationPlan, context: CompileContext, *, dtype: str | None = None) -> str | None:
+        """The first reason this backend cannot serve `plan` in `context`, or None when it can."""
+
+        if not self.available:
+            return self.reason
+        wanted = (("collective", plan.collective, self.collectives), ("strategy", plan.strategy, self.strategies),
+                  ("output layout", plan.output_layout, self.output_layouts),
+                  ("dtype", dtype or context.dtype, self.dtypes))
+        for what, value, offered in wanted:
+            if offered and value not in offered:
+                return f"{what} {value!r} is not supported"
+        if plan.compression is not None and self.bits and plan.compression.bit not in self.bits:
+            return f"bit width {plan.compression.bit} is not supported"
+        if plan.async_op and not self.supports_async:
+            return "asynchronous execution is not supported"
+        if context.allow_dynamic_shape and not self.supports_dynamic_shape:
+            return "dynamic shape is not supported"
+        return None
 
 
 @dataclass(frozen=True)
@@ -69,24 +80,39 @@ class StrategyChoice:
     fallback: tuple[str, ...] = ()
 
     def __post_init__(self) -> None:
-        for attr in ("strategy", "reason", "policy_id"):
-            need_text(getattr(self, attr), attr)
-        for attr in ("expected_speedup", "observed_speedup"):
-            value = getattr(self, attr)
-            if value is not None and value <= 0:
-                raise ValueError(f"{attr} must be > 0")
+        need_texts(self, "strategy", "reason", "policy_id")
+        for name in ("expected_speedup", "observed_speedup"):
+            speedup = getattr(self, name)
+            if speedup is not None and speedup <= 0:
+                raise ValueError(f"{name} must be > 0")
         if self.observed_speedup is not None and not self.baseline:
-            raise ValueError("observed_speedup requires an explicit baseline")
+            raise ValueError("observed_speedup requires an explicit baseline")   # a speed-up over what?
         if self.benchmark_matched and not self.evidence:
             raise ValueError("benchmark-matched choices require evidence")
-        names = tuple(self.fallback)
-        if any(not n.strip() for n in names):
-            raise ValueError("fallback strategies must not be empty")
-        object.__setattr__(self, "fallback", names)
+        freeze(self, fallback=text_tuple(self.fallback, "fallback", message="fallback strategies must not be empty"))
+
+    @property
+    def speedup(self) -> float | None:
+        """The recorded speed-up, whichever kind it is (same-semantics expectation or cross-semantics observation)."""
+
+        return self.expected_speedup if self.expected_speedup is not None else self.observed_speedup
+
+    def explain(self) -> str:
+        parts = [f"{self.strategy}: {self.reason} [{self.policy_id}]"]
+        if self.speedup is not None:
+            against = f" over {self.baseline}" if self.baseline else ""
+            parts.append(f"{self.speedup:.2f}x{against}")
+        if self.evidence:
+            parts.append(f"evidence: {self.evidence}")
+        if self.fallback:
+            parts.append("then " + ", ".join(self.fallback))
+        return "; ".join(parts)
 
 
 @runtime_checkable
 class AutoStrategySelector(Protocol):
+    """Backend-owned policy: picks one concrete strategy for an `auto` request without running anything."""
+
     def __call__(self, plan: CommunicationPlan, context: CompileContext) -> StrategyChoice: ...
 
 

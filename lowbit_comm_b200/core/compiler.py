@@ -241,48 +241,9 @@ def _pick_backend(plan: CommunicationPlan, context: CompileContext, registry: Ba
     raise UnsupportedCollective(f"{plan.collective}:{plan.strategy}", reason=reason)
 
 
-def _stage_signature(stage) -> tuple[object, ...]:
-    return (stage.name, stage.collective, stage.strategy, stage.backend, stage.compression,
-            ObjectIdentity(stage.process_group), stage.output_layout, stage.async_op)
-
-
 def make_cache_key(requested: CommunicationPlan, effective: CommunicationPlan, context: CompileContext,
                    registry: BackendRegistry, resolved: ResolvedPlan) -> CompileCacheKey:
-    comp = effective.compression
-    return CompileCacheKey(
-        registry_identity=ObjectIdentity(registry),
-        backend=effective.backend,
-        collective=effective.collective,
-        requested_strategy=requested.strategy,
-        executed_strategy=effective.strategy,
-        fallback=requested.fallback,
-        output_layout=effective.output_layout,
-        async_op=effective.async_op,
-        root=effective.root,
-        reduce_op=effective.reduce_op,
-        stage_signature=tuple(_stage_signature(s) for s in effective.stages),
-        shape_class=context.shape,  # exact shapes: no backend proves a wider class yet
-        dtype=context.dtype,
-        layout=context.layout,
-        rank=context.rank,
-        world_size=context.world_size,
-        device=context.device,
-        local_rank=context.local_rank,
-        local_world_size=context.local_world_size,
-        node_id=context.node_id,
-        node_count=context.node_count,
-        process_group_identity=ObjectIdentity(context.process_group),
-        process_group_identities=tuple((n, ObjectIdentity(g)) for n, g in sorted(context.process_groups.items())),
-        bit=None if comp is None else comp.bit,
-        group_size=None if comp is None else comp.group_size,
-        compression=comp,
-        topology_signature=context.topology_signature,
-        device_architecture=context.device_architecture,
-        strategy_policy_id=resolved.strategy_policy_id,
-        workspace_budget_bytes=context.workspace_budget_bytes,
-        allow_dynamic_shape=context.allow_dynamic_shape,
-        workspace_policy=effective.workspace_policy,
-    )
+    return CompileCacheKey.of(requested, effective, context, registry, resolved.strategy_policy_id)
 
 
 def _build(backend, effective: CommunicationPlan, context: CompileContext, resolved: ResolvedPlan,

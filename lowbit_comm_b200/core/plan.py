@@ -11,7 +11,10 @@ from dataclasses import dataclass, field
 from types import MappingProxyType
 
 from ..config import CompressionConfig
-from ._checks import is_plain_int, need_optional_index, need_shape, need_text
+from ._checks import (freeze, is_plain_int, need_optional_index, need_optional_minimum, need_shape, need_text,
+                      need_texts, read_only, text_tuple)
+
+_DTYPE_BYTES = {"fp16": 2, "bf16": 2, "fp32": 4, "float16": 2, "bfloat16": 2, "float32": 4}
 
 
 def _check_compression(value) -> None:
@@ -33,9 +36,14 @@ class CommunicationStage:
     async_op: bool = True
 
     def __post_init__(self) -> None:
-        for attr in ("name", "collective", "strategy", "backend", "output_layout"):
-            need_text(getattr(self, attr), attr)
+        need_texts(self, "name", "collective", "strategy", "backend", "output_layout")
         _check_compression(self.compression)
+
+    @property
+    def key(self) -> tuple[str, str, str, str]:
+        """(collective, strategy, backend, output layout): what a registry is asked for."""
+
+        return (self.collective, self.strategy, self.backend, self.output_layout)
 
 
 @dataclass(frozen=True)
@@ -48,10 +56,16 @@ class WorkspacePolicy:
     stream_safe: bool = True
 
     def __post_init__(self) -> None:
-        if self.max_cached_bytes is not None and self.max_cached_bytes < 0:
-            raise ValueError("max_cached_bytes must be >= 0")
-        if self.max_entries is not None and self.max_entries <= 0:
-            raise ValueError("max_entries must be > 0")
+        need_optional_minimum(self.max_cached_bytes, 0, "max_cached_bytes")
+        need_optional_minimum(self.max_entries, 1, "max_entries")
+
+    def admits(self, cached_bytes: int, entries: int) -> bool:
+        """Whether a cache holding `cached_bytes` in `entries` buffers is inside the policy."""
+
+        if not self.cache:
+            return cached_bytes == 0 and entries == 0
+        return (self.max_cached_bytes is None or cached_bytes <= self.max_cached_bytes) and \
+            (self.max_entries is None or entries <= self.max_entries)
 
 
 @dataclass(frozen=True)
@@ -71,9 +85,7 @@ class CommunicationPlan:
     workspace_policy: WorkspacePolicy = WorkspacePolicy()
 
     def __post_init__(self) -> None:
-        for attr in ("collective", "strategy", "backend", "output_layout"):
-            need_text(getattr(self, attr), attr)
-        need_text(self.reduce_op, "reduce_op")
+        need_texts(self, "collective", "strategy", "backend", "output_layout", "reduce_op")
         _check_compression(self.compression)
         if not isinstance(self.workspace_policy, WorkspacePolicy):
             raise TypeError("workspace_policy must be a WorkspacePolicy")
@@ -82,13 +94,23 @@ class CommunicationPlan:
         stages = tuple(self.stages)
         if not all(isinstance(s, CommunicationStage) for s in stages):
             raise TypeError("stages must contain only CommunicationStage values")
-        fallback = tuple(self.fallback)
-        for name in fallback:
-            need_text(name, "fallback strategy")
-        object.__setattr__(self, "stages", stages)
-        object.__setattr__(self, "fallback", fallback)
+        freeze(self, stages=stages,
+               fallback=text_tuple(self.fallback, "fallback", message="fallback strategy must be a non-empty string"))
         if self.strategy == "hierarchical" and not stages:
             raise ValueError("hierarchical strategy requires at least one stage")
+
+    @property
+    def key(self) -> tuple[str, str, str, str]:
+        return (self.collective, self.strategy, self.backend, self.output_layout)
+
+    @property
+    def is_compressed(self) -> bool:
+        return self.compression is not None and self.strategy != "native_nccl"
+
+    def candidates(self) -> tuple[str, ...]:
+        """The requested strategy followed by its fallback chain, duplicates removed, in order."""
+
+        return tuple(dict.fromkeys((self.strategy, *self.fallback)))
 
 
 @dataclass(frozen=True)
@@ -117,21 +139,16 @@ class CompileContext:
             raise ValueError("world_size must be > 0")
         if not 0 <= self.rank < self.world_size:
             raise ValueError("rank must be >= 0 and < world_size")
-        for attr in ("device", "dtype", "layout", "topology_signature", "device_architecture"):
-            need_text(getattr(self, attr), attr)
-        object.__setattr__(self, "shape", need_shape(self.shape))
-        if self.local_world_size is not None and self.local_world_size <= 0:
-            raise ValueError("local_world_size must be > 0")
+        need_texts(self, "device", "dtype", "layout", "topology_signature", "device_architecture")
+        need_optional_minimum(self.local_world_size, 1, "local_world_size")
         need_optional_index(self.local_rank, self.local_world_size, "local_rank", "local_world_size")
-        if self.node_count is not None and self.node_count <= 0:
-            raise ValueError("node_count must be > 0")
+        need_optional_minimum(self.node_count, 1, "node_count")
         need_optional_index(self.node_id, self.node_count, "node_id", "node_count")
-        if self.workspace_budget_bytes is not None and self.workspace_budget_bytes < 0:
-            raise ValueError("workspace_budget_bytes must be >= 0")
+        need_optional_minimum(self.workspace_budget_bytes, 0, "workspace_budget_bytes")
         groups = dict(self.process_groups)
         if any(not isinstance(k, str) or not k.strip() for k in groups):
             raise ValueError("process_groups keys must be non-empty strings")
-        object.__setattr__(self, "process_groups", MappingProxyType(groups))
+        freeze(self, shape=need_shape(self.shape), process_groups=read_only(groups))
 
     @property
     def numel(self) -> int:
@@ -139,3 +156,19 @@ class CompileContext:
         for dim in self.shape:
             total *= dim
         return total
+
+    @property
+    def nbytes(self) -> int:
+        """Bytes of the tensor when the dtype name is one of the source dtypes (fp16 / bf16 / fp32), else 0."""
+
+        return self.numel * _DTYPE_BYTES.get(self.dtype, 0)
+
+    @property
+    def has_node_layout(self) -> bool:
+        """True when local rank / local world size / node id / node count are all known and consistent."""
+
+        facts = (self.local_rank, self.local_world_size, self.node_id, self.node_count)
+        if any(f is None for f in facts):
+            return False
+        return self.world_size == self.local_world_size * self.node_count and \
+            self.rank == self.node_id * self.local_world_size + self.local_rank
