@@ -4,12 +4,17 @@ Parity: ccdl_comm/communication/bucket_fusion.py:11-177 (same inputs, outputs
 and rules: consecutive buckets only, bounded element count and bucket count,
 same dtype unless told otherwise, "full bucket" consumers stay alone).  It is a
 scheduling contract; a transport may use or ignore the plan.
+
+The planner is one pass over the buckets with a `_Run` that accumulates the open group; `launches_saved`
+(an addition) is what a fused transport gains: one collective per group instead of one per bucket, which on
+NVSwitch is a latency saving, not a bandwidth one.
 """
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Any, Sequence
+from collections.abc import Iterable, Iterator
+from dataclasses import asdict, dataclass, field
+from typing import Any
 
 DEFAULT_MAX_FUSED_BUCKET_NUMEL = 4_000_000
 DEFAULT_MAX_FUSED_BUCKET_COUNT = 8
@@ -34,8 +39,10 @@ class BucketFusionGroup:
     reason: str
 
     def to_metadata(self) -> dict[str, Any]:
-        return dict(bucket_indices=self.bucket_indices, total_numel=self.total_numel, dtype=self.dtype,
-                    fused=self.fused, reason=self.reason)
+        return asdict(self)
+
+
+_TALLY_NAMES = ("group_count", "fused_group_count", "fused_bucket_count", "skipped_bucket_count", "total_fused_numel")
 
 
 @dataclass(frozen=True)
@@ -43,75 +50,91 @@ class BucketFusionPlan:
     enabled: bool
     groups: tuple[BucketFusionGroup, ...]
 
-    def _count(self, fused: bool, what=len) -> int:
-        return sum(what(g.bucket_indices) for g in self.groups if g.fused is fused)
+    def _tally(self) -> dict[str, int]:
+        tally = dict.fromkeys(_TALLY_NAMES, 0)
+        for group in self.groups:
+            members = len(group.bucket_indices)
+            tally["group_count"] += 1
+            if group.fused:
+                tally["fused_group_count"] += 1
+                tally["fused_bucket_count"] += members
+                tally["total_fused_numel"] += group.total_numel
+            else:
+                tally["skipped_bucket_count"] += members
+        return tally
+
+    group_count = property(lambda self: len(self.groups))
+    fused_group_count = property(lambda self: self._tally()["fused_group_count"])
+    fused_bucket_count = property(lambda self: self._tally()["fused_bucket_count"])
+    skipped_bucket_count = property(lambda self: self._tally()["skipped_bucket_count"])
+    total_fused_numel = property(lambda self: self._tally()["total_fused_numel"])
 
     @property
-    def group_count(self) -> int:
-        return len(self.groups)
+    def launches_saved(self) -> int:
+        """Collectives a transport that honours the plan does not have to launch."""
 
-    @property
-    def fused_group_count(self) -> int:
-        return sum(1 for g in self.groups if g.fused)
-
-    @property
-    def fused_bucket_count(self) -> int:
-        return self._count(True)
-
-    @property
-    def skipped_bucket_count(self) -> int:
-        return self._count(False)
-
-    @property
-    def total_fused_numel(self) -> int:
-        return sum(g.total_numel for g in self.groups if g.fused)
+        tally = self._tally()
+        return tally["fused_bucket_count"] - tally["fused_group_count"]
 
     def to_metadata(self) -> dict[str, Any]:
-        return {"enabled": self.enabled, "group_count": self.group_count,
-                "fused_group_count": self.fused_group_count, "fused_bucket_count": self.fused_bucket_count,
-                "skipped_bucket_count": self.skipped_bucket_count, "total_fused_numel": self.total_fused_numel,
-                "groups": [g.to_metadata() for g in self.groups]}
+        return {"enabled": self.enabled, **self._tally(), "groups": [g.to_metadata() for g in self.groups]}
+
+
+class _Run:
+    """The group that is still open: consecutive buckets that may share one launch."""
+
+    def __init__(self, numel_limit: int, count_limit: int, same_dtype: bool) -> None:
+        self._limits = (numel_limit, count_limit, same_dtype)
+        self._members: list[BucketDescriptor] = []
+        self._numel = 0
+
+    def admits(self, bucket: BucketDescriptor) -> bool:
+        numel_limit, count_limit, same_dtype = self._limits
+        if not self._members:
+            return True
+        return (len(self._members) < count_limit and self._numel + bucket.numel <= numel_limit
+                and not (same_dtype and bucket.dtype != self._members[-1].dtype))
+
+    def add(self, bucket: BucketDescriptor) -> None:
+        self._members.append(bucket)
+        self._numel += bucket.numel
+
+    def close(self) -> Iterator[BucketFusionGroup]:
+        """Yields the finished group (nothing when the run is empty) and starts a new run."""
+
+        if self._members:
+            several = len(self._members) > 1
+            yield BucketFusionGroup(tuple(b.index for b in self._members), self._numel, self._members[0].dtype,
+                                    several, "compatible adjacent buckets" if several else "single compatible bucket")
+        self._members, self._numel = [], 0
 
 
 def _alone(bucket: BucketDescriptor, why: str) -> BucketFusionGroup:
     return BucketFusionGroup((bucket.index,), bucket.numel, bucket.dtype, False, why)
 
 
-def _close(run: list[BucketDescriptor]) -> BucketFusionGroup:
-    many = len(run) > 1
-    return BucketFusionGroup(tuple(b.index for b in run), sum(b.numel for b in run), run[0].dtype, many,
-                             "compatible adjacent buckets" if many else "single compatible bucket")
+def _groups(buckets: Iterable[BucketDescriptor], enabled: bool, run: _Run) -> Iterator[BucketFusionGroup]:
+    for bucket in buckets:
+        if bucket.numel <= 0:
+            raise ValueError("bucket numel must be positive")
+        if not enabled:
+            yield _alone(bucket, "fusion disabled")
+        elif bucket.requires_full_bucket:
+            yield from run.close()
+            yield _alone(bucket, "requires full-bucket consumer")
+        else:
+            if not run.admits(bucket):
+                yield from run.close()
+            run.add(bucket)
+    yield from run.close()
 
 
-def plan_bucket_fusion(buckets: Sequence[BucketDescriptor], *, enabled: bool = True,
+def plan_bucket_fusion(buckets: Iterable[BucketDescriptor], *, enabled: bool = True,
                        max_fused_numel: int = DEFAULT_MAX_FUSED_BUCKET_NUMEL,
                        max_bucket_count: int = DEFAULT_MAX_FUSED_BUCKET_COUNT,
                        require_same_dtype: bool = True) -> BucketFusionPlan:
-    if max_fused_numel <= 0:
-        raise ValueError("max_fused_numel must be positive")
-    if max_bucket_count <= 0:
-        raise ValueError("max_bucket_count must be positive")
-    out: list[BucketFusionGroup] = []
-    run: list[BucketDescriptor] = []
-    for b in buckets:
-        if b.numel <= 0:
-            raise ValueError("bucket numel must be positive")
-        if not enabled:
-            out.append(_alone(b, "fusion disabled"))
-            continue
-        if b.requires_full_bucket:
-            if run:
-                out.append(_close(run))
-                run = []
-            out.append(_alone(b, "requires full-bucket consumer"))
-            continue
-        fits = bool(run) and len(run) < max_bucket_count \
-            and sum(x.numel for x in run) + b.numel <= max_fused_numel \
-            and (not require_same_dtype or b.dtype == run[-1].dtype)
-        if run and not fits:
-            out.append(_close(run))
-            run = []
-        run.append(b)
-    if run:
-        out.append(_close(run))
-    return BucketFusionPlan(enabled, tuple(out))
+    for name, limit in (("max_fused_numel", max_fused_numel), ("max_bucket_count", max_bucket_count)):
+        if limit <= 0:
+            raise ValueError(f"{name} must be positive")
+    run = _Run(max_fused_numel, max_bucket_count, require_same_dtype)
+    return BucketFusionPlan(enabled, tuple(_groups(buckets, enabled, run)))

@@ -1,116 +1,153 @@
-"""Public shortcuts for the nine native collectives (parity: ccdl_comm/collectives/api.py:14-337).
+"""The nine uncompressed collectives behind the same compile/run interface as the compressed ones.
 
-Every function returns a `CollectiveWork`; pass `compiled_plan` to reuse a plan
-made by `compile_collective` in steady state.
+`lbc.all_reduce(t)`, `lbc.broadcast(t, src=1)` ... each describe their call as a `_Call` (which tensor stands
+for the shape, what is handed to the executor, who is root) and `_Call.submit` does the rest: compile -- or take
+the caller's `compiled_plan` -- run, and for a synchronous one-off call wait.  One-off calls compile against
+one process-wide default registry per device kind and through a small LRU of compiled plans, so a loop that
+calls `lbc.all_reduce(t)` with the same shape compiles once.  Every function returns a `CollectiveWork`.
+Names and keyword arguments are the reference's (ccdl_comm/collectives/api.py:14-337).
 """
 
 from __future__ import annotations
 
+from dataclasses import dataclass
 from importlib import import_module
 from typing import Any
 
-from ...core.compiler import compile as compile_plan, normalize_dtype
+from ...core.compiler import CompileCache, compile as compile_plan, normalize_dtype
 from ...core.executor import CompiledCommunicationPlan
 from ...core.plan import CommunicationPlan, CompileContext
 from ...core.registry import BackendRegistry
 from ..native_collectives import NATIVE_COLLECTIVES, NativeCollectiveInput
+
+_default_registries: dict[bool, BackendRegistry] = {}
+_one_off_plans = CompileCache(max_entries=32)
 
 
 def native_collectives() -> tuple[str, ...]:
     return NATIVE_COLLECTIVES
 
 
+def _default_registry(on_cuda: bool) -> BackendRegistry:
+    registry = _default_registries.get(on_cuda)
+    if registry is None:
+        from ..backend_cuda import register_cuda_backends
+
+        registry = BackendRegistry()
+        register_cuda_backends(registry, allow_cpu=not on_cuda)
+        _default_registries[on_cuda] = registry
+    return registry
+
+
+def _architecture(device: str, torch: Any | None) -> str:
+    """`sm_<major><minor>` of a CUDA device, "unknown" for anything else or when it cannot be asked."""
+
+    if not device.startswith("cuda"):
+        return "unknown"
+    try:
+        major, minor = (torch or import_module("torch")).cuda.get_device_capability(device)
+    except Exception:  # noqa: BLE001  (no torch, no driver, bad index: the fact is simply not known)
+        return "unknown"
+    return f"sm_{major}{minor}"
+
+
 def context_from_tensor(tensor: object | None, *, group: object | None = None, device: str | None = None,
                         dist: Any | None = None, torch: Any | None = None) -> CompileContext:
-    d = dist if dist is not None else import_module("torch.distributed")
-    rank = int(d.get_rank(group=group))
-    world = int(d.get_world_size(group=group))
+    """Compile-time facts read off one representative tensor and the process group.  Without a tensor and
+    without `device`, the current CUDA device is meant when there is one, else the CPU."""
+
+    dist = dist or import_module("torch.distributed")
     where = device or str(getattr(tensor, "device", ""))
     if not where:
-        t = torch if torch is not None else import_module("torch")
-        where = f"cuda:{int(t.cuda.current_device())}" if t.cuda.is_available() else "cpu"
-    arch = "unknown"
-    if where.startswith("cuda"):
-        try:
-            t = torch if torch is not None else import_module("torch")
-            major, minor = t.cuda.get_device_capability(where)
-            arch = f"sm_{major}{minor}"
-        except Exception:  # noqa: BLE001
-            arch = "unknown"
-    return CompileContext(rank=rank, world_size=world, device=where, shape=tuple(getattr(tensor, "shape", ())),
-                          dtype=normalize_dtype(str(getattr(tensor, "dtype", "fp32"))), process_group=group,
-                          device_architecture=arch)
+        cuda = (torch or import_module("torch")).cuda
+        where = f"cuda:{int(cuda.current_device())}" if cuda.is_available() else "cpu"
+    return CompileContext(
+        rank=int(dist.get_rank(group=group)), world_size=int(dist.get_world_size(group=group)), device=where,
+        shape=tuple(getattr(tensor, "shape", ())), dtype=normalize_dtype(str(getattr(tensor, "dtype", "fp32"))),
+        process_group=group, device_architecture=_architecture(where, torch))
 
 
 def compile_collective(sample: object | None, *, collective: str, group: object | None = None, root: int = 0,
                        op: str = "sum", async_op: bool = False, plan: CommunicationPlan | None = None,
-                       registry: BackendRegistry | None = None, device: str | None = None) -> CompiledCommunicationPlan:
-    active = plan or CommunicationPlan(collective=collective, strategy="native_nccl", backend="cuda",
-                                       output_layout="full", async_op=async_op, root=root, reduce_op=op)
-    if active.collective != collective:
-        raise ValueError(f"plan collective {active.collective!r} does not match requested collective {collective!r}")
+                       registry: BackendRegistry | None = None, device: str | None = None,
+                       cache: CompileCache | None = None) -> CompiledCommunicationPlan:
+    """A reusable plan for one native collective on tensors shaped like `sample`."""
+
+    if plan is None:
+        plan = CommunicationPlan(collective=collective, strategy="native_nccl", backend="cuda", output_layout="full",
+                                 async_op=async_op, root=root, reduce_op=op)
+    elif plan.collective != collective:
+        raise ValueError(f"plan collective {plan.collective!r} does not match requested collective {collective!r}")
     context = context_from_tensor(sample, group=group, device=device)
-    reg = registry
-    if reg is None:
-        from ..backend_cuda import register_cuda_backends
-
-        reg = BackendRegistry()
-        register_cuda_backends(reg, allow_cpu=not context.device.startswith("cuda"))
-    return compile_plan(active, context, registry=reg)
+    return compile_plan(plan, context, cache=cache,
+                        registry=registry or _default_registry(context.device.startswith("cuda")))
 
 
-def _run(sample, invocation, *, collective, group, root=0, op="sum", async_op=False, plan=None, compiled_plan=None,
-         device=None):
-    compiled = compiled_plan or compile_collective(sample, collective=collective, group=group, root=root, op=op,
-                                                   async_op=async_op, plan=plan, device=device)
-    work = compiled.run(invocation)
-    if not async_op and compiled_plan is None:
-        work.wait()
-    return work
+@dataclass(frozen=True)
+class _Call:
+    collective: str
+    sample: object | None          # stands for shape, dtype and device at compile time
+    payload: object                # what the executor's run() receives
+    root: int = 0
+    op: str = "sum"
+
+    def submit(self, *, group, async_op, plan, compiled_plan, device=None):
+        if compiled_plan is not None:
+            return compiled_plan.run(self.payload)
+        work = compile_collective(self.sample, collective=self.collective, group=group, root=self.root, op=self.op,
+                                  async_op=async_op, plan=plan, device=device, cache=_one_off_plans).run(self.payload)
+        if not async_op:
+            work.wait()
+        return work
+
+
+def _lists(tensor=None, *, inputs=(), outputs=()) -> NativeCollectiveInput:
+    return NativeCollectiveInput(tensor=tensor, input_tensors=tuple(inputs), output_tensors=tuple(outputs))
 
 
 def all_reduce(tensor, *, op="sum", group=None, async_op=False, plan=None, compiled_plan=None):
-    return _run(tensor, tensor, collective="all_reduce", group=group, op=op, async_op=async_op, plan=plan,
-                compiled_plan=compiled_plan)
-
-
-def all_gather(tensor, *, output_tensors=(), group=None, async_op=False, plan=None, compiled_plan=None):
-    return _run(tensor, NativeCollectiveInput(tensor=tensor, output_tensors=tuple(output_tensors)),
-                collective="all_gather", group=group, async_op=async_op, plan=plan, compiled_plan=compiled_plan)
-
-
-def reduce_scatter(output, *, input_tensors, op="sum", group=None, async_op=False, plan=None, compiled_plan=None):
-    return _run(output, NativeCollectiveInput(tensor=output, input_tensors=tuple(input_tensors)),
-                collective="reduce_scatter", group=group, op=op, async_op=async_op, plan=plan,
-                compiled_plan=compiled_plan)
-
-
-def all_to_all(*, output_tensors, input_tensors, group=None, async_op=False, plan=None, compiled_plan=None):
-    sample = input_tensors[0] if input_tensors else None
-    return _run(sample, NativeCollectiveInput(input_tensors=tuple(input_tensors), output_tensors=tuple(output_tensors)),
-                collective="all_to_all", group=group, async_op=async_op, plan=plan, compiled_plan=compiled_plan)
+    call = _Call("all_reduce", tensor, tensor, op=op)
+    return call.submit(group=group, async_op=async_op, plan=plan, compiled_plan=compiled_plan)
 
 
 def broadcast(tensor, *, src=0, group=None, async_op=False, plan=None, compiled_plan=None):
-    return _run(tensor, tensor, collective="broadcast", group=group, root=src, async_op=async_op, plan=plan,
-                compiled_plan=compiled_plan)
+    call = _Call("broadcast", tensor, tensor, root=src)
+    return call.submit(group=group, async_op=async_op, plan=plan, compiled_plan=compiled_plan)
 
 
 def reduce(tensor, *, dst=0, op="sum", group=None, async_op=False, plan=None, compiled_plan=None):
-    return _run(tensor, tensor, collective="reduce", group=group, root=dst, op=op, async_op=async_op, plan=plan,
-                compiled_plan=compiled_plan)
+    call = _Call("reduce", tensor, tensor, root=dst, op=op)
+    return call.submit(group=group, async_op=async_op, plan=plan, compiled_plan=compiled_plan)
+
+
+def all_gather(tensor, *, output_tensors=(), group=None, async_op=False, plan=None, compiled_plan=None):
+    call = _Call("all_gather", tensor, _lists(tensor, outputs=output_tensors))
+    return call.submit(group=group, async_op=async_op, plan=plan, compiled_plan=compiled_plan)
 
 
 def gather(tensor, *, gather_list=(), dst=0, group=None, async_op=False, plan=None, compiled_plan=None):
-    return _run(tensor, NativeCollectiveInput(tensor=tensor, output_tensors=tuple(gather_list)), collective="gather",
-                group=group, root=dst, async_op=async_op, plan=plan, compiled_plan=compiled_plan)
+    call = _Call("gather", tensor, _lists(tensor, outputs=gather_list), root=dst)
+    return call.submit(group=group, async_op=async_op, plan=plan, compiled_plan=compiled_plan)
+
+
+def reduce_scatter(output, *, input_tensors, op="sum", group=None, async_op=False, plan=None, compiled_plan=None):
+    call = _Call("reduce_scatter", output, _lists(output, inputs=input_tensors), op=op)
+    return call.submit(group=group, async_op=async_op, plan=plan, compiled_plan=compiled_plan)
 
 
 def scatter(output, *, scatter_list=(), src=0, group=None, async_op=False, plan=None, compiled_plan=None):
-    return _run(output, NativeCollectiveInput(tensor=output, input_tensors=tuple(scatter_list)), collective="scatter",
-                group=group, root=src, async_op=async_op, plan=plan, compiled_plan=compiled_plan)
+    call = _Call("scatter", output, _lists(output, inputs=scatter_list), root=src)
+    return call.submit(group=group, async_op=async_op, plan=plan, compiled_plan=compiled_plan)
+
+
+def all_to_all(*, output_tensors, input_tensors, group=None, async_op=False, plan=None, compiled_plan=None):
+    both = (*input_tensors, *output_tensors)
+    if not both:
+        raise ValueError("all_to_all requires at least one tensor")
+    call = _Call("all_to_all", both[0], _lists(inputs=input_tensors, outputs=output_tensors))
+    return call.submit(group=group, async_op=async_op, plan=plan, compiled_plan=compiled_plan)
 
 
 def barrier(*, group=None, async_op=False, device=None, plan=None, compiled_plan=None):
-    return _run(None, NativeCollectiveInput(), collective="barrier", group=group, async_op=async_op, plan=plan,
-                compiled_plan=compiled_plan, device=device)
+    call = _Call("barrier", None, _lists())
+    return call.submit(group=group, async_op=async_op, plan=plan, compiled_plan=compiled_plan, device=device)

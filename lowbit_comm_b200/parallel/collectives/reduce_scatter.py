@@ -1,5 +1,13 @@
-"""`compressed_reduce_scatter` and the reduced-shard interface
-(parity: ccdl_comm/collectives/reduce_scatter.py:19-115)."""
+"""Compressed reduce-scatter, with the result either re-assembled on every rank (`compressed_reduce_scatter`)
+or left as this rank's shard (`compressed_reduce_scatter_shard`, for sharded optimizers).
+
+Routes of the full-layout call: an injected `reduce_scatter` transport, or else the communicator's two-stage
+peer-memory path; then `all_gather_fallback` when the first declines.  Routes of the shard call: a compiled
+plan when the caller holds one, else an injected `reduce_scatter_shard` transport, else the communicator.
+`out` may be a caller-owned flat tensor (or an output lease) that receives the shard; whoever serves the call
+validates its shape, dtype, device, contiguity and aliasing.  Keyword names are the reference's
+(ccdl_comm/collectives/reduce_scatter.py:19-115); `group` is an addition.
+"""
 
 from __future__ import annotations
 
@@ -8,83 +16,46 @@ from typing import Any
 
 from ...config import CompressionConfig
 from ...core.shard import ReducedShard
-from ...core.work import CollectiveWork, ImmediateWork
-from ...exceptions import UnsupportedCollective
+from ...core.work import CollectiveWork
+from ._routes import as_requested, check_reduction, first_that_serves, injected
 
 
-def _as_work(value: Any, async_op: bool) -> Any:
-    is_work = callable(getattr(value, "wait", None)) and not hasattr(value, "shape") and not isinstance(value, ReducedShard)
-    if async_op:
-        return value if is_work else ImmediateWork(value)
-    return value.wait() if is_work else value
-
-
-def compressed_reduce_scatter(
-    tensor: Any,
-    *,
-    config: CompressionConfig,
-    op: str = "mean",
-    async_op: bool = False,
-    dtype: str = "auto",
-    reduce_scatter: Callable[..., Any] | None = None,
-    all_gather_fallback: Callable[..., Any] | None = None,
-    extension_status: Any | None = None,
-    group: Any | None = None,
-) -> Any:
-    """Full-layout result computed through a compressed reduce-scatter + gather.
-
-    With an injected `reduce_scatter` transport that transport runs (or
-    `all_gather_fallback` when it raises `UnsupportedCollective`); otherwise the
-    group's communicator runs its two-stage path and returns the full tensor.
-    """
-
-    if op not in ("sum", "mean"):
-        raise UnsupportedCollective(f"reduce_scatter:{op}", reason="only op='sum' and op='mean' are implemented")
-    if reduce_scatter is not None:
-        try:
-            return _as_work(reduce_scatter(tensor, config=config, op=op, async_op=async_op, dtype=dtype,
-                                           extension_status=extension_status), async_op)
-        except UnsupportedCollective:
-            if all_gather_fallback is None:
-                raise
-            return _as_work(all_gather_fallback(tensor, config=config, op=op, async_op=async_op, dtype=dtype,
-                                                extension_status=extension_status), async_op)
+def _communicator(group: Any | None):
     from ..communicator import get_communicator
 
-    result = get_communicator(group).reduce_scatter_full(tensor, config=config, op=op, dtype=dtype)
-    return _as_work(result, async_op)
+    return get_communicator(group)
 
 
-def compressed_reduce_scatter_shard(
-    tensor: Any,
-    *,
-    config: CompressionConfig,
-    op: str = "mean",
-    async_op: bool = False,
-    dtype: str = "auto",
-    reduce_scatter_shard: Callable[..., Any] | None = None,
-    extension_status: Any | None = None,
-    compiled_plan: Any | None = None,
-    out: Any | None = None,
-    group: Any | None = None,
-) -> ReducedShard | CollectiveWork[ReducedShard]:
-    """Reduce across ranks and keep only this rank's shard (for sharded optimizers).
+def compressed_reduce_scatter(tensor: Any, *, config: CompressionConfig, op: str = "mean", async_op: bool = False,
+                              dtype: str = "auto", reduce_scatter: Callable[..., Any] | None = None,
+                              all_gather_fallback: Callable[..., Any] | None = None,
+                              extension_status: Any | None = None, group: Any | None = None) -> Any:
+    check_reduction("reduce_scatter", op)
+    request = {"config": config, "op": op, "async_op": async_op, "dtype": dtype,
+               "extension_status": extension_status}
+    if reduce_scatter is None:
+        routes = [lambda t: _communicator(group).reduce_scatter_full(t, config=config, op=op, dtype=dtype)]
+    else:
+        routes = [injected(reduce_scatter, request)]
+    if all_gather_fallback is not None:
+        routes.append(injected(all_gather_fallback, request))
+    return as_requested(first_that_serves(routes, tensor, what="reduce_scatter"), async_op)
 
-    `out` may be a caller-owned flat tensor (or an output lease) that receives the
-    shard; it is validated for shape, dtype, device, contiguity and aliasing.
-    """
 
-    if op not in ("sum", "mean"):
-        raise UnsupportedCollective(f"reduce_scatter:{op}", reason="only op='sum' and op='mean' are implemented")
+def compressed_reduce_scatter_shard(tensor: Any, *, config: CompressionConfig, op: str = "mean",
+                                    async_op: bool = False, dtype: str = "auto",
+                                    reduce_scatter_shard: Callable[..., Any] | None = None,
+                                    extension_status: Any | None = None, compiled_plan: Any | None = None,
+                                    out: Any | None = None,
+                                    group: Any | None = None) -> ReducedShard | CollectiveWork[ReducedShard]:
+    check_reduction("reduce_scatter", op)
+    into = {} if out is None else {"out": out}
     if compiled_plan is not None:
-        work = compiled_plan.run(tensor, out=out) if out is not None else compiled_plan.run(tensor)
-        return _as_work(work, async_op)
-    if reduce_scatter_shard is not None:
-        kwargs = dict(config=config, op=op, async_op=async_op, dtype=dtype, extension_status=extension_status)
-        if out is not None:
-            kwargs["out"] = out
-        return _as_work(reduce_scatter_shard(tensor, **kwargs), async_op)
-    from ..communicator import get_communicator
-
-    return get_communicator(group).reduce_scatter_shard(tensor, config=config, op=op, async_op=async_op,
-                                                        dtype=dtype, out=out)
+        route = lambda t: compiled_plan.run(t, **into)                                     # noqa: E731
+    elif reduce_scatter_shard is not None:
+        route = injected(reduce_scatter_shard, {"config": config, "op": op, "async_op": async_op, "dtype": dtype,
+                                                "extension_status": extension_status}, **into)
+    else:
+        route = lambda t: _communicator(group).reduce_scatter_shard(                       # noqa: E731
+            t, config=config, op=op, async_op=async_op, dtype=dtype, out=out)
+    return as_requested(route(tensor), async_op)

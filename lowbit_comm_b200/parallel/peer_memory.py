@@ -31,7 +31,7 @@ from typing import Any
 
 import torch
 
-from ..exceptions import AsyncCommunicationError, CCDLError, CCDLUnavailableError
+from ..exceptions import AsyncCommunicationError, CCDLError, CCDLUnavailableError, DeviceWaitStatus
 from ..ops.loader import require_extension
 
 MAX_CHANNELS = 256
@@ -266,15 +266,12 @@ class PeerGroup:
 
     # -- status ---------------------------------------------------------------
     def read_status(self) -> dict:
-        code, phase, peer, seen, expected = self._ext.status_read(self.status_host)
-        return {"code": code, "phase": phase, "peer": peer, "seen": seen, "expected": expected}
+        return DeviceWaitStatus(*self._ext.status_read(self.status_host))._asdict()
 
     def check_status(self) -> None:
-        st = self.read_status()
-        if st["code"] != 0:
-            raise AsyncCommunicationError(
-                f"device wait timed out on rank {self.rank} (phase {st['phase']}, flag {st['peer']}, "
-                f"saw epoch {st['seen']}, expected {st['expected']})", status=st)
+        status = DeviceWaitStatus(*self._ext.status_read(self.status_host))
+        if status.timed_out:
+            raise AsyncCommunicationError.from_wait(self.rank, status)
 
     def clear_status(self) -> None:
         self._ext.status_clear(self.status_host)

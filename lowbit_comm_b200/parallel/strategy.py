@@ -1,15 +1,17 @@
-"""DDP-level strategy planner (torch-free).
+"""Which collective a DDP gradient hook should use (torch-free).
 
-Parity: ccdl_comm/communication/strategy.py:11-177 — same inputs, outputs and
-decisions (world <= 2 -> all_gather; multi-node -> hierarchical when the
-transport and process groups exist; single node -> reduce_scatter when
-available; otherwise fall back to all_gather with a reason).  Added: the
-`native_nccl` strategy name (uncompressed pass-through).
+The automatic choice is an ordered rule table (`_AUTO_RULES`): the first rule whose condition holds for the
+job's shape and the transports that exist names the strategy and says why; a rule that settles for
+`all_gather` because something better is missing marks the plan as a fallback.  Inputs, outputs, decisions
+and reason texts are the reference's (ccdl_comm/communication/strategy.py:11-177).  Added: the `native_nccl`
+strategy name (uncompressed pass-through).
 """
 
 from __future__ import annotations
 
+from collections.abc import Callable
 from dataclasses import dataclass, field
+from typing import NamedTuple
 
 from ..exceptions import UnsupportedCollective
 
@@ -57,43 +59,67 @@ class StrategyPlan:
     capability_flags: dict[str, bool]
 
 
+class _Job(NamedTuple):
+    """What the automatic rules look at."""
+
+    world_size: int
+    nodes: int | None
+    has_process_groups: bool
+    caps: CollectiveCapabilities
+
+    @property
+    def multi_node(self) -> bool:
+        return self.nodes is not None and self.nodes > 1
+
+
+class _Rule(NamedTuple):
+    applies: Callable[[_Job], bool]
+    strategy: str
+    reason: str
+    settles: bool = False        # True: all_gather chosen because the better transport is missing
+
+
+_AUTO_RULES: tuple[_Rule, ...] = (
+    _Rule(lambda j: j.world_size <= 2, "all_gather", "world_size<=2 uses validated all_gather path"),
+    # more than one node
+    _Rule(lambda j: j.multi_node and not j.caps.hierarchical, "all_gather",
+          "multi-node hierarchical unavailable; falling back to all_gather", True),
+    _Rule(lambda j: j.multi_node and not j.has_process_groups, "all_gather",
+          "process groups unavailable for multi-node hierarchical strategy; falling back to all_gather", True),
+    _Rule(lambda j: j.multi_node, "hierarchical", "multi-node hierarchical strategy selected"),
+    # one node
+    _Rule(lambda j: j.caps.reduce_scatter, "reduce_scatter", "single-node capable reduce_scatter strategy selected"),
+    _Rule(lambda j: j.caps.hierarchical and j.caps.hierarchical_recommended, "hierarchical",
+          "single-node hierarchical strategy selected"),
+    _Rule(lambda j: j.caps.hierarchical, "all_gather",
+          "hierarchical transport is not performance-recommended for single-node auto strategy; "
+          "falling back to all_gather", True),
+    _Rule(lambda j: True, "all_gather",
+          "reduce_scatter and hierarchical unavailable for single-node auto strategy; falling back to all_gather",
+          True),
+)
+
+
 def plan_ddp_compression_strategy(*, requested_strategy: str, world_size: int, rank: int = 0,
                                   local_world_size: int | None = None, node_count: int | None = None,
                                   bucket_numel: int = 0, topology: TopologyInfo | None = None,
                                   capabilities: CollectiveCapabilities | None = None) -> StrategyPlan:
-    del bucket_numel  # accepted for signature parity; sizes are handled by the strategy table
+    """`bucket_numel`, `rank` and `local_world_size` are accepted for callers written against the reference;
+    size-dependent choices are the strategy table's job."""
+
     wanted = requested_strategy.strip().lower()
     if wanted not in SUPPORTED_STRATEGIES:
         raise UnsupportedCollective(requested_strategy,
                                     reason="explicit strategy is unknown and no fallback was declared")
     caps = capabilities or CollectiveCapabilities()
-    flags = caps.flags()
     if wanted in _NEEDS_CAPABILITY and not getattr(caps, wanted):
         raise UnsupportedCollective(wanted, reason=f"{wanted} transport unavailable for explicit strategy")
-
-    def chosen(strategy: str, why: str, fallback: bool = False) -> StrategyPlan:
-        return StrategyPlan(wanted, strategy, "all_gather", why, fallback, flags)
-
-    if wanted != "auto":
-        return chosen(wanted, f"explicit strategy {wanted}")
-    topo = topology or TopologyInfo(rank=rank, world_size=world_size, local_world_size=local_world_size,
-                                    node_count=node_count)
-    nodes = topo.node_count if topo.node_count is not None else node_count
-    if world_size <= 2:
-        return chosen("all_gather", "world_size<=2 uses validated all_gather path")
-    if nodes is not None and nodes > 1:
-        if not caps.hierarchical:
-            return chosen("all_gather", "multi-node hierarchical unavailable; falling back to all_gather", True)
-        if not topo.has_process_groups:
-            return chosen("all_gather", "process groups unavailable for multi-node hierarchical strategy; "
-                                        "falling back to all_gather", True)
-        return chosen("hierarchical", "multi-node hierarchical strategy selected")
-    if caps.reduce_scatter:
-        return chosen("reduce_scatter", "single-node capable reduce_scatter strategy selected")
-    if caps.hierarchical and caps.hierarchical_recommended:
-        return chosen("hierarchical", "single-node hierarchical strategy selected")
-    if caps.hierarchical:
-        return chosen("all_gather", "hierarchical transport is not performance-recommended for single-node auto "
-                                    "strategy; falling back to all_gather", True)
-    return chosen("all_gather", "reduce_scatter and hierarchical unavailable for single-node auto strategy; "
-                                "falling back to all_gather", True)
+    if wanted == "auto":
+        nodes = topology.node_count if topology is not None and topology.node_count is not None else node_count
+        job = _Job(world_size, nodes, bool(topology and topology.has_process_groups), caps)
+        rule = next(r for r in _AUTO_RULES if r.applies(job))
+        strategy, reason, settles = rule.strategy, rule.reason, rule.settles
+    else:
+        strategy, reason, settles = wanted, f"explicit strategy {wanted}", False
+    return StrategyPlan(requested_strategy=wanted, strategy=strategy, fallback_strategy="all_gather", reason=reason,
+                        requires_fallback=settles, capability_flags=caps.flags())

@@ -15,8 +15,10 @@ uncompressed NCCL all-reduce is as fast and exact.
 
 from __future__ import annotations
 
+import math
 from collections.abc import Callable
 from dataclasses import dataclass
+from typing import NamedTuple
 
 from ..config import CompressionConfig
 from ..core.backend import StrategyChoice
@@ -30,14 +32,33 @@ PRODUCTION_PROFILE = CompressionConfig(bit=8, group_size=64)
 
 
 def _numel(shape: tuple[int, ...]) -> int:
-    total = 1
-    for d in shape:
-        total *= d
-    return total
+    return math.prod(shape)
 
 
 def normalize_architecture(value: str) -> str:
     return "_".join(value.strip().lower().replace("-", " ").split())
+
+
+def _profile(compression: CompressionConfig) -> tuple:
+    """The part of a compression config that changes the wire format (error-feedback settings do not)."""
+
+    return (compression.bit, compression.group_size, compression.topk, compression.quant_type)
+
+
+class RuleDomain(NamedTuple):
+    """Everything a rule is measured for except the size range.  Rules of one domain must not overlap."""
+
+    collective: str
+    output_layout: str
+    device_architecture: str
+    world_size: int
+    dtype: str
+    profile: tuple
+
+    @classmethod
+    def of_request(cls, plan: CommunicationPlan, context: CompileContext) -> "RuleDomain":
+        return cls(plan.collective, plan.output_layout, normalize_architecture(context.device_architecture),
+                   context.world_size, normalize_dtype(context.dtype), _profile(plan.compression))
 
 
 @dataclass(frozen=True)
@@ -61,18 +82,24 @@ class CudaStrategyRule:
             raise ValueError("strategy rule speedup must be > 0")
 
     @property
-    def domain(self) -> tuple:
-        return (self.collective, self.output_layout, self.device_architecture, self.world_size, self.dtype,
-                self.compression)
+    def domain(self) -> RuleDomain:
+        return RuleDomain(self.collective, self.output_layout, self.device_architecture, self.world_size, self.dtype,
+                          _profile(self.compression))
+
+    def covers(self, numel: int) -> bool:
+        return self.min_numel <= numel <= self.max_numel
+
+    def overlaps(self, other: "CudaStrategyRule") -> bool:
+        return self.domain == other.domain and (self.covers(other.min_numel) or other.covers(self.min_numel))
 
     def matches(self, context: CompileContext, compression: CompressionConfig, *, collective: str,
                 output_layout: str) -> bool:
-        same_profile = (compression.bit, compression.group_size, compression.topk, compression.quant_type) == \
-            (self.compression.bit, self.compression.group_size, self.compression.topk, self.compression.quant_type)
-        return (collective == self.collective and output_layout == self.output_layout
-                and normalize_architecture(context.device_architecture) == self.device_architecture
-                and context.world_size == self.world_size and normalize_dtype(context.dtype) == self.dtype
-                and same_profile and self.min_numel <= _numel(context.shape) <= self.max_numel)
+        asked = RuleDomain(collective, output_layout, normalize_architecture(context.device_architecture),
+                           context.world_size, normalize_dtype(context.dtype), _profile(compression))
+        return asked == self.domain and self.covers(_numel(context.shape))
+
+
+_SERVED = {("all_reduce", "full"), ("reduce_scatter", "shard")}
 
 
 class CudaStrategyTable:
@@ -80,10 +107,12 @@ class CudaStrategyTable:
                  evidence: str = B200_EVIDENCE, min_compress_numel: int = 262_144) -> None:
         self._rules = tuple(rules)
         self.policy_id, self.evidence, self.min_compress_numel = policy_id, evidence, min_compress_numel
-        for i, a in enumerate(self._rules):
-            for b in self._rules[i + 1:]:
-                if a.domain == b.domain and a.min_numel <= b.max_numel and b.min_numel <= a.max_numel:
-                    raise ValueError("CUDA strategy table contains overlapping rules")
+        self._by_domain: dict[RuleDomain, list[CudaStrategyRule]] = {}
+        for rule in self._rules:
+            same_domain = self._by_domain.setdefault(rule.domain, [])
+            if any(rule.overlaps(earlier) for earlier in same_domain):
+                raise ValueError("CUDA strategy table contains overlapping rules")
+            same_domain.append(rule)
 
     @property
     def rules(self) -> tuple[CudaStrategyRule, ...]:
@@ -138,48 +167,63 @@ class CudaStrategyTable:
             for (layout, world), speedup in published.items())
         return cls(rules, policy_id="cuda-task13-a6000-v1", evidence="tests/benchmarks/reports/task13_topology")
 
+    # -- selection --------------------------------------------------------------------------------------
+    def lookup(self, plan: CommunicationPlan, context: CompileContext) -> CudaStrategyRule | None:
+        """The measured rule that covers this request exactly, if there is one."""
+
+        numel = _numel(context.shape)
+        candidates = self._by_domain.get(RuleDomain.of_request(plan, context), ())
+        return next((rule for rule in candidates if rule.covers(numel)), None)
+
     def select(self, plan: CommunicationPlan, context: CompileContext) -> StrategyChoice:
         if not isinstance(plan, CommunicationPlan):
             raise TypeError("plan must be a CommunicationPlan")
         if not isinstance(context, CompileContext):
             raise TypeError("context must be a CompileContext")
-        comp = plan.compression
-        if comp is None:
-            return StrategyChoice("native_nccl", "uncompressed auto request uses native NCCL", self.policy_id, False)
-        semantic = (plan.collective, plan.output_layout)
-        if semantic not in {("all_reduce", "full"), ("reduce_scatter", "shard")}:
+        if plan.compression is None:
+            return self._unmeasured("native_nccl", "uncompressed auto request uses native NCCL")
+        if (plan.collective, plan.output_layout) not in _SERVED:
             raise UnsupportedCollective(f"{plan.collective}:{plan.output_layout}",
                                         reason="CUDA strategy table has no safe semantics for this request")
-        for rule in self._rules:
-            if rule.matches(context, comp, collective=plan.collective, output_layout=plan.output_layout):
-                same = rule.same_semantics_baseline
-                return StrategyChoice(
-                    rule.strategy,
-                    f"benchmark table {self.policy_id} matched all validated dimensions; observed speedup {rule.speedup:.2f}x",
-                    self.policy_id, True, expected_speedup=rule.speedup if same else None,
-                    observed_speedup=None if same else rule.speedup,
-                    baseline=None if same else "nccl_bf16_full_output_reference", evidence=self.evidence,
-                    fallback=("native_nccl",) if rule.output_layout == "full" else ())
-        if semantic == ("all_reduce", "full"):
-            small = _numel(context.shape) < self.min_compress_numel
-            why = ("small bucket uses uncompressed NCCL: launch latency dominates below "
-                   f"{self.min_compress_numel} elements") if small else \
-                "unverified dimensions use safe uncompressed NCCL: " + ", ".join(self._mismatches(context, comp))
-            return StrategyChoice("native_nccl", why, self.policy_id, False)
-        return StrategyChoice("compressed", "unverified sharded dimensions retain the only registered semantically "
-                              "compatible ReducedShard transport", self.policy_id, False)
+        rule = self.lookup(plan, context)
+        if rule is not None:
+            return self._measured(rule)
+        if plan.output_layout == "shard":
+            return self._unmeasured("compressed", "unverified sharded dimensions retain the only registered "
+                                                  "semantically compatible ReducedShard transport")
+        if _numel(context.shape) < self.min_compress_numel:
+            return self._unmeasured("native_nccl", "small bucket uses uncompressed NCCL: launch latency dominates "
+                                                   f"below {self.min_compress_numel} elements")
+        return self._unmeasured("native_nccl", "unverified dimensions use safe uncompressed NCCL: "
+                                + ", ".join(self._mismatches(context, plan.compression)))
+
+    def _unmeasured(self, strategy: str, why: str) -> StrategyChoice:
+        return StrategyChoice(strategy, why, self.policy_id, False)
+
+    def _measured(self, rule: CudaStrategyRule) -> StrategyChoice:
+        """A full-output rule compares like with like (expected speed-up, NCCL as the way back); a shard rule
+        is measured against NCCL's *full* all-reduce, so its speed-up is an observation with a named baseline."""
+
+        why = (f"benchmark table {self.policy_id} matched all validated dimensions; "
+               f"observed speedup {rule.speedup:.2f}x")
+        if rule.same_semantics_baseline:
+            kind = {"expected_speedup": rule.speedup}
+        else:
+            kind = {"observed_speedup": rule.speedup, "baseline": "nccl_bf16_full_output_reference"}
+        return StrategyChoice(rule.strategy, why, self.policy_id, True, evidence=self.evidence,
+                              fallback=("native_nccl",) if rule.output_layout == "full" else (), **kind)
 
     def _mismatches(self, context: CompileContext, comp: CompressionConfig) -> tuple[str, ...]:
-        out = []
-        if normalize_architecture(context.device_architecture) != "sm_100":
-            out.append("device_architecture")
-        if context.world_size not in {r.world_size for r in self._rules}:
-            out.append("world_size")
-        if normalize_dtype(context.dtype) not in {r.dtype for r in self._rules}:
-            out.append("dtype")
-        if (comp.bit, comp.group_size, comp.topk, comp.quant_type) != (8, 64, 0, "linear"):
-            out.append("compression_profile")
-        return tuple(out) or ("unmatched_rule",)
+        """Which dimensions of the request no rule of this table was measured for."""
+
+        measured = {name: {getattr(rule, name) for rule in self._rules}
+                    for name in ("device_architecture", "world_size", "dtype")}
+        asked = {"device_architecture": normalize_architecture(context.device_architecture),
+                 "world_size": context.world_size, "dtype": normalize_dtype(context.dtype)}
+        missing = [name for name, value in asked.items() if value not in measured[name]]
+        if _profile(comp) not in {_profile(rule.compression) for rule in self._rules}:
+            missing.append("compression_profile")
+        return tuple(missing) or ("unmatched_rule",)
 
     def as_selector(self) -> Callable[[CommunicationPlan, CompileContext], StrategyChoice]:
-        return lambda plan, context: self.select(plan, context)
+        return self.select

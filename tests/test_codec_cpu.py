@@ -122,6 +122,13 @@ def test_quantizer_facade_and_fallback_codec():
     assert Quantizer.from_dict(q.to_dict()).config == q.config
     with pytest.raises(ValueError):
         Quantizer().dequantize(p, x.shape)
+    assert q.is_quantized() and q.is_quantized(p) and not q.is_quantized(x)
+    assert q.wire_bytes(130) == p.numel() and q.roundtrip(x).dtype == x.dtype
+    err = q.error(x)
+    assert 0 < err["relative_rms"] < 0.02 and err["rms"] <= err["max_abs"]
+    calls = []
+    spy = Quantizer(cfg(), dtype="bf16", quantize_fn=lambda t, c, **kw: calls.append(sorted(kw)) or p)
+    assert spy.quantize(x) is p and calls == [["extension_status", "output"]]
     payload = quantize_tensor_fallback(x.float(), cfg())
     assert payload.buffer.dtype == torch.int8 and payload.metadata["scales"].dtype == torch.float32
     assert payload.metadata["original_numel"] == 130 and payload.buffer.numel() == 192
