@@ -1,0 +1,171 @@
+"""Behaviour the control plane adds on top of the reference's surface: write-once registry with diagnostics,
+grouped cache key, settle-once work objects, route lists, device wait status, named compression profiles."""
+
+import pytest
+
+from lowbit_comm_b200.config import CompressionConfig
+from lowbit_comm_b200.core.backend import BackendCapabilities
+from lowbit_comm_b200.core.executor import CompileCacheKey
+from lowbit_comm_b200.core.info import ExecutionCounters
+from lowbit_comm_b200.core.plan import CommunicationPlan, CompileContext
+from lowbit_comm_b200.core.registry import BackendKey, BackendRegistry
+from lowbit_comm_b200.core.work import BoundCollectiveWork, CompletionWork, ImmediateWork, bind_execution_work
+from lowbit_comm_b200.exceptions import (AsyncCommunicationError, BackendRegistrationError, DeviceWaitStatus,
+                                         UnsupportedCollective)
+from lowbit_comm_b200.parallel.bucket_fusion import BucketDescriptor, plan_bucket_fusion
+from lowbit_comm_b200.parallel.collectives._routes import as_requested, first_that_serves, injected
+from lowbit_comm_b200.parallel.strategy_table import CudaStrategyRule, CudaStrategyTable, PRODUCTION_PROFILE
+
+
+class _Backend:
+    name, abi_version = "fake", 1
+
+    def capabilities(self, context):
+        return BackendCapabilities(backend="fake", available=True)
+
+    def compile(self, plan, context):
+        raise NotImplementedError
+
+
+def test_registry_is_write_once_and_suggests_near_keys():
+    registry = BackendRegistry()
+
+    @registry.provides(collective="all_reduce", strategy="compressed", backend="cuda", output_layout="full")
+    class Provided(_Backend):
+        pass
+
+    key = BackendKey("all_reduce", "compressed", "cuda", "full")
+    assert key in registry and isinstance(registry.resolve(key), Provided)
+    with pytest.raises(BackendRegistrationError, match="already registered"):
+        registry.register(key, _Backend)
+    with pytest.raises(ValueError):
+        registry.register(BackendKey("all_reduce", " ", "cuda", "full"), _Backend)
+    with pytest.raises(TypeError):
+        registry.register(key._replace(strategy="other"), "not callable")
+    typo = key._replace(strategy="compresed")
+    assert typo.distance(key) == 1 and registry.nearest(typo) == (key,)
+    assert registry.nearest(BackendKey("a", "b", "c", "d")) == ()
+    assert registry.strategies_for("all_reduce", "cuda", "full") == {"compressed"}
+    with pytest.raises(UnsupportedCollective):
+        registry.resolve(typo)
+    registry.register(typo, lambda: object())
+    with pytest.raises(BackendRegistrationError, match="did not return"):
+        registry.resolve(typo)
+    registry.register_strategy_selector("cuda", lambda plan, context: None)
+    with pytest.raises(BackendRegistrationError):
+        registry.register_strategy_selector("cuda", lambda plan, context: None)
+    assert registry.strategy_selector("cuda") is not None and registry.strategy_selector("other") is None
+
+
+def test_cache_key_groups_facts_and_names_what_changed():
+    plan = CommunicationPlan(collective="all_reduce", strategy="compressed", backend="cuda", output_layout="full",
+                             compression=CompressionConfig())
+    ctx = CompileContext(rank=0, world_size=4, device="cuda:0", shape=(1024,), dtype="bf16")
+    registry = BackendRegistry()
+    one = CompileCacheKey.of(plan, plan, ctx, registry, None)
+    same = CompileCacheKey.of(plan, plan, ctx, registry, None)
+    assert one == same and hash(one) == hash(same) and one.differs_from(same) == ()
+    assert (one.collective, one.bit, one.group_size, one.world_size, one.shape_class) == ("all_reduce", 8, 64, 4, (1024,))
+    other_ctx = CompileContext(rank=1, world_size=4, device="cuda:1", shape=(2048,), dtype="bf16")
+    moved = CompileCacheKey.of(plan, plan, other_ctx, BackendRegistry(), None)
+    assert set(moved.differs_from(one)) == {"registry_identity", "shape_class", "rank", "device"}
+    with pytest.raises(AttributeError):
+        one.no_such_fact
+
+
+def test_work_objects_settle_once_and_count_once():
+    counters = ExecutionCounters()
+    calls = []
+    work = CompletionWork("early", complete=lambda: calls.append(1) or "late", execution_counters=counters)
+    assert not work.query() and work.wait() == "late" and work.wait() == "late" and calls == [1]
+    snap = counters.snapshot()
+    assert (snap.completed_runs, snap.failed_runs, snap.wait_calls, snap.query_calls) == (1, 0, 2, 1)
+
+    def boom():
+        raise RuntimeError("transport died")
+
+    failing = CompletionWork(None, complete=boom, execution_counters=counters)
+    for _ in range(2):
+        with pytest.raises(RuntimeError, match="transport died"):
+            failing.wait()
+    assert counters.snapshot().failed_runs == 1 and failing.query()
+
+    class Foreign:
+        def wait(self):
+            return 7
+
+        def is_completed(self):
+            return False
+
+    bound = bind_execution_work(Foreign(), None, counters)
+    assert isinstance(bound, BoundCollectiveWork) and not bound.query() and bound.wait() == 7 and bound.query()
+    plain = bind_execution_work(3, None, counters)
+    assert isinstance(plain, ImmediateWork) and plain.result == 3 and plain == ImmediateWork(3)
+    assert bind_execution_work(plain, None, counters) is plain
+    elsewhere = bind_execution_work(plain, None, ExecutionCounters())
+    assert elsewhere is not plain and elsewhere.result == 3
+
+
+def test_routes_fall_through_on_refusal_only():
+    def declines(t):
+        raise UnsupportedCollective("x", reason="not here")
+
+    assert first_that_serves([declines, lambda t: t + 1], 1, what="demo") == 2
+    with pytest.raises(UnsupportedCollective, match="not here"):
+        first_that_serves([declines], 1, what="demo")
+    with pytest.raises(UnsupportedCollective, match="no demo route"):
+        first_that_serves([], 1, what="demo")
+    with pytest.raises(ZeroDivisionError):
+        first_that_serves([lambda t: 1 / 0, lambda t: t], 1, what="demo")
+    seen = {}
+    injected(lambda t, **kw: seen.update(kw), {"op": "sum"}, out=None, extra=5)(0)
+    assert seen == {"op": "sum", "extra": 5}
+    assert as_requested(4, False) == 4 and as_requested(4, True).wait() == 4
+    assert as_requested(ImmediateWork(5), False) == 5
+
+
+def test_device_wait_status_round_trips_into_the_error():
+    quiet = DeviceWaitStatus()
+    assert not quiet.timed_out
+    status = DeviceWaitStatus(code=1, phase=0, peer=3, seen=4, expected=5)
+    error = AsyncCommunicationError.from_wait(2, status)
+    assert status.timed_out and "rank 2" in str(error) and "reduce-scatter" in str(error)
+    assert error.status == {"code": 1, "phase": 0, "peer": 3, "seen": 4, "expected": 5}
+    assert DeviceWaitStatus(1, 9, 0, 0, 0).phase_name == "phase 9"
+    assert AsyncCommunicationError("plain").status == {}
+
+
+def test_named_profiles_and_labels():
+    assert CompressionConfig.production() == CompressionConfig()
+    four = CompressionConfig.int4("e2m1", group_size=32)
+    assert (four.bit, four.quant_type, four.group_size, four.max_code) == (4, "e2m1", 32, 7)
+    assert four.evolve(topk=1).describe() == "int4 g32 e2m1 top1 ef=always"
+    with pytest.raises(ValueError):
+        four.evolve(group_size=48)
+    assert CompressionConfig.from_dict({**four.to_dict(), "from_the_future": 1}) == four
+
+
+def test_fusion_plan_counts_saved_launches():
+    buckets = [BucketDescriptor(i, 100, "bf16") for i in range(5)] + [BucketDescriptor(5, 100, "bf16", requires_full_bucket=True)]
+    plan = plan_bucket_fusion(buckets, max_bucket_count=3)
+    assert [g.bucket_indices for g in plan.groups] == [(0, 1, 2), (3, 4), (5,)]
+    assert plan.launches_saved == 3 and plan.to_metadata()["fused_bucket_count"] == 5
+    assert plan_bucket_fusion(buckets, enabled=False).launches_saved == 0
+
+
+def test_strategy_table_lookup_is_by_domain_and_rejects_overlap():
+    table = CudaStrategyTable.for_b200()
+    plan = CommunicationPlan(collective="all_reduce", strategy="auto", backend="cuda", output_layout="full",
+                             compression=CompressionConfig(error_feedback=False))
+    big = CompileContext(rank=0, world_size=8, device="cuda:0", shape=(1 << 26,), dtype="bf16", device_architecture="sm_100")
+    rule = table.lookup(plan, big)
+    assert rule is not None and rule.strategy == "reduce_scatter" and table.select(plan, big).benchmark_matched
+    small = CompileContext(rank=0, world_size=8, device="cuda:0", shape=(1 << 20,), dtype="bf16", device_architecture="sm_100")
+    assert table.lookup(plan, small).strategy == "all_gather"
+    odd = CompileContext(rank=0, world_size=3, device="cuda:0", shape=(1 << 26,), dtype="bf16", device_architecture="sm_100")
+    assert table.lookup(plan, odd) is None and "world_size" in table.select(plan, odd).reason
+    base = dict(collective="all_reduce", output_layout="full", device_architecture="sm_100", world_size=2, dtype="bf16",
+                compression=PRODUCTION_PROFILE, strategy="all_gather", speedup=1.1, same_semantics_baseline=True)
+    with pytest.raises(ValueError, match="overlapping"):
+        CudaStrategyTable((CudaStrategyRule(min_numel=0, max_numel=10, **base),
+                           CudaStrategyRule(min_numel=10, max_numel=20, **base)))
