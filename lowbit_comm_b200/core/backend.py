@@ -8,7 +8,7 @@ automatic strategy selector, with the evidence it rests on.  Field names follow 
 
 from __future__ import annotations
 
-from collections.abc import Mapping
+from collections.abc import Callable, Mapping
 from dataclasses import dataclass, field
 from typing import Protocol, runtime_checkable
 
@@ -45,24 +45,25 @@ class BackendCapabilities:
         if not self.available and not (self.reason and self.reason.strip()):
             raise ValueError("reason is required when backend is unavailable")
 
-    def why_not(self, plan: CommunicationPlan, context: CompileContext, *, dtype: str | None = None) -> str | None:
-        """The first reason this backend cannot serve `plan` in `context`, or None when it can."""
+    def why_not(self, plan: CommunicationPlan, context: CompileContext, *,
+                normalize_dtype: Callable[[str], str] = str) -> str | None:
+        """The first reason this backend cannot serve `plan` in `context`, or None when it can.  The compiler
+        collects these reasons for every candidate it had to pass over."""
 
         if not self.available:
-            return self.reason
-        wanted = (("collective", plan.collective, self.collectives), ("strategy", plan.strategy, self.strategies),
-                  ("output layout", plan.output_layout, self.output_layouts),
-                  ("dtype", dtype or context.dtype, self.dtypes))
-        for what, value, offered in wanted:
-            if offered and value not in offered:
-                return f"{what} {value!r} is not supported"
-        if plan.compression is not None and self.bits and plan.compression.bit not in self.bits:
-            return f"bit width {plan.compression.bit} is not supported"
-        if plan.async_op and not self.supports_async:
-            return "asynchronous execution is not supported"
-        if context.allow_dynamic_shape and not self.supports_dynamic_shape:
-            return "dynamic shape is not supported"
-        return None
+            return self.reason or "backend is unavailable"
+        bit = None if plan.compression is None else plan.compression.bit
+        dtypes = {normalize_dtype(name) for name in self.dtypes}
+        checks = (
+            (plan.collective in self.collectives, f"collective {plan.collective!r}"),
+            (plan.strategy in self.strategies, f"strategy {plan.strategy!r}"),
+            (normalize_dtype(context.dtype) in dtypes, f"dtype {context.dtype!r}"),
+            (bit is None or bit in self.bits, f"bit {bit}"),
+            (plan.output_layout in self.output_layouts, f"output layout {plan.output_layout!r}"),
+            (self.supports_async or not plan.async_op, "async execution"),
+            (self.supports_dynamic_shape or not context.allow_dynamic_shape, "dynamic shape"),
+        )
+        return next((f"{what} is unsupported" for served, what in checks if not served), None)
 
 
 @dataclass(frozen=True)

@@ -15,7 +15,7 @@ from dataclasses import dataclass, replace
 
 from ..exceptions import BackendRegistrationError, UnsupportedCollective
 from .backend import BackendCapabilities, StrategyChoice
-from .executor import CompileCacheKey, CompiledCommunicationPlan, CompiledExecutor, ObjectIdentity
+from .executor import CompileCacheKey, CompiledCommunicationPlan, CompiledExecutor
 from .info import ExecutionInfo
 from .plan import CommunicationPlan, CompileContext
 from .registry import BackendKey, BackendRegistry
@@ -187,25 +187,9 @@ def _describe(plan: CommunicationPlan, context: CompileContext, strategy: str, o
 
 def capability_rejection(caps: BackendCapabilities, plan: CommunicationPlan,
                          context: CompileContext) -> str | None:
-    """Reason the backend cannot serve `plan`, or None when it can."""
+    """Reason the backend cannot serve `plan`, or None when it can (dtype spellings are normalised first)."""
 
-    if not caps.available:
-        return caps.reason or "backend is unavailable"
-    if plan.collective not in caps.collectives:
-        return f"collective {plan.collective!r} is unsupported"
-    if plan.strategy not in caps.strategies:
-        return f"strategy {plan.strategy!r} is unsupported"
-    if normalize_dtype(context.dtype) not in {normalize_dtype(d) for d in caps.dtypes}:
-        return f"dtype {context.dtype!r} is unsupported"
-    if plan.compression is not None and plan.compression.bit not in caps.bits:
-        return f"bit {plan.compression.bit} is unsupported"
-    if plan.output_layout not in caps.output_layouts:
-        return f"output layout {plan.output_layout!r} is unsupported"
-    if plan.async_op and not caps.supports_async:
-        return "async execution is unsupported"
-    if context.allow_dynamic_shape and not caps.supports_dynamic_shape:
-        return "dynamic shape is unsupported"
-    return None
+    return caps.why_not(plan, context, normalize_dtype=normalize_dtype)
 
 
 def _pick_backend(plan: CommunicationPlan, context: CompileContext, registry: BackendRegistry):
@@ -214,7 +198,8 @@ def _pick_backend(plan: CommunicationPlan, context: CompileContext, registry: Ba
     for strategy, origin in _candidates(plan, context, registry, choice):
         key = _key(plan, strategy)
         if key not in registry:
-            refused.append(f"{strategy}: backend key is not registered")
+            close = ", ".join(str(k) for k in registry.nearest(key, limit=2))
+            refused.append(f"{strategy}: backend key is not registered" + (f" (closest: {close})" if close else ""))
             continue
         backend = registry.resolve(key)
         if backend.name != plan.backend:

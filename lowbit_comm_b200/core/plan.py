@@ -8,11 +8,10 @@ from __future__ import annotations
 
 from collections.abc import Mapping
 from dataclasses import dataclass, field
-from types import MappingProxyType
 
 from ..config import CompressionConfig
-from ._checks import (freeze, is_plain_int, need_optional_index, need_optional_minimum, need_shape, need_text,
-                      need_texts, read_only, text_tuple)
+from ._checks import (freeze, is_plain_int, need_optional_index, need_optional_minimum, need_shape, need_texts,
+                      read_only, text_tuple)
 
 _DTYPE_BYTES = {"fp16": 2, "bf16": 2, "fp32": 4, "float16": 2, "bfloat16": 2, "float32": 4}
 
