@@ -67,6 +67,8 @@ def main() -> None:
                     help="two-stage gather: peer loads by the decode kernel (pull) or peer stores by the reduce kernel")
     ap.add_argument("--gather-order", type=int, choices=(0, 1), default=None,
                     help="pull gather: 1 = tiles round-robin over the owners (default), 0 = linear sweep")
+    ap.add_argument("--gather-prefetch", type=int, choices=(0, 2, 4), default=None,
+                    help="decode stage: tiles of peer loads in flight per thread (0 = general reduce kernel)")
     ap.add_argument("--multicast", action="store_true",
                     help="arenas from the symmetric-memory allocator: broadcasts use multimem stores")
     ap.add_argument("--out", default="gpurun_out/allreduce_sweep.json")
@@ -103,6 +105,10 @@ def main() -> None:
         from lowbit_comm_b200.ops.loader import require_extension as _req
 
         _req().set_gather_order(args.gather_order)
+    if args.gather_prefetch is not None:
+        from lowbit_comm_b200.ops.loader import require_extension as _req
+
+        _req().set_gather_prefetch(args.gather_prefetch)
     if args.gather is not None:
         big.set_gather_mode(args.gather)
     if args.chunk_mib is not None:

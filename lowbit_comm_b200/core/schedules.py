@@ -178,3 +178,45 @@ def compile_direct_exchange_schedule(*, chunk_plan: ChunkPlan, rank: int) -> Dir
     r = _index(rank, plan.world_size, "rank")
     order = tuple((r + k) % plan.world_size for k in range(plan.world_size))
     return DirectExchangeSchedule(plan, r, order, order)
+
+
+@dataclass(frozen=True)
+class GatherTile:
+    """One 256-thread tile of the decode stage: `count` 16-element chunks of owner `owner`'s reduced shard,
+    starting at chunk `start` of that shard."""
+
+    owner: int
+    start: int
+    count: int
+
+
+def gather_tiles(*, block: int, grid: int, shard_chunks: int, world_size: int, first_owner: int,
+                 tiles_in_flight: int = 1, tile_chunks: int = 256) -> tuple[tuple[GatherTile, ...], ...]:
+    """The order in which block `block` of a `grid`-block decode kernel reads the reduced shards.
+
+    Tiles are numbered so that consecutive tiles belong to consecutive owners, starting at `first_owner`
+    (the rank itself): tile t is chunks [(t // W) * tile_chunks, ...) of owner (t + first_owner) % W.  A
+    block takes tiles block, block + grid, block + 2 grid ... and issues the loads of `tiles_in_flight`
+    of them before it decodes the first; each inner tuple is one such batch.  At any instant the blocks of
+    a GPU therefore read from all owners at once, and the GPUs, which start at their own index, never
+    gang up on one owner.  This is the tiling of `gather_decode_kernel` (and, with one tile in flight, of
+    the general reduce kernel's gather order 1), stated on the host so that it can be checked there.
+    """
+
+    if min(grid, shard_chunks, world_size, tiles_in_flight, tile_chunks) <= 0:
+        raise ValueError("grid, shard_chunks, world_size, tiles_in_flight and tile_chunks must be positive")
+    _index(block, grid, "block")
+    _index(first_owner, world_size, "first_owner")
+    tiles_per_shard = -(-shard_chunks // tile_chunks)
+    num_tiles = tiles_per_shard * world_size
+    batches = []
+    for t0 in range(block, num_tiles, grid * tiles_in_flight):
+        batch = []
+        for j in range(tiles_in_flight):
+            tile = t0 + j * grid
+            if tile >= num_tiles:
+                continue
+            start = (tile // world_size) * tile_chunks
+            batch.append(GatherTile((tile + first_owner) % world_size, start, min(tile_chunks, shard_chunks - start)))
+        batches.append(tuple(batch))
+    return tuple(batches)

@@ -329,6 +329,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("push_variant"), py::arg("reduce_bulk") = false, py::arg("reduce_push_blocks") = 0);
 
     m.def("set_gather_order", [](int order) { lbc_set_gather_order(order); }, py::arg("order"));
+    m.def("set_gather_prefetch", [](int tiles) { lbc_set_gather_prefetch(tiles); }, py::arg("tiles"));
+    m.def("get_gather_prefetch", []() { return lbc_get_gather_prefetch(); });
     m.def("arena_alloc", &lbc::arena_alloc);
     m.def("arena_free", &lbc::arena_free);
     m.def("ipc_get_handle", [](uintptr_t p) { return py::bytes(lbc::ipc_get_handle(p)); });

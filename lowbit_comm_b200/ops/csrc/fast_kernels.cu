@@ -620,6 +620,86 @@ __global__ void __launch_bounds__(kThreads, 4) reduce_kernel(const LbcReduce p) 
 }
 
 // ---------------------------------------------------------------------------
+// gather-decode with several tiles in flight
+// ---------------------------------------------------------------------------
+// The decode stage of the two-stage all-reduce, specialised: every group has exactly one source (its
+// owner's reduced shard, in this GPU's arena or in a peer's), nothing is re-encoded and nothing is pushed.
+// In `reduce_kernel` a thread has one 16-byte load in flight, and a load that crosses NVLink takes a few
+// microseconds to come back, so the stage is bound by latency, not by the links.  Here a thread first
+// issues the loads of U tiles (U x 16 bytes of codes and U scales in flight) and only then decodes them.
+// The tiles are dealt as in `reduce_kernel`'s gather order 1: tile t belongs to owner (t + first_src) % R
+// and covers chunks [(t / R) * 256, (t / R) * 256 + 256) of that owner's shard; neighbouring blocks read
+// from neighbouring owners, so all owners are read at once whatever the grid.  Results are bit-identical to `reduce_kernel` (same decode, one rounding).
+// Served: planar sources, group_offset 0, no destinations, no accumulation.
+template <typename T, int G, int BIT, int U>
+__global__ void __launch_bounds__(kThreads, U > 2 ? 3 : 4) gather_decode_kernel(const LbcReduce p) {
+    constexpr int lanes = G / kElemsPerThread;
+    constexpr int VB = G * BIT / 8;
+    constexpr int MB = sizeof(T);
+    constexpr int CB = kElemsPerThread * BIT / 8;
+    constexpr int lim = BIT == 8 ? 127 : 7;
+
+    if (!block_wait(p.wait)) return;
+
+    T* out = static_cast<T*>(p.out);
+    const T* prep = static_cast<const T*>(p.prepared);
+    T* rout = static_cast<T*>(p.residual_out);
+    const int64_t n = p.numel;
+    const int64_t num_chunks = (n + G - 1) / G * lanes;
+    const bool o_vec = out == nullptr || (reinterpret_cast<uintptr_t>(out) & 31) == 0;
+    const bool p_vec = prep == nullptr || (reinterpret_cast<uintptr_t>(prep) & 31) == 0;
+    const bool r_vec = rout == nullptr || (reinterpret_cast<uintptr_t>(rout) & 31) == 0;
+    const int64_t R = p.num_src;
+    const int64_t shard_chunks = p.src_shard_groups * lanes;
+    const int64_t tiles_per_shard = (shard_chunks + kThreads - 1) / kThreads;
+    const int64_t num_tiles = tiles_per_shard * R;
+    const int64_t scale_base = p.src_shard_groups * VB;      // scales follow the codes in every shard payload
+
+    for (int64_t t0 = blockIdx.x; t0 < num_tiles; t0 += int64_t(gridDim.x) * U) {
+        uint4 codes[U];
+        float step[U];
+        int64_t first[U];          // first element of the chunk, -1 when this thread has nothing to do in tile j
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const int64_t tile = t0 + int64_t(j) * gridDim.x;               // block-uniform
+            const int64_t owner = (tile + p.first_src) % R;
+            const int64_t within = (tile / R) * kThreads + threadIdx.x;     // chunk inside the owner's shard
+            const int64_t chunk = owner * shard_chunks + within;
+            const bool live = tile < num_tiles && within < shard_chunks && chunk < num_chunks;
+            first[j] = live ? chunk * kElemsPerThread : int64_t(-1);
+            codes[j] = make_uint4(0u, 0u, 0u, 0u);
+            step[j] = 0.0f;
+            if (live) {
+                const int64_t gl = within / lanes;
+                const int lane = int(within - gl * lanes);
+                const uint8_t* base = p.src[owner];
+                codes[j] = load_codes(base + gl * VB + lane * CB, CB);
+                step[j] = load_scale<T>(base + scale_base + gl * MB);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            if (first[j] < 0) continue;
+            float acc[16];
+            codes16<T, BIT>(codes[j], acc);
+            const float s = step[j] / float(lim);
+            // the same two roundings as the general kernel with one source: fma(code, step, +0), then the scale
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = __fmul_rn(__fmaf_rn(acc[i], s, 0.0f), p.scale);
+            if (rout != nullptr) {
+                float pv[16];
+                load16<T>(prep, first[j], n, p_vec, pv, prep != rout);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) pv[i] -= acc[i];
+                store16<T>(rout, first[j], n, r_vec, pv);
+            }
+            if (out != nullptr) store16<T>(out, first[j], n, o_vec, acc);   // store16 rounds to T
+        }
+    }
+    grid_signal(p.signal);
+}
+
+// ---------------------------------------------------------------------------
 // elementwise helpers
 // ---------------------------------------------------------------------------
 template <typename T>
@@ -730,6 +810,7 @@ static int g_push_variant = 1;
 // requantize-and-broadcast stage were 4-8 % faster than per-thread stores on the full grid.
 static int g_reduce_bulk = 1;
 static int g_gather_order = 1;          // decode stage of the all-reduce: 1 = tiles round-robin over the owners, 0 = linear sweep
+static int g_gather_prefetch = 0;       // decode stage: 0 = reduce_kernel, 2 or 4 = gather_decode_kernel with that many tiles in flight
 static int g_reduce_push_blocks = 0;   // grid cap of reduce kernels that also push: 0 = two per SM, < 0 = none
 
 static bool tiled_path_ok(const LbcQuantPush* p) {
@@ -772,6 +853,17 @@ struct ReduceLauncher {
         }
         const int grid = grid_for(groups * (G / kElemsPerThread), cap);
         LbcReduce launch = *p;
+        if constexpr (BIT == 8) {
+            const bool plain_gather = p->src_shard_groups > 0 && p->num_dst == 0 && p->group_offset == 0 &&
+                                      p->accumulate == 0 && p->compact == 0;
+            if (plain_gather && g_gather_prefetch >= 2) {
+                if (g_gather_prefetch >= 4)
+                    gather_decode_kernel<T, G, BIT, 4><<<grid, kThreads, 0, stream>>>(launch);
+                else
+                    gather_decode_kernel<T, G, BIT, 2><<<grid, kThreads, 0, stream>>>(launch);
+                return cudaGetLastError();
+            }
+        }
         launch.gather_order = g_gather_order;
         launch.bulk_store = p->num_dst > 1 ? g_reduce_bulk : 0;   // a single (local) destination takes plain stores
         reduce_kernel<T, G, BIT><<<grid, kThreads, 0, stream>>>(launch);
@@ -792,6 +884,10 @@ void lbc_set_push_variant(int push_variant, int reduce_bulk, int reduce_push_blo
 }
 
 void lbc_set_gather_order(int order) { lbc::g_gather_order = order != 0; }
+
+void lbc_set_gather_prefetch(int tiles) { lbc::g_gather_prefetch = tiles >= 4 ? 4 : (tiles >= 2 ? 2 : 0); }
+
+int lbc_get_gather_prefetch(void) { return lbc::g_gather_prefetch; }
 
 cudaError_t lbc_quant_push(const LbcQuantPush* p, cudaStream_t stream) {
     if (p == nullptr || p->numel < 0 || p->num_dst < 0 || p->num_dst > LBC_MAX_RANKS) return cudaErrorInvalidValue;

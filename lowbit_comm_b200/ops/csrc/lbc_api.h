@@ -142,6 +142,11 @@ int lbc_default_max_blocks(void);
 void lbc_set_push_variant(int push_variant, int reduce_bulk, int reduce_push_blocks);
 // Gather-mode decode: 1 (default) deals 256-thread tiles round-robin over the source shards, 0 sweeps linearly.
 void lbc_set_gather_order(int order);
+// Gather-mode decode of 8-bit planar shards: 0 (default) runs the general reduce kernel, one 16-byte load in
+// flight per thread; 2 or 4 runs the specialised kernel that issues the loads of that many tiles before it
+// decodes the first (same results, more bytes in flight over NVLink).  Other values round down.
+void lbc_set_gather_prefetch(int tiles);
+int lbc_get_gather_prefetch(void);
 
 #ifdef __cplusplus
 }

@@ -167,6 +167,11 @@ class FusedWorkspace:
         # 600 GB/s per GPU with the local work fully overlapped); False = the reduce stage stores its shard
         # into every rank's gather region.
         self.pull_gather = os.environ.get("LBC_GATHER", "pull") != "push"
+        # Decode stage with several tiles of peer loads in flight per thread (2 or 4); process-wide, off unless
+        # asked for.  `ext.set_gather_prefetch` changes it at run time.
+        prefetch = os.environ.get("LBC_GATHER_PREFETCH")
+        if prefetch is not None and hasattr(self.ext, "set_gather_prefetch"):
+            self.ext.set_gather_prefetch(int(prefetch))
         self._build_native()
 
     def _build_native(self) -> None:

@@ -169,3 +169,37 @@ def test_strategy_table_lookup_is_by_domain_and_rejects_overlap():
     with pytest.raises(ValueError, match="overlapping"):
         CudaStrategyTable((CudaStrategyRule(min_numel=0, max_numel=10, **base),
                            CudaStrategyRule(min_numel=10, max_numel=20, **base)))
+
+
+def test_peer_group_turns_the_status_word_into_an_error():
+    from lowbit_comm_b200.parallel.peer_memory import PeerGroup
+
+    class FakeExt:
+        word = (0, 0, 0, 0, 0)
+
+        def status_read(self, host):
+            return self.word
+
+    group = object.__new__(PeerGroup)       # no arena: only the status path is exercised
+    group._ext, group.status_host, group.rank = FakeExt(), 0, 5
+    group.check_status()
+    assert group.read_status() == {"code": 0, "phase": 0, "peer": 0, "seen": 0, "expected": 0}
+    FakeExt.word = (1, 1, 2, 6, 7)
+    with pytest.raises(AsyncCommunicationError, match=r"rank 5 \(phase 1: all-gather, flag 2, saw epoch 6, expected 7\)") as info:
+        group.check_status()
+    assert info.value.status["expected"] == 7 and info.value.status["seen"] == 6
+
+
+def test_gather_prefetch_switch_rounds_down_to_a_built_depth():
+    from lowbit_comm_b200.ops.loader import load_cuda_extension
+
+    status = load_cuda_extension()
+    if not status.available:
+        pytest.skip(f"extension not built: {status.reason}")
+    ext = status.module
+    try:
+        for asked, got in ((0, 0), (1, 0), (2, 2), (3, 2), (4, 4), (9, 4), (-1, 0)):
+            ext.set_gather_prefetch(asked)
+            assert ext.get_gather_prefetch() == got
+    finally:
+        ext.set_gather_prefetch(0)

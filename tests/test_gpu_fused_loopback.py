@@ -6,6 +6,8 @@ waits for a flag always starts after the kernels that set it.  Results are
 compared with the torch oracle composed the same way.
 """
 
+import os
+
 import pytest
 import torch
 
@@ -143,6 +145,39 @@ def test_gather_sweep_orders(ext, order, world, dtype, bit, group):
                 assert torch.equal(dev_r[r].cpu().view(torch.uint8), want[1][r].view(torch.uint8)), (n, r)
     finally:
         ext.set_gather_order(1)
+        PeerGroup.close_loopback(groups)
+
+
+@pytest.mark.skipif(os.environ.get("LBC_TEST_NEW_KERNELS") != "1",
+                    reason="gather_decode_kernel has not run on a GPU yet; set LBC_TEST_NEW_KERNELS=1 to run it")
+@pytest.mark.parametrize("depth", (2, 4))
+@pytest.mark.parametrize("world", (3, 8))
+@pytest.mark.parametrize("dtype,group", [("bf16", 64), ("fp16", 16), ("fp32", 32)])
+def test_gather_decode_with_tiles_in_flight(ext, depth, world, dtype, group):
+    """The specialised decode kernel (several tiles of loads in flight) gives the general kernel's bits."""
+
+    cfg = CompressionConfig(bit=8, group_size=group)
+    max_numel = 200_000
+    groups, wss = _make(world, dtype, cfg, max_numel)
+    ext.set_gather_prefetch(depth)
+    try:
+        assert ext.get_gather_prefetch() == depth
+        for step, n in enumerate((world * group * 8, 12_345, 1, max_numel, group * 8 * world * 31 + 5)):
+            xs = _inputs(world, n, dtype, seed=600 + step)
+            rs = _inputs(world, n, dtype, seed=700 + step)
+            dev_x = [x.cuda() for x in xs]
+            dev_r = [r.cuda() for r in rs]
+            run_loopback(wss, "all_reduce", [(dev_x[r],) for r in range(world)],
+                         [{"residual": dev_r[r]} for r in range(world)], stages=2)
+            want = _expected_two_stage(xs, rs, cfg, dtype)
+            for r in range(world):
+                assert torch.equal(dev_x[r].cpu().view(torch.uint8), want[0].view(torch.uint8)), (n, r)
+                assert torch.equal(dev_r[r].cpu().view(torch.uint8), want[1][r].view(torch.uint8)), (n, r)
+        torch.cuda.synchronize()
+        for g in groups:
+            g.check_status()
+    finally:
+        ext.set_gather_prefetch(0)
         PeerGroup.close_loopback(groups)
 
 

@@ -88,3 +88,49 @@ def test_argument_checks():
         compile_tree_schedule(chunk_plan=plan, rank=True)
     with pytest.raises(ValueError):
         compile_tree_schedule(chunk_plan=plan, rank=0, root=5)
+
+
+@pytest.mark.parametrize("world,groups_total,group,grid,depth", [
+    (8, 8 * 1024, 64, 592, 4), (8, 8 * 1000 + 8, 64, 7, 2), (4, 4 * 40, 16, 3, 4), (2, 2 * 8, 32, 1, 2),
+    (8, 8 * 8, 64, 1000, 4), (3, 3 * 24, 64, 5, 1),
+])
+def test_gather_tiles_cover_every_chunk_once_and_stay_inside_the_shard(world, groups_total, group, grid, depth):
+    """Mirror of the decode kernel's addressing: element ranges are covered exactly once and every byte
+    offset a thread computes lies inside the owner's shard payload (codes, then scales)."""
+
+    from lowbit_comm_b200.core.schedules import gather_tiles
+
+    lanes, value_bytes, scale_bytes, chunk_bytes = group // 16, group, 2, 16      # int8 codes, 16-bit scales
+    shard_groups = groups_total // world
+    shard_chunks = shard_groups * lanes
+    payload_bytes = shard_groups * (value_bytes + scale_bytes)
+    for first_owner in {0, world - 1}:
+        seen = []
+        for block in range(grid):
+            for batch in gather_tiles(block=block, grid=grid, shard_chunks=shard_chunks, world_size=world,
+                                      first_owner=first_owner, tiles_in_flight=depth):
+                assert len(batch) <= depth
+                for tile in batch:
+                    assert 0 <= tile.owner < world and tile.count > 0
+                    for within in range(tile.start, tile.start + tile.count):
+                        group_in_shard, lane = divmod(within, lanes)
+                        code_offset = group_in_shard * value_bytes + lane * chunk_bytes
+                        scale_offset = shard_groups * value_bytes + group_in_shard * scale_bytes
+                        assert code_offset + chunk_bytes <= shard_groups * value_bytes
+                        assert shard_groups * value_bytes <= scale_offset and scale_offset + scale_bytes <= payload_bytes
+                        seen.append(tile.owner * shard_chunks + within)
+        assert sorted(seen) == list(range(world * shard_chunks))
+
+
+def test_gather_tiles_start_at_the_rank_and_spread_over_owners():
+    from lowbit_comm_b200.core.schedules import gather_tiles
+
+    first = [gather_tiles(block=0, grid=16, shard_chunks=4096, world_size=8, first_owner=r, tiles_in_flight=4)[0]
+             for r in range(8)]
+    assert [batch[0].owner for batch in first] == list(range(8))          # every rank begins with its own shard
+    in_flight = gather_tiles(block=3, grid=17, shard_chunks=4096, world_size=8, first_owner=2, tiles_in_flight=4)[0]
+    assert len({t.owner for t in in_flight}) == 4                          # grid not a multiple of W: 4 owners at once
+    with pytest.raises(ValueError):
+        gather_tiles(block=0, grid=0, shard_chunks=1, world_size=1, first_owner=0)
+    with pytest.raises(ValueError):
+        gather_tiles(block=4, grid=4, shard_chunks=1, world_size=1, first_owner=0)
