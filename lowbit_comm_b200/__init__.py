@@ -19,7 +19,7 @@ from .core import (AutoStrategySelector, BackendCapabilities, BackendKey, Backen
                    ReducedShard, ResolvedPlan, StrategyChoice, WorkspacePolicy, bind_execution_work, compile,
                    resolve_plan)
 from .exceptions import (AsyncCommunicationError, BackendRegistrationError, CCDLError, CCDLUnavailableError,
-                         TorchDistributedUnavailableError, UnsupportedCollective)
+                         DeviceWaitStatus, TorchDistributedUnavailableError, UnsupportedCollective)
 from .plugin import CCDLCommunicationPlugin, PluginDecision
 
 __version__ = "0.1.0"
@@ -65,7 +65,15 @@ _LAZY = {
 }
 
 
+# whole modules under the name code written against the reference imports them by
+_LAZY_MODULES = {"ccdl_cuda_ops": ".ops.native_ops", "native_ops": ".ops.native_ops"}
+
+
 def __getattr__(name: str):
+    if name in _LAZY_MODULES:
+        value = import_module(_LAZY_MODULES[name], __name__)
+        globals()[name] = value
+        return value
     target = _LAZY.get(name)
     if target is None:
         raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
@@ -74,4 +82,4 @@ def __getattr__(name: str):
     return value
 
 
-__all__ = sorted([n for n in globals() if not n.startswith("_")] + list(_LAZY))
+__all__ = sorted([n for n in globals() if not n.startswith("_")] + list(_LAZY) + list(_LAZY_MODULES))
