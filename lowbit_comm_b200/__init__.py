@@ -62,6 +62,8 @@ _LAZY = {
     "make_native_topology_reduce_scatter_shard": ".parallel.transports",
     "make_torch_hierarchical_all_reduce": ".parallel.transports",
     "make_legacy_topology_all_reduce": ".parallel.transports",
+    "make_schedule_all_reduce": ".parallel.schedule_executors",
+    "PipelinedRingExecutor": ".parallel.schedule_executors", "TreeExecutor": ".parallel.schedule_executors",
 }
 
 

@@ -4,10 +4,10 @@ The reference drives its ring, tree and hierarchical all-reduce from immutable s
 (world size, rank): `PipelinedRingSchedule`, `TreeSchedule`, hierarchical stages
 (ccdl_comm/cuda/transports/pipelined_ring.py:14-120, 285-332; tree.py:15-75, 277-307).  On an NVSwitch
 node this library executes none of them hop by hop: every strategy name lands on the direct one-hop
-exchange of the fused kernels (`DirectExchangeSchedule` below states who writes to and reads from whom).
-The ring and tree schedules are still compiled here, with the reference's field names, for tools and
-callers that inspect them, and so that the topology definitions stay testable: `tests/test_schedules.py`
-executes them on integers and checks that they reduce and restore every chunk.
+exchange of the fused kernels (`DirectExchangeSchedule` below states who writes to and reads from whom,
+`gather_tiles` in which order a decode kernel reads).  The ring and tree schedules, with the reference's
+field names, drive `parallel/schedule_executors.py` for groups without peer access (other nodes, CPU ranks);
+`tests/test_schedules.py` executes them on integers and checks that they reduce and restore every chunk.
 """
 
 from __future__ import annotations

@@ -10,6 +10,8 @@ onto the `Communicator` of its process group, i.e. onto the fused push / reduce 
 the tensors are on CUDA and onto the same staging through torch.distributed otherwise.  On an NVSwitch
 node every peer is one hop away, so the ring, tree and pairwise schedules of the reference collapse into
 the one-stage and two-stage direct exchanges; the method names are accepted and select between those two.
+The ring and the tree also exist as real hop-by-hop executors (`parallel/schedule_executors.py`), for groups
+that span nodes or have no peer access; `make_native_topology_all_reduce(hop_by_hop=True)` selects them.
 Arguments that only made sense for the reference's host-driven schedules (workspace allocators, chunk
 plans, fused-kernel switches, future factories) are accepted and ignored.
 """
@@ -75,10 +77,16 @@ def make_torch_compressed_reduce_scatter_all_gather(*, group: Any | None = None,
 
 
 def make_native_topology_all_reduce(*, method: str | None = None, group: Any | None = None,
-                                    **_ignored: Any) -> Callable[..., Any]:
-    """transport(...) -> the full reduced tensor; `method` is one of the reference's topology names."""
+                                    hop_by_hop: bool = False, **_ignored: Any) -> Callable[..., Any]:
+    """transport(...) -> the full reduced tensor; `method` is one of the reference's topology names.
+    `hop_by_hop=True` (an addition, for "ring" and "tree") runs the schedule over point-to-point operations
+    instead of the direct exchange: the choice for groups that span nodes or have no peer access."""
 
     strategy = _strategy_for(method)
+    if hop_by_hop:
+        from .schedule_executors import make_schedule_all_reduce
+
+        return make_schedule_all_reduce(method=method or "ring", group=group)
 
     def transport(tensor: Any, *, config: CompressionConfig, op: str, async_op: bool, dtype: str,
                   extension_status: Any | None = None) -> Any:
