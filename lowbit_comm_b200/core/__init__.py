@@ -9,9 +9,10 @@ from .hierarchy import (CompiledStage, HierarchicalExecutor, StageExecution, can
 from .info import ExecutionCounters, ExecutionCounterSnapshot, ExecutionInfo
 from .plan import CommunicationPlan, CommunicationStage, CompileContext, WorkspacePolicy
 from .registry import BackendKey, BackendRegistry
-from .schedules import (DirectExchangeSchedule, GatherTile, PipelinedRingSchedule, RingAllGatherStep, RingReduceScatterStep,
-                        TreeEdge, TreeSchedule, compile_direct_exchange_schedule, compile_pipelined_ring_schedule,
-                        compile_tree_schedule, gather_tiles)
+from .schedules import (ButterflySchedule, DirectExchangeSchedule, GatherTile, PairwiseSchedule, PairwiseStep,
+                        PipelinedRingSchedule, RingAllGatherStep, RingReduceScatterStep, TreeEdge, TreeSchedule,
+                        compile_butterfly_schedule, compile_direct_exchange_schedule, compile_pairwise_schedule,
+                        compile_pipelined_ring_schedule, compile_tree_schedule, gather_tiles)
 from .shard import ReducedShard
 from .work import (BoundCollectiveWork, CollectiveWork, CompletionWork, ImmediateWork,
                    bind_execution_work)

@@ -220,3 +220,61 @@ def gather_tiles(*, block: int, grid: int, shard_chunks: int, world_size: int, f
             batch.append(GatherTile((tile + first_owner) % world_size, start, min(tile_chunks, shard_chunks - start)))
         batches.append(tuple(batch))
     return tuple(batches)
+
+
+# ---- pairwise exchange and butterfly: the other two hop-by-hop shapes ------------------------------------
+@dataclass(frozen=True)
+class PairwiseStep:
+    """Round k of the shifted pairwise exchange: this rank sends its contribution to the chunk owned by
+    `send_peer` straight to that owner and receives `recv_peer`'s contribution to its own chunk.  In the
+    gather phase the same pairs exchange finished chunks: own chunk out, `recv_peer`'s chunk in."""
+
+    step_index: int
+    send_peer: int
+    recv_peer: int
+    send_chunk: ChunkRange
+    recv_chunk: ChunkRange
+
+
+@dataclass(frozen=True)
+class PairwiseSchedule:
+    chunk_plan: ChunkPlan
+    rank: int
+    steps: tuple[PairwiseStep, ...]
+
+    @property
+    def local_chunk(self) -> ChunkRange:
+        return self.chunk_plan.chunk_for_rank(self.rank)
+
+
+def compile_pairwise_schedule(*, chunk_plan: ChunkPlan, rank: int) -> PairwiseSchedule:
+    """W - 1 rounds; in round k rank r sends to r + k and receives from r - k (mod W), so every round is a
+    permutation and works for any world size (the reference pairs ranks by XOR, which needs a power of two:
+    ccdl_comm/communication/topology_transport.py:751-863).  Every contribution crosses the network once and
+    is quantized once, unlike the ring, where a chunk is re-quantized at each of its W - 1 hops."""
+
+    plan = _plan(chunk_plan)
+    W = plan.world_size
+    r = _index(rank, W, "rank")
+    steps = tuple(PairwiseStep(k - 1, (r + k) % W, (r - k) % W, plan.chunk_for_rank((r + k) % W),
+                               plan.chunk_for_rank(r)) for k in range(1, W))
+    return PairwiseSchedule(plan, r, steps)
+
+
+@dataclass(frozen=True)
+class ButterflySchedule:
+    """Recursive doubling: in round k the rank exchanges its whole partial sum with `peers[k]` = rank XOR 2^k.
+    log2(W) rounds of full-size messages: the latency-optimal shape for small tensors."""
+
+    world_size: int
+    rank: int
+    peers: tuple[int, ...]
+
+
+def compile_butterfly_schedule(*, world_size: int, rank: int) -> ButterflySchedule:
+    if isinstance(world_size, bool) or not isinstance(world_size, int) or world_size <= 0:
+        raise ValueError("world_size must be a positive integer")
+    if world_size & (world_size - 1):
+        raise ValueError("recursive doubling needs a power-of-two world size")
+    r = _index(rank, world_size, "rank")
+    return ButterflySchedule(world_size, r, tuple(r ^ (1 << k) for k in range(world_size.bit_length() - 1)))

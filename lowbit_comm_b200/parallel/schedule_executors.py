@@ -1,4 +1,5 @@
-"""Hop-by-hop compressed all-reduce over `torch.distributed` point-to-point operations: ring and tree.
+"""Hop-by-hop compressed all-reduce over `torch.distributed` point-to-point operations: ring, tree, pairwise
+exchange and recursive doubling.
 
 Inside one NVSwitch domain the fused peer-memory kernels make every peer one hop away and these schedules are
 not needed.  They are for the groups those kernels cannot serve: ranks on different nodes (NCCL over the
@@ -9,6 +10,10 @@ ring   W - 1 reduce-scatter steps -- quantize the outgoing chunk, exchange paylo
        decode-and-add the incoming one -- then W - 1 gather steps that pass the finished chunks around.
 tree   reduce towards the root along the binary tree (children's payloads are decoded and added, the partial
        sum is quantized and sent up), then the root's payload travels back down.
+p2p    W - 1 rounds in which every rank sends its contribution to a chunk straight to the chunk's owner; the
+       owners reduce; the finished payloads are exchanged in W - 1 more rounds.  One quantization per
+       contribution, like the fused two-stage path.
+butterfly  recursive doubling, power-of-two groups: log2(W) exchanges of the whole partial sum.
 
 Role parity: the reference's pipelined ring and tree executors (ccdl_comm/cuda/transports/pipelined_ring.py:
 166-282, tree.py:141-274, torch_topology.py:67-230).  Two deliberate differences.  A finished chunk is
@@ -33,7 +38,8 @@ from typing import Any
 
 from ..config import CompressionConfig
 from ..core.chunking import ChunkPlan
-from ..core.schedules import compile_pipelined_ring_schedule, compile_tree_schedule
+from ..core.schedules import (compile_butterfly_schedule, compile_pairwise_schedule, compile_pipelined_ring_schedule,
+                              compile_tree_schedule)
 from ..exceptions import UnsupportedCollective
 
 _REDUCTIONS = ("sum", "mean")
@@ -243,16 +249,87 @@ class TreeExecutor(_ScheduleExecutor):
         self._decode(down, buffers.work, add=False)      # the root decodes its own payload too
 
 
-_EXECUTORS = {"ring": PipelinedRingExecutor, "tree": TreeExecutor}
+class PairwiseExecutor(_ScheduleExecutor):
+    """Shifted pairwise exchange: every contribution goes straight to the owner of its chunk (one hop, one
+    quantization), the owners reduce, and the finished payloads are exchanged the same way.  The dataflow of
+    the fused two-stage all-reduce, over point-to-point operations."""
+
+    method = "p2p"
+
+    def __init__(self, **kwargs: Any) -> None:
+        super().__init__(**kwargs)
+        padded = _ceil_to(self.numel, self.config.group_size * self.world_size)
+        self.chunk_plan = ChunkPlan.build(padded, self.world_size)
+        self.schedule = compile_pairwise_schedule(chunk_plan=self.chunk_plan, rank=self.rank)
+        self.chunk_payload_bytes = self._payload_bytes(self.chunk_plan.shard_numel)
+
+    def _make_buffers(self) -> _Buffers:
+        return _Buffers(self._torch, self.chunk_plan.padded_numel, self.chunk_payload_bytes, 2 + self.world_size,
+                        self._torch_dtype, self.device)
+
+    def _chunk(self, buffers: _Buffers, owner: int) -> Any:
+        lo, hi = self.chunk_plan.bounds(owner)
+        return buffers.work[lo:hi]
+
+    def _steps(self, buffers: _Buffers, inflight: list[Any]) -> None:
+        outgoing, incoming = buffers.payloads[0], buffers.payloads[1]
+        slots = buffers.payloads[2:]
+        mine = self._chunk(buffers, self.rank)
+        for step in self.schedule.steps:
+            self._encode(self._chunk(buffers, step.send_peer), outgoing)
+            self._exchange(outgoing, step.send_peer, incoming, step.recv_peer, inflight)
+            self._decode(incoming, mine, add=True)
+        if self.op == "mean" and self.world_size > 1:
+            mine.copy_((mine.float() * (1.0 / self.world_size)).to(mine.dtype))
+        self._encode(mine, slots[self.rank])
+        self._decode(slots[self.rank], mine, add=False)
+        for step in self.schedule.steps:                  # same pairs, the other way round: own chunk out, the sender's in
+            self._exchange(slots[self.rank], step.send_peer, slots[step.recv_peer], step.recv_peer, inflight)
+            self._decode(slots[step.recv_peer], self._chunk(buffers, step.recv_peer), add=False)
+
+
+class ButterflyExecutor(_ScheduleExecutor):
+    """Recursive doubling on a power-of-two group: log2(W) exchanges of the whole quantized partial sum.  Both
+    partners add the same two decoded payloads (their own included), so they stay bit-identical round by round."""
+
+    method = "butterfly"
+
+    def __init__(self, **kwargs: Any) -> None:
+        super().__init__(**kwargs)
+        self.padded_numel = _ceil_to(self.numel, self.config.group_size)
+        try:
+            self.schedule = compile_butterfly_schedule(world_size=self.world_size, rank=self.rank)
+        except ValueError as exc:
+            raise UnsupportedCollective(f"butterfly:W={self.world_size}", reason=str(exc)) from None
+        self.payload_bytes = self._payload_bytes(self.padded_numel)
+
+    def _make_buffers(self) -> _Buffers:
+        return _Buffers(self._torch, self.padded_numel, self.payload_bytes, 2, self._torch_dtype, self.device)
+
+    def _steps(self, buffers: _Buffers, inflight: list[Any]) -> None:
+        outgoing, incoming = buffers.payloads
+        for peer in self.schedule.peers:
+            self._encode(buffers.work, outgoing)
+            self._exchange(outgoing, peer, incoming, peer, inflight)
+            self._decode(outgoing, buffers.work, add=False)
+            self._decode(incoming, buffers.work, add=True)
+        if self.op == "mean" and self.world_size > 1:
+            buffers.work.copy_((buffers.work.float() * (1.0 / self.world_size)).to(buffers.work.dtype))
+
+
+# the reference's topology names for these shapes: its "tree" method is the recursive doubling, its compiled
+# tree executor the rooted binary tree; both are offered, under "butterfly" and "tree"
+_EXECUTORS = {"ring": PipelinedRingExecutor, "tree": TreeExecutor, "p2p": PairwiseExecutor,
+              "butterfly": ButterflyExecutor}
 
 
 def compile_schedule_all_reduce(method: str, **kwargs: Any) -> _ScheduleExecutor:
-    """`method` "ring" or "tree"; keyword arguments as for the executor classes."""
+    """`method` "ring", "tree", "p2p" or "butterfly"; keyword arguments as for the executor classes."""
 
     try:
         return _EXECUTORS[method](**kwargs)
     except KeyError:
-        raise UnsupportedCollective(f"schedule:{method}", reason="hop-by-hop schedules exist for 'ring' and 'tree'") from None
+        raise UnsupportedCollective(f"schedule:{method}", reason=f"hop-by-hop schedules exist for {sorted(_EXECUTORS)}") from None
 
 
 def make_schedule_all_reduce(*, method: str = "ring", group: Any | None = None, root: int = 0) -> Callable[..., Any]:
@@ -262,7 +339,7 @@ def make_schedule_all_reduce(*, method: str = "ring", group: Any | None = None, 
     returned; with `async_op` it comes wrapped in a finished work object (the steps are already enqueued)."""
 
     if method not in _EXECUTORS:
-        raise UnsupportedCollective(f"schedule:{method}", reason="hop-by-hop schedules exist for 'ring' and 'tree'")
+        raise UnsupportedCollective(f"schedule:{method}", reason=f"hop-by-hop schedules exist for {sorted(_EXECUTORS)}")
     compiled: dict[tuple, _ScheduleExecutor] = {}
 
     def transport(tensor: Any, *, config: CompressionConfig, op: str = "mean", async_op: bool = False,

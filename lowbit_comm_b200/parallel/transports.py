@@ -26,8 +26,8 @@ from ..exceptions import UnsupportedCollective
 
 # the reference's method names -> the exchange that serves them here
 ONE_STAGE_METHODS = frozenset({"all_gather", "gather", "overlap-gather"})
-TWO_STAGE_METHODS = frozenset({"ring", "tree", "p2p", "overlap-p2p", "overlap-tree", "overlap-scale", "topology",
-                               "reduce_scatter", "compressed"})
+TWO_STAGE_METHODS = frozenset({"ring", "tree", "p2p", "butterfly", "overlap-p2p", "overlap-tree", "overlap-scale",
+                               "topology", "reduce_scatter", "compressed"})
 
 
 def _communicator(group: Any):
@@ -79,14 +79,15 @@ def make_torch_compressed_reduce_scatter_all_gather(*, group: Any | None = None,
 def make_native_topology_all_reduce(*, method: str | None = None, group: Any | None = None,
                                     hop_by_hop: bool = False, **_ignored: Any) -> Callable[..., Any]:
     """transport(...) -> the full reduced tensor; `method` is one of the reference's topology names.
-    `hop_by_hop=True` (an addition, for "ring" and "tree") runs the schedule over point-to-point operations
+    `hop_by_hop=True` (an addition, for "ring", "tree", "p2p" and "butterfly") runs the schedule over point-to-point operations
     instead of the direct exchange: the choice for groups that span nodes or have no peer access."""
 
     strategy = _strategy_for(method)
     if hop_by_hop:
         from .schedule_executors import make_schedule_all_reduce
 
-        return make_schedule_all_reduce(method=method or "ring", group=group)
+        hops = {None: "ring", "overlap-p2p": "p2p", "overlap-tree": "tree"}.get(method, method)
+        return make_schedule_all_reduce(method=hops, group=group)
 
     def transport(tensor: Any, *, config: CompressionConfig, op: str, async_op: bool, dtype: str,
                   extension_status: Any | None = None) -> Any:

@@ -69,13 +69,48 @@ def _replay_tree(xs, cfg, dtype, op, root=0):
     return _dec(_enc(_scaled(work[root], world, op), cfg), padded, cfg, dtype)[:n]
 
 
+def _replay_pairwise(xs, cfg, dtype, op):
+    world, n = len(xs), xs[0].numel()
+    unit = cfg.group_size * world
+    padded = -(-n // unit) * unit
+    shard = padded // world
+    work = [torch.zeros(padded, dtype=DT[dtype]) for _ in range(world)]
+    for w, x in zip(work, xs):
+        w[:n] = x
+    final = torch.empty(padded, dtype=DT[dtype])
+    for owner in range(world):
+        mine = work[owner][owner * shard:(owner + 1) * shard].clone()
+        for k in range(1, world):                                    # contributions arrive from owner - k
+            sender = (owner - k) % world
+            _dec(_enc(work[sender][owner * shard:(owner + 1) * shard], cfg), shard, cfg, dtype, into=mine, add=True)
+        final[owner * shard:(owner + 1) * shard] = _dec(_enc(_scaled(mine, world, op), cfg), shard, cfg, dtype)
+    return final[:n]
+
+
+def _replay_butterfly(xs, cfg, dtype, op):
+    world, n = len(xs), xs[0].numel()
+    padded = -(-n // cfg.group_size) * cfg.group_size
+    work = [torch.zeros(padded, dtype=DT[dtype]) for _ in range(world)]
+    for w, x in zip(work, xs):
+        w[:n] = x
+    for k in range(world.bit_length() - 1):
+        sent = [_enc(w, cfg) for w in work]
+        for r in range(world):
+            _dec(sent[r], padded, cfg, dtype, into=work[r])
+            _dec(sent[r ^ (1 << k)], padded, cfg, dtype, into=work[r], add=True)
+    assert all(torch.equal(w.view(torch.uint8), work[0].view(torch.uint8)) for w in work)
+    return _scaled(work[0], world, op)[:n]
+
+
 def _worker(rank: int, world: int, port: int) -> None:
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         import lowbit_comm_b200 as lbc
-        from lowbit_comm_b200.parallel.schedule_executors import (PipelinedRingExecutor, TreeExecutor,
+        from lowbit_comm_b200.exceptions import UnsupportedCollective
+        from lowbit_comm_b200.parallel.schedule_executors import (ButterflyExecutor, PairwiseExecutor,
+                                                                  PipelinedRingExecutor, TreeExecutor,
                                                                   make_schedule_all_reduce)
 
         cases = [("bf16", lbc.CompressionConfig(), 64 * 13 + 5, "mean"),
@@ -84,7 +119,13 @@ def _worker(rank: int, world: int, port: int) -> None:
         for dtype, cfg, n, op in cases:
             xs = _inputs(world, n, dtype, seed=n)
             exact = torch.stack([x.float() for x in xs]).sum(0) / (world if op == "mean" else 1)
-            for cls, replay in ((PipelinedRingExecutor, _replay_ring), (TreeExecutor, _replay_tree)):
+            shapes = [(PipelinedRingExecutor, _replay_ring), (TreeExecutor, _replay_tree), (PairwiseExecutor, _replay_pairwise)]
+            if world & (world - 1) == 0:
+                shapes.append((ButterflyExecutor, _replay_butterfly))
+            else:
+                with pytest.raises(UnsupportedCollective):
+                    ButterflyExecutor(numel=n, dtype=dtype, config=cfg, op=op)
+            for cls, replay in shapes:
                 executor = cls(numel=n, dtype=dtype, config=cfg, op=op)
                 want = replay(xs, cfg, dtype, op)
                 for _ in range(2):                                   # buffers are reused across runs
@@ -114,6 +155,9 @@ def _worker(rank: int, world: int, port: int) -> None:
         assert torch.equal(work.wait().view(torch.uint8),
                            _replay_tree(xs, cfg, "bf16", "sum", root=world - 1).view(torch.uint8))
         assert len(ring_t.executors) == 1
+        direct = lbc.make_native_topology_all_reduce(method="p2p", hop_by_hop=True)(
+            xs[rank].clone(), config=cfg, op="mean", async_op=False, dtype="bf16")
+        assert torch.equal(direct.view(torch.uint8), _replay_pairwise(xs, cfg, "bf16", "mean").view(torch.uint8))
 
         if world >= 4:                                                # a sub-group: peers are addressed globally
             members = [1, 3]
@@ -138,7 +182,7 @@ def test_unknown_method_and_reduction_are_refused():
     from lowbit_comm_b200.parallel.schedule_executors import compile_schedule_all_reduce, make_schedule_all_reduce
 
     with pytest.raises(UnsupportedCollective):
-        make_schedule_all_reduce(method="butterfly")
+        make_schedule_all_reduce(method="hypercube")
     with pytest.raises(UnsupportedCollective):
         compile_schedule_all_reduce("mesh", numel=1, dtype="bf16", config=None)
 

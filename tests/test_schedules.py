@@ -134,3 +134,36 @@ def test_gather_tiles_start_at_the_rank_and_spread_over_owners():
         gather_tiles(block=0, grid=0, shard_chunks=1, world_size=1, first_owner=0)
     with pytest.raises(ValueError):
         gather_tiles(block=4, grid=4, shard_chunks=1, world_size=1, first_owner=0)
+
+
+@pytest.mark.parametrize("world", (1, 2, 3, 5, 8))
+def test_pairwise_schedule_delivers_every_contribution_to_its_owner(world):
+    from lowbit_comm_b200.core.chunking import ChunkPlan
+    from lowbit_comm_b200.core.schedules import compile_pairwise_schedule
+
+    plan = ChunkPlan.build(world * 4, world)
+    scheds = [compile_pairwise_schedule(chunk_plan=plan, rank=r) for r in range(world)]
+    received = {r: {r} for r in range(world)}                  # contributors summed into chunk r at its owner
+    for k in range(world - 1):
+        sends = {(r, s.steps[k].send_peer) for r, s in enumerate(scheds)}
+        recvs = {(s.steps[k].recv_peer, r) for r, s in enumerate(scheds)}
+        assert sends == recvs and len({dst for _, dst in sends}) == world       # every round is a permutation
+        for r, s in enumerate(scheds):
+            step = s.steps[k]
+            assert step.send_chunk == plan.chunk_for_rank(step.send_peer) and step.recv_chunk == s.local_chunk
+            received[r].add(step.recv_peer)
+    assert all(received[r] == set(range(world)) for r in range(world))
+
+
+def test_butterfly_schedule_pairs_are_mutual_and_need_a_power_of_two():
+    from lowbit_comm_b200.core.schedules import compile_butterfly_schedule
+
+    scheds = [compile_butterfly_schedule(world_size=8, rank=r) for r in range(8)]
+    reach = [{r} for r in range(8)]
+    for k in range(3):
+        assert all(scheds[scheds[r].peers[k]].peers[k] == r for r in range(8))
+        reach = [reach[r] | reach[scheds[r].peers[k]] for r in range(8)]
+    assert all(known == set(range(8)) for known in reach)
+    assert compile_butterfly_schedule(world_size=1, rank=0).peers == ()
+    with pytest.raises(ValueError, match="power-of-two"):
+        compile_butterfly_schedule(world_size=6, rank=0)
