@@ -63,6 +63,7 @@ _LAZY = {
     "make_torch_hierarchical_all_reduce": ".parallel.transports",
     "make_legacy_topology_all_reduce": ".parallel.transports",
     "make_schedule_all_reduce": ".parallel.schedule_executors",
+    "make_schedule_reduce_scatter_shard": ".parallel.schedule_executors",
     "PipelinedRingExecutor": ".parallel.schedule_executors", "TreeExecutor": ".parallel.schedule_executors",
     "PairwiseExecutor": ".parallel.schedule_executors", "ButterflyExecutor": ".parallel.schedule_executors",
 }

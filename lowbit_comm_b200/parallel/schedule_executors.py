@@ -142,8 +142,10 @@ class _ScheduleExecutor:
                             if not all(done(r) for r in requests)]
         return len(self._quarantine)
 
-    def run(self, tensor: Any, out: Any | None = None) -> Any:
-        """All-reduce `tensor` (flattened); the result goes to `out`, or back into `tensor` when `out` is None."""
+    def _guarded(self, tensor: Any, steps: Callable[[_Buffers, list[Any]], None],
+                 collect: Callable[[_Buffers], Any]) -> Any:
+        """Loads `tensor` into the work buffer, runs `steps` with the failure handling described in the module
+        docstring, and returns `collect(buffers)`."""
 
         if tensor.numel() != self.numel:
             raise ValueError(f"this executor was compiled for {self.numel} elements, got {tensor.numel()}")
@@ -159,24 +161,86 @@ class _ScheduleExecutor:
             buffers.work[: self.numel].copy_(tensor.reshape(-1))
             buffers.work[self.numel:].zero_()
             try:
-                self._steps(buffers, inflight)
+                steps(buffers, inflight)
             except BaseException:
                 # whatever is still in flight may write into these buffers later: never reuse them
                 self._quarantine.append((buffers, list(inflight)))
                 self._buffers = None
                 raise
-            target = tensor if out is None else out
-            target.reshape(-1).copy_(buffers.work[: self.numel])
+            result = collect(buffers)
             self.runs += 1
-            return target
+            return result
         finally:
             self._busy.release()
+
+    def run(self, tensor: Any, out: Any | None = None) -> Any:
+        """All-reduce `tensor` (flattened); the result goes to `out`, or back into `tensor` when `out` is None."""
+
+        def collect(buffers: _Buffers) -> Any:
+            target = tensor if out is None else out
+            target.reshape(-1).copy_(buffers.work[: self.numel])
+            return target
+
+        return self._guarded(tensor, self._steps, collect)
 
     def __call__(self, tensor: Any, out: Any | None = None) -> Any:
         return self.run(tensor, out)
 
 
-class PipelinedRingExecutor(_ScheduleExecutor):
+class _ChunkedExecutor(_ScheduleExecutor):
+    """Shapes whose first phase is a reduce-scatter (ring, pairwise): they can stop there and hand out the
+    owner's exact reduced chunk as a `ReducedShard`."""
+
+    chunk_plan: ChunkPlan
+
+    def _reduce_scatter_phase(self, buffers: _Buffers, inflight: list[Any]) -> Any:
+        """Runs the reduce-scatter; returns this rank's chunk of the work buffer, reduced and scaled."""
+
+        raise NotImplementedError
+
+    def _gather_phase(self, buffers: _Buffers, inflight: list[Any]) -> None:
+        raise NotImplementedError
+
+    def _steps(self, buffers: _Buffers, inflight: list[Any]) -> None:
+        self._reduce_scatter_phase(buffers, inflight)
+        self._gather_phase(buffers, inflight)
+
+    def _chunk(self, buffers: _Buffers, owner: int) -> Any:
+        lo, hi = self.chunk_plan.bounds(owner)
+        return buffers.work[lo:hi]
+
+    def _scale_mean(self, mine: Any) -> None:
+        if self.op == "mean" and self.world_size > 1:
+            mine.copy_((mine.float() * (1.0 / self.world_size)).to(mine.dtype))
+
+    def run_reduce_scatter(self, tensor: Any, out: Any | None = None) -> Any:
+        """Reduce-scatter only: a `ReducedShard` holding chunk `rank` of the reduced, padded tensor (not
+        re-quantized).  `out`, when given, is a flat tensor of `shard_numel` elements that receives it."""
+
+        from ..core.shard import ReducedShard
+
+        shard_numel = self.chunk_plan.shard_numel
+        if out is not None and (out.numel() != shard_numel or out.dtype != self._torch_dtype):
+            raise ValueError(f"out must hold {shard_numel} elements of {self._torch_dtype}")
+
+        def collect(buffers: _Buffers) -> Any:
+            mine = self._chunk(buffers, self.rank)
+            if out is None:
+                shard = mine.clone()
+            else:
+                out.reshape(-1).copy_(mine)
+                shard = out
+            return ReducedShard(shard=shard, shard_index=self.rank, shard_numel=shard_numel,
+                                original_shape=tuple(tensor.shape), original_numel=self.numel,
+                                world_size=self.world_size, reduce=self.op, padded_numel=self.chunk_plan.padded_numel,
+                                dtype=self.dtype, transport=f"schedule_{self.method}",
+                                metadata={"fused": False, "caller_owned_output": out is not None,
+                                          "group_aligned": True})
+
+        return self._guarded(tensor, self._reduce_scatter_phase, collect)
+
+
+class PipelinedRingExecutor(_ChunkedExecutor):
     """Ring reduce-scatter of W group-aligned shards followed by a ring all-gather of the owners' payloads."""
 
     method = "ring"
@@ -194,20 +258,19 @@ class PipelinedRingExecutor(_ScheduleExecutor):
         return _Buffers(self._torch, self.chunk_plan.padded_numel, self.chunk_payload_bytes, 2 + self.world_size,
                         self._torch_dtype, self.device)
 
-    def _chunk(self, buffers: _Buffers, owner: int) -> Any:
-        lo, hi = self.chunk_plan.bounds(owner)
-        return buffers.work[lo:hi]
-
-    def _steps(self, buffers: _Buffers, inflight: list[Any]) -> None:
+    def _reduce_scatter_phase(self, buffers: _Buffers, inflight: list[Any]) -> Any:
         outgoing, incoming = buffers.payloads[0], buffers.payloads[1]
-        slots = buffers.payloads[2:]                      # slots[owner]: the finished payload of that owner's chunk
         for step in self.schedule.steps:
             self._encode(self._chunk(buffers, step.send_chunk_owner), outgoing)
             self._exchange(outgoing, step.send_peer, incoming, step.recv_peer, inflight)
             self._decode(incoming, self._chunk(buffers, step.recv_chunk_owner), add=True)
         mine = self._chunk(buffers, self.rank)
-        if self.op == "mean" and self.world_size > 1:
-            mine.copy_((mine.float() * (1.0 / self.world_size)).to(mine.dtype))
+        self._scale_mean(mine)
+        return mine
+
+    def _gather_phase(self, buffers: _Buffers, inflight: list[Any]) -> None:
+        slots = buffers.payloads[2:]                      # slots[owner]: the finished payload of that owner's chunk
+        mine = self._chunk(buffers, self.rank)
         self._encode(mine, slots[self.rank])
         self._decode(slots[self.rank], mine, add=False)  # the owner keeps what everybody else will decode
         for step in self.schedule.gather_steps:
@@ -249,7 +312,7 @@ class TreeExecutor(_ScheduleExecutor):
         self._decode(down, buffers.work, add=False)      # the root decodes its own payload too
 
 
-class PairwiseExecutor(_ScheduleExecutor):
+class PairwiseExecutor(_ChunkedExecutor):
     """Shifted pairwise exchange: every contribution goes straight to the owner of its chunk (one hop, one
     quantization), the owners reduce, and the finished payloads are exchanged the same way.  The dataflow of
     the fused two-stage all-reduce, over point-to-point operations."""
@@ -267,20 +330,19 @@ class PairwiseExecutor(_ScheduleExecutor):
         return _Buffers(self._torch, self.chunk_plan.padded_numel, self.chunk_payload_bytes, 2 + self.world_size,
                         self._torch_dtype, self.device)
 
-    def _chunk(self, buffers: _Buffers, owner: int) -> Any:
-        lo, hi = self.chunk_plan.bounds(owner)
-        return buffers.work[lo:hi]
-
-    def _steps(self, buffers: _Buffers, inflight: list[Any]) -> None:
+    def _reduce_scatter_phase(self, buffers: _Buffers, inflight: list[Any]) -> Any:
         outgoing, incoming = buffers.payloads[0], buffers.payloads[1]
-        slots = buffers.payloads[2:]
         mine = self._chunk(buffers, self.rank)
         for step in self.schedule.steps:
             self._encode(self._chunk(buffers, step.send_peer), outgoing)
             self._exchange(outgoing, step.send_peer, incoming, step.recv_peer, inflight)
             self._decode(incoming, mine, add=True)
-        if self.op == "mean" and self.world_size > 1:
-            mine.copy_((mine.float() * (1.0 / self.world_size)).to(mine.dtype))
+        self._scale_mean(mine)
+        return mine
+
+    def _gather_phase(self, buffers: _Buffers, inflight: list[Any]) -> None:
+        slots = buffers.payloads[2:]
+        mine = self._chunk(buffers, self.rank)
         self._encode(mine, slots[self.rank])
         self._decode(slots[self.rank], mine, add=False)
         for step in self.schedule.steps:                  # same pairs, the other way round: own chunk out, the sender's in
@@ -356,6 +418,34 @@ def make_schedule_all_reduce(*, method: str = "ring", group: Any | None = None, 
                                                          device=tensor.device, op=op, **extra)
         result = executor.run(tensor)
         return ImmediateWork(result) if async_op else result
+
+    transport.executors = compiled
+    return transport
+
+
+def make_schedule_reduce_scatter_shard(*, method: str = "p2p", group: Any | None = None) -> Callable[..., Any]:
+    """Like `make_schedule_all_reduce`, but the transport stops after the reduce-scatter and returns a
+    `ReducedShard` (`transport(tensor, *, config, op, async_op, dtype, extension_status=None, out=None)`).
+    `method` is "ring" or "p2p", the two shapes that reduce-scatter first."""
+
+    cls = _EXECUTORS.get(method)
+    if cls is None or not issubclass(cls, _ChunkedExecutor):
+        raise UnsupportedCollective(f"schedule:{method}", reason="a reduced shard needs a 'ring' or 'p2p' schedule")
+    compiled: dict[tuple, _ChunkedExecutor] = {}
+
+    def transport(tensor: Any, *, config: CompressionConfig, op: str = "mean", async_op: bool = False,
+                  dtype: str = "auto", extension_status: Any | None = None, out: Any | None = None) -> Any:
+        from ..core.work import ImmediateWork
+        from ..ops import codec
+
+        name = codec.resolve_dtype(dtype, tensor)
+        key = (tensor.numel(), name, config, op, str(tensor.device))
+        executor = compiled.get(key)
+        if executor is None:
+            executor = compiled[key] = cls(numel=tensor.numel(), dtype=name, config=config, group=group,
+                                           device=tensor.device, op=op)
+        shard = executor.run_reduce_scatter(tensor, out=out)
+        return ImmediateWork(shard) if async_op else shard
 
     transport.executors = compiled
     return transport

@@ -99,10 +99,16 @@ def make_native_topology_all_reduce(*, method: str | None = None, group: Any | N
 
 
 def make_native_topology_reduce_scatter_shard(*, method: str | None = None, group: Any | None = None,
-                                              **_ignored: Any) -> Callable[..., Any]:
-    """transport(...) -> `ReducedShard`.  Unlike the reference's ring, sizes need not divide by the world size."""
+                                              hop_by_hop: bool = False, **_ignored: Any) -> Callable[..., Any]:
+    """transport(...) -> `ReducedShard`.  Unlike the reference's ring, sizes need not divide by the world size.
+    `hop_by_hop=True` runs the "ring" or "p2p" reduce-scatter over point-to-point operations."""
 
-    _strategy_for(method)   # validates the name; every method is the same direct scatter here
+    _strategy_for(method)   # validates the name; without hop_by_hop every method is the same direct scatter
+    if hop_by_hop:
+        from .schedule_executors import make_schedule_reduce_scatter_shard
+
+        return make_schedule_reduce_scatter_shard(method={None: "p2p", "overlap-p2p": "p2p"}.get(method, method),
+                                                  group=group)
 
     def transport(tensor: Any, *, config: CompressionConfig, op: str, async_op: bool, dtype: str,
                   extension_status: Any | None = None, out: Any | None = None) -> Any:

@@ -30,6 +30,9 @@ def _dec(payload, n, cfg, dtype, into=None, add=False):
     return codec.dequantize_tensor(payload, (n,), cfg, dtype=dtype, output=into, reduce_op="sum" if add else "none")
 
 
+_SHARDS = {}        # (method, owner) -> the owner's exact reduced chunk of the most recent replay
+
+
 def _scaled(x, world, op):
     return x if op == "sum" or world == 1 else (x.float() * (1.0 / world)).to(x.dtype)
 
@@ -52,6 +55,7 @@ def _replay_ring(xs, cfg, dtype, op):
     final = torch.empty(padded, dtype=DT[dtype])
     for owner in range(world):
         mine = _scaled(work[owner][owner * shard:(owner + 1) * shard], world, op)
+        _SHARDS[("ring", owner)] = mine.clone()
         final[owner * shard:(owner + 1) * shard] = _dec(_enc(mine, cfg), shard, cfg, dtype)
     return final[:n]
 
@@ -83,6 +87,7 @@ def _replay_pairwise(xs, cfg, dtype, op):
         for k in range(1, world):                                    # contributions arrive from owner - k
             sender = (owner - k) % world
             _dec(_enc(work[sender][owner * shard:(owner + 1) * shard], cfg), shard, cfg, dtype, into=mine, add=True)
+        _SHARDS[("p2p", owner)] = _scaled(mine, world, op).clone()
         final[owner * shard:(owner + 1) * shard] = _dec(_enc(_scaled(mine, world, op), cfg), shard, cfg, dtype)
     return final[:n]
 
@@ -135,6 +140,15 @@ def _worker(rank: int, world: int, port: int) -> None:
                 if cfg.bit == 8:
                     bound = 0.03 * world * exact.abs().max().item() + 1e-6
                     assert (got.float() - exact).abs().max().item() <= bound
+                if hasattr(executor, "run_reduce_scatter"):
+                    shard = executor.run_reduce_scatter(xs[rank].clone())
+                    want_shard = _SHARDS[(executor.method, rank)]
+                    assert shard.shard_index == rank and shard.world_size == world and shard.original_numel == n
+                    assert shard.transport == f"schedule_{executor.method}" and shard.reduce == op
+                    assert torch.equal(shard.shard.view(torch.uint8), want_shard.view(torch.uint8))
+                    mine_out = torch.empty(shard.shard_numel, dtype=DT[dtype])
+                    assert executor.run_reduce_scatter(xs[rank].clone(), out=mine_out).shard is mine_out
+                    assert torch.equal(mine_out.view(torch.uint8), want_shard.view(torch.uint8))
                 out = torch.empty(n, dtype=DT[dtype])
                 kept = xs[rank].clone()
                 assert executor.run(kept, out=out) is out and torch.equal(kept, xs[rank])
@@ -155,6 +169,10 @@ def _worker(rank: int, world: int, port: int) -> None:
         assert torch.equal(work.wait().view(torch.uint8),
                            _replay_tree(xs, cfg, "bf16", "sum", root=world - 1).view(torch.uint8))
         assert len(ring_t.executors) == 1
+        shard_t = lbc.make_native_topology_reduce_scatter_shard(method="ring", hop_by_hop=True)
+        _replay_ring(xs, cfg, "bf16", "mean")
+        shard = lbc.compressed_reduce_scatter_shard(xs[rank].clone(), config=cfg, reduce_scatter_shard=shard_t)
+        assert torch.equal(shard.shard.view(torch.uint8), _SHARDS[("ring", rank)].view(torch.uint8))
         direct = lbc.make_native_topology_all_reduce(method="p2p", hop_by_hop=True)(
             xs[rank].clone(), config=cfg, op="mean", async_op=False, dtype="bf16")
         assert torch.equal(direct.view(torch.uint8), _replay_pairwise(xs, cfg, "bf16", "mean").view(torch.uint8))
