@@ -79,13 +79,18 @@ def make_torch_compressed_reduce_scatter_all_gather(*, group: Any | None = None,
 def make_native_topology_all_reduce(*, method: str | None = None, group: Any | None = None,
                                     hop_by_hop: bool = False, **_ignored: Any) -> Callable[..., Any]:
     """transport(...) -> the full reduced tensor; `method` is one of the reference's topology names.
-    `hop_by_hop=True` (an addition, for "ring", "tree", "p2p" and "butterfly") runs the schedule over point-to-point operations
-    instead of the direct exchange: the choice for groups that span nodes or have no peer access."""
+    `hop_by_hop=True` (an addition) runs the method as named through torch.distributed instead of the direct
+    exchange: "ring", "tree", "p2p", "butterfly" as schedules of point-to-point operations (the choice for groups
+    that span nodes or have no peer access), "overlap-scale" as a library int8 all-reduce under a shared scale."""
 
     strategy = _strategy_for(method)
     if hop_by_hop:
         from .schedule_executors import make_schedule_all_reduce
 
+        if method == "overlap-scale":
+            from .shared_scale import make_shared_scale_all_reduce
+
+            return make_shared_scale_all_reduce(group=group)
         hops = {None: "ring", "overlap-p2p": "p2p", "overlap-tree": "tree"}.get(method, method)
         return make_schedule_all_reduce(method=hops, group=group)
 

@@ -177,6 +177,21 @@ def _worker(rank: int, world: int, port: int) -> None:
             xs[rank].clone(), config=cfg, op="mean", async_op=False, dtype="bf16")
         assert torch.equal(direct.view(torch.uint8), _replay_pairwise(xs, cfg, "bf16", "mean").view(torch.uint8))
 
+        # shared-scale int8 all-reduce: the library adds the codes; floor(127 / W) levels keep the sum inside int8
+        from lowbit_comm_b200.parallel.shared_scale import shared_scale_levels
+
+        scale_t = lbc.make_native_topology_all_reduce(method="overlap-scale", hop_by_hop=True)
+        worst = [torch.full((130,), 3.0 * (1 if r % 2 == 0 else 1), dtype=torch.bfloat16) for r in range(world)]
+        got = scale_t(worst[rank].clone(), config=cfg, op="sum", async_op=False, dtype="bf16")
+        assert torch.equal(got, torch.full((130,), 3.0 * world, dtype=torch.bfloat16))      # same sign everywhere: no overflow
+        exact = torch.stack([x.float() for x in xs]).mean(0)
+        got = scale_t(xs[rank].clone(), config=cfg, op="mean", async_op=True, dtype="bf16").wait()
+        amax = torch.stack([x.float().abs() for x in xs]).amax()
+        assert (got.float() - exact).abs().max() <= amax / shared_scale_levels(world) / 2 + 1e-3
+        gathered = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(gathered, got)
+        assert all(torch.equal(g, got) for g in gathered)
+
         if world >= 4:                                                # a sub-group: peers are addressed globally
             members = [1, 3]
             sub = dist.new_group(members, backend="gloo")
@@ -203,6 +218,11 @@ def test_unknown_method_and_reduction_are_refused():
         make_schedule_all_reduce(method="hypercube")
     with pytest.raises(UnsupportedCollective):
         compile_schedule_all_reduce("mesh", numel=1, dtype="bf16", config=None)
+    from lowbit_comm_b200.parallel.shared_scale import shared_scale_levels
+
+    assert [shared_scale_levels(w) for w in (1, 2, 8, 127)] == [127, 63, 15, 1]
+    with pytest.raises(UnsupportedCollective):
+        shared_scale_levels(128)
 
 
 class _Request:
