@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import threading
 from collections.abc import Callable, Mapping
+from dataclasses import dataclass, replace
 from typing import Any
 
 from ..config import CompressionConfig
@@ -25,7 +26,7 @@ from ..core.executor import CompiledCommunicationPlan
 from ..core.info import ExecutionCounters, ExecutionInfo
 from ..core.plan import CommunicationPlan, CompileContext
 from ..core.registry import BackendKey, BackendRegistry
-from ..core.work import ImmediateWork, bind_execution_work
+from ..core.work import bind_execution_work
 from ..exceptions import UnsupportedCollective
 from ..ops.loader import CudaExtensionStatus, load_cuda_extension
 from ..ops.sizing import estimate_quantized_size
@@ -62,6 +63,53 @@ def _check_tensor(tensor: Any, context: CompileContext) -> None:
         raise TypeError(f"tensor dtype {tensor.dtype} does not match the compiled dtype {context.dtype}")
 
 
+@dataclass(frozen=True)
+class PrecollectedPayloadExecution:
+    """What reducing already-gathered payloads did: where the result is, and whether the fused
+    decode + mean (+ residual) kernel served it or why not (ccdl_comm/cuda/executors.py:16-27)."""
+
+    output: object
+    fused: bool
+    fallback_reason: str | None = None
+
+    def __post_init__(self) -> None:
+        if self.fused and self.fallback_reason is not None:
+            raise ValueError("fused execution must not provide a fallback reason")
+        if not self.fused and not self.fallback_reason:
+            raise ValueError("fallback execution requires a fallback reason")
+
+
+@dataclass(frozen=True)
+class FusedReducedShardCapability:
+    """Compile-time answer to "can this reduce-scatter hand out its shard through the fused kernels?"
+    (ccdl_comm/cuda/compiler.py:69-79)."""
+
+    available: bool
+    reason: str | None = None
+
+    def __post_init__(self) -> None:
+        if self.available and self.reason is not None:
+            raise ValueError("available fused ReducedShard capability must not have a fallback reason")
+        if not self.available and not self.reason:
+            raise ValueError("unavailable fused ReducedShard capability requires a fallback reason")
+
+
+def fused_reduced_shard_capability(plan: CommunicationPlan, context: CompileContext,
+                                   *, peer_access: bool) -> FusedReducedShardCapability:
+    """The fused scatter + reduce kernels serve linear profiles without top-k on CUDA tensors of ranks with
+    peer access; everything else goes through the all-to-all staging of torch.distributed."""
+
+    from ..ops import codec
+
+    if not str(context.device).startswith("cuda"):
+        return FusedReducedShardCapability(False, f"device {context.device!r} has no peer-memory path")
+    if plan.compression is None or not codec.is_fast_profile(plan.compression):
+        return FusedReducedShardCapability(False, "the compression profile needs the general codec kernels")
+    if not peer_access:
+        return FusedReducedShardCapability(False, "no peer access between the ranks of this group")
+    return FusedReducedShardCapability(True)
+
+
 class CudaAllReduceExecutor:
     """Runs one precompiled compressed all-reduce (or all-gather) operation."""
 
@@ -72,11 +120,8 @@ class CudaAllReduceExecutor:
         self._operation = operation
         self._precollected = precollected
         self.execution_info = execution_info
+        self.last_execution_info = execution_info      # what the most recent precollected run actually did
         self.execution_counters = ExecutionCounters()
-
-    @property
-    def last_execution_info(self) -> ExecutionInfo:
-        return self.execution_info
 
     def run(self, tensor: Any):
         self.execution_counters._record_run()
@@ -98,7 +143,17 @@ class CudaAllReduceExecutor:
         except BaseException:
             self.execution_counters._record_failed()
             raise
-        return bind_execution_work(result, self.execution_info, self.execution_counters)
+        info = self.execution_info
+        if isinstance(result, PrecollectedPayloadExecution):
+            if result.fused:
+                info = replace(info, fallback_used=False, fallback_reason=None,
+                               fast_path="cuda_fused_dequant_reduce_mean_ef")
+            else:
+                info = replace(info, fallback_used=True, fallback_reason=result.fallback_reason,
+                               fast_path="per_payload_decode")
+            result = result.output
+        self.last_execution_info = info
+        return bind_execution_work(result, info, self.execution_counters)
 
 
 class CompressedReduceScatterExecutor:
@@ -208,11 +263,18 @@ class CudaCommunicationBackend:
                 from ..ops import codec
 
                 if residual is not None:
-                    codec.inplace_dequantize_reduce_mean_update_error_feedback(
+                    fused = codec.inplace_dequantize_reduce_mean_update_error_feedback(
                         payloads, prepared, output, residual, cfg, reduce=op)
                 else:
-                    codec.inplace_dequantize_reduce_mean(payloads, output, cfg, reduce=op)
-                return ImmediateWork(output)
+                    fused = codec.inplace_dequantize_reduce_mean(payloads, output, cfg, reduce=op)
+                if fused:
+                    return PrecollectedPayloadExecution(output, True)
+                # profiles or payload counts the fused kernel does not take: decode payload by payload
+                codec.dequantize_reduce_tensors(payloads, tuple(output.shape), cfg, dtype=dtype, output=output, reduce=op)
+                if residual is not None:
+                    codec.update_error_feedback_residual(prepared, output, residual)
+                return PrecollectedPayloadExecution(output, False, "profile or payload count outside the fused "
+                                                                   "decode-reduce kernel")
 
             return CudaAllReduceExecutor(operation, info, precollected=precollected)
         if plan.collective == "all_gather":

@@ -12,10 +12,12 @@ from __future__ import annotations
 
 from collections import OrderedDict
 from collections.abc import Callable
+from dataclasses import dataclass
 from importlib import import_module
-from typing import Any
+from typing import Any, NamedTuple
 
 from ...config import CompressionConfig
+from ...core.executor import ObjectIdentity
 from ...core.info import ExecutionCounters, ExecutionInfo
 from ...ops import codec
 from ...ops.oracle import TORCH_DTYPES
@@ -30,6 +32,51 @@ def _numel(shape) -> int:
     for d in shape:
         total *= int(d)
     return total
+
+
+@dataclass(frozen=True)
+class DynamicGatherMetadata:
+    """What a rank announces before its fixed-size payload (protocol `object_v1` pickles `to_wire()`; `tensor_v1`
+    sends the same facts as a 16 x int64 `MetadataPacket`).  Field names are the reference's
+    (ccdl_comm/cuda/dynamic_gather_executor.py:36-52); `flags` is an addition (bit 0: empty tensor)."""
+
+    protocol_version: int
+    shape: tuple[int, ...]
+    dtype: str
+    payload_numel: int
+    flags: int = 0
+
+    def to_wire(self) -> dict[str, object]:
+        return {"protocol_version": self.protocol_version, "shape": self.shape, "dtype": self.dtype,
+                "payload_numel": self.payload_numel, "flags": self.flags}
+
+    @classmethod
+    def from_wire(cls, wire: dict) -> "DynamicGatherMetadata":
+        version = int(wire.get("protocol_version", 1))
+        if version != 1:
+            raise ValueError(f"unsupported dynamic all-gather metadata version {version}")
+        return cls(version, tuple(int(d) for d in wire["shape"]), str(wire["dtype"]), int(wire["payload_numel"]),
+                   int(wire.get("flags", 0)))
+
+    def packet(self) -> MetadataPacket:
+        return MetadataPacket(self.shape, self.dtype, self.payload_numel, self.flags)
+
+
+class DynamicGatherCacheKey(NamedTuple):
+    """Everything that makes two dynamic all-gathers need different executors.  Objects (process group, injected
+    codec functions, the extension status) take part by identity and are kept alive by the key, so an id can
+    never be recycled into a stale hit."""
+
+    shape_class: tuple[int, ...]
+    dtype: str
+    world_size: int | None
+    config: CompressionConfig
+    metadata_protocol: str
+    process_group: ObjectIdentity
+    distributed: ObjectIdentity
+    extension_status: ObjectIdentity
+    quantize: ObjectIdentity
+    dequantize: ObjectIdentity
 
 
 class CudaDynamicGatherExecutor:
@@ -76,9 +123,10 @@ class CudaDynamicGatherExecutor:
         world = dist.get_world_size(**self._kw())
         if self.protocol == "object_v1":
             objs: list[Any] = [None] * world
-            dist.all_gather_object(objs, {"shape": local.shape, "dtype": local.dtype,
-                                          "payload_numel": local.payload_numel, "flags": local.flags}, **self._kw())
-            return [MetadataPacket(tuple(o["shape"]), o["dtype"], int(o["payload_numel"]), int(o["flags"])) for o in objs]
+            mine = DynamicGatherMetadata(self.metadata_protocol_version, local.shape, local.dtype,
+                                         local.payload_numel, local.flags)
+            dist.all_gather_object(objs, mine.to_wire(), **self._kw())
+            return [DynamicGatherMetadata.from_wire(o).packet() for o in objs]
         words = torch.tensor(local.encode(), dtype=torch.int64)
         if device.type == "cuda":
             words = words.pin_memory().to(device, non_blocking=True)
@@ -126,9 +174,17 @@ class CudaDynamicGatherExecutor:
 
 
 class DynamicGatherExecutorCache:
-    def __init__(self, max_entries: int = 16) -> None:
+    """Bounded LRU of executors; keys are `DynamicGatherCacheKey`s (any hashable is accepted)."""
+
+    def __init__(self, max_entries: int = 32) -> None:
+        if isinstance(max_entries, bool) or not isinstance(max_entries, int) or max_entries <= 0:
+            raise ValueError("max_entries must be a positive integer")
         self._max = max_entries
-        self._items: "OrderedDict[tuple, CudaDynamicGatherExecutor]" = OrderedDict()
+        self._items: "OrderedDict[Any, CudaDynamicGatherExecutor]" = OrderedDict()
+
+    @property
+    def max_entries(self) -> int:
+        return self._max
 
     def get_or_create(self, key: tuple, factory: Callable[[], CudaDynamicGatherExecutor]):
         hit = self._items.get(key)
@@ -151,7 +207,10 @@ _DEFAULT_CACHE = DynamicGatherExecutorCache()
 def compile_dynamic_all_gather(*, shape_class, config: CompressionConfig, dtype: str, group: Any | None = None,
                                extension_status: Any | None = None, cache: DynamicGatherExecutorCache | None = None,
                                metadata_protocol: str = "object_v1", **kw) -> CudaDynamicGatherExecutor:
-    key = (tuple(shape_class), config, dtype, id(group), metadata_protocol)
+    key = DynamicGatherCacheKey(
+        tuple(int(d) for d in shape_class), dtype, None, config, metadata_protocol, ObjectIdentity(group),
+        ObjectIdentity(kw.get("import_module_fn")), ObjectIdentity(extension_status), ObjectIdentity(kw.get("quantize")),
+        ObjectIdentity(kw.get("dequantize")))
 
     def build():
         return CudaDynamicGatherExecutor(shape_class=tuple(shape_class), config=config, dtype=dtype, group=group,

@@ -130,6 +130,14 @@ class _ScheduleExecutor:
     def quarantined(self) -> int:
         return len(self._quarantine)
 
+    # the reference's names for the same two things (cuda/transports/pipelined_ring.py:166-204)
+    @property
+    def pending_submission_count(self) -> int:
+        return len(self._quarantine)
+
+    def reap_pending(self) -> int:
+        return self.reap()
+
     def reap(self) -> int:
         """Frees quarantined buffer sets whose requests have all completed; never waits.  Returns how many
         sets are still held."""

@@ -111,6 +111,39 @@ def _worker(rank: int, world: int, port: int) -> None:
                                    lbc.CompileContext(rank=rank, world_size=world, device="cpu", shape=(n,), dtype="bf16"),
                                    allow_cpu=True)
         assert torch.equal(direct.run(xs[rank].clone()).wait().view(torch.uint8), one.view(torch.uint8))
+        # payloads that are already gathered (the hook's path): fused decode + mean + residual, or payload by payload
+        from lowbit_comm_b200.ops import codec, oracle
+        from lowbit_comm_b200.parallel.backend_cuda import (FusedReducedShardCapability, PrecollectedPayloadExecution,
+                                                            fused_reduced_shard_capability)
+
+        payloads = [codec.quantize_tensor(x, cfg) for x in xs]
+        out, residual = torch.empty_like(xs[rank]), torch.zeros_like(xs[rank])
+        got = direct.run_precollected_payloads(payloads, xs[rank], out, residual).wait()
+        y, y32 = oracle.reduce_mean(payloads, n, cfg, "bf16")
+        assert got is out and torch.equal(out.view(torch.uint8), y.view(torch.uint8))
+        assert torch.equal(residual.view(torch.uint8), oracle.residual_update(xs[rank], y32).view(torch.uint8))
+        assert direct.last_execution_info.fast_path == "cuda_fused_dequant_reduce_mean_ef"
+        topk = lbc.CompressionConfig(topk=1)
+        general = compile_cuda_plan(lbc.CommunicationPlan(collective="all_reduce", strategy="all_gather", compression=topk),
+                                    lbc.CompileContext(rank=rank, world_size=world, device="cpu", shape=(n,), dtype="bf16"),
+                                    allow_cpu=True)
+        payloads = [codec.quantize_tensor(x, topk) for x in xs]
+        out2, residual2 = torch.empty_like(xs[rank]), torch.zeros_like(xs[rank])
+        general.run_precollected_payloads(payloads, xs[rank], out2, residual2).wait()
+        want = codec.dequantize_reduce_tensors(payloads, (n,), topk, dtype="bf16", reduce="mean")
+        assert torch.equal(out2.view(torch.uint8), want.view(torch.uint8)) and residual2.abs().max() > 0
+        assert general.last_execution_info.fallback_used and "fused" in general.last_execution_info.fallback_reason
+        with pytest.raises(ValueError):
+            PrecollectedPayloadExecution(out, False)
+        with pytest.raises(ValueError):
+            FusedReducedShardCapability(True, "but")
+        shard_plan = lbc.CommunicationPlan(collective="reduce_scatter", strategy="compressed", output_layout="shard",
+                                           compression=cfg)
+        cpu_ctx = lbc.CompileContext(rank=rank, world_size=world, device="cpu", shape=(n,), dtype="bf16")
+        gpu_ctx = lbc.CompileContext(rank=rank, world_size=world, device="cuda:0", shape=(n,), dtype="bf16")
+        assert not fused_reduced_shard_capability(shard_plan, cpu_ctx, peer_access=True).available
+        assert fused_reduced_shard_capability(shard_plan, gpu_ctx, peer_access=True).available
+        assert "peer access" in fused_reduced_shard_capability(shard_plan, gpu_ctx, peer_access=False).reason
         auto = compile_cuda_shortcut(xs[rank], collective="all_reduce", strategy="auto", output_layout="full", config=cfg)
         assert auto.execution_info.requested_strategy == "auto"
         assert auto.execution_info.details["strategy_policy_id"] == "b200-nvlink5-v1"

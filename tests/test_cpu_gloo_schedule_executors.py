@@ -285,7 +285,7 @@ def test_failed_step_quarantines_buffers_until_their_requests_complete():
     assert (got[:128] - folded).abs().max() < 0.02 and torch.equal(got[128:], got[:128])
     for request in fake.stuck:
         request.done = True
-    assert executor.reap() == 0
+    assert executor.pending_submission_count == 1 and executor.reap_pending() == 0 and executor.reap() == 0
 
 
 def test_executor_is_not_reentrant():
