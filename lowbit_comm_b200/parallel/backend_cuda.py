@@ -114,11 +114,17 @@ class CudaAllReduceExecutor:
     """Runs one precompiled compressed all-reduce (or all-gather) operation."""
 
     def __init__(self, operation: Callable[[Any], Any], execution_info: ExecutionInfo, *,
-                 precollected: Callable[..., Any] | None = None) -> None:
+                 precollected: Callable[..., Any] | None = None,
+                 precollected_operation: Callable[..., Any] | None = None) -> None:
+        """`precollected(payloads, prepared, output, residual)` serves `run_precollected_payloads`;
+        `precollected_operation` is the reference's name for the same argument."""
+
         if not callable(operation):
             raise TypeError("operation must be callable")
+        if not isinstance(execution_info, ExecutionInfo):
+            raise TypeError("execution_info must be an ExecutionInfo")
         self._operation = operation
-        self._precollected = precollected
+        self._precollected = precollected if precollected is not None else precollected_operation
         self.execution_info = execution_info
         self.last_execution_info = execution_info      # what the most recent precollected run actually did
         self.execution_counters = ExecutionCounters()

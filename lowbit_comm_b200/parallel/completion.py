@@ -123,15 +123,22 @@ def _shared_comm_stream(cuda: Any) -> Any:
 
 
 class CudaCompletionManager:
-    def __init__(self, *, extension_status=None, torch_module=None) -> None:
+    def __init__(self, *, extension_status=None, torch_module=None, torch_provider=None) -> None:
+        """`torch_module` is the module itself, `torch_provider` a zero-argument callable that returns it (the
+        reference's spelling, ccdl_comm/communication/cuda_completion.py:176-183); tests pass fakes either way."""
+
         self._status = extension_status
         self._torch = torch_module
+        self._torch_provider = torch_provider
 
     def _t(self):
         if self._torch is None:
-            import torch
+            if self._torch_provider is not None:
+                self._torch = self._torch_provider()
+            else:
+                import torch
 
-            self._torch = torch
+                self._torch = torch
         return self._torch
 
     def record_for(self, tensor: Any, stream: Any = None):

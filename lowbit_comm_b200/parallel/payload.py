@@ -27,14 +27,20 @@ class CompressedPayload:
 
 @dataclass(frozen=True)
 class GatheredPayloads:
+    """One payload per rank, in rank order.  `world_size` may be given, as transports written against the
+    reference do (ccdl_comm/communication/gather_reduce.py:11-15); it defaults to the number of payloads
+    and must agree with it."""
+
     payloads: tuple[Any, ...]
+    world_size: int | None = None
 
     def __post_init__(self) -> None:
-        object.__setattr__(self, "payloads", tuple(self.payloads))
-
-    @property
-    def world_size(self) -> int:
-        return len(self.payloads)
+        payloads = tuple(self.payloads)
+        object.__setattr__(self, "payloads", payloads)
+        if self.world_size is None:
+            object.__setattr__(self, "world_size", len(payloads))
+        elif int(self.world_size) != len(payloads):
+            raise ValueError(f"world_size {self.world_size} does not match {len(payloads)} gathered payloads")
 
 
 def payload_buffer(payload: Any) -> Any:

@@ -368,33 +368,67 @@ class DequantizedWorkspaceCache:
         self._items.clear()
 
 
-class ShardCommunicationWorkspaceCache:
-    """send / recv / reduced buffers of the torch.distributed reduce-scatter path, by bucket key."""
+def _held_bytes(buffer: Any) -> int:
+    """Bytes a cached buffer keeps alive (0 for objects that do not say)."""
 
-    def __init__(self, *, max_entries: int | None = None) -> None:
-        self._max_entries = max_entries
+    nbytes = getattr(buffer, "nbytes", None)
+    if nbytes is not None:
+        return int(nbytes)
+    numel, width = getattr(buffer, "numel", None), getattr(buffer, "element_size", None)
+    return int(numel()) * int(width()) if callable(numel) and callable(width) else 0
+
+
+class ShardCommunicationWorkspaceCache:
+    """send / recv / reduced buffers of the torch.distributed reduce-scatter path, by bucket key.
+
+    An LRU with two optional limits, entries and bytes (ccdl_comm/communication/workspace.py:83-200): whatever
+    was used least recently is dropped until both hold again, so a buffer larger than the byte budget is
+    handed out but not kept.  The two allocators can be replaced (a pool, a recording fake)."""
+
+    def __init__(self, *, quantized_allocator: Callable[[Any, Any, str], Any] | None = None,
+                 reduced_allocator: Callable[[Any, tuple[int, ...], Any], Any] | None = None,
+                 max_entries: int | None = None, max_cached_bytes: int | None = None) -> None:
+        if max_entries is not None and max_entries < 1:
+            raise ValueError("max_entries must be >= 1 or None")
+        if max_cached_bytes is not None and max_cached_bytes < 0:
+            raise ValueError("max_cached_bytes must be >= 0 or None")
+        self._allocate_quantized = quantized_allocator
+        self._allocate_reduced = reduced_allocator
+        self._max_entries, self._max_bytes = max_entries, max_cached_bytes
         self._items: "OrderedDict[tuple, Any]" = OrderedDict()
+        self._bytes = 0
+
+    @property
+    def cached_bytes(self) -> int:
+        return self._bytes
+
+    def __len__(self) -> int:
+        return len(self._items)
+
+    def _over_budget(self) -> bool:
+        return (self._max_entries is not None and len(self._items) > self._max_entries) or \
+            (self._max_bytes is not None and self._bytes > self._max_bytes)
 
     def get(self, key: Any, kind: str, index: int, factory: Callable[[], Any]) -> Any:
         if kind not in ("send", "recv", "reduced"):
             raise ValueError(f"unknown workspace kind {kind!r}")
         full = (key, kind, index)
         held = self._items.get(full)
-        if held is None:
-            held = factory()
-            self._items[full] = held
-            while self._max_entries is not None and len(self._items) > self._max_entries:
-                self._items.popitem(last=False)
-        else:
+        if held is not None:
             self._items.move_to_end(full)
+            return held
+        held = factory()
+        self._items[full] = held
+        self._bytes += _held_bytes(held)
+        while self._items and self._over_budget():
+            _, dropped = self._items.popitem(last=False)
+            self._bytes -= _held_bytes(dropped)
         return held
 
     def clear(self, key: Any | None = None) -> None:
-        if key is None:
-            self._items.clear()
-        else:
-            for full in [f for f in self._items if f[0][0] == key or f[0] == key]:
-                del self._items[full]
+        doomed = [f for f in self._items if key is None or f[0][0] == key or f[0] == key]
+        for full in doomed:
+            self._bytes -= _held_bytes(self._items.pop(full))
 
     # The reference's three accessors (ccdl_comm/communication/workspace.py:105-170): one cached buffer per
     # (bucket, role, index, world size, tensor signature); a changed signature allocates a new one.
@@ -407,10 +441,15 @@ class ShardCommunicationWorkspaceCache:
                             world_size: int) -> Any:
         """uint8 payload buffer for chunk `chunk_index` of `tensor` (the send side of the all-to-all)."""
 
-        from ..ops.codec import allocate_quantized_buffer
+        def allocate() -> Any:
+            if self._allocate_quantized is not None:
+                return self._allocate_quantized(tensor, config, dtype)
+            from ..ops.codec import allocate_quantized_buffer
+
+            return allocate_quantized_buffer(tensor, config, dtype=dtype)
 
         key = (bucket_key, world_size, self._signature(tensor), dtype, config)
-        return self.get(key, "send", chunk_index, lambda: allocate_quantized_buffer(tensor, config, dtype=dtype))
+        return self.get(key, "send", chunk_index, allocate)
 
     def get_received_payload(self, bucket_key: Any, payload_template: Any, index: int, *, world_size: int,
                              config: Any) -> Any:
@@ -424,6 +463,8 @@ class ShardCommunicationWorkspaceCache:
         """The reduced shard of this rank, in the source dtype."""
 
         key = (bucket_key, world_size, self._signature(tensor), tuple(shape), dtype, config)
+        if self._allocate_reduced is not None:
+            return self.get(key, "reduced", rank, lambda: self._allocate_reduced(tensor, tuple(shape), config))
         return self.get(key, "reduced", rank, lambda: tensor.new_empty(tuple(shape)))
 
 
