@@ -336,9 +336,14 @@ class DDPCommHook:
         self.policy: ErrorFeedbackPolicy | None = None
         self.peer_engine: _PeerEngine | None = None
         self.stats = {"buckets": 0, "bypassed": 0, "peer": 0, "torch": 0}
+        self._layouts: dict[Any, tuple] = {}          # bucket key -> ((parameter id, numel), ...) last seen
+        self._names: dict[int, str] = {}              # parameter id -> name (after bind_module)
+        self._pending_named: dict[str, Any] = {}      # residuals of a name-keyed checkpoint, not yet assembled
+        self._adopted: set = set()
 
     def __call__(self, state, bucket):  # no annotations: DDP validates them when present
         self.stats["buckets"] += 1
+        self._follow_layout(bucket)
         result = self._process_bucket(bucket)
         if hasattr(result, "set_result") or hasattr(result, "then"):
             return result
@@ -346,13 +351,106 @@ class DDPCommHook:
         future.set_result(result)
         return future
 
+    # -- bucket layouts ---------------------------------------------------------------------------------
+    # DDP fills a bucket with its parameters' gradients in one order during the first iteration and, after it
+    # has rebuilt its buckets, in another; a residual is only meaningful in the order it was computed in.  The
+    # hook therefore remembers, per bucket, which parameter owned which segment, and re-orders the residual
+    # when the order changes.  With `bind_module` the parameters also have names, and checkpoints store the
+    # residual per parameter name, so a resumed process, which starts in the first-iteration order again,
+    # picks up exactly the residual it left with.
+    def bind_module(self, module: Any) -> "DDPCommHook":
+        """Give the hook the (unwrapped) model so that it can name the parameters it sees in buckets."""
+
+        self._names = {id(p): name for name, p in module.named_parameters()}
+        return self
+
+    @staticmethod
+    def _segments(bucket: Any) -> tuple[tuple[int, int], ...] | None:
+        """((parameter id, numel), ...) in bucket order, or None for buckets that cannot say (fakes)."""
+
+        params = getattr(bucket, "parameters", None)
+        if not callable(params):
+            return None
+        try:
+            return tuple((id(p), int(p.numel())) for p in params())
+        except (RuntimeError, TypeError):
+            return None
+
+    def _follow_layout(self, bucket: Any) -> None:
+        if self.feedback is None:
+            return
+        layout = self._segments(bucket)
+        if layout is None:
+            return
+        key = _bucket_key(bucket)
+        self._adopt_named_residual(key, layout, bucket)
+        known = self._layouts.get(key)
+        self._layouts[key] = layout
+        if known is None or known == layout:
+            return
+        residual = self.feedback.get(key)
+        if residual is None:
+            return
+        if sorted(known) != sorted(layout) or residual.numel() != sum(n for _, n in layout):
+            self.feedback.clear(key)            # other parameters in this bucket now: the residual means nothing
+            return
+        pieces, at = {}, 0
+        flat = residual.reshape(-1)
+        for owner, numel in known:
+            pieces[owner] = flat[at:at + numel]
+            at += numel
+        import torch
+
+        self.feedback.set(key, torch.cat([pieces[owner] for owner, _ in layout]).reshape(residual.shape))
+
+    def _adopt_named_residual(self, key: Any, layout, bucket: Any) -> None:
+        """After `load_state_dict` of a name-keyed checkpoint: assemble this bucket's residual in its current
+        order the first time the bucket is seen."""
+
+        if not self._pending_named or key in self._adopted or not self._names:
+            return
+        self._adopted.add(key)
+        names = [self._names.get(owner) for owner, _ in layout]
+        if any(n is None or n not in self._pending_named for n in names):
+            return
+        import torch
+
+        buffer = bucket.buffer()
+        parts = [self._pending_named[n].reshape(-1).to(device=buffer.device, dtype=buffer.dtype) for n in names]
+        if [p.numel() for p in parts] != [numel for _, numel in layout]:
+            return
+        self.feedback.set(key, torch.cat(parts).reshape(buffer.shape))
+        self._layouts[key] = layout
+
+    def _named_residuals(self) -> dict:
+        named = {}
+        if not self._names or self.feedback is None:
+            return named
+        for key, layout in self._layouts.items():
+            residual = self.feedback.get(key)
+            if residual is None or residual.numel() != sum(n for _, n in layout):
+                continue
+            at, flat = 0, residual.detach().reshape(-1)
+            for owner, numel in layout:
+                name = self._names.get(owner)
+                if name is not None:
+                    named[name] = flat[at:at + numel].clone()
+                at += numel
+        return named
+
     # checkpoint / resume of the error-feedback state (an addition)
     def state_dict(self) -> dict:
         return {"feedback": self.feedback.state_dict() if self.feedback else {},
-                "policy": self.policy.state_dict() if self.policy else {}}
+                "policy": self.policy.state_dict() if self.policy else {},
+                "residual_by_parameter": self._named_residuals()}
 
     def load_state_dict(self, state: dict) -> None:
-        if self.feedback is not None and state.get("feedback"):
+        named = state.get("residual_by_parameter") or {}
+        if self.feedback is not None and named and self._names:
+            # per-parameter residuals are re-assembled bucket by bucket, in whatever order the buckets have here
+            self.feedback.load_state_dict({"residuals": {}})
+            self._pending_named, self._adopted, self._layouts = dict(named), set(), {}
+        elif self.feedback is not None and state.get("feedback"):
             self.feedback.load_state_dict(state["feedback"])
         if self.policy is not None and state.get("policy"):
             self.policy.load_state_dict(state["policy"])
@@ -405,6 +503,7 @@ def create_ddp_comm_hook(
     max_bucket_numel: int | None = None,
     max_blocks: int = 0,
     local_group_size: int | None = None,
+    module: Any | None = None,
 ) -> Callable[[Any, Any], Any]:
     """Build the hook: `ddp_model.register_comm_hook(state=None, hook=hook)`."""
 
@@ -607,6 +706,24 @@ def create_ddp_comm_hook(
         processor = DDPBucketProcessor(config=config, quantize=q, dequantize=dq, all_reduce=all_reduce,
                                        error_feedback=feedback)
 
+    def with_feedback(bucket: Any, transport: Callable[[Any, str], Any]) -> Any:
+        """Error feedback around a transport that only knows how to all-reduce a tensor: what is sent is
+        T(gradient + residual), and the residual becomes what the transport lost of it.  The reference leaves
+        its hierarchical and topology strategies without error feedback (ccdl_comm/communication/ddp_hook.py:
+        148-177); here every strategy has it, as on the peer-memory path."""
+
+        key = _bucket_key(bucket)
+        original = bucket.buffer()
+        decision = policy.decide(key, numel=_numel(original))
+        prepared = feedback.compensate(key, original) if decision.apply else original
+        name = _resolve_dtype(dtype, prepared)
+        # transports reduce in place; `prepared` is still needed for the residual
+        restored = transport(_clone(prepared) if decision.update else prepared, name)
+        if decision.update:
+            feedback.update(key, original=prepared, transmitted=restored)
+        policy.advance(key)
+        return restored
+
     def torch_bucket(bucket: Any) -> Any:
         hook_ref[0].stats["torch"] += 1
         tensor = bucket.buffer()
@@ -616,13 +733,13 @@ def create_ddp_comm_hook(
         if effective == "hierarchical":
             from .collectives.hierarchical import compressed_hierarchical_all_reduce
 
-            return compressed_hierarchical_all_reduce(
-                tensor, config=config, op=reduce, async_op=False, dtype=name,
+            return with_feedback(bucket, lambda t, nm: compressed_hierarchical_all_reduce(
+                t, config=config, op=reduce, async_op=False, dtype=nm,
                 hierarchical_all_reduce=hierarchical_all_reduce, extension_status=extension_status,
-                local_group_size=local_group_size)
+                local_group_size=local_group_size))
         if effective == "topology" and topology_all_reduce is not None:
-            return topology_all_reduce(tensor, config=config, op=reduce, async_op=False, dtype=name,
-                                       extension_status=extension_status)
+            return with_feedback(bucket, lambda t, nm: topology_all_reduce(
+                t, config=config, op=reduce, async_op=False, dtype=nm, extension_status=extension_status))
         if effective == "all_reduce" and processor is not None:
             return processor.process(bucket, dtype=name, reduce=reduce)
         if effective in ("reduce_scatter", "topology"):
@@ -650,6 +767,9 @@ def create_ddp_comm_hook(
     hook.feedback, hook.policy, hook.peer_engine = feedback, policy, peer
     hook.state_dict = holder.state_dict
     hook.load_state_dict = holder.load_state_dict
+    hook.bind_module = holder.bind_module
+    if module is not None:
+        holder.bind_module(module)
     hook.gpu_launches = lambda: holder.gpu_launches
     hook._ccdl_strategy_plan = plan
     hook._ccdl_effective_strategy = effective

@@ -374,3 +374,58 @@ def test_cuda_stream_work_orders_streams_without_host_waits():
     with CudaStreamWork(torch=Torch, async_op=False) as sync:
         pass
     assert sync.stream is Cuda.current and log[-1] == ("event.wait",) and sync.query()
+
+
+class LayoutBucket(FakeBucket):
+    """A bucket that also says which parameters its gradient segments belong to, like DDP's GradBucket."""
+
+    def __init__(self, params, index=0):
+        super().__init__(torch.cat([p.grad.reshape(-1) for p in params]), index)
+        self._params = list(params)
+
+    def parameters(self):
+        return self._params
+
+
+def test_residual_follows_the_parameters_when_the_bucket_order_changes():
+    torch.manual_seed(3)
+    model = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Linear(16, 4))
+    params = list(model.parameters())
+    for p in params:
+        p.grad = torch.randn_like(p) * 0.01
+    feedback = ErrorFeedbackState()
+    hook = create_ddp_comm_hook(CompressionConfig(), strategy="all_gather", all_gather=mirrored_gather(2),
+                                error_feedback=feedback, future_factory=FakeFuture, module=model)
+    hook(None, LayoutBucket(params))                                   # first-iteration order
+    first = feedback.get(0).clone()
+    assert first.abs().max() > 0
+    sizes = [p.numel() for p in params]
+    by_param = dict(zip((id(p) for p in params), first.split(sizes)))
+    reordered = list(reversed(params))
+    hook.holder._follow_layout(LayoutBucket(reordered))                # what the next call does first
+    moved = feedback.get(0)
+    assert torch.equal(moved, torch.cat([by_param[id(p)] for p in reordered]))
+    saved = hook.state_dict()
+    names = [name for name, _ in model.named_parameters()]
+    assert sorted(saved["residual_by_parameter"]) == sorted(names)
+    assert torch.equal(saved["residual_by_parameter"][names[0]], by_param[id(params[0])])
+
+    # a fresh hook on a fresh copy of the model, buckets in the original order again
+    twin = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Linear(16, 4))
+    for p, q in zip(twin.parameters(), params):
+        p.grad = q.grad.clone()
+    feedback2 = ErrorFeedbackState()
+    hook2 = create_ddp_comm_hook(CompressionConfig(), strategy="all_gather", all_gather=mirrored_gather(2),
+                                 error_feedback=feedback2, future_factory=FakeFuture)
+    hook2.bind_module(twin)
+    hook2.load_state_dict(saved)
+    assert feedback2.get(0) is None                                    # assembled when the bucket shows up
+    hook2.holder._follow_layout(LayoutBucket(list(twin.parameters())))
+    assert torch.equal(feedback2.get(0), first)
+
+    # other parameters under the same bucket index: the old residual is dropped, not misapplied
+    stranger = torch.nn.Linear(3, 3)
+    for p in stranger.parameters():
+        p.grad = torch.zeros_like(p)
+    hook.holder._follow_layout(LayoutBucket(list(stranger.parameters())))
+    assert feedback.get(0) is None
