@@ -202,3 +202,138 @@ def test_backend_contract_violations_are_reported():
         StrategyChoice(strategy="a", reason="b", policy_id="c", benchmark_matched=True)
     with pytest.raises(ValueError):
         StrategyChoice(strategy="a", reason="b", policy_id="c", benchmark_matched=False, observed_speedup=2.0)
+
+
+def plan_for(strategy, **kw):
+    return CommunicationPlan(collective="all_reduce", strategy=strategy, backend="fake", compression=CFG, **kw)
+
+
+def test_resolve_plan_is_a_dry_run_over_registry_membership():
+    backend = FakeBackend()
+    reg = registry_with(backend, strategies=("all_gather", "reduce_scatter"))
+    assert resolve_plan(plan_for("all_gather"), ctx(), reg).executed_strategy == "all_gather"
+    fell = resolve_plan(plan_for("ring", fallback=("auto", "reduce_scatter")), ctx(), reg)
+    assert (fell.executed_strategy, fell.fallback_used) == ("reduce_scatter", True) and "ring" in fell.fallback_reason
+    with pytest.raises(UnsupportedCollective, match="no fallback was declared"):
+        resolve_plan(plan_for("ring"), ctx(), reg)
+    with pytest.raises(UnsupportedCollective, match="no supported fallback"):
+        resolve_plan(plan_for("ring", fallback=("tree",)), ctx(), reg)
+    declared = resolve_plan(plan_for("auto", fallback=("all_gather",)), ctx(), reg)
+    assert declared.requested_strategy == "auto" and declared.executed_strategy == "all_gather" and declared.fallback_used
+    generic = resolve_plan(plan_for("auto"), ctx(), reg)                # no selector: the generic order, 4 ranks
+    assert generic.executed_strategy == "reduce_scatter" and not generic.fallback_used
+    two = resolve_plan(plan_for("auto"), ctx(world_size=2), reg)
+    assert two.executed_strategy == "all_gather"
+    with pytest.raises(UnsupportedCollective, match="found no registered backend"):
+        resolve_plan(plan_for("auto"), ctx(), BackendRegistry())
+    reg.register_strategy_selector("fake", lambda plan, context: StrategyChoice(
+        "tree", "measured", "policy-1", False, fallback=("all_gather",)))
+    chosen = resolve_plan(plan_for("auto"), ctx(), reg)
+    assert chosen.executed_strategy == "all_gather" and chosen.fallback_used and chosen.strategy_policy_id == "policy-1"
+    lonely = registry_with(backend, strategies=("reduce_scatter",))
+    lonely.register_strategy_selector("fake", lambda plan, context: StrategyChoice("tree", "measured", "p", False))
+    with pytest.raises(UnsupportedCollective, match="declared fallbacks are not registered"):
+        resolve_plan(plan_for("auto"), ctx(), lonely)
+    assert backend.compiled == []                                       # nothing was compiled along the way
+    for bad in ((None, ctx(), reg), (plan_for("auto"), None, reg), (plan_for("auto"), ctx(), None)):
+        with pytest.raises(TypeError):
+            resolve_plan(*bad)
+
+
+def test_backends_that_break_the_contract_are_reported_as_such():
+    def compile_with(backend, strategy="all_gather"):
+        reg = BackendRegistry()
+        reg.register(BackendKey("all_reduce", strategy, "fake", "full"), lambda: backend)
+        return compile(plan_for(strategy), ctx(), registry=reg)
+
+    misnamed = FakeBackend(name="other")
+    with pytest.raises(BackendRegistrationError, match="does not match registry key"):
+        compile_with(misnamed)
+
+    class NoCaps(FakeBackend):
+        def capabilities(self, context):
+            return {"available": True}
+
+    with pytest.raises(BackendRegistrationError, match="did not return BackendCapabilities"):
+        compile_with(NoCaps())
+
+    class ForeignCaps(FakeBackend):
+        def capabilities(self, context):
+            return replace(self._caps, backend="elsewhere")
+
+    with pytest.raises(BackendRegistrationError, match="capability backend"):
+        compile_with(ForeignCaps())
+
+    class NoExecutor(FakeBackend):
+        def compile(self, plan, context):
+            return object()
+
+    with pytest.raises(BackendRegistrationError, match="did not return a CompiledExecutor"):
+        compile_with(NoExecutor())
+
+    class BadInfo(FakeBackend):
+        def compile(self, plan, context):
+            executor = FakeExecutor(plan.strategy)
+            executor.execution_info = "fast"
+            return executor
+
+    with pytest.raises(BackendRegistrationError, match="did not expose ExecutionInfo"):
+        compile_with(BadInfo())
+
+    class OtherBackendInfo(FakeBackend):
+        def compile(self, plan, context):
+            return FakeExecutor(plan.strategy, backend="elsewhere")
+
+    with pytest.raises(BackendRegistrationError, match="inconsistent backend"):
+        compile_with(OtherBackendInfo())
+
+    class OtherStrategyInfo(FakeBackend):
+        def compile(self, plan, context):
+            return FakeExecutor("ring")
+
+    with pytest.raises(BackendRegistrationError, match="inconsistent executed strategy"):
+        compile_with(OtherStrategyInfo())
+
+    class FrozenExecutor:
+        __slots__ = ("_info",)
+
+        def __init__(self, strategy):
+            self._info = info(strategy)
+
+        execution_info = property(lambda self: self._info)
+
+        def run(self, tensor):
+            return ImmediateWork(tensor)
+
+    class Frozen(FakeBackend):
+        def compile(self, plan, context):
+            return FrozenExecutor(plan.strategy)
+
+    with pytest.raises(BackendRegistrationError, match="must allow compile-time ExecutionInfo binding"):
+        compile_with(Frozen())
+
+    reg = registry_with(FakeBackend())
+    reg.register_strategy_selector("fake", lambda plan, context: "all_gather")
+    with pytest.raises(BackendRegistrationError, match="did not return StrategyChoice"):
+        compile(plan_for("auto"), ctx(), registry=reg)
+    with pytest.raises(TypeError, match="CompileCache"):
+        compile(plan_for("all_gather"), ctx(), registry=registry_with(FakeBackend()), cache={})
+
+
+def test_compile_cache_checks_what_goes_in():
+    cache = CompileCache(max_entries=2)
+    compiled = compile(plan_for("all_gather"), ctx(), registry=registry_with(FakeBackend()), cache=cache)
+    assert cache.max_entries == 2 and len(cache) == 1 and cache.get(compiled.cache_key) is compiled
+    cache.put(compiled.cache_key, compiled)
+    with pytest.raises(TypeError):
+        cache.put("key", compiled)
+    with pytest.raises(TypeError):
+        cache.put(compiled.cache_key, "compiled")
+    with pytest.raises(TypeError):
+        cache.get_or_create(compiled.cache_key, "factory")
+    cache.clear()
+    with pytest.raises(TypeError, match="must return"):
+        cache.get_or_create(compiled.cache_key, lambda: "not a plan")
+    assert len(cache) == 0
+    with pytest.raises(ValueError):
+        CompileCache(max_entries=0)
