@@ -147,3 +147,59 @@ def test_facade_rejects_bad_payloads():
         codec.dequantize_tensor(torch.empty(132, dtype=torch.int8), (128,), c, dtype="bf16")
     with pytest.raises(ValueError):
         codec.dequantize_tensor(codec.quantize_tensor(x, c), (128,), c, dtype="bf16", reduce_op="sum")
+
+
+def test_codec_corners_on_cpu():
+    from lowbit_comm_b200.ops import oracle
+
+    c = cfg()
+    x = torch.randn(4, 50, dtype=torch.bfloat16) * 0.1
+    meta = {}
+    payload = codec.quantize_tensor(x.t(), c, metadata=meta)                   # a non-contiguous view
+    assert meta == {"original_numel": 200, "padded_numel": 256, "num_groups": 4, "dtype": "bf16", "compact": False}
+    assert torch.equal(payload, oracle.encode(x.t().contiguous().reshape(-1), c))
+    empty = codec.quantize_tensor(torch.empty(0, dtype=torch.bfloat16), c)
+    assert empty.numel() == 0 and codec.dequantize_tensor(empty, (0,), c, dtype="bf16").numel() == 0
+
+    # stochastic rounding has no host-codec twin: the oracle serves it, with the prepared value on request
+    noisy = CompressionConfig(stochastic=True)
+    residual = torch.randn(200, dtype=torch.bfloat16) * 0.01
+    prepared = torch.empty(200, dtype=torch.bfloat16)
+    torch.manual_seed(5)
+    a = codec.quantize_tensor(x.reshape(-1), noisy, residual=residual, prepared_out=prepared)
+    torch.manual_seed(5)
+    b = codec.quantize_tensor(x.reshape(-1), noisy, residual=residual)
+    assert torch.equal(a, b) and torch.equal(prepared, oracle.prepare(x.reshape(-1), residual))
+    back = codec.dequantize_tensor(a, (200,), noisy, dtype="bf16")
+    assert (back.float() - prepared.float()).abs().max() <= prepared.float().abs().max() / 127 * 1.01 + 1e-6
+
+    # top-k payloads decode through the oracle as well, with and without accumulation
+    topk = CompressionConfig(topk=2)
+    p = codec.quantize_tensor(x.reshape(-1), topk)
+    once = codec.dequantize_tensor(p, (200,), topk, dtype="bf16")
+    twice = codec.dequantize_tensor(p, (200,), topk, dtype="bf16", output=once.clone(), reduce_op="sum")
+    assert torch.equal(twice, (once.float() + once.float()).to(torch.bfloat16))
+
+    good = codec.quantize_tensor(x.reshape(-1), c)
+    with pytest.raises(ValueError, match="unsupported reduce_op"):
+        codec.dequantize_tensor(good, (200,), c, dtype="bf16", reduce_op="max")
+    with pytest.raises(ValueError, match="wrong number of elements"):
+        codec.dequantize_tensor(good, (200,), c, dtype="bf16", output=torch.empty(199, dtype=torch.bfloat16))
+    with pytest.raises(TypeError, match="wrong dtype"):
+        codec.dequantize_tensor(good, (200,), c, dtype="bf16", output=torch.empty(200, dtype=torch.float16))
+    with pytest.raises(ValueError, match="contiguous"):
+        codec.dequantize_tensor(good, (200,), c, dtype="bf16", output=torch.empty(400, dtype=torch.bfloat16)[::2])
+    with pytest.raises(ValueError, match="expected"):
+        codec.quantize_tensor(x.reshape(-1), c, output=torch.empty(good.numel() + 1, dtype=torch.uint8))
+    with pytest.raises(TypeError, match="uint8"):
+        codec.quantize_tensor(x.reshape(-1), c, output=torch.empty(good.numel(), dtype=torch.int8))
+    with pytest.raises(ValueError, match="contiguous"):
+        codec.quantize_tensor(x.reshape(-1), c, output=torch.empty(2 * good.numel(), dtype=torch.uint8)[::2])
+    with pytest.raises(ValueError, match="unsupported dtype"):
+        codec.resolve_dtype("fp64")
+    with pytest.raises(ValueError, match="needs a tensor"):
+        codec.resolve_dtype("auto")
+    with pytest.raises(ValueError, match="at least one payload"):
+        codec.dequantize_reduce_tensors([], (200,), c, dtype="bf16")
+    with pytest.raises(ValueError, match="unsupported reduce"):
+        codec.dequantize_reduce_tensors([good], (200,), c, dtype="bf16", reduce="max")
