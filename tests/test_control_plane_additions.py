@@ -203,3 +203,81 @@ def test_gather_prefetch_switch_rounds_down_to_a_built_depth():
             assert ext.get_gather_prefetch() == got
     finally:
         ext.set_gather_prefetch(0)
+
+
+def test_native_shortcuts_hand_the_right_payload_to_a_compiled_plan():
+    import lowbit_comm_b200 as lbc
+    from lowbit_comm_b200.parallel.native_collectives import NativeCollectiveInput
+
+    class Plan:
+        def __init__(self):
+            self.seen = []
+
+        def run(self, payload):
+            self.seen.append(payload)
+            return ImmediateWork(payload)
+
+    plan = Plan()
+    a, b, c = object(), object(), object()
+    assert lbc.all_reduce(a, compiled_plan=plan).wait() is a
+    assert lbc.broadcast(a, src=1, compiled_plan=plan).wait() is a and lbc.reduce(a, dst=2, compiled_plan=plan).wait() is a
+    lbc.all_gather(a, output_tensors=[b, c], compiled_plan=plan)
+    lbc.gather(a, gather_list=[b], dst=1, compiled_plan=plan)
+    lbc.reduce_scatter(a, input_tensors=[b, c], compiled_plan=plan)
+    lbc.scatter(a, scatter_list=[b, c], src=0, compiled_plan=plan)
+    lbc.all_to_all(output_tensors=[a], input_tensors=[b], compiled_plan=plan)
+    lbc.barrier(compiled_plan=plan)
+    lists = plan.seen[3:]
+    assert all(isinstance(p, NativeCollectiveInput) for p in lists)
+    assert (lists[0].tensor, lists[0].output_tensors, lists[0].input_tensors) == (a, (b, c), ())
+    assert (lists[1].tensor, lists[1].output_tensors) == (a, (b,))
+    assert (lists[2].tensor, lists[2].input_tensors) == (a, (b, c)) and lists[3].input_tensors == (b, c)
+    assert (lists[4].tensor, lists[4].input_tensors, lists[4].output_tensors) == (None, (b,), (a,))
+    assert lists[5] == NativeCollectiveInput()
+    with pytest.raises(ValueError, match="at least one tensor"):
+        lbc.all_to_all(output_tensors=[], input_tensors=[])
+    assert lbc.native_collectives()[0] == "all_reduce" and len(lbc.native_collectives()) == 9
+
+
+def test_plan_context_info_and_choice_helpers():
+    from lowbit_comm_b200.core.backend import StrategyChoice
+    from lowbit_comm_b200.core.info import ExecutionCounterSnapshot, ExecutionInfo
+    from lowbit_comm_b200.core.plan import WorkspacePolicy
+
+    plan = CommunicationPlan(collective="all_reduce", strategy="auto", backend="cuda", compression=CompressionConfig(),
+                             fallback=("all_gather", "auto", "all_gather"))
+    assert plan.key == ("all_reduce", "auto", "cuda", "full") and plan.is_compressed
+    assert plan.candidates() == ("auto", "all_gather")
+    assert not CommunicationPlan(collective="all_reduce", strategy="native_nccl", backend="cuda").is_compressed
+    ctx = CompileContext(rank=5, world_size=8, device="cuda:1", shape=(4, 256), dtype="bf16", local_rank=1,
+                         local_world_size=4, node_id=1, node_count=2)
+    assert ctx.nbytes == 4 * 256 * 2 and ctx.has_node_layout
+    assert not CompileContext(rank=0, world_size=8, device="cuda:0", shape=(1,), dtype="bf16").has_node_layout
+    assert not CompileContext(rank=6, world_size=8, device="cuda:0", shape=(1,), dtype="bf16", local_rank=1,
+                              local_world_size=4, node_id=1, node_count=2).has_node_layout
+    policy = WorkspacePolicy(max_cached_bytes=100, max_entries=2)
+    assert policy.admits(100, 2) and not policy.admits(101, 1) and not policy.admits(1, 3)
+    assert WorkspacePolicy(cache=False).admits(0, 0) and not WorkspacePolicy(cache=False).admits(1, 1)
+
+    info = ExecutionInfo(requested_strategy="auto", executed_strategy="all_gather", backend="cuda", fallback_used=True,
+                         fallback_reason="ring missing", stage_names=("push", "reduce"), original_bytes=200,
+                         compressed_bytes=104, compression_ratio=200 / 104, workspace_cache_hit=False,
+                         async_capable=True, fast_path="fused")
+    assert info.saved_bytes == 96 and info.with_details(note=1).details["note"] == 1 and not info.details
+    text = info.summary()
+    assert "auto -> all_gather (ring missing)" in text and "[push > reduce]" in text and "200 -> 104 bytes" in text
+    assert ExecutionCounterSnapshot(5, 2, 1, 0, 0).in_flight == 2
+
+    measured = StrategyChoice("reduce_scatter", "table hit", "p1", True, expected_speedup=1.25, evidence="profiles/x.md",
+                              fallback=("native_nccl",))
+    assert measured.speedup == 1.25
+    assert measured.explain() == "reduce_scatter: table hit [p1]; 1.25x; evidence: profiles/x.md; then native_nccl"
+    observed = StrategyChoice("compressed", "shard", "p1", False, observed_speedup=1.7, baseline="nccl full")
+    assert "1.70x over nccl full" in observed.explain() and StrategyChoice("a", "b", "c", False).speedup is None
+    for bad in (dict(expected_speedup=0.0), dict(observed_speedup=1.2), dict(benchmark_matched=True)):
+        kwargs = {"benchmark_matched": False, **bad}
+        matched = kwargs.pop("benchmark_matched")
+        with pytest.raises(ValueError):
+            StrategyChoice("a", "b", "c", matched, **kwargs)
+    with pytest.raises(ValueError, match="positive integers"):
+        BackendCapabilities(backend="x", available=True, bits=frozenset({0}))
