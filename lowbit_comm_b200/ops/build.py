@@ -39,7 +39,7 @@ def cuda_sources() -> list[Path]:
 
 
 HOST_SOURCE = "host_codec.cpp"       # plain C++ (no torch, no CUDA): its own small library
-HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-fno-fast-math"]
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-ffp-contract=off", "-fno-fast-math"]
 
 
 def cxx_sources() -> list[Path]:

@@ -19,7 +19,10 @@
 // fp32 rounding except the explicit fmaf.
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
+#include <thread>
+#include <vector>
 
 namespace {
 
@@ -83,6 +86,38 @@ inline uint16_t float_to_bf16(float f) {
     return uint16_t((x + 0x7FFFu + ((x >> 16) & 1u)) >> 16);
 }
 
+// Groups are independent, so the loops over groups are split into contiguous ranges, one per thread.  The
+// result does not depend on the split (each group is computed by the same scalar code), only the time does.
+// LBC_HOST_THREADS caps the thread count (default: hardware threads, at most 8; several CPU ranks on one
+// machine may want 1); tensors below 8192 groups per thread are not worth a thread.
+inline int64_t host_threads_for(int64_t groups) {
+    static const int64_t cap = [] {
+        const char* env = std::getenv("LBC_HOST_THREADS");
+        int64_t n = env != nullptr ? std::atoll(env) : int64_t(std::thread::hardware_concurrency());
+        return n < 1 ? int64_t(1) : (n > 8 && env == nullptr ? int64_t(8) : n);
+    }();
+    const int64_t useful = groups / 8192;
+    return useful < cap ? (useful < 1 ? 1 : useful) : cap;
+}
+
+template <typename Body>
+void for_group_ranges(int64_t groups, Body body) {
+    const int64_t threads = host_threads_for(groups);
+    if (threads <= 1) {
+        body(int64_t(0), groups);
+        return;
+    }
+    const int64_t per = (groups + threads - 1) / threads;
+    std::vector<std::thread> helpers;
+    helpers.reserve(size_t(threads - 1));
+    for (int64_t t = 1; t < threads; ++t) {
+        const int64_t lo = t * per, hi = lo + per < groups ? lo + per : groups;
+        if (lo < hi) helpers.emplace_back(body, lo, hi);
+    }
+    body(int64_t(0), per < groups ? per : groups);
+    for (auto& h : helpers) h.join();
+}
+
 template <int DT> struct Src;
 template <> struct Src<kFP16> {
     using T = uint16_t;
@@ -140,8 +175,9 @@ int quantize(int group, int bit, bool compact, const void* x_, const void* res_,
     const int word = int(sizeof(T));
     const Layout lay = layout_of(numel, group, bit, word, compact);
     const float lim = bit == 8 ? 127.0f : 7.0f;
+    for_group_ranges(lay.groups, [=](int64_t g_lo, int64_t g_hi) {
     float p[64];
-    for (int64_t g = 0; g < lay.groups; ++g) {
+    for (int64_t g = g_lo; g < g_hi; ++g) {
         const int64_t first = g * group;
         float amax = 0.0f;
         for (int i = 0; i < group; ++i) {
@@ -174,6 +210,7 @@ int quantize(int group, int bit, bool compact, const void* x_, const void* res_,
         }
         std::memcpy(lay.meta(out, g), &stored, sizeof(T));
     }
+    });
     return 0;
 }
 
@@ -185,7 +222,8 @@ int dequantize(int group, int bit, bool compact, const uint8_t* payload, int64_t
     const int word = int(sizeof(T));
     const Layout lay = layout_of(numel, group, bit, word, compact);
     const float lim = bit == 8 ? 127.0f : 7.0f;
-    for (int64_t g = 0; g < lay.groups; ++g) {
+    for_group_ranges(lay.groups, [=](int64_t g_lo, int64_t g_hi) {
+    for (int64_t g = g_lo; g < g_hi; ++g) {
         T stored;
         std::memcpy(&stored, lay.meta(payload, g), sizeof(T));
         const float step = S::up(stored) / lim;
@@ -197,6 +235,7 @@ int dequantize(int group, int bit, bool compact, const uint8_t* payload, int64_t
             out[idx] = accumulate ? S::down(S::up(out[idx]) + S::up(y)) : y;
         }
     }
+    });
     return 0;
 }
 
@@ -211,8 +250,9 @@ int reduce(int group, int bit, bool compact, const uint8_t* const* payloads, int
     const int word = int(sizeof(T));
     const Layout lay = layout_of(numel, group, bit, word, compact);
     const float lim = bit == 8 ? 127.0f : 7.0f;
+    for_group_ranges(lay.groups, [=](int64_t g_lo, int64_t g_hi) {
     float acc[64];
-    for (int64_t g = 0; g < lay.groups; ++g) {
+    for (int64_t g = g_lo; g < g_hi; ++g) {
         for (int i = 0; i < group; ++i) acc[i] = 0.0f;
         for (int r = 0; r < num; ++r) {
             T stored;
@@ -230,6 +270,7 @@ int reduce(int group, int bit, bool compact, const uint8_t* const* payloads, int
             if (out != nullptr) out[idx] = S::down(y32);
         }
     }
+    });
     return 0;
 }
 

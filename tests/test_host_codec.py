@@ -156,3 +156,29 @@ def test_arguments_are_validated():
         host_codec.quantize(x.float(), cfg, "bf16", torch.empty(132, dtype=torch.uint8))
     with pytest.raises(ValueError):
         host_codec.dequantize(torch.empty(132, dtype=torch.uint8), 128, cfg, "bf16", torch.empty(64, dtype=torch.bfloat16))
+
+
+def test_large_tensors_split_over_threads_give_the_same_bytes():
+    """Above 8192 groups per thread the host codec splits its group loops over threads; ranges are disjoint,
+    so the bytes must equal the oracle's whatever the split (odd sizes put a ragged range at the end)."""
+
+    import torch
+
+    from lowbit_comm_b200.config import CompressionConfig
+    from lowbit_comm_b200.ops import codec, oracle
+
+    cfg = CompressionConfig()
+    n = 64 * 8192 * 3 + 37
+    g = torch.Generator().manual_seed(21)
+    x = (torch.randn(n, generator=g) * 0.02).to(torch.bfloat16)
+    r = (torch.randn(n, generator=g) * 0.002).to(torch.bfloat16)
+    prepared = torch.empty_like(x)
+    payload = codec.quantize_tensor(x, cfg, residual=r, prepared_out=prepared)
+    assert torch.equal(payload, oracle.encode(x, cfg, residual=r)) and torch.equal(prepared, oracle.prepare(x, r))
+    assert torch.equal(codec.dequantize_tensor(payload, (n,), cfg, dtype="bf16"), oracle.decode(payload, n, cfg, "bf16"))
+    other = codec.quantize_tensor(-x, cfg)
+    out, residual = torch.empty_like(x), torch.empty_like(x)
+    assert codec.inplace_dequantize_reduce_mean_update_error_feedback([payload, other], prepared, out, residual, cfg,
+                                                                       reduce="mean")
+    y, y32 = oracle.reduce_mean([payload, other], n, cfg, "bf16")
+    assert torch.equal(out, y) and torch.equal(residual, oracle.residual_update(prepared, y32))
