@@ -52,7 +52,7 @@ def main() -> None:
     dtype = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}[args.dtype]
 
     torch.manual_seed(1234)
-    model = SyntheticMLP(WIDTHS, dtype=dtype).to(device)
+    model = SyntheticMLP(WIDTHS, dtype=dtype, bias=False).to(device)      # 62 914 560 weights, as published
     ddp = DDP(model, device_ids=[local_rank], bucket_cap_mb=25, gradient_as_bucket_view=True)
     note = "none (NCCL all-reduce)"
     hook = None

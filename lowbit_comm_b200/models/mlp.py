@@ -11,11 +11,11 @@ from torch import nn
 
 
 class SyntheticMLP(nn.Module):
-    def __init__(self, widths=(1024, 4096, 4096, 1024), dtype=torch.float32) -> None:
+    def __init__(self, widths=(1024, 4096, 4096, 1024), dtype=torch.float32, bias: bool = True) -> None:
         super().__init__()
         layers: list[nn.Module] = []
         for i, (a, b) in enumerate(zip(widths[:-1], widths[1:])):
-            layers.append(nn.Linear(a, b, dtype=dtype))
+            layers.append(nn.Linear(a, b, bias=bias, dtype=dtype))
             if i < len(widths) - 2:
                 layers.append(nn.GELU())
         self.net = nn.Sequential(*layers)

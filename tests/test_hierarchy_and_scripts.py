@@ -71,3 +71,19 @@ def test_bench_contract_flags_and_defaults(monkeypatch):
                 '"vs_baseline"', '"dtype"', '"data"', '"config"', '"e2e"', '"h2d_bytes_per_step"',
                 '"d2h_bytes_per_step"', '"gpu_launches"', '"clocks"'):
         assert key in src, key
+
+
+def test_benchmark_and_example_scripts_load_and_describe_their_workload():
+    mlp = _load("benchmarks/mlp_ddp.py", "mlp_ddp_script")
+    assert mlp.WIDTHS == (2048, 4096, 4096, 4096, 4096, 1024)
+    weights = sum(a * b for a, b in zip(mlp.WIDTHS[:-1], mlp.WIDTHS[1:]))
+    assert weights == 62_914_560                       # the parameter count of the reference's published run (no biases)
+    from lowbit_comm_b200.models.mlp import SyntheticMLP
+
+    tiny = SyntheticMLP((4, 8, 2), bias=False)
+    assert sum(p.numel() for p in tiny.parameters()) == 4 * 8 + 8 * 2
+    src = open(os.path.join(ROOT, "benchmarks", "mlp_ddp.py")).read()
+    for key in ('"metric"', '"value"', '"unit"', '"n_gpus"', '"ms_per_step"', '"h2d_bytes_per_step"', '"gpu_launches"'):
+        assert key in src, key
+    example = _load("examples/cpu_gloo_mlp.py", "cpu_gloo_mlp_example")
+    assert example.MODES == ("plain", "wire_codec", "fallback_codec") and callable(example.worker)
