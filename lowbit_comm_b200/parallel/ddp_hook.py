@@ -340,6 +340,7 @@ class DDPCommHook:
         self._names: dict[int, str] = {}              # parameter id -> name (after bind_module)
         self._pending_named: dict[str, Any] = {}      # residuals of a name-keyed checkpoint, not yet assembled
         self._adopted: set = set()
+        self._stable: dict[Any, int] = {}             # bucket key -> consecutive calls with an unchanged layout
 
     def __call__(self, state, bucket):  # no annotations: DDP validates them when present
         self.stats["buckets"] += 1
@@ -376,16 +377,21 @@ class DDPCommHook:
         except (RuntimeError, TypeError):
             return None
 
+    _SETTLED_AFTER = 4      # DDP re-orders its buckets once, after the first iteration
+
     def _follow_layout(self, bucket: Any) -> None:
         if self.feedback is None:
             return
+        key = _bucket_key(bucket)
+        if self._stable.get(key, 0) >= self._SETTLED_AFTER and not self._pending_named:
+            return                                  # seen unchanged often enough: stop asking the bucket
         layout = self._segments(bucket)
         if layout is None:
             return
-        key = _bucket_key(bucket)
         self._adopt_named_residual(key, layout, bucket)
         known = self._layouts.get(key)
         self._layouts[key] = layout
+        self._stable[key] = self._stable.get(key, 0) + 1 if known == layout else 0
         if known is None or known == layout:
             return
         residual = self.feedback.get(key)
@@ -421,6 +427,8 @@ class DDPCommHook:
             return
         self.feedback.set(key, torch.cat(parts).reshape(buffer.shape))
         self._layouts[key] = layout
+        for name in names:                           # handed over: the checkpoint copy is not needed any more
+            self._pending_named.pop(name, None)
 
     def _named_residuals(self) -> dict:
         named = {}
@@ -449,7 +457,7 @@ class DDPCommHook:
         if self.feedback is not None and named and self._names:
             # per-parameter residuals are re-assembled bucket by bucket, in whatever order the buckets have here
             self.feedback.load_state_dict({"residuals": {}})
-            self._pending_named, self._adopted, self._layouts = dict(named), set(), {}
+            self._pending_named, self._adopted, self._layouts, self._stable = dict(named), set(), {}, {}
         elif self.feedback is not None and state.get("feedback"):
             self.feedback.load_state_dict(state["feedback"])
         if self.policy is not None and state.get("policy"):
