@@ -87,6 +87,7 @@ class _SettlesOnce(CollectiveWork[T]):
         self._error: BaseException | None = None
         self._reported = False
         self._lock = threading.Lock()
+        self._driver: int | None = None      # thread that is inside _drive(), to catch a wait on itself
 
     # what subclasses provide
     def _drive(self) -> Any:
@@ -118,14 +119,19 @@ class _SettlesOnce(CollectiveWork[T]):
 
     def wait(self) -> T:
         self._note("wait")
+        if self._driver == threading.get_ident():
+            raise RuntimeError("wait() was called by this work's own completion step; it would wait for itself")
         with self._lock:
             if not self._settled:
+                self._driver = threading.get_ident()
                 try:
                     outcome = self._drive()
                 except BaseException as exc:      # kept: every later waiter sees the same failure
                     self._settle(error=exc)
                 else:
                     self._settle(outcome)
+                finally:
+                    self._driver = None
         if self._error is not None:
             raise self._error
         return self._value

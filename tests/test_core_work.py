@@ -131,3 +131,16 @@ def test_execution_info_validation():
     ok = ExecutionInfo(**{**base, "fallback_used": True, "fallback_reason": "no peer access", "details": {"k": 1}})
     with pytest.raises(TypeError):
         ok.details["k"] = 2
+
+
+def test_a_completion_step_that_waits_on_its_own_work_is_an_error_not_a_deadlock():
+    from lowbit_comm_b200.core.work import CompletionWork
+
+    holder = {}
+    work = CompletionWork(None, complete=lambda: holder["work"].wait())
+    holder["work"] = work
+    with pytest.raises(RuntimeError, match="wait for itself"):
+        work.wait()
+    with pytest.raises(RuntimeError, match="wait for itself"):       # the failure is the work's outcome now
+        work.wait()
+    assert work.query()
