@@ -97,17 +97,23 @@ void CompressedWork::finish_locked_out() {
 }
 
 py::object CompressedWork::wait() {
-    bool mine = false;
+    bool mine = false, self_wait = false;
     {
         py::gil_scoped_release nogil;
         std::unique_lock<std::mutex> lock(mutex_);
         if (phase_ == Phase::Idle) {
             phase_ = Phase::Running;
+            runner_ = std::this_thread::get_id();
             mine = true;
+        } else if (phase_ == Phase::Running && runner_ == std::this_thread::get_id()) {
+            // the callback (or the transport's wait) of this very work called wait(): it would wait for itself
+            self_wait = true;
         } else {
             done_cv_.wait(lock, [this] { return phase_ == Phase::Done; });
         }
     }
+    if (self_wait)
+        throw std::runtime_error("wait() was called by this work's own completion step; it would wait for itself");
     if (mine) {
         finish_locked_out();
         {

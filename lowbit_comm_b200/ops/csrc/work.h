@@ -8,6 +8,7 @@
 #include <exception>
 #include <memory>
 #include <mutex>
+#include <thread>
 #include <vector>
 
 namespace py = pybind11;
@@ -44,6 +45,7 @@ class CompressedWork {
     int device_ = 0;
     bool callback_ran_ = false;
     Phase phase_ = Phase::Idle;
+    std::thread::id runner_;         // the thread inside finish_locked_out(), to refuse a wait on itself
     mutable std::mutex mutex_;
     std::condition_variable done_cv_;
     std::shared_ptr<py::error_already_set> py_error_;

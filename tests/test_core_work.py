@@ -133,11 +133,11 @@ def test_execution_info_validation():
         ok.details["k"] = 2
 
 
-def test_a_completion_step_that_waits_on_its_own_work_is_an_error_not_a_deadlock():
-    from lowbit_comm_b200.core.work import CompletionWork
-
+@pytest.mark.timeout(60)
+@pytest.mark.parametrize("name,make", FACTORIES)
+def test_a_completion_step_that_waits_on_its_own_work_is_an_error_not_a_deadlock(name, make):
     holder = {}
-    work = CompletionWork(None, complete=lambda: holder["work"].wait())
+    work = make(None, complete=lambda: holder["work"].wait())
     holder["work"] = work
     with pytest.raises(RuntimeError, match="wait for itself"):
         work.wait()
