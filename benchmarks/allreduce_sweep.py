@@ -69,6 +69,8 @@ def main() -> None:
                     help="pull gather: 1 = tiles round-robin over the owners (default), 0 = linear sweep")
     ap.add_argument("--gather-prefetch", type=int, choices=(0, 2, 4), default=None,
                     help="decode stage: tiles of peer loads in flight per thread (0 = general reduce kernel)")
+    ap.add_argument("--kernel-names", action="store_true",
+                    help="record which CUDA kernels one (untimed) call launches, from torch.profiler")
     ap.add_argument("--multicast", action="store_true",
                     help="arenas from the symmetric-memory allocator: broadcasts use multimem stores")
     ap.add_argument("--out", default="gpurun_out/allreduce_sweep.json")
@@ -203,12 +205,18 @@ def main() -> None:
                     ours(stages)()
                 phases = ws.phase_timer.summary()
                 ws.phase_timer = None
+            launched = None
+            if args.kernel_names:                       # a separate call after the timed ones: evidence only
+                from lowbit_comm_b200.utils.tracing import kernel_names
+
+                launched = kernel_names(ours(stages))
             tag = f"_p{push_variant}r{int(reduce_bulk)}b{k2_blocks}" if args.variants else ""
             rows.append({"impl": f"ours_{stages}stage{tag}", "mib": mib, "world": world, "ms": t,
                          "algbw_gbs": nbytes / (t * 1e-3) / 1e9, "rel_l2": rel, **roof,
                          "roofline_frac": roof["roofline_us"] / (t * 1e3), "peak_kind": peak_kind,
                          "phases_ms": phases, "multicast": multicast_on, "chunk_mib": args.chunk_mib,
-                         "gather": "pull" if big.pull_gather else "push"})
+                         "gather": "pull" if big.pull_gather else "push",
+                         "gather_prefetch": ext.get_gather_prefetch(), "kernels": launched})
         ext.set_push_variant(1, True, 0)
         nccl_buf = x.clone()
 

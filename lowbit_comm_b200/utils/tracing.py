@@ -54,3 +54,30 @@ class PhaseTimer:
         import statistics
 
         return {k: statistics.median(v) for k, v in self.totals.items() if v}
+
+
+def kernel_names(fn, *, torch_module=None) -> dict[str, int]:
+    """Runs `fn()` once under `torch.profiler` and returns {CUDA kernel name: launches}.
+
+    Evidence, not measurement: benchmark records use it to show which kernels served an operation (the
+    reference does the same with `profile.key_averages()`, tests/distributed/fused_reduced_shard_perf.py:
+    244-274).  Never time anything inside this call.  On a machine without CUDA the result is empty.
+    """
+
+    torch = torch_module
+    if torch is None:
+        import torch
+    profiler = torch.profiler
+    activities = [profiler.ProfilerActivity.CPU]
+    if torch.cuda.is_available():
+        activities.append(profiler.ProfilerActivity.CUDA)
+    with profiler.profile(activities=activities) as prof:
+        fn()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+    counts: dict[str, int] = {}
+    for event in prof.events():
+        device = getattr(event, "device_type", None)
+        if device is not None and "cuda" in str(device).lower():
+            counts[event.name] = counts.get(event.name, 0) + 1
+    return counts

@@ -63,3 +63,39 @@ def test_tracing_is_a_no_op_unless_enabled(monkeypatch):
     timer = tracing.PhaseTimer()
     timer.flush()                                      # nothing marked: nothing to do
     assert timer.summary() == {}
+
+
+def test_kernel_names_is_empty_without_a_gpu_and_counts_device_events_with_a_fake():
+    import types
+
+    import torch
+
+    from lowbit_comm_b200.utils.tracing import kernel_names
+
+    if not torch.cuda.is_available():
+        assert kernel_names(lambda: torch.ones(4) + 1) == {}
+
+    class Profile:
+        def __init__(self, activities):
+            self.activities = activities
+
+        def __enter__(self):
+            return self
+
+        def __exit__(self, *exc):
+            return False
+
+        def events(self):
+            make = types.SimpleNamespace
+            return [make(name="quant_push_tiled_kernel", device_type="DeviceType.CUDA"),
+                    make(name="aten::add", device_type="DeviceType.CPU"),
+                    make(name="quant_push_tiled_kernel", device_type="DeviceType.CUDA"),
+                    make(name="reduce_kernel", device_type="DeviceType.CUDA")]
+
+    ran = []
+    fake = types.SimpleNamespace(
+        profiler=types.SimpleNamespace(profile=lambda activities: Profile(activities),
+                                       ProfilerActivity=types.SimpleNamespace(CPU="cpu", CUDA="cuda")),
+        cuda=types.SimpleNamespace(is_available=lambda: True, synchronize=lambda: ran.append("sync")))
+    counts = kernel_names(lambda: ran.append("fn"), torch_module=fake)
+    assert counts == {"quant_push_tiled_kernel": 2, "reduce_kernel": 1} and ran == ["fn", "sync"]
