@@ -9,8 +9,10 @@ fp16 / W in {2,4}; this table carries rules measured on B200 with the sweep in
 Rule of thumb the measurements support on NVLink 5: the one-stage path (every
 rank reduces W payloads) wins for W <= 2 and for small tensors, where launch
 count dominates; the two-stage path wins for W >= 4 above a few MiB because it
-moves 2(W-1)/W payloads instead of W-1.  Below `min_compress_numel` elements an
-uncompressed NCCL all-reduce is as fast and exact.
+moves 2(W-1)/W payloads instead of W-1.  Full-output rules start at the size
+from which the fused path was measured faster than NCCL's bf16 all-reduce
+(`B200_CROSSOVER_NUMEL`); below it, and below `min_compress_numel` elements in
+any case, `auto` keeps the uncompressed NCCL all-reduce, which is exact.
 """
 
 from __future__ import annotations
@@ -118,6 +120,10 @@ class CudaStrategyTable:
     def rules(self) -> tuple[CudaStrategyRule, ...]:
         return self._rules
 
+    # Elements (16-bit) from which the fused all-reduce was measured faster than NCCL's bf16 all-reduce on B200:
+    # 2 MiB on 2 GPUs, 128 MiB on 4, 64 MiB on 8 (profiles/allreduce_sweep_b200.md).  Below it `auto` keeps NCCL.
+    B200_CROSSOVER_NUMEL = {2: 1 << 20, 4: 1 << 26, 8: 1 << 25}
+
     @classmethod
     def for_b200(cls, measured: dict | None = None) -> "CudaStrategyTable":
         """Rules for sm_100 / bf16+fp16 / W in {2,4,8}; `measured` overrides the recorded speed-ups
@@ -138,14 +144,15 @@ class CudaStrategyTable:
                               same_semantics_baseline=layout == "full")
                 if layout == "shard":
                     rules.append(CudaStrategyRule(min_numel=262_144, max_numel=1 << 31, strategy="compressed", **common))
-                elif world <= 2:
-                    rules.append(CudaStrategyRule(min_numel=262_144, max_numel=1 << 31, strategy="all_gather", **common))
-                else:
-                    # one stage while tensor bytes x W <= 64 MiB (measured crossover: 16 MiB on 4 GPUs, 8 MiB on 8)
-                    one_stage_max = (64 << 20) // (2 * world)
-                    rules.append(CudaStrategyRule(min_numel=262_144, max_numel=one_stage_max, strategy="all_gather",
-                                                  **common))
-                    rules.append(CudaStrategyRule(min_numel=one_stage_max + 1, max_numel=1 << 31,
+                    continue
+                # full output: compressed only from the size at which it was measured to beat NCCL's bf16 all-reduce
+                start = cls.B200_CROSSOVER_NUMEL.get(world, 1 << 25)
+                # one stage while tensor bytes x W <= 64 MiB (measured: 16 MiB on 4 GPUs, 8 MiB on 8), and always for W <= 2
+                one_stage_max = (1 << 31) if world <= 2 else (64 << 20) // (2 * world)
+                if start <= one_stage_max:
+                    rules.append(CudaStrategyRule(min_numel=start, max_numel=one_stage_max, strategy="all_gather", **common))
+                if one_stage_max < 1 << 31:
+                    rules.append(CudaStrategyRule(min_numel=max(start, one_stage_max + 1), max_numel=1 << 31,
                                                   strategy="reduce_scatter", **common))
         return cls(tuple(rules))
 
@@ -194,6 +201,9 @@ class CudaStrategyTable:
         if _numel(context.shape) < self.min_compress_numel:
             return self._unmeasured("native_nccl", "small bucket uses uncompressed NCCL: launch latency dominates "
                                                    f"below {self.min_compress_numel} elements")
+        if not self._mismatches(context, plan.compression, quiet=True):
+            return self._unmeasured("native_nccl", "below the measured crossover uncompressed NCCL is as fast or "
+                                                   "faster: the size is outside every rule of this world size")
         return self._unmeasured("native_nccl", "unverified dimensions use safe uncompressed NCCL: "
                                 + ", ".join(self._mismatches(context, plan.compression)))
 
@@ -213,8 +223,9 @@ class CudaStrategyTable:
         return StrategyChoice(rule.strategy, why, self.policy_id, True, evidence=self.evidence,
                               fallback=("native_nccl",) if rule.output_layout == "full" else (), **kind)
 
-    def _mismatches(self, context: CompileContext, comp: CompressionConfig) -> tuple[str, ...]:
-        """Which dimensions of the request no rule of this table was measured for."""
+    def _mismatches(self, context: CompileContext, comp: CompressionConfig, *, quiet: bool = False) -> tuple[str, ...]:
+        """Which dimensions of the request no rule of this table was measured for (`quiet`: an empty tuple
+        instead of the "unmatched_rule" placeholder when every dimension is known)."""
 
         measured = {name: {getattr(rule, name) for rule in self._rules}
                     for name in ("device_architecture", "world_size", "dtype")}
@@ -223,7 +234,7 @@ class CudaStrategyTable:
         missing = [name for name, value in asked.items() if value not in measured[name]]
         if _profile(comp) not in {_profile(rule.compression) for rule in self._rules}:
             missing.append("compression_profile")
-        return tuple(missing) or ("unmatched_rule",)
+        return tuple(missing) or (() if quiet else ("unmatched_rule",))
 
     def as_selector(self) -> Callable[[CommunicationPlan, CompileContext], StrategyChoice]:
         return self.select

@@ -161,7 +161,9 @@ def test_strategy_table_lookup_is_by_domain_and_rejects_overlap():
     rule = table.lookup(plan, big)
     assert rule is not None and rule.strategy == "reduce_scatter" and table.select(plan, big).benchmark_matched
     small = CompileContext(rank=0, world_size=8, device="cuda:0", shape=(1 << 20,), dtype="bf16", device_architecture="sm_100")
-    assert table.lookup(plan, small).strategy == "all_gather"
+    assert table.lookup(plan, small) is None and table.select(plan, small).strategy == "native_nccl"
+    pair = CompileContext(rank=0, world_size=2, device="cuda:0", shape=(1 << 20,), dtype="bf16", device_architecture="sm_100")
+    assert table.lookup(plan, pair).strategy == "all_gather"
     odd = CompileContext(rank=0, world_size=3, device="cuda:0", shape=(1 << 26,), dtype="bf16", device_architecture="sm_100")
     assert table.lookup(plan, odd) is None and "world_size" in table.select(plan, odd).reason
     base = dict(collective="all_reduce", output_layout="full", device_architecture="sm_100", world_size=2, dtype="bf16",

@@ -82,9 +82,12 @@ def test_b200_strategy_table():
 
     full = CommunicationPlan(collective="all_reduce", strategy="auto", compression=cfg)
     assert table.select(full, ctx(2, 1 << 24)).strategy == "all_gather"
-    big = table.select(full, ctx(8, 1 << 24))
+    big = table.select(full, ctx(8, 1 << 25))
     assert big.strategy == "reduce_scatter" and big.benchmark_matched and big.evidence and big.fallback == ("native_nccl",)
-    assert table.select(full, ctx(8, 1 << 20)).strategy == "all_gather"
+    assert table.select(full, ctx(2, 1 << 20)).strategy == "all_gather"
+    between = table.select(full, ctx(8, 1 << 24))                    # 32 MiB on 8 GPUs: NCCL was measured faster
+    assert between.strategy == "native_nccl" and "crossover" in between.reason and not between.benchmark_matched
+    assert table.select(full, ctx(4, 1 << 26)).strategy == "reduce_scatter"
     small = table.select(full, ctx(8, 1000))
     assert small.strategy == "native_nccl" and "small bucket" in small.reason and not small.benchmark_matched
     other = table.select(full, ctx(8, 1 << 24, arch="sm_90"))
