@@ -341,6 +341,7 @@ class DDPCommHook:
         self._pending_named: dict[str, Any] = {}      # residuals of a name-keyed checkpoint, not yet assembled
         self._adopted: set = set()
         self._stable: dict[Any, int] = {}             # bucket key -> consecutive calls with an unchanged layout
+        self._loaded_numels: dict[Any, list[int]] = {}  # segment sizes of a loaded, unnamed checkpoint, per bucket
 
     def __call__(self, state, bucket):  # no annotations: DDP validates them when present
         self.stats["buckets"] += 1
@@ -389,6 +390,7 @@ class DDPCommHook:
         if layout is None:
             return
         self._adopt_named_residual(key, layout, bucket)
+        self._reconcile_loaded(key, layout)
         known = self._layouts.get(key)
         self._layouts[key] = layout
         self._stable[key] = self._stable.get(key, 0) + 1 if known == layout else 0
@@ -408,6 +410,27 @@ class DDPCommHook:
         import torch
 
         self.feedback.set(key, torch.cat([pieces[owner] for owner, _ in layout]).reshape(residual.shape))
+
+    def _reconcile_loaded(self, key: Any, layout) -> None:
+        """A residual loaded from a checkpoint without parameter names is in the segment order of the process
+        that saved it.  If this bucket's segments have other sizes in other places, the residual is re-ordered
+        when the sizes identify the segments (no two alike), and dropped otherwise: losing one step of error
+        feedback is harmless, adding it to the wrong parameters is not."""
+
+        saved = self._loaded_numels.pop(key, None)
+        if saved is None or self.feedback is None:
+            return
+        here = [numel for _, numel in layout]
+        residual = self.feedback.get(key)
+        if residual is None or saved == here:
+            return
+        if sorted(saved) != sorted(here) or len(set(saved)) != len(saved) or residual.numel() != sum(saved):
+            self.feedback.clear(key)
+            return
+        import torch
+
+        pieces = dict(zip(saved, residual.reshape(-1).split(saved)))
+        self.feedback.set(key, torch.cat([pieces[numel] for numel in here]).reshape(residual.shape))
 
     def _adopt_named_residual(self, key: Any, layout, bucket: Any) -> None:
         """After `load_state_dict` of a name-keyed checkpoint: assemble this bucket's residual in its current
@@ -450,7 +473,8 @@ class DDPCommHook:
     def state_dict(self) -> dict:
         return {"feedback": self.feedback.state_dict() if self.feedback else {},
                 "policy": self.policy.state_dict() if self.policy else {},
-                "residual_by_parameter": self._named_residuals()}
+                "residual_by_parameter": self._named_residuals(),
+                "segment_numels": {key: [numel for _, numel in layout] for key, layout in self._layouts.items()}}
 
     def load_state_dict(self, state: dict) -> None:
         named = state.get("residual_by_parameter") or {}
@@ -460,6 +484,8 @@ class DDPCommHook:
             self._pending_named, self._adopted, self._layouts, self._stable = dict(named), set(), {}, {}
         elif self.feedback is not None and state.get("feedback"):
             self.feedback.load_state_dict(state["feedback"])
+            self._loaded_numels = {key: list(sizes) for key, sizes in (state.get("segment_numels") or {}).items()}
+            self._layouts, self._stable = {}, {}
         if self.policy is not None and state.get("policy"):
             self.policy.load_state_dict(state["policy"])
 

@@ -429,3 +429,45 @@ def test_residual_follows_the_parameters_when_the_bucket_order_changes():
         p.grad = torch.zeros_like(p)
     hook.holder._follow_layout(LayoutBucket(list(stranger.parameters())))
     assert feedback.get(0) is None
+
+
+def test_unnamed_checkpoint_is_reordered_by_segment_size_or_dropped():
+    torch.manual_seed(4)
+    model = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Linear(16, 4))         # sizes 128, 16, 64, 4: all different
+    params = list(model.parameters())
+    for p in params:
+        p.grad = torch.randn_like(p) * 0.01
+
+    def fresh():
+        feedback = ErrorFeedbackState()
+        hook = create_ddp_comm_hook(CompressionConfig(), strategy="all_gather", all_gather=mirrored_gather(2),
+                                    error_feedback=feedback, future_factory=FakeFuture)
+        return hook, feedback
+
+    hook, feedback = fresh()
+    hook(None, LayoutBucket(list(reversed(params))))                 # the saving process ended in this order
+    saved = hook.state_dict()
+    assert saved["residual_by_parameter"] == {} and saved["segment_numels"] == {0: [4, 64, 16, 128]}
+    by_size = dict(zip([4, 64, 16, 128], feedback.get(0).split([4, 64, 16, 128])))
+
+    hook2, feedback2 = fresh()
+    hook2.load_state_dict(saved)
+    hook2.holder._follow_layout(LayoutBucket(params))                # the resuming process starts in the other order
+    assert torch.equal(feedback2.get(0), torch.cat([by_size[n] for n in (128, 16, 64, 4)]))
+
+    twins = torch.nn.Sequential(torch.nn.Linear(4, 4, bias=False), torch.nn.Linear(4, 4, bias=False))   # 16 and 16
+    for p in twins.parameters():
+        p.grad = torch.randn_like(p) * 0.01
+    hook3, feedback3 = fresh()
+    hook3(None, LayoutBucket(list(twins.parameters())))
+    state = hook3.state_dict()
+    state["segment_numels"] = {0: [16, 16]}
+    hook4, feedback4 = fresh()
+    hook4.load_state_dict(state)
+    hook4.holder._follow_layout(LayoutBucket(list(twins.parameters())))
+    assert feedback4.get(0) is not None                               # same order: kept as it is
+    hook5, feedback5 = fresh()
+    state["segment_numels"] = {0: [8, 24]}
+    hook5.load_state_dict(state)
+    hook5.holder._follow_layout(LayoutBucket(list(twins.parameters())))
+    assert feedback5.get(0) is None                                   # cannot tell whose residual is whose: dropped
