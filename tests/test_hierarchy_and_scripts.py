@@ -85,5 +85,9 @@ def test_benchmark_and_example_scripts_load_and_describe_their_workload():
     src = open(os.path.join(ROOT, "benchmarks", "mlp_ddp.py")).read()
     for key in ('"metric"', '"value"', '"unit"', '"n_gpus"', '"ms_per_step"', '"h2d_bytes_per_step"', '"gpu_launches"'):
         assert key in src, key
+    micro = open(os.path.join(ROOT, "benchmarks", "micro_suite.py")).read()
+    for case in ("reduced_shard", "async_vs_sync", "dynamic_gather", "p2p"):
+        assert f'case="{case}"' in micro, case
+    assert callable(_load("benchmarks/micro_suite.py", "micro_suite_script").main)
     example = _load("examples/cpu_gloo_mlp.py", "cpu_gloo_mlp_example")
     assert example.MODES == ("plain", "wire_codec", "fallback_codec") and callable(example.worker)
