@@ -34,6 +34,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--cases", nargs="+", default=["reduced_shard", "async_vs_sync", "dynamic_gather", "p2p"])
     ap.add_argument("--out", default="gpurun_out/micro_suite.json")
+    ap.add_argument("--cpu", action="store_true",
+                    help="dry run on CPU ranks (gloo, host timer, no L2 flush): checks the script, measures nothing useful")
     args = ap.parse_args()
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
 
@@ -47,26 +49,39 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29541")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    if args.cpu:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        flush = lambda: None                                                        # noqa: E731
+    else:
+        torch.cuda.set_device(local_rank)
+        dev = torch.device("cuda", local_rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        flush = L2Flusher(dev)
     cfg = lbc.CompressionConfig(error_feedback=False)
-    flush = L2Flusher(dev)
 
     def measure(fn) -> float:
         """Median milliseconds of `fn()`, maximum over ranks."""
+
+        import time
 
         times = []
         for i in range(args.warmup + args.iters):
             flush()
             dist.barrier()
-            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            fn()
-            stop.record()
-            torch.cuda.synchronize()
+            if args.cpu:
+                began = time.perf_counter()
+                fn()
+                elapsed = (time.perf_counter() - began) * 1e3
+            else:
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                fn()
+                stop.record()
+                torch.cuda.synchronize()
+                elapsed = start.elapsed_time(stop)
             if i >= args.warmup:
-                times.append(start.elapsed_time(stop))
+                times.append(elapsed)
         t = torch.tensor([statistics.median(times)], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
@@ -98,9 +113,13 @@ def main() -> None:
             t_ours = measure(lambda: lbc.compressed_reduce_scatter_shard(x, config=cfg, op="mean", out=own_out))
             lo = probe.shard_index * probe.shard_numel
             err = rel_l2(own_out[: max(0, min(n - lo, probe.shard_numel))], exact[lo:lo + probe.shard_numel])
-            t_rs = measure(lambda: dist.reduce_scatter_tensor(shard_out, x, op=dist.ReduceOp.AVG))
             full = x.clone()
-            t_full = measure(lambda: dist.all_reduce(full, op=dist.ReduceOp.AVG))
+            if args.cpu:                                   # gloo has neither reduce_scatter_tensor nor AVG
+                t_rs = float("nan")
+                t_full = measure(lambda: dist.all_reduce(full))
+            else:
+                t_rs = measure(lambda: dist.reduce_scatter_tensor(shard_out, x, op=dist.ReduceOp.AVG))
+                t_full = measure(lambda: dist.all_reduce(full, op=dist.ReduceOp.AVG))
             record(case="reduced_shard", mib=mib, ours_ms=t_ours, nccl_reduce_scatter_ms=t_rs, nccl_all_reduce_ms=t_full,
                    speedup_vs_nccl_full=t_full / t_ours, speedup_vs_nccl_reduce_scatter=t_rs / t_ours, rel_l2=err,
                    transport=probe.transport)
@@ -136,7 +155,8 @@ def main() -> None:
             dist.all_reduce(err, op=dist.ReduceOp.MAX)
             record(case="p2p", mib=mib, ms=t, rel_l2=float(err.item()))
         del x, exact
-        torch.cuda.empty_cache()
+        if not args.cpu:
+            torch.cuda.empty_cache()
 
     if rank == 0:
         os.makedirs(os.path.dirname(os.path.join(ROOT, args.out)) or ".", exist_ok=True)

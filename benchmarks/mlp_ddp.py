@@ -33,6 +33,8 @@ def main() -> None:
     ap.add_argument("--dtype", choices=("fp16", "bf16", "fp32"), default="fp16")
     ap.add_argument("--strategy", default="auto")
     ap.add_argument("--out", default="gpurun_out/mlp_ddp.json")
+    ap.add_argument("--cpu", action="store_true",
+                    help="dry run on CPU ranks (gloo, host timer, narrow model): checks the script, measures nothing useful")
     args = ap.parse_args()
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
 
@@ -46,14 +48,20 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29531")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    widths = WIDTHS
+    if args.cpu:
+        device = torch.device("cpu")
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        args.dtype, widths = "fp32", tuple(w // 16 for w in WIDTHS)
+    else:
+        torch.cuda.set_device(local_rank)
+        device = torch.device("cuda", local_rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     dtype = {"fp16": torch.float16, "bf16": torch.bfloat16, "fp32": torch.float32}[args.dtype]
 
     torch.manual_seed(1234)
-    model = SyntheticMLP(WIDTHS, dtype=dtype, bias=False).to(device)      # 62 914 560 weights, as published
-    ddp = DDP(model, device_ids=[local_rank], bucket_cap_mb=25, gradient_as_bucket_view=True)
+    model = SyntheticMLP(widths, dtype=dtype, bias=False).to(device)      # 62 914 560 weights, as published
+    ddp = DDP(model, device_ids=None if args.cpu else [local_rank], bucket_cap_mb=25, gradient_as_bucket_view=True)
     note = "none (NCCL all-reduce)"
     hook = None
     if args.impl == "ours":
@@ -85,8 +93,10 @@ def main() -> None:
     opt = torch.optim.SGD(ddp.parameters(), lr=0.01)
     total = args.warmup + args.steps
     gen = torch.Generator().manual_seed(100 + rank)
-    xs = torch.randn(total, args.batch, WIDTHS[0], generator=gen).to(dtype).pin_memory()
-    ys = torch.randn(total, args.batch, WIDTHS[-1], generator=gen).to(dtype).pin_memory()
+    xs = torch.randn(total, args.batch, widths[0], generator=gen).to(dtype)
+    ys = torch.randn(total, args.batch, widths[-1], generator=gen).to(dtype)
+    if not args.cpu:
+        xs, ys = xs.pin_memory(), ys.pin_memory()
 
     def step(i: int) -> float:
         x, y = xs[i].to(device, non_blocking=True), ys[i].to(device, non_blocking=True)
@@ -99,28 +109,37 @@ def main() -> None:
     for i in range(args.warmup):
         step(i)
     dist.barrier()
-    torch.cuda.synchronize()
-    torch.cuda.reset_peak_memory_stats()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    last = 0.0
-    for i in range(args.warmup, total):
-        last = step(i)
-    stop.record()
-    torch.cuda.synchronize()
+    last, peak_mib = 0.0, 0.0
+    if args.cpu:
+        import time
+
+        began = time.perf_counter()
+        for i in range(args.warmup, total):
+            last = step(i)
+        elapsed_ms = (time.perf_counter() - began) * 1e3
+    else:
+        torch.cuda.synchronize()
+        torch.cuda.reset_peak_memory_stats()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(args.warmup, total):
+            last = step(i)
+        stop.record()
+        torch.cuda.synchronize()
+        elapsed_ms, peak_mib = start.elapsed_time(stop), torch.cuda.max_memory_allocated() / 2**20
     dist.barrier()
-    ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
+    ms = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     if rank == 0:
         line = {"metric": "synthetic MLP DDP training throughput", "value": args.batch * world * args.steps / (ms.item() * 1e-3),
                 "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms.item() / args.steps, "higher_is_better": True, "scaling": "weak", "dtype": args.dtype,
                 "impl": args.impl, "data": "synthetic (normal inputs and targets, random-init weights)",
-                "config": {"model": "mlp " + "-".join(map(str, WIDTHS)), "params": sum(p.numel() for p in model.parameters()),
+                "config": {"model": "mlp " + "-".join(map(str, widths)), "params": sum(p.numel() for p in model.parameters()),
                            "micro_batch_per_gpu": args.batch, "optimizer": "SGD lr 0.01", "bucket_cap_mb": 25, "hook": note,
                            "l2": "a step touches more than 126 MB; no explicit flush"},
                 "e2e": {"h2d_bytes_per_step": int(xs[0].numel() + ys[0].numel()) * xs.element_size(), "d2h_bytes_per_step": 4},
-                "peak_memory_mib": torch.cuda.max_memory_allocated() / 2**20,
+                "peak_memory_mib": peak_mib,
                 "gpu_launches": hook.gpu_launches() if hook is not None else 0, "final_loss": last}
         print(json.dumps(line), flush=True)
         os.makedirs(os.path.dirname(os.path.join(ROOT, args.out)), exist_ok=True)
