@@ -91,3 +91,31 @@ def test_benchmark_and_example_scripts_load_and_describe_their_workload():
     assert callable(_load("benchmarks/micro_suite.py", "micro_suite_script").main)
     example = _load("examples/cpu_gloo_mlp.py", "cpu_gloo_mlp_example")
     assert example.MODES == ("plain", "wire_codec", "fallback_codec") and callable(example.worker)
+
+
+@pytest.mark.timeout(600)
+def test_benchmark_scripts_dry_run_on_two_cpu_ranks(tmp_path):
+    """`--cpu` runs the same calls on gloo ranks: the scripts' use of the public API stays checked without a GPU."""
+
+    import json
+    import socket
+    import subprocess
+
+    def torchrun(script, *flags):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+               "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, script), "--cpu", *flags]
+        done = subprocess.run(cmd, capture_output=True, text=True, timeout=500, cwd=ROOT)
+        assert done.returncode == 0, done.stderr[-2000:]
+        return [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
+
+    out = tmp_path / "micro.json"
+    rows = torchrun("benchmarks/micro_suite.py", "--sizes-mib", "0.25", "--iters", "1", "--warmup", "1", "--out", str(out))
+    assert {r["case"] for r in rows} == {"reduced_shard", "async_vs_sync", "dynamic_gather", "p2p"}
+    assert all(r["rel_l2"] < 0.01 for r in rows if "rel_l2" in r)
+    assert [r["case"] for r in json.loads(out.read_text())] == [r["case"] for r in rows]
+    out = tmp_path / "mlp.json"
+    (line,) = torchrun("benchmarks/mlp_ddp.py", "--steps", "2", "--warmup", "1", "--out", str(out))
+    assert line["unit"] == "samples/s" and line["n_gpus"] == 2 and line["value"] > 0 and line["impl"] == "ours"
