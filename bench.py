@@ -13,13 +13,22 @@ Configuration (fixed by the benchmark definition): 12 layers, d_model 768,
 token ids, micro-batch 8 per GPU, AdamW lr 6e-4, bf16 parameters and gradients,
 25 MB DDP buckets.  Weak scaling: per-GPU work is fixed.
 
-Two timed regions of K steps each follow W warm-up steps; both are bracketed by a
-barrier and a device synchronise and timed with CUDA events, max over ranks:
+After the W warm-up steps an untimed settle phase runs until three consecutive steps
+agree within 2 % and at least 3 s have passed (a GPU of a fresh lease idles at a few
+hundred MHz and needs seconds, not steps, to reach its working clocks); its length is
+reported as `settle_steps`.  Then two kinds of region, K steps each, are timed
+alternately three times (value, e2e, value, e2e, value, e2e); every region is bracketed
+by a barrier and a device synchronise and timed with CUDA events, max over ranks, and
+the reported numbers are the medians of the three samples (all samples are printed):
   value : inputs already on the device, no host read-back inside the loop
   e2e   : every step copies its token batch from pinned host memory and reads the
           loss back to the host
 A training step touches far more than the 126 MB L2 (248 MB of parameters alone),
 so no explicit L2 flush is needed between steps.
+
+All three arms train the same model classes (`baseline/plain_models.py`, stock torch
+modules that import nothing from either library), so the arms differ in the gradient
+hook only.
 """
 
 from __future__ import annotations
@@ -47,14 +56,14 @@ class ClockSampler:
     def __init__(self, gpu_index: int) -> None:
         self.gpu_index = gpu_index
         self.proc = None
-        self.path = os.path.join(ROOT, "gpurun_out", f"clocks_{os.getpid()}.csv")
+        self.path = os.path.join(ROOT, "bench_out", f"clocks_{os.getpid()}.csv")
 
     def start(self) -> None:
         try:
             os.makedirs(os.path.dirname(self.path), exist_ok=True)
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={CLOCK_QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=self.out, stderr=subprocess.DEVNULL)
+                                          "-lms", "100"], stdout=self.out, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
@@ -107,28 +116,27 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--ef-mode", choices=("reference", "local"), default="reference")
     ap.add_argument("--ref-strategy", default="all_gather")
     ap.add_argument("--bucket-mb", type=int, default=None)
+    ap.add_argument("--repeats", type=int, default=3, help="timed samples of each region (the median is reported)")
+    ap.add_argument("--settle-s", type=float, default=3.0,
+                    help="minimum length of the untimed settle phase after the warm-up (0 = none)")
     ap.add_argument("--hook-max-blocks", type=int, default=0,
                     help="grid cap of the hook's kernels (0 = library default: the full persistent grid)")
     return ap.parse_args()
 
 
-def build_model(name: str, impl: str):
-    import torch
+def build_model(name: str):
+    """(model, vocabulary, sequence length): the same stock-torch classes for every arm."""
 
-    if impl == "reference" and name.startswith("gpt2"):
-        sys.path.insert(0, os.path.join(ROOT, "baseline"))
-        from plain_models import PlainGPT2
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    from plain_models import PlainGPT2, PlainLlama
 
-        if name == "gpt2-tiny":
-            return PlainGPT2(2, 2, 64, 257, 32), 257, 32
+    if name == "gpt2-tiny":
+        return PlainGPT2(2, 2, 64, 257, 32), 257, 32
+    if name == "gpt2-small":
         return PlainGPT2(), 50257, 1024
-    from lowbit_comm_b200.models import GPT2, GPT2Config, Llama, LlamaConfig
-
-    cfg = {"gpt2-small": GPT2Config(), "gpt2-tiny": GPT2Config.tiny(), "llama-3b": LlamaConfig(),
-           "llama-tiny": LlamaConfig.tiny()}[name]
-    model = GPT2(cfg) if name.startswith("gpt2") else Llama(cfg)
-    del torch
-    return model, cfg.vocab_size, cfg.seq_len
+    if name == "llama-tiny":
+        return PlainLlama(2, 64, 4, 2, 128, 257, 32), 257, 32
+    return PlainLlama(), 128256, 2048
 
 
 def main() -> None:
@@ -163,7 +171,7 @@ def main() -> None:
     bucket_mb = args.bucket_mb or (50 if args.model == "llama-3b" else 25)
 
     torch.manual_seed(1234)
-    model, vocab, seq = build_model(args.model, args.impl)
+    model, vocab, seq = build_model(args.model)
     model = model.to(device=device, dtype=torch.bfloat16)
     n_params = sum(p.numel() for p in model.parameters())
     ddp = DDP(model, device_ids=[local_rank], bucket_cap_mb=bucket_mb, gradient_as_bucket_view=True)
@@ -195,9 +203,10 @@ def main() -> None:
             return
 
     opt = torch.optim.AdamW(ddp.parameters(), lr=6e-4, fused=True)
-    total_steps = args.warmup + 2 * args.steps
+    repeats = max(1, args.repeats)
     gen = torch.Generator().manual_seed(99 + rank)
-    host_tokens = torch.randint(0, vocab, (total_steps, batch, seq + 1), generator=gen, dtype=torch.int64).pin_memory()
+    pool = args.warmup + 2 * args.steps            # distinct batches; regions draw from the pool in turn
+    host_tokens = torch.randint(0, vocab, (pool, batch, seq + 1), generator=gen, dtype=torch.int64).pin_memory()
 
     def train_step(tok: "torch.Tensor"):
         loss = ddp(tok[:, :-1], tok[:, 1:])
@@ -209,6 +218,25 @@ def main() -> None:
     last = None
     for i in range(args.warmup):  # warm-up, end-to-end style
         last = train_step(host_tokens[i].to(device, non_blocking=True)).item()
+
+    # settle: untimed for the result, timed only to decide when the clocks and the caches have settled
+    settle_steps, settle_s = 0, 0.0
+    if args.settle_s > 0:
+        recent: list[float] = []
+        t_start = time.perf_counter()
+        while settle_steps < 2000:
+            t0 = time.perf_counter()
+            last = train_step(host_tokens[settle_steps % pool].to(device, non_blocking=True)).item()
+            recent = (recent + [time.perf_counter() - t0])[-3:]
+            settle_steps += 1
+            elapsed = time.perf_counter() - t_start
+            steady = len(recent) == 3 and max(recent) <= 1.02 * min(recent)
+            flag = torch.tensor([1.0 if (steady and elapsed >= args.settle_s) or elapsed >= 10 * args.settle_s else 0.0],
+                                device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)      # every rank leaves in the same step
+            if flag.item() > 0:
+                break
+        settle_s = time.perf_counter() - t_start
 
     def timed(fn) -> float:
         dist.barrier()
@@ -228,27 +256,28 @@ def main() -> None:
         sampler.start()
         time.sleep(0.3)
 
-    # region 1: device-resident inputs, no host read-back
     staged = [host_tokens[args.warmup + i].to(device) for i in range(args.steps)]
-    launches_before = hook.gpu_launches() if hook is not None else 0
+    losses: list[float] = []
 
-    def device_region():
+    def device_region():     # device-resident inputs, no host read-back
         for tok in staged:
             train_step(tok)
 
-    device_ms = timed(device_region)
-    launches = (hook.gpu_launches() - launches_before) if hook is not None else 0
-
-    # region 2: end to end through the public API (H2D of the inputs, D2H of the loss, every step)
-    losses = []
-
-    def e2e_region():
+    def e2e_region():        # through the public API: H2D of the inputs and D2H of the loss, every step
         for i in range(args.steps):
             tok = host_tokens[args.warmup + args.steps + i].to(device, non_blocking=True)
             losses.append(train_step(tok).item())
 
-    e2e_ms = timed(e2e_region)
+    device_samples, e2e_samples, launches = [], [], 0
+    for _ in range(repeats):
+        launches_before = hook.gpu_launches() if hook is not None else 0
+        device_samples.append(timed(device_region))
+        launches = (hook.gpu_launches() - launches_before) if hook is not None else 0
+        e2e_samples.append(timed(e2e_region))
     clocks = sampler.stop() if rank == 0 else None
+    device_ms, e2e_ms = statistics.median(device_samples), statistics.median(e2e_samples)
+    if hook is not None and hasattr(hook, "check_status"):
+        hook.check_status()
 
     tokens_per_step = batch * seq * world
     value = tokens_per_step * args.steps / (device_ms * 1e-3)
@@ -263,6 +292,7 @@ def main() -> None:
             "config": {"model": args.model, "params": n_params, "global_batch": batch * world,
                        "micro_batch_per_gpu": batch, "seq_len": seq, "parallelism": f"dp{world}",
                        "optimizer": "AdamW lr 6e-4 (fused)", "bucket_cap_mb": bucket_mb,
+                       "model_class": type(model).__name__ + " (baseline/plain_models.py)",
                        "hook": (f"lowbit_comm_b200 int8 g64 EF({args.ef_mode}) strategy={args.strategy} "
                                 f"effective={getattr(hook, '_ccdl_effective_strategy', None)}") if args.impl == "ours"
                        else (ref_note or "none (NCCL bf16 all-reduce)"),
@@ -270,6 +300,10 @@ def main() -> None:
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": batch * (seq + 1) * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
+            "timing": {"settle_steps": settle_steps, "settle_s": round(settle_s, 2), "repeats": repeats,
+                       "value_ms_per_step_samples": [round(m / args.steps, 4) for m in device_samples],
+                       "e2e_ms_per_step_samples": [round(m / args.steps, 4) for m in e2e_samples],
+                       "reported": "median of the samples; regions alternate value, e2e"},
             "clocks": clocks,
             "final_loss": losses[-1] if losses else last,
         }

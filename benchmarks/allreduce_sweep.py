@@ -5,13 +5,15 @@
 
 One bf16 gradient tensor per size (x2 steps), values N(0, 1e-3) with 0.1 %
 outliers x100, int8 group-64 payload with error feedback.  Arms: this library
-(one-stage and two-stage fused paths), NCCL bf16 all-reduce, and optionally the
-unmodified reference's `compressed_all_reduce` (strategy all_gather) from
-baseline/_ref.  Every sample is timed on the device with CUDA events after an
-L2 flush and a barrier; the reported time is the max over ranks of each rank's
-median.  algBW = tensor bytes / time.  The roofline of a fused path is the
-slower of its HBM traffic at the measured copy bandwidth and its NVLink traffic
-at the measured 770 GB/s per direction.
+(the default choice, and the one-stage and two-stage paths forced), NCCL bf16
+all-reduce, and optionally the unmodified reference from baseline/_ref: its
+`compressed_all_reduce` with strategy all_gather and with strategy topology (its
+compiled pipelined ring) and its `compressed_reduce_scatter_shard`.  Every sample
+is timed on the device with CUDA events after an L2 flush and a barrier; the
+reported time is the max over ranks of each rank's median.  algBW = tensor bytes /
+time.  The roofline of a fused path (`lowbit_comm_b200.utils.roofline`) is the
+slower of its HBM traffic at the measured copy bandwidth and its NVLink traffic at
+770 GB/s per direction (the measured peer-copy rate of this pool; 900 nominal).
 """
 
 from __future__ import annotations
@@ -25,34 +27,6 @@ import sys
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
-LINK_GBS = 770.0
-
-
-def hbm_peak() -> tuple[float, str]:
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        return float(json.load(open(path))["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
-
-
-def roofline_us(nbytes: int, world: int, stages: int, error_feedback: bool, hbm_gbs: float) -> dict:
-    c = 66.0 / 128.0
-    payload = c * nbytes
-    ef = 2 if error_feedback else 0  # extra tensor-sized reads+writes per kernel that touches the residual
-    if stages == 2:
-        hbm = (1 + ef) * nbytes + payload          # K1: read grad (+residual, +prepared), payload lands in HBM
-        hbm += 2 * payload                         # K2: read W slots of the shard, requantized shard lands in HBM
-        hbm += payload + (1 + ef) * nbytes         # K3: read payload (+prepared), write result (+residual)
-        link = 2 * payload * (world - 1) / world
-    else:
-        hbm = (1 + ef) * nbytes + world * payload  # K1: as above, W payloads land in HBM
-        hbm += world * payload + (1 + ef) * nbytes  # reduce: read W payloads (+prepared), write result (+residual)
-        link = payload * (world - 1)
-    t_hbm = hbm / (hbm_gbs * 1e9) * 1e6
-    t_link = link / (LINK_GBS * 1e9) * 1e6
-    return {"t_hbm_us": t_hbm, "t_link_us": t_link, "roofline_us": max(t_hbm, t_link)}
-
-
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--min-mib", type=float, default=1)
@@ -60,6 +34,15 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--with-reference", action="store_true")
+    ap.add_argument("--ref-arms", default="all_gather,topology,shard",
+                    help="reference paths to time: all_gather, topology (compiled ring), shard (reduce-scatter shard)")
+    ap.add_argument("--ref-max-mib", type=float, default=1024)
+    ap.add_argument("--engine", choices=("pipe", "legacy"), default="pipe",
+                    help="pipe: one persistent kernel per all-reduce; legacy: the K1/K2/K3 kernel sequence")
+    ap.add_argument("--arms", default="auto,1,2", help="paths of this library to time: auto, 1 (one stage), 2 (two stages)")
+    ap.add_argument("--chunk-rows", type=int, default=None, help="pipelined engine: rows of one chunk over all shards")
+    ap.add_argument("--ring", type=int, default=None, help="pipelined engine: rows in flight per block (2..4)")
+    ap.add_argument("--no-ef", action="store_true", help="time the collectives without error feedback")
     ap.add_argument("--chunk-mib", type=float, default=None, help="pipeline chunk size (0 = no pipelining)")
     ap.add_argument("--variants", action="store_true", help="time every push/reduce kernel variant")
     ap.add_argument("--phases", action="store_true", help="also time K1/K2/K3 separately (Python launch path)")
@@ -73,7 +56,7 @@ def main() -> None:
                     help="record which CUDA kernels one (untimed) call launches, from torch.profiler")
     ap.add_argument("--multicast", action="store_true",
                     help="arenas from the symmetric-memory allocator: broadcasts use multimem stores")
-    ap.add_argument("--out", default="gpurun_out/allreduce_sweep.json")
+    ap.add_argument("--out", default="bench_out/allreduce_sweep.json")
     args = ap.parse_args()
 
     import torch
@@ -90,10 +73,12 @@ def main() -> None:
 
     from lowbit_comm_b200 import CompressionConfig
     from lowbit_comm_b200.parallel.communicator import Communicator
+    from lowbit_comm_b200.utils.roofline import MEASURED_LINK_GBS, fused_all_reduce_roofline, measured_hbm_gbs
     from lowbit_comm_b200.utils.timing import L2Flusher
 
     cfg = CompressionConfig()
-    hbm_gbs, peak_kind = hbm_peak()
+    hbm_gbs, peak_kind = measured_hbm_gbs(ROOT)
+    os.environ["LBC_ENGINE"] = args.engine
     flush = L2Flusher(dev)
     max_numel = int(args.max_mib * 1024 * 1024 // 2)
     from lowbit_comm_b200.parallel.fused import FusedWorkspace
@@ -113,6 +98,10 @@ def main() -> None:
         _req().set_gather_prefetch(args.gather_prefetch)
     if args.gather is not None:
         big.set_gather_mode(args.gather)
+    if args.engine == "pipe" and args.chunk_rows is not None:
+        big._pipe.set_chunk_rows(args.chunk_rows)
+    if args.engine == "pipe" and args.ring is not None:
+        big._pipe.set_ring_depth(args.ring)
     if args.chunk_mib is not None:
         big.set_chunking(int(max(args.chunk_mib, 1e-3) * (1 << 20)), 1 if args.chunk_mib == 0 else 8)
 
@@ -124,9 +113,10 @@ def main() -> None:
 
             reference_env.activate(need_cuda_extension=True)
             from ccdl_comm.collectives import compressed_all_reduce as ref_all_reduce
+            from ccdl_comm.collectives import compressed_reduce_scatter_shard as ref_shard
             from ccdl_comm.config import CompressionConfig as RefConfig
 
-            ref = (ref_all_reduce, RefConfig(bit=8, group_size=64, topk=0))
+            ref = (ref_all_reduce, ref_shard, RefConfig(bit=8, group_size=64, topk=0))
         except Exception as exc:  # noqa: BLE001
             if rank == 0:
                 print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}))
@@ -151,7 +141,8 @@ def main() -> None:
 
     multicast_on = bool(comm.peer_group is not None and comm.peer_group.multicast_ptr)
     if rank == 0:
-        print(json.dumps({"multicast_arena": multicast_on}), flush=True)
+        print(json.dumps({"multicast_arena": multicast_on, "engine": args.engine, "link_gbs": MEASURED_LINK_GBS,
+                          "hbm_gbs": hbm_gbs, "peak_kind": peak_kind}), flush=True)
     rows = []
     mib = args.min_mib
     while mib <= args.max_mib:
@@ -164,13 +155,14 @@ def main() -> None:
         dist.all_reduce(exact)
         exact /= world
         nbytes = n * 2
-        residual = torch.zeros_like(x)
+        residual = None if args.no_ef else torch.zeros_like(x)
         work = x.clone()
 
         def ours(stages):
+            strategy = {0: "auto", 1: "all_gather", 2: "reduce_scatter"}[stages]
+
             def run():
-                comm.all_reduce(x, out=work, config=cfg, op="mean",
-                                strategy="all_gather" if stages == 1 else "reduce_scatter", residual=residual)
+                comm.all_reduce(x, out=work, config=cfg, op="mean", strategy=strategy, residual=residual)
             return run
 
         from lowbit_comm_b200.ops.loader import require_extension
@@ -180,21 +172,27 @@ def main() -> None:
         if args.variants:
             combos = [(0, True, 0), (1, True, 0), (2, True, 0), (1, False, 0), (1, False, -1), (1, True, -1),
                       (1, True, 592)]
-        for stages, (push_variant, reduce_bulk, k2_blocks) in [(s, c) for s in ((1, 2) if world > 1 else (1,))
-                                                               for c in combos]:
+        from lowbit_comm_b200.parallel.fused import default_stages
+
+        arms = [{"auto": 0, "1": 1, "2": 2}[a] for a in args.arms.split(",") if a]
+        for stages, (push_variant, reduce_bulk, k2_blocks) in [(s, c) for s in arms for c in combos]:
             if stages == 1 and (not reduce_bulk or k2_blocks):
                 continue
             ext.set_push_variant(push_variant, reduce_bulk, k2_blocks)
-            residual.zero_()
+            if residual is not None:
+                residual.zero_()
             t = measure(ours(stages))
             comm.check_status()
-            residual.zero_()
+            if residual is not None:
+                residual.zero_()
             ours(stages)()
             torch.cuda.synchronize()
             rel = ((work.float() - exact).norm() / exact.norm()).item()
-            roof = roofline_us(nbytes, world, stages, True, hbm_gbs)
+            ran = stages or default_stages(world, nbytes)
+            roof = fused_all_reduce_roofline(nbytes, world, stages=ran, error_feedback=residual is not None,
+                                             hbm_gbs=hbm_gbs)
             phases = None
-            if args.phases:
+            if args.phases and args.engine == "legacy":
                 from lowbit_comm_b200.utils.tracing import PhaseTimer
 
                 ws = comm.workspace(x, cfg, "bf16")
@@ -211,7 +209,9 @@ def main() -> None:
 
                 launched = kernel_names(ours(stages))
             tag = f"_p{push_variant}r{int(reduce_bulk)}b{k2_blocks}" if args.variants else ""
-            rows.append({"impl": f"ours_{stages}stage{tag}", "mib": mib, "world": world, "ms": t,
+            rows.append({"impl": ("ours_auto" if stages == 0 else f"ours_{stages}stage") + tag, "stages_run": ran,
+                         "engine": args.engine, "error_feedback": residual is not None,
+                         "mib": mib, "world": world, "ms": t,
                          "algbw_gbs": nbytes / (t * 1e-3) / 1e9, "rel_l2": rel, **roof,
                          "roofline_frac": roof["roofline_us"] / (t * 1e3), "peak_kind": peak_kind,
                          "phases_ms": phases, "multicast": multicast_on, "chunk_mib": args.chunk_mib,
@@ -226,24 +226,28 @@ def main() -> None:
         t = measure(nccl)
         rows.append({"impl": "nccl_bf16", "mib": mib, "world": world, "ms": t,
                      "algbw_gbs": nbytes / (t * 1e-3) / 1e9})
-        if ref is not None and mib <= 256:
-            ref_fn, ref_cfg = ref
-
-            def reference():
-                return ref_fn(x, config=ref_cfg, op="mean", strategy="all_gather")
-
-            try:
-                t = measure(reference)
-                out = reference()
-                torch.cuda.synchronize()
-                rel = ((out.float() - exact).norm() / exact.norm()).item()
-                rows.append({"impl": "reference_all_gather", "mib": mib, "world": world, "ms": t,
-                             "algbw_gbs": nbytes / (t * 1e-3) / 1e9, "rel_l2": rel})
-            except Exception as exc:  # noqa: BLE001
-                rows.append({"impl": "reference_all_gather", "mib": mib, "world": world,
-                             "error": f"{type(exc).__name__}: {exc}"[:200]})
+        if ref is not None and mib <= args.ref_max_mib:
+            ref_all, ref_shard_fn, ref_cfg = ref
+            ref_calls = {
+                "all_gather": lambda: ref_all(x, config=ref_cfg, op="mean", strategy="all_gather"),
+                "topology": lambda: ref_all(x, config=ref_cfg, op="mean", strategy="topology"),
+                "shard": lambda: ref_shard_fn(x, config=ref_cfg, op="mean"),
+            }
+            for arm in [a for a in args.ref_arms.split(",") if a in ref_calls]:
+                name = {"all_gather": "reference_all_gather", "topology": "reference_topology_ring",
+                        "shard": "reference_reduce_scatter_shard"}[arm]
+                try:
+                    t = measure(ref_calls[arm])
+                    out = ref_calls[arm]()
+                    torch.cuda.synchronize()
+                    row = {"impl": name, "mib": mib, "world": world, "ms": t, "algbw_gbs": nbytes / (t * 1e-3) / 1e9}
+                    if arm != "shard":
+                        row["rel_l2"] = ((out.float() - exact).norm() / exact.norm()).item()
+                    rows.append(row)
+                except Exception as exc:  # noqa: BLE001
+                    rows.append({"impl": name, "mib": mib, "world": world, "error": f"{type(exc).__name__}: {exc}"[:200]})
         if rank == 0:
-            for r in rows[-12:]:
+            for r in rows[-16:]:
                 if r["mib"] == mib:
                     print(json.dumps(r), flush=True)
         del x, work, residual, nccl_buf, exact, mask

@@ -1,9 +1,14 @@
 """Single-GPU microbenchmark of the codec and fused kernels (HBM roofline check).
 
-Usage: python benchmarks/kernel_bench.py [--mib 64 256] [--worlds 1 2 8] [--profile] [--out FILE]
+Usage: python benchmarks/kernel_bench.py [--mib 64 256] [--worlds 1 2 8] [--with-reference] [--profile] [--out FILE]
 Every kernel is timed with CUDA events after warm-up with an L2 flush between
 iterations; bandwidth = algorithmic bytes / median time, reported as a fraction
 of the measured copy bandwidth in MEASURED_PEAKS.json (fallback 6650 GB/s).
+`--with-reference` also times the unmodified reference's own kernels (its extension
+built for sm_100 under baseline/_ref, loaded into the same process) on the same
+tensors: `inplace_quantize_pack`, `inplace_dequantize_reduce_mean` and
+`inplace_dequantize_reduce_mean_update_error_feedback`
+(ccdl_comm/quantization/codec.py:161-217, 355-466).
 """
 
 from __future__ import annotations
@@ -37,8 +42,22 @@ def main() -> None:
     ap.add_argument("--worlds", type=int, nargs="*", default=[1, 2, 8])
     ap.add_argument("--profile", action="store_true", help="one warm-up + one timed launch per kernel (for ncu)")
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--out", default="gpurun_out/kernel_bench.json")
+    ap.add_argument("--with-reference", action="store_true")
+    ap.add_argument("--out", default="bench_out/kernel_bench.json")
     args = ap.parse_args()
+    ref = None
+    if args.with_reference:
+        try:
+            sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline"))
+            import reference_env
+
+            _, ref_status = reference_env.activate(need_cuda_extension=True)
+            from ccdl_comm.config import CompressionConfig as RefConfig
+            from ccdl_comm.quantization import codec as ref_codec
+
+            ref = (ref_codec, RefConfig(bit=8, group_size=64, topk=0), ref_status)
+        except Exception as exc:  # noqa: BLE001
+            print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}), flush=True)
     cfg = CompressionConfig()
     peak, peak_kind = peak_gbs()
     flush = None if args.profile else L2Flusher()
@@ -79,6 +98,37 @@ def main() -> None:
         z = torch.empty_like(x)
         t = time_cuda(lambda: z.copy_(x), iters=args.iters, flush=flush, warmup=warm)
         record("torch copy_ (reference point)", mib, 4 * n, t)
+        if ref is not None:
+            rc, rcfg, rstatus = ref
+            rout = rc.allocate_quantized_buffer(x, rcfg) if hasattr(rc, "allocate_quantized_buffer") else out.clone()
+            rout = rout.reshape(-1) if rout.numel() == pb else torch.empty(pb, dtype=torch.uint8, device="cuda")
+            try:
+                ok = rc.inplace_quantize_pack(x, rout, None, rcfg, extension_status=rstatus)
+                t = time_cuda(lambda: rc.inplace_quantize_pack(x, rout, None, rcfg, extension_status=rstatus),
+                              iters=args.iters, flush=flush, warmup=warm)
+                record("reference inplace_quantize_pack", mib, 2 * n + pb, t, fused=bool(ok))
+                t = time_cuda(lambda: rc.inplace_quantize_pack(x, rout, res, rcfg, extension_status=rstatus),
+                              iters=args.iters, flush=flush, warmup=warm)
+                record("reference inplace_quantize_pack(+residual)", mib, 4 * n + pb, t)
+                rbufs = [rout] + [rout.clone() for _ in range(7)]
+                t = time_cuda(lambda: rc.inplace_dequantize_reduce_mean(rbufs[:1], y, rcfg, extension_status=rstatus,
+                                                                        reduce="mean"),
+                              iters=args.iters, flush=flush, warmup=warm)
+                record("reference inplace_dequantize_reduce_mean(1 payload)", mib, 2 * n + pb, t)
+                t = time_cuda(lambda: rc.inplace_dequantize_reduce_mean(rbufs, y, rcfg, extension_status=rstatus,
+                                                                        reduce="mean"),
+                              iters=args.iters, flush=flush, warmup=warm)
+                record("reference inplace_dequantize_reduce_mean(8 payloads)", mib, 2 * n + 8 * pb, t)
+                prep, restored = x.clone(), torch.empty_like(x)
+                t = time_cuda(lambda: rc.inplace_dequantize_reduce_mean_update_error_feedback(
+                    rbufs[:1], prep, restored, res, rcfg, extension_status=rstatus, reduce="mean"),
+                    iters=args.iters, flush=flush, warmup=warm)
+                record("reference inplace_dequantize_reduce_mean_update_error_feedback(1 payload)", mib,
+                       6 * n + pb, t)
+                del rbufs, prep, restored
+            except Exception as exc:  # noqa: BLE001
+                print(json.dumps({"impl": "reference", "mib": mib, "error": f"{type(exc).__name__}: {exc}"[:300]}),
+                      flush=True)
         del bufs
         for world in args.worlds:
             need = FusedWorkspace.required_bytes(world, "bf16", cfg, n, world <= 2) + (1 << 20)

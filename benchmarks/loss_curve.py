@@ -47,7 +47,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--lr", type=float, default=6e-4)
     ap.add_argument("--with-reference", action="store_true")
-    ap.add_argument("--out", default="gpurun_out/loss_curve.json")
+    ap.add_argument("--out", default="bench_out/loss_curve.json")
     args = ap.parse_args()
 
     import torch

@@ -1,7 +1,7 @@
 """The smaller latency figures the reference publishes, measured here through the public API on N GPUs.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-        benchmarks/micro_suite.py [--sizes-mib 1 16 64] [--iters 10] [--out gpurun_out/micro_suite.json]
+        benchmarks/micro_suite.py [--sizes-mib 1 16 64] [--iters 10] [--out bench_out/micro_suite.json]
 
 Cases (each row names the call that is timed):
   reduced_shard      compressed_reduce_scatter_shard (ReducedShard output) vs NCCL reduce_scatter_tensor and vs NCCL's
@@ -33,7 +33,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--cases", nargs="+", default=["reduced_shard", "async_vs_sync", "dynamic_gather", "p2p"])
-    ap.add_argument("--out", default="gpurun_out/micro_suite.json")
+    ap.add_argument("--out", default="bench_out/micro_suite.json")
     ap.add_argument("--cpu", action="store_true",
                     help="dry run on CPU ranks (gloo, host timer, no L2 flush): checks the script, measures nothing useful")
     args = ap.parse_args()

@@ -32,7 +32,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--dtype", choices=("fp16", "bf16", "fp32"), default="fp16")
     ap.add_argument("--strategy", default="auto")
-    ap.add_argument("--out", default="gpurun_out/mlp_ddp.json")
+    ap.add_argument("--out", default="bench_out/mlp_ddp.json")
     ap.add_argument("--cpu", action="store_true",
                     help="dry run on CPU ranks (gloo, host timer, narrow model): checks the script, measures nothing useful")
     args = ap.parse_args()

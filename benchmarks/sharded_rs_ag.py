@@ -29,7 +29,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--local-group", type=int, default=4)
-    ap.add_argument("--out", default="gpurun_out/sharded_rs_ag.json")
+    ap.add_argument("--out", default="bench_out/sharded_rs_ag.json")
     args = ap.parse_args()
 
     import torch

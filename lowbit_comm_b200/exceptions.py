@@ -11,6 +11,10 @@ from __future__ import annotations
 from typing import NamedTuple
 
 WAIT_PHASE_NAMES = ("reduce-scatter", "all-gather", "p2p data", "p2p ack")
+# phases of the pipelined all-reduce kernel (ops/csrc/pipe_kernels.cu)
+PIPE_PHASE_NAMES = {8: "pipelined all-reduce: quantize rows", 9: "pipelined all-reduce: peers' quantized rows",
+                    10: "pipelined all-reduce: an owner's reduced rows", 11: "pipelined all-reduce: rendezvous",
+                    12: "pipelined all-reduce: a bulk load never completed"}
 
 
 class DeviceWaitStatus(NamedTuple):
@@ -29,6 +33,8 @@ class DeviceWaitStatus(NamedTuple):
 
     @property
     def phase_name(self) -> str:
+        if self.phase in PIPE_PHASE_NAMES:
+            return PIPE_PHASE_NAMES[self.phase]
         return WAIT_PHASE_NAMES[self.phase] if 0 <= self.phase < len(WAIT_PHASE_NAMES) else f"phase {self.phase}"
 
     def describe(self, rank: int) -> str:

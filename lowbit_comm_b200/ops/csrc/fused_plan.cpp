@@ -343,6 +343,111 @@ class FusedAllReducePlan {
     cudaEvent_t start_ = nullptr;
 };
 
+// ---------------------------------------------------------------------------------------------
+// Pipelined all-reduce: one persistent kernel per collective (pipe_kernels.cu).  The plan resolves
+// the geometry (shards, rows, chunks) from the element count; regions are fixed at construction.
+// ---------------------------------------------------------------------------------------------
+class PipeAllReducePlan {
+  public:
+    PipeAllReducePlan(int dtype, int group_size, int bit, int rank, std::vector<uintptr_t> peer_ptrs, int64_t q_off,
+                      int64_t q_bytes, int64_t ag_off, int64_t ag_bytes, int64_t ctl_off, unsigned long long timeout_ns,
+                      uintptr_t status_device, int max_blocks, int64_t max_numel)
+        : dtype_(dtype), group_(group_size), bit_(bit), rank_(rank), peers_(std::move(peer_ptrs)), q_off_(q_off),
+          q_bytes_(q_bytes), ag_off_(ag_off), ag_bytes_(ag_bytes), ctl_off_(ctl_off), timeout_ns_(timeout_ns),
+          status_(status_device), max_blocks_(max_blocks), max_numel_(max_numel) {
+        world_ = static_cast<int>(peers_.size());
+        if (world_ < 1 || world_ > LBC_MAX_RANKS) throw std::invalid_argument("bad world size");
+        if (rank_ < 0 || rank_ >= world_) throw std::invalid_argument("bad rank");
+        if (LBC_PIPE_ROW_ELEMS % group_ != 0) throw std::invalid_argument("group size must divide the row length");
+        group_bytes_ = group_ * bit_ / 8 + (dtype_ == LBC_FP32 ? 4 : 2);
+    }
+
+    // Rows of one chunk over all shards: below this a chunk is too small to keep the grid busy.
+    void set_chunk_rows(int64_t min_rows, int max_chunks) {
+        min_chunk_rows_ = std::max<int64_t>(min_rows, 1);
+        max_chunks_ = std::max(1, std::min(max_chunks, LBC_PIPE_MAX_CHUNKS));
+    }
+    void set_ring_depth(int depth) { ring_depth_ = depth; }
+    void set_max_blocks(int blocks) { max_blocks_ = blocks; }
+    // Device buffer of [grid][8] 64-bit cycle counters filled by every launch (0 = off): where the blocks'
+    // time goes (waiting for loads, computing, at barriers, claiming and issuing, asleep on flags).
+    void set_profile_buffer(uintptr_t ptr) { profile_ = ptr; }
+
+    // Enqueues the collective on `stream`; returns the number of kernels launched.
+    int all_reduce(uintptr_t x, uintptr_t out, uintptr_t residual, int64_t numel, int stages, double scale,
+                   bool update_residual, bool ef_local, unsigned int epoch, uintptr_t stream_ptr, int phase_mask,
+                   bool gate) {
+        if (numel < 0 || numel > max_numel_) throw std::invalid_argument("numel exceeds the workspace capacity");
+        if (numel == 0) return 0;
+        if (stages != 1 && stages != 2) throw std::invalid_argument("stages must be 1 or 2");
+        cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+        LbcPipe p{};
+        p.dtype = dtype_;
+        p.group_size = group_;
+        p.bit = bit_;
+        p.world = world_;
+        p.rank = rank_;
+        p.stages = stages;
+        p.phase_mask = phase_mask;
+        p.x = reinterpret_cast<const void*>(x);
+        p.out = reinterpret_cast<void*>(out);
+        p.residual = reinterpret_cast<const void*>(residual);
+        const bool want_ref = residual != 0 && update_residual && !ef_local;
+        const bool want_local = residual != 0 && update_residual && ef_local;
+        if (want_ref) {
+            p.prepared_out = reinterpret_cast<void*>(residual);
+            p.prepared = reinterpret_cast<const void*>(residual);
+            p.residual_out = reinterpret_cast<void*>(residual);
+        }
+        if (want_local) p.local_ef_out = reinterpret_cast<void*>(residual);
+        p.numel = numel;
+        p.scale = static_cast<float>(scale);
+        for (int r = 0; r < world_; ++r) p.arena[r] = reinterpret_cast<uint8_t*>(peers_[r]);
+        const int shards = stages == 2 ? world_ : 1;
+        const int64_t groups = ceil_div(numel, group_);
+        p.shard_groups = round_up(ceil_div(groups, shards), kAlignGroups);
+        p.shard_stride = round_up(p.shard_groups * group_bytes_, 256);
+        if (p.shard_stride * shards > q_bytes_ || (stages == 2 && p.shard_groups * group_bytes_ > ag_bytes_))
+            throw std::runtime_error("the pipelined workspace is too small for this tensor");
+        p.q_off = q_off_;
+        p.ag_off = ag_off_;
+        p.ctl_off = ctl_off_;
+        const int64_t row_groups = LBC_PIPE_ROW_ELEMS / group_;
+        const int64_t shard_rows = ceil_div(p.shard_groups, row_groups);
+        int64_t chunks = std::min<int64_t>(max_chunks_, (shard_rows * shards) / min_chunk_rows_);
+        chunks = std::max<int64_t>(1, chunks);
+        p.rows_per_chunk = ceil_div(shard_rows, chunks);
+        p.num_chunks = static_cast<int>(ceil_div(shard_rows, p.rows_per_chunk));
+        p.epoch = epoch;
+        p.timeout_ns = timeout_ns_;
+        p.status = reinterpret_cast<void*>(status_);
+        p.max_blocks = max_blocks_;
+        p.ring_depth = ring_depth_;
+        p.profile = reinterpret_cast<unsigned long long*>(profile_);
+        int launches = 0;
+        if (gate && world_ > 1) {
+            check(lbc_pipe_gate(p.arena, world_, rank_, ctl_off_, epoch, timeout_ns_, p.status, stream), "pipe_gate");
+            ++launches;
+        }
+        check(lbc_pipe_allreduce(&p, stream), "pipe_allreduce");
+        return launches + 1;
+    }
+
+  private:
+    int dtype_, group_, bit_, rank_, world_ = 1;
+    std::vector<uintptr_t> peers_;
+    int64_t q_off_, q_bytes_, ag_off_, ag_bytes_, ctl_off_;
+    unsigned long long timeout_ns_;
+    uintptr_t status_;
+    int max_blocks_;
+    int64_t max_numel_;
+    int64_t group_bytes_ = 66;
+    int64_t min_chunk_rows_ = 4096;
+    int max_chunks_ = LBC_PIPE_MAX_CHUNKS;
+    int ring_depth_ = 0;
+    uintptr_t profile_ = 0;
+};
+
 }  // namespace
 
 void bind_fused_plan(py::module_& m) {
@@ -360,6 +465,35 @@ void bind_fused_plan(py::module_& m) {
         .def("all_reduce", &FusedAllReducePlan::all_reduce, py::arg("x"), py::arg("out"), py::arg("residual"),
              py::arg("numel"), py::arg("stages"), py::arg("scale"), py::arg("update_residual"), py::arg("ef_local"),
              py::arg("epoch"), py::arg("stream"));
+    py::class_<PipeAllReducePlan>(m, "PipeAllReducePlan")
+        .def(py::init<int, int, int, int, std::vector<uintptr_t>, int64_t, int64_t, int64_t, int64_t, int64_t,
+                      unsigned long long, uintptr_t, int, int64_t>(),
+             py::arg("dtype"), py::arg("group_size"), py::arg("bit"), py::arg("rank"), py::arg("peer_ptrs"),
+             py::arg("q_off"), py::arg("q_bytes"), py::arg("ag_off"), py::arg("ag_bytes"), py::arg("ctl_off"),
+             py::arg("timeout_ns"), py::arg("status_device"), py::arg("max_blocks"), py::arg("max_numel"))
+        .def("set_chunk_rows", &PipeAllReducePlan::set_chunk_rows, py::arg("min_rows"),
+             py::arg("max_chunks") = LBC_PIPE_MAX_CHUNKS)
+        .def("set_ring_depth", &PipeAllReducePlan::set_ring_depth, py::arg("depth"))
+        .def("set_max_blocks", &PipeAllReducePlan::set_max_blocks, py::arg("blocks"))
+        .def("set_profile_buffer", &PipeAllReducePlan::set_profile_buffer, py::arg("ptr"))
+        .def("all_reduce", &PipeAllReducePlan::all_reduce, py::arg("x"), py::arg("out"), py::arg("residual"),
+             py::arg("numel"), py::arg("stages"), py::arg("scale"), py::arg("update_residual"), py::arg("ef_local"),
+             py::arg("epoch"), py::arg("stream"), py::arg("phase_mask") = static_cast<int>(LBC_PIPE_ALL),
+             py::arg("gate") = false);
+    // free-function form, so that callers that record and replay launches can treat it like the other launchers
+    m.def("pipe_all_reduce",
+          [](PipeAllReducePlan& plan, uintptr_t x, uintptr_t out, uintptr_t residual, int64_t numel, int stages,
+             double scale, bool update_residual, bool ef_local, unsigned int epoch, uintptr_t stream, int phase_mask,
+             bool gate) {
+              return plan.all_reduce(x, out, residual, numel, stages, scale, update_residual, ef_local, epoch, stream,
+                                     phase_mask, gate);
+          });
+    m.attr("PIPE_QUANT") = static_cast<int>(LBC_PIPE_QUANT);
+    m.attr("PIPE_REDUCE") = static_cast<int>(LBC_PIPE_REDUCE);
+    m.attr("PIPE_DECODE") = static_cast<int>(LBC_PIPE_DECODE);
+    m.attr("PIPE_ALL") = static_cast<int>(LBC_PIPE_ALL);
+    m.attr("PIPE_CTL_BYTES") = static_cast<int>(LBC_PIPE_CTL_BYTES);
+    m.attr("PIPE_CTL_LOCAL") = static_cast<int>(LBC_PIPE_CTL_LOCAL);
 }
 
 }  // namespace lbc

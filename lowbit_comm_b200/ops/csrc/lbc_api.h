@@ -96,6 +96,67 @@ typedef struct {
 cudaError_t lbc_quant_push(const LbcQuantPush* p, cudaStream_t stream);
 cudaError_t lbc_reduce(const LbcReduce* p, cudaStream_t stream);
 
+// ---- pipelined all-reduce: one persistent kernel, every NVLink byte moved by bulk loads ----------
+// Every rank quantizes its tensor into its OWN arena (phase QUANT), the owner of a shard pulls that
+// shard's rows from all ranks with bulk asynchronous loads, reduces and requantizes them into its own
+// arena (phase REDUCE), and every rank pulls the reduced shards and decodes them (phase DECODE).  Rows of
+// 4096 elements are the unit of work; a tensor is cut into up to LBC_PIPE_MAX_CHUNKS chunks and a
+// chunk's rows become visible to the other ranks through one epoch flag per (rank, chunk), so the three
+// phases of different chunks overlap inside one launch.  With stages == 1 there is one "shard" (the
+// whole tensor), every rank reduces all W payloads and writes the result directly (no DECODE phase).
+// The reference moves the same bytes with NCCL calls between kernels (ccdl_comm/cuda/transports/
+// pipelined_ring.py:236-316); it has no counterpart of this kernel.
+#define LBC_PIPE_MAX_CHUNKS 16
+#define LBC_PIPE_ROW_ELEMS 4096
+enum LbcPipePhase { LBC_PIPE_QUANT = 1, LBC_PIPE_REDUCE = 2, LBC_PIPE_DECODE = 4, LBC_PIPE_ALL = 7 };
+// Control block of one workspace (same offset in every arena; zero when the arena is created):
+#define LBC_PIPE_CTL_FLAGS_QUANT 0      // u32 [LBC_MAX_RANKS][LBC_PIPE_MAX_CHUNKS], written by the peers
+#define LBC_PIPE_CTL_FLAGS_REDUCE 1024  // u32 [LBC_MAX_RANKS][LBC_PIPE_MAX_CHUNKS], written by the peers
+#define LBC_PIPE_CTL_FLAGS_GATE 2048    // u32 [LBC_MAX_RANKS], written by the peers (rendezvous)
+#define LBC_PIPE_CTL_LOCAL 2304         // u32 ticket, exit count, done[2][LBC_PIPE_MAX_CHUNKS]: local scratch
+#define LBC_PIPE_CTL_BYTES 2560
+
+typedef struct {
+    int dtype, group_size, bit;
+    int world, rank;
+    int stages;                 // 2 = reduce-scatter + gather, 1 = every rank reduces all payloads
+    int phase_mask;             // LbcPipePhase bits; LBC_PIPE_ALL in production, single phases for one-GPU emulation
+    const void* x;              // T[numel]
+    void* out;                  // T[numel], may alias x
+    const void* residual;       // optional T[numel]: prepared = T(x + residual)
+    void* prepared_out;         // optional T[numel]: receives `prepared` (may alias residual)
+    void* local_ef_out;         // optional T[numel]: receives T(prepared - dequant(quant(prepared)))
+    const void* prepared;       // optional T[numel]: read by the last phase ...
+    void* residual_out;         // ... which writes T(float(prepared) - result) here (may alias prepared)
+    int64_t numel;
+    float scale;                // applied to the fp32 sum
+    uint8_t* arena[LBC_MAX_RANKS];  // base of every rank's arena (peer mappings)
+    int64_t q_off;              // own quantized payload: `shards` planar payloads, `shard_stride` apart
+    int64_t shard_stride;
+    int64_t ag_off;             // own reduced shard, one planar payload (stages == 2)
+    int64_t ctl_off;            // control block
+    int64_t shard_groups;       // groups per shard, a multiple of 8
+    int num_chunks;             // <= LBC_PIPE_MAX_CHUNKS
+    int64_t rows_per_chunk;     // rows of one shard per chunk
+    unsigned int epoch;
+    unsigned long long timeout_ns;
+    void* status;               // LbcStatus*, device visible
+    int max_blocks;             // 0 = two blocks per SM
+    int ring_depth;             // rows in flight per block, 0 = default (3)
+    int stage_bytes;            // filled in by the launcher
+    unsigned long long* profile;  // optional [gridDim.x][8] cycle counters (see pipe_kernels.cu), NULL = off
+} LbcPipe;
+
+cudaError_t lbc_pipe_allreduce(const LbcPipe* p, cudaStream_t stream);
+// One warp: raises this rank's gate flag on every rank, then waits (bounded) for all ranks' gate flags.
+// Enqueued in front of the pipelined kernel it lines the ranks up, so a rank that is ahead of its peers
+// parks 32 threads instead of a grid of blocks that hold shared memory while they wait.
+cudaError_t lbc_pipe_gate(uint8_t* const* arena, int world, int rank, int64_t ctl_off, unsigned int epoch,
+                          unsigned long long timeout_ns, void* status, cudaStream_t stream);
+// Geometry the host needs to size regions and chunks.
+int lbc_pipe_stage_bytes(int dtype, int group_size, int bit, int world, int stages, int with_residual,
+                         int with_prepared);
+
 // ---- general path: top-k, 4-bit code-books, stochastic rounding --------------
 typedef struct {
     int dtype, group_size, bit, topk, quant_type, stochastic, compact;

@@ -14,6 +14,24 @@ constexpr int kMaxDevices = 64;
 
 static __device__ __align__(256) unsigned char g_payload_scratch[LBC_NO_ALLOC_SCRATCH_BYTES];
 
+// The planar payload of `numel` elements is groups * (G * BIT / 8) code bytes followed by groups * sizeof(T)
+// scale bytes, with no padding in between.  The array must hold it for every profile the entry point serves;
+// a layout change that adds bytes (padding between the two regions, wider scales) has to show up here.
+constexpr long long payload_bytes(long long numel, int group, int bit, int scale_bytes) {
+    return (numel + group - 1) / group * (group * bit / 8 + scale_bytes);
+}
+constexpr bool scratch_holds_every_profile() {
+    for (int group : {16, 32, 64})
+        for (int bit : {4, 8})
+            for (int scale_bytes : {2, 4})
+                if (payload_bytes(LBC_NO_ALLOC_MAX_NUMEL, group, bit, scale_bytes) > LBC_NO_ALLOC_SCRATCH_BYTES)
+                    return false;
+    return true;
+}
+static_assert(scratch_holds_every_profile(), "LBC_NO_ALLOC_SCRATCH_BYTES is too small for a served profile");
+static_assert(payload_bytes(LBC_NO_ALLOC_MAX_NUMEL, 16, 8, 4) == LBC_NO_ALLOC_SCRATCH_BYTES,
+              "the stated worst case (fp32 source, groups of 16, 8 bit) should fill the array exactly");
+
 std::mutex g_setup_mutex;
 unsigned char* g_scratch_address[kMaxDevices] = {};
 thread_local cudaError_t t_last_cuda_error = cudaSuccess;

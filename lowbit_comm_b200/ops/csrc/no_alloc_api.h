@@ -27,6 +27,10 @@
 //    without an ordering between them) race on it.  Serialise them.
 //  * The call allocates nothing: no cudaMalloc/cudaFree, no allocating library
 //    routine.  Inputs and outputs are the caller's.
+//  * Aliasing: residual_in and residual_out may be one buffer, and out may be x.
+//    But x is read through the non-coherent path (ld.global.nc) while
+//    residual_out is being written, so x must not overlap residual_out (nor
+//    residual_in): keep the input and the residual in separate buffers.
 #pragma once
 
 #include <cuda_runtime.h>

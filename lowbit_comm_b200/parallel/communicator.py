@@ -149,6 +149,8 @@ class Communicator:
 
         from .fused import FusedWorkspace
 
+        if self.peer_group is not None:
+            self.peer_group.check_status()       # a kernel of an earlier collective gave up: raise, do not go on
         key = (dtype, config.bit, config.group_size)
         ws = self._workspaces.get(key)
         if ws is not None and ws.max_numel >= tensor.numel():

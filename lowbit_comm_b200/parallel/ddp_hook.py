@@ -30,6 +30,7 @@ from importlib import import_module
 from typing import Any
 
 from ..config import CompressionConfig
+from ..exceptions import CCDLUnavailableError
 from ..ops import codec
 from ..ops.error_feedback import ErrorFeedbackPolicy, ErrorFeedbackState
 from ..ops.loader import CudaExtensionStatus, load_cuda_extension
@@ -284,13 +285,24 @@ class AsyncShardPipeline:
 
 
 class _PeerEngine:
-    """Lazily built peer group + fused workspaces for one hook."""
+    """Lazily built peer group + fused workspaces for one hook.
+
+    Sizing.  DDP hands the hook buckets of very different sizes (the first iteration's buckets differ from
+    the rebuilt ones, and `find_unused_parameters` starts with tiny ones), so nothing is sized from the first
+    bucket alone: a workspace holds the next power of two of the largest bucket seen (or `max_bucket_numel`),
+    the arena is created with room for one doubling, and when a bucket outgrows both, the arena is rebuilt
+    collectively (every rank sees the same bucket sizes in the same order, so every rank takes this branch in
+    the same call).  An arena handed in by the caller is never rebuilt; outgrowing it is an error.
+    """
+
+    MIN_CAP = 1 << 20
 
     def __init__(self, *, config: CompressionConfig, process_group, peer_group, arena_bytes, max_bucket_numel,
                  max_blocks: int, ef_mode: str) -> None:
         self.config = config
         self.process_group = process_group
         self.group = peer_group
+        self._own_group = peer_group is None
         self.arena_bytes = arena_bytes
         self.max_bucket_numel = max_bucket_numel
         self.max_blocks = max_blocks
@@ -298,32 +310,90 @@ class _PeerEngine:
         self.workspaces: dict[str, Any] = {}
         self.stream = None
         self.launch_count = 0
+        self.rebuilds = 0
+        self._retired_launches = 0
 
-    def ensure(self, tensor, dtype: str):
-        import torch
-
-        from .completion import comm_stream
-        from .fused import FusedWorkspace
+    # seams for tests: how a group and a workspace are made
+    def _make_group(self, total: int, device):
         from .peer_memory import PeerGroup
 
-        ws = self.workspaces.get(dtype)
-        if ws is not None and ws.max_numel >= tensor.numel():
-            return ws
-        cap = max(int(self.max_bucket_numel or 0), tensor.numel())
-        cap = 1 << max(20, (cap - 1).bit_length())  # next power of two, at least 1 Mi elements
-        world = _dist_fact("get_world_size", 1) if self.group is None else self.group.world_size
-        if self.group is None:
-            dist = import_module("torch.distributed")
-            pg = self.process_group if self.process_group is not None else dist.group.WORLD
-            world = dist.get_world_size(pg)
-            need = FusedWorkspace.required_bytes(world, dtype, self.config, cap, True)
-            total = int(self.arena_bytes) if self.arena_bytes else 2 * need + (64 << 20)
-            self.group = PeerGroup.create(pg, total, torch.device("cuda", tensor.device.index))
+        dist = import_module("torch.distributed")
+        pg = self.process_group if self.process_group is not None else dist.group.WORLD
+        return PeerGroup.create(pg, total, device)
+
+    def _make_workspace(self, dtype: str, cap: int):
+        from .fused import FusedWorkspace
+
         ws = FusedWorkspace(self.group, dtype=dtype, config=self.config, max_numel=cap, max_blocks=self.max_blocks)
+        ws.gate = ws.group.world_size > 1     # line the ranks up before the persistent kernel takes the SMs
+        return ws
+
+    def _need(self, world: int, dtype: str, cap: int) -> int:
+        from .fused import FusedWorkspace
+
+        return FusedWorkspace.required_bytes(world, dtype, self.config, cap, False, engine="pipe") + (1 << 20)
+
+    def _world(self) -> int:
+        if self.group is not None:
+            return self.group.world_size
+        dist = import_module("torch.distributed")
+        pg = self.process_group if self.process_group is not None else dist.group.WORLD
+        return dist.get_world_size(pg)
+
+    def ensure(self, tensor, dtype: str):
+        ws = self.workspaces.get(dtype)
+        numel = tensor.numel()
+        if ws is not None and ws.max_numel >= numel:
+            return ws
+        cap = max(int(self.max_bucket_numel or 0), numel, self.MIN_CAP)
+        cap = 1 << (cap - 1).bit_length()                 # next power of two
+        world = self._world()
+        need = self._need(world, dtype, cap)
+        device = tensor.device
+        if self.group is None:
+            total = int(self.arena_bytes) if self.arena_bytes else 2 * need
+            self.group = self._make_group(total, device)
+        elif self.group.bytes_free < need:
+            if not self._own_group:
+                raise CCDLUnavailableError(
+                    f"the peer arena handed to the hook has {self.group.bytes_free} bytes free, a bucket of "
+                    f"{numel} elements needs {need}; create it larger or let the hook own its arena")
+            # rebuild: room for every dtype's workspace at its new capacity, and for one doubling of this one
+            others = sum(self._need(world, d, w.max_numel) for d, w in self.workspaces.items() if d != dtype)
+            caps = {d: w.max_numel for d, w in self.workspaces.items() if d != dtype}
+            self._retired_launches += sum(w.launches for w in self.workspaces.values())
+            self.group.close()                            # synchronises the device and meets the peers on the host
+            self.workspaces.clear()
+            self.group = self._make_group(max(int(self.arena_bytes or 0), 2 * need + others), device)
+            self.rebuilds += 1
+            for d, c in caps.items():
+                self.workspaces[d] = self._make_workspace(d, c)
+        ws = self._make_workspace(dtype, cap)
         self.workspaces[dtype] = ws
         if self.stream is None:
-            self.stream = comm_stream(tensor.device)
+            from .completion import comm_stream
+
+            self.stream = comm_stream(device)
         return ws
+
+    def check_status(self) -> None:
+        if self.group is not None:
+            self.group.check_status()
+
+    def reset_after_error(self) -> None:
+        """After `check_status` raised: drain the device, zero the scratch counters, clear the status word."""
+
+        if self.group is None:
+            return
+        self.group.reset_after_error()
+        for ws in self.workspaces.values():
+            reset = getattr(ws, "reset_pipe_control", None)
+            if callable(reset):
+                reset()
+
+    @property
+    def launches(self) -> int:
+        return self._retired_launches + sum(ws.launches for ws in self.workspaces.values())
 
 
 class DDPCommHook:
@@ -492,7 +562,20 @@ class DDPCommHook:
     @property
     def gpu_launches(self) -> int:
         eng = self.peer_engine
-        return sum(ws.launches for ws in eng.workspaces.values()) if eng else 0
+        return eng.launches if eng else 0
+
+    def check_status(self) -> None:
+        """Raises `AsyncCommunicationError` when a kernel of an earlier bucket gave up waiting for a peer (its
+        bucket then kept this rank's local gradient).  Reads pinned host memory, no synchronisation: call it
+        after `optimizer.step()` or wherever a wrong step must not go unnoticed; the hook itself calls it
+        before every bucket."""
+
+        if self.peer_engine is not None:
+            self.peer_engine.check_status()
+
+    def reset_after_error(self) -> None:
+        if self.peer_engine is not None:
+            self.peer_engine.reset_after_error()
 
 
 def create_ddp_comm_hook(
@@ -585,6 +668,7 @@ def create_ddp_comm_hook(
         tensor = bucket.buffer()
         key = _bucket_key(bucket)
         name = _resolve_dtype(dtype, tensor)
+        peer.check_status()                     # an earlier bucket's wait ran out: say so now, not never
         ws = peer.ensure(tensor, name)
         decision = policy.decide(key, numel=tensor.numel())
         residual = feedback.residual_for(key, tensor) if (decision.apply or decision.update) else None
@@ -802,6 +886,8 @@ def create_ddp_comm_hook(
     hook.state_dict = holder.state_dict
     hook.load_state_dict = holder.load_state_dict
     hook.bind_module = holder.bind_module
+    hook.check_status = holder.check_status
+    hook.reset_after_error = holder.reset_after_error
     if module is not None:
         holder.bind_module(module)
     hook.gpu_launches = lambda: holder.gpu_launches

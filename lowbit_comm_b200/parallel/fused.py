@@ -30,6 +30,18 @@ kernel not followed by such a barrier (gather region, RS region used by
 reduce-scatter alone) are double buffered by epoch parity, which the same argument
 makes sufficient.
 
+Engines.  The default engine ("pipe") runs the whole all-reduce as ONE persistent kernel
+(`ops/csrc/pipe_kernels.cu`): every rank quantizes into its own arena, shard owners pull rows from all
+ranks with bulk asynchronous loads, reduce and requantize them, and every rank pulls and decodes the
+reduced rows; per-chunk epoch flags let the three phases of neighbouring chunks overlap inside the
+launch.  Its regions: the own quantized payload (written by this rank, read by the peers' REDUCE
+rows), the own reduced shard (read by the peers' DECODE rows) and a control block of flags and
+counters.  Reuse without extra barriers: a rank's kernel only ends after it has decoded every chunk,
+i.e. after every owner finished reducing (= reading this rank's payload); and a rank requantizes
+chunk c of collective t+1 only after every peer's QUANT flag of t+1, which a peer raises after its
+kernel of collective t (the one that read this rank's reduced shard) has ended.
+The "legacy" engine is the K1/K2/K3 sequence described above; reduce-scatter and all-gather use it.
+
 This replaces the reference's quantize -> NCCL all_to_all / all_gather ->
 dequantize chains (ccdl_comm/communication/reduce_scatter_transport.py:186-377,
 ccdl_comm/collectives/all_reduce.py:158-271).
@@ -126,7 +138,7 @@ class FusedWorkspace:
     """Symmetric regions + channel for tensors of up to `max_numel` elements."""
 
     def __init__(self, group: PeerGroup, *, dtype: str, config: CompressionConfig, max_numel: int,
-                 max_blocks: int = 0, with_gather_region: bool | None = None) -> None:
+                 max_blocks: int = 0, with_gather_region: bool | None = None, engine: str | None = None) -> None:
         if not is_fast_profile(config):
             raise ValueError("fused collectives serve linear / top-k 0 / deterministic profiles")
         self.group = group
@@ -141,13 +153,24 @@ class FusedWorkspace:
         W = group.world_size
         self.shard_stride = _round_up(max(cap.shard_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
         self.rs_bytes = W * self.shard_stride
-        self.rs_off = [group.alloc(self.rs_bytes), group.alloc(self.rs_bytes)]
         self.ag_bytes = _round_up(max(cap.total_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
-        self.ag_off = group.alloc(self.ag_bytes)
         self.gather_stride = _round_up(max(cap.full_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
+        self.rs_off: list[int] | None = None       # legacy regions are reserved on first use (`_ensure_legacy`)
+        self.ag_off: int | None = None
         self.gather_off: list[int] | None = None
-        if with_gather_region or (with_gather_region is None and W <= 2):
-            self._ensure_gather()
+        self._want_gather = bool(with_gather_region or (with_gather_region is None and W <= 2))
+        # pipelined engine: own quantized payload, own reduced shard, control block
+        self.engine = (engine or os.environ.get("LBC_ENGINE", "pipe")).lower()
+        if self.engine not in ("pipe", "legacy"):
+            raise ValueError("engine must be 'pipe' or 'legacy'")
+        if not hasattr(self.ext, "PipeAllReducePlan"):
+            self.engine = "legacy"
+        self.gate = False                           # rendezvous kernel in front of the pipelined kernel
+        self._pipe = None
+        if self.engine == "pipe":
+            self._build_pipe()
+        else:
+            self._ensure_legacy()
         self.channels = [group.new_channel() for _ in range(MAX_CHUNKS)]
         self.channel = self.channels[0]
         self.launches = 0
@@ -172,7 +195,70 @@ class FusedWorkspace:
         prefetch = os.environ.get("LBC_GATHER_PREFETCH")
         if prefetch is not None and hasattr(self.ext, "set_gather_prefetch"):
             self.ext.set_gather_prefetch(int(prefetch))
-        self._build_native()
+        if self.rs_off is not None:
+            self._build_native()
+
+    # -- pipelined engine -------------------------------------------------------
+    @staticmethod
+    def pipe_region_bytes(world_size: int, dtype: str, config: CompressionConfig, max_numel: int) -> tuple[int, int]:
+        """(own payload bytes, reduced shard bytes) the pipelined engine needs for `max_numel` elements."""
+
+        group_bytes = config.group_size * config.bit // 8 + dtype_bytes(dtype)
+        groups = -(-max(1, max_numel) // config.group_size)
+        one = _round_up(_round_up(groups, ALIGN_GROUPS) * group_bytes, 256)
+        shard_groups = _round_up(-(-groups // world_size), ALIGN_GROUPS)
+        two = world_size * _round_up(shard_groups * group_bytes, 256)
+        return max(one, two), _round_up(shard_groups * group_bytes, 256)
+
+    def _build_pipe(self) -> None:
+        group = self.group
+        q_bytes, ag_bytes = self.pipe_region_bytes(group.world_size, self.dtype, self.config, self.max_numel)
+        self.pipe_q_off, self.pipe_q_bytes = group.alloc(q_bytes), q_bytes
+        self.pipe_ag_off, self.pipe_ag_bytes = group.alloc(ag_bytes), ag_bytes
+        self.pipe_ctl_off = group.alloc(int(self.ext.PIPE_CTL_BYTES))
+        self._pipe = self.ext.PipeAllReducePlan(
+            _DTYPE_CODE[self.dtype], self.config.group_size, self.config.bit, group.rank, list(group.peer_ptrs),
+            self.pipe_q_off, q_bytes, self.pipe_ag_off, ag_bytes, self.pipe_ctl_off, group.timeout_ns,
+            group.status_device, self.max_blocks, self.max_numel)
+        rows = os.environ.get("LBC_PIPE_CHUNK_ROWS")
+        if rows:
+            self._pipe.set_chunk_rows(int(rows))
+        depth = os.environ.get("LBC_PIPE_RING")
+        if depth:
+            self._pipe.set_ring_depth(int(depth))
+
+    def set_engine(self, engine: str) -> None:
+        """"pipe": one persistent kernel per all-reduce; "legacy": the K1/K2/K3 kernel sequence."""
+
+        if engine not in ("pipe", "legacy"):
+            raise ValueError("engine must be 'pipe' or 'legacy'")
+        if engine == "pipe" and self._pipe is None:
+            if not hasattr(self.ext, "PipeAllReducePlan"):
+                raise ValueError("this build has no pipelined engine")
+            self._build_pipe()
+        if engine == "legacy":
+            self._ensure_legacy()
+        self.engine = engine
+
+    def reset_pipe_control(self) -> None:
+        """After a failed collective: zero this rank's local counters of the pipelined engine."""
+
+        if self._pipe is not None:
+            local = int(self.ext.PIPE_CTL_LOCAL)
+            with torch.cuda.device(self.group.device):
+                self.ext.memset_async(self.group.local_ptr + self.pipe_ctl_off + local, 0,
+                                      int(self.ext.PIPE_CTL_BYTES) - local)
+
+    def _ensure_legacy(self) -> None:
+        if self.rs_off is not None:
+            return
+        group = self.group
+        self.rs_off = [group.alloc(self.rs_bytes), group.alloc(self.rs_bytes)]
+        self.ag_off = group.alloc(self.ag_bytes)
+        if self._want_gather:
+            self._ensure_gather()
+        if hasattr(self, "channels"):
+            self._build_native()
 
     def _build_native(self) -> None:
         group = self.group
@@ -207,13 +293,21 @@ class FusedWorkspace:
 
     @staticmethod
     def required_bytes(world_size: int, dtype: str, config: CompressionConfig, max_numel: int,
-                       with_gather_region: bool) -> int:
-        cap = geometry(max_numel + _chunk_slack(world_size, config), world_size, dtype, config)
-        shard = _round_up(max(cap.shard_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
-        total = 2 * world_size * shard + _round_up(max(cap.total_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
-        if with_gather_region:
-            total += 2 * world_size * _round_up(max(cap.full_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
-        return total + 32 * 256   # rounding and canaries of the five regions
+                       with_gather_region: bool, engine: str = "both") -> int:
+        """Arena bytes one workspace may reserve: "pipe" (all-reduce only), "legacy", or "both"."""
+
+        total = 0
+        if engine in ("pipe", "both"):
+            q_bytes, ag_bytes = FusedWorkspace.pipe_region_bytes(world_size, dtype, config, max_numel)
+            total += q_bytes + ag_bytes + 4096 + 4 * 512
+        if engine in ("legacy", "both"):
+            cap = geometry(max_numel + _chunk_slack(world_size, config), world_size, dtype, config)
+            shard = _round_up(max(cap.shard_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
+            total += 2 * world_size * shard + _round_up(max(cap.total_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
+            if with_gather_region:
+                total += 2 * world_size * _round_up(max(cap.full_groups, ALIGN_GROUPS) * cap.group_bytes, 256)
+            total += 32 * 256   # rounding and canaries of the five regions
+        return total
 
     def _ensure_gather(self) -> list[int]:
         if self.gather_off is None:
@@ -222,6 +316,31 @@ class FusedWorkspace:
             if getattr(self, "_native", None) is not None:
                 self._build_native()
         return self.gather_off
+
+    def _pipe_all_reduce(self, x, out, residual, update_residual: bool, scale: float, stages: int, ef_mode: str):
+        n = x.numel()
+        if n > self.max_numel or x.dtype != self._torch_dtype or not x.is_contiguous():
+            self._geom(x)  # raises the precise error
+        target = x if out is None else out
+        if n == 0:
+            return target
+        if target.dtype != x.dtype or target.numel() != n or not target.is_contiguous():
+            raise ValueError("out must be a contiguous tensor of the input's dtype and size")
+        if residual is not None and (residual.dtype != x.dtype or residual.numel() != n or not residual.is_contiguous()):
+            raise ValueError("residual must be a contiguous tensor of the input's dtype and size")
+        epoch = self.group.next_epoch(self.channel)
+        args = (self._pipe, x.data_ptr(), target.data_ptr(), 0 if residual is None else residual.data_ptr(), n, stages,
+                scale, bool(update_residual), ef_mode == "local", epoch, _current_stream_ptr(x.device))
+        if self.group.process_group is None and self.group.world_size > 1:
+            # emulated ranks on one GPU: one launch per phase, so that the ranks can be interleaved by phase
+            phases = [self.ext.PIPE_QUANT, self.ext.PIPE_REDUCE] + ([self.ext.PIPE_DECODE] if stages == 2 else [])
+            for mask in phases:
+                self.ext.pipe_all_reduce(*args, int(mask), False)
+                self.launches += 1
+        else:
+            done = self.ext.pipe_all_reduce(*args, int(self.ext.PIPE_ALL), bool(self.gate))
+            self.launches += 1 if done is None else done      # None: a recorder deferred the launch
+        return target
 
     # -- helpers ---------------------------------------------------------------
     def _geom(self, x: torch.Tensor) -> FusedGeometry:
@@ -312,6 +431,11 @@ class FusedWorkspace:
             stages = default_stages(self.group.world_size, x.numel() * x.element_size(),
                                     bool(self.group.multicast_ptr))
         scale = self._scale(op)
+        if ef_mode not in ("reference", "local"):
+            raise ValueError("ef_mode must be 'reference' or 'local'")
+        if self.engine == "pipe" and self.phase_timer is None:
+            return self._pipe_all_reduce(x, out, residual, update_residual, scale, stages, ef_mode)
+        self._ensure_legacy()
         if self._native is not None and self.phase_timer is None:
             # hot path: one binding crossing; geometry is recomputed natively
             n = x.numel()
@@ -381,6 +505,7 @@ class FusedWorkspace:
         given, uses this rank's own quantization error.
         """
 
+        self._ensure_legacy()
         geo = self._geom(x)
         if out_shard.numel() != geo.shard_numel:
             raise ValueError(f"out_shard must hold {geo.shard_numel} elements")
@@ -399,6 +524,7 @@ class FusedWorkspace:
     def all_gather(self, x: torch.Tensor, outs: list[torch.Tensor]) -> list[torch.Tensor]:
         """Every rank contributes `x` (same shape everywhere); outs[r] = decode(rank r's payload)."""
 
+        self._ensure_legacy()
         geo = self._geom(x)
         g = self.group
         if len(outs) != g.world_size:
@@ -460,7 +586,7 @@ class _Recorder:
 
     def __getattr__(self, name):
         attr = getattr(self._ext, name)
-        if name in ("quant_push", "reduce", "push_bytes", "wait_signal"):
+        if name in ("quant_push", "reduce", "push_bytes", "wait_signal", "pipe_all_reduce"):
             def defer(*a, **k):
                 self._steps.append(lambda: attr(*a, **k))
             return defer

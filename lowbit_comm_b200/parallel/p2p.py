@@ -71,8 +71,13 @@ class PeerMailbox:
         self.capacity = -(-capacity_bytes // 256) * 256
         self.offset = group.alloc(self.capacity * group.world_size)   # slot [source rank] on every rank
         self.channel = group.new_channel()
-        self._sent = [0] * group.world_size
+        # The kernels of a send (or a receive) count their blocks on a scratch counter before the last one
+        # signals.  Sends to different peers may overlap on different streams, so every peer has its own
+        # counters: a channel per peer, used for its counter words only (the flags stay on `self.channel`).
+        self._counter_channels = [group.new_channel() for _ in range(group.world_size)]
+        self._sent = [0] * group.world_size       # epochs count modulo 2^32, like the kernels' comparison
         self._received = [0] * group.world_size
+        self._any_sent = [False] * group.world_size
         self.ext = group._ext
 
     def send(self, tensor, dst: int, config: CompressionConfig, dtype: str) -> None:
@@ -82,13 +87,14 @@ class PeerMailbox:
         need = estimate_quantized_size(n, dtype=dtype, config=config).quantized_bytes
         if need > self.capacity:
             raise ValueError(f"payload of {need} bytes exceeds the mailbox capacity {self.capacity}")
-        self._sent[dst] += 1
-        epoch = self._sent[dst]
-        if epoch > 1:  # the receiver must have drained the previous message
-            self.ext.wait_signal((g.flags_addr(g.rank, self.channel, PHASE_P2P_ACK) + 4 * dst, 1, epoch - 1,
+        previous = self._sent[dst]
+        epoch = self._sent[dst] = (previous + 1) & 0xFFFFFFFF
+        if self._any_sent[dst]:  # the receiver must have drained the previous message
+            self.ext.wait_signal((g.flags_addr(g.rank, self.channel, PHASE_P2P_ACK) + 4 * dst, 1, previous,
                                   g.timeout_ns, g.status_device, PHASE_P2P_ACK), None)
+        self._any_sent[dst] = True
         signal = ([g.flags_addr(dst, self.channel, PHASE_P2P_DATA)], g.rank, epoch,
-                  g.counter_addr(self.channel, PHASE_P2P_DATA))
+                  g.counter_addr(self._counter_channels[dst], PHASE_P2P_DATA))
         self.ext.quant_push(tensor.reshape(-1), None, None, None, [g.addr(dst, self.offset + g.rank * self.capacity)],
                             self.ext.PUSH_BROADCAST, 0, groups, 0, config.group_size, config.bit, signal, 0)
 
@@ -96,12 +102,11 @@ class PeerMailbox:
         g = self.group
         n = out.numel()
         groups = -(-n // config.group_size)
-        self._received[src] += 1
-        epoch = self._received[src]
+        epoch = self._received[src] = (self._received[src] + 1) & 0xFFFFFFFF
         wait = (g.flags_addr(g.rank, self.channel, PHASE_P2P_DATA) + 4 * src, 1, epoch, g.timeout_ns,
                 g.status_device, PHASE_P2P_DATA)
         ack = ([g.flags_addr(src, self.channel, PHASE_P2P_ACK)], g.rank, epoch,
-               g.counter_addr(self.channel, PHASE_P2P_ACK))
+               g.counter_addr(self._counter_channels[src], PHASE_P2P_ACK))
         self.ext.reduce([g.local_ptr + self.offset + src * self.capacity], groups, 0, False, n,
                         codec._DTYPE_CODE[dtype], config.group_size, config.bit, 1.0, out.reshape(-1), False, None, None,
                         [], 0, 0, ack, wait, 0)

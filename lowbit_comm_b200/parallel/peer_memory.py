@@ -41,7 +41,11 @@ FLAG_BYTES = MAX_CHANNELS * NUM_PHASES * MAX_RANKS * 4
 COUNTER_OFFSET = FLAG_BYTES
 DATA_OFFSET = 128 * 1024
 CANARY_BYTES, CANARY_VALUE = 256, 0xA5
-DEFAULT_TIMEOUT_NS = 20_000_000_000  # 20 s: far above any real skew, far below a watchdog
+# How long a kernel waits for a peer's flag before it gives up and reports through the status word: the
+# scale of a collective library's watchdog (minutes), because a rank may legitimately be late by a whole
+# evaluation pass or a checkpoint write.  Tests pass short limits explicitly.
+DEFAULT_TIMEOUT_NS = 600_000_000_000
+CLOSE_BARRIER_LIMIT_S = 60.0
 
 PHASE_REDUCE_SCATTER, PHASE_ALL_GATHER, PHASE_P2P_DATA, PHASE_P2P_ACK = range(NUM_PHASES)
 
@@ -55,7 +59,8 @@ class PeerGroup:
 
     def __init__(self, *, rank: int, world_size: int, device: torch.device, nbytes: int, peer_ptrs: list[int],
                  ext: Any, owner: bool, process_group: Any = None, opened: list[int] | None = None,
-                 timeout_ns: int = DEFAULT_TIMEOUT_NS, multicast_ptr: int = 0, keepalive: Any = None) -> None:
+                 timeout_ns: int = DEFAULT_TIMEOUT_NS, multicast_ptr: int = 0, keepalive: Any = None,
+                 uid: str = "", barrier: Any = None) -> None:
         if world_size > MAX_RANKS:
             raise CCDLUnavailableError(f"peer groups support at most {MAX_RANKS} ranks")
         self.rank = rank
@@ -77,6 +82,8 @@ class PeerGroup:
         self._channels_used = 0
         self._lock = threading.Lock()
         self._closed = False
+        self._uid = uid                           # the same string on every rank of the group: names its store keys
+        self._barrier = barrier                   # host-side barrier of the group used by close(); None = store counter
         host, dev = ext.status_alloc()
         self.status_host, self.status_device = host, dev
 
@@ -109,9 +116,9 @@ class PeerGroup:
             local = ext.arena_alloc(nbytes)
             handle = ext.ipc_get_handle(local) if world > 1 else b""
             infos: list[Any] = [None] * world
-            dist.all_gather_object(infos, (device.index, handle), group=process_group)
+            dist.all_gather_object(infos, (device.index, handle, os.urandom(8).hex()), group=process_group)
             ptrs, opened = [], []
-            for peer, (peer_dev, peer_handle) in enumerate(infos):
+            for peer, (peer_dev, peer_handle, _) in enumerate(infos):
                 if peer == rank:
                     ptrs.append(local)
                     continue
@@ -124,7 +131,7 @@ class PeerGroup:
             torch.cuda.synchronize(device)
         dist.barrier(group=process_group)
         return cls(rank=rank, world_size=world, device=device, nbytes=nbytes, peer_ptrs=ptrs, ext=ext, owner=True,
-                   process_group=process_group, opened=opened, timeout_ns=timeout_ns)
+                   process_group=process_group, opened=opened, timeout_ns=timeout_ns, uid=infos[0][2])
 
     @classmethod
     def _create_symmetric(cls, process_group: Any, nbytes: int, device: torch.device, ext: Any, rank: int,
@@ -155,8 +162,9 @@ class PeerGroup:
             ok = False
             error = f"{type(exc).__name__}: {exc}"
         votes: list[Any] = [None] * world
-        dist.all_gather_object(votes, bool(ok), group=process_group)
-        if not all(votes):
+        dist.all_gather_object(votes, (bool(ok), os.urandom(8).hex()), group=process_group)
+        uid = votes[0][1]
+        if not all(v[0] for v in votes):
             if rank == 0 and os.environ.get("LBC_DEBUG"):
                 print(f"[lowbit_comm_b200] multicast arena unavailable ({error or 'a peer failed'}); using CUDA IPC")
             del tensor, handle
@@ -165,7 +173,7 @@ class PeerGroup:
         return cls(rank=rank, world_size=world, device=device, nbytes=nbytes,
                    peer_ptrs=[int(p) for p in handle.buffer_ptrs], ext=ext, owner=False,
                    process_group=process_group, opened=[], timeout_ns=timeout_ns,
-                   multicast_ptr=int(handle.multicast_ptr), keepalive=(tensor, handle))
+                   multicast_ptr=int(handle.multicast_ptr), keepalive=(tensor, handle), uid=uid)
 
     @classmethod
     def loopback(cls, world_size: int, nbytes: int, device: torch.device | None = None, *,
@@ -247,7 +255,10 @@ class PeerGroup:
 
     # -- signalling helpers ---------------------------------------------------
     def next_epoch(self, channel: int) -> int:
-        self._epochs[channel] = (self._epochs[channel] + 1) & 0x7FFFFFFF
+        """Epochs count modulo 2^32, 0 included: the kernels compare `int(seen - epoch) >= 0`, which stays
+        right across the wrap as long as a flag is never more than 2^31 collectives behind."""
+
+        self._epochs[channel] = (self._epochs[channel] + 1) & 0xFFFFFFFF
         return self._epochs[channel]
 
     def signal_all(self, channel: int, phase: int, epoch: int, ranks=None):
@@ -269,6 +280,9 @@ class PeerGroup:
         return DeviceWaitStatus(*self._ext.status_read(self.status_host))._asdict()
 
     def check_status(self) -> None:
+        """Raises when a kernel of this group gave up waiting.  Reads pinned host memory: no device
+        synchronisation, cheap enough to call before every collective."""
+
         status = DeviceWaitStatus(*self._ext.status_read(self.status_host))
         if status.timed_out:
             raise AsyncCommunicationError.from_wait(self.rank, status)
@@ -286,7 +300,31 @@ class PeerGroup:
         self.clear_status()
 
     # -- teardown ---------------------------------------------------------------
+    def _store_barrier(self) -> None:
+        """Every rank of the group adds one to a counter in the job's key-value store and waits (bounded)
+        until the counter shows all of them.  Host only: no kernel, no collective on a GPU."""
+
+        import time
+
+        import torch.distributed as dist
+
+        limit = float(os.environ.get("LBC_CLOSE_TIMEOUT_S", CLOSE_BARRIER_LIMIT_S))
+        try:
+            store = dist.distributed_c10d._get_default_store()
+            key = f"lbc_close_{self._uid or id(self.process_group)}"
+            store.add(key, 1)
+            deadline = time.monotonic() + limit
+            while int(store.add(key, 0)) < self.world_size and time.monotonic() < deadline:
+                time.sleep(0.01)
+        except Exception:  # noqa: BLE001 - no store (torn-down job): give the peers a moment instead
+            time.sleep(min(limit, 2.0))
+
     def close(self, *, free_arena: bool = True) -> None:
+        """Collective over the group.  A peer's kernel may still be loading from this rank's arena (the
+        gather stage reads the owners' memory) or storing into it after this rank's own stream has drained,
+        so the arena is unmapped and freed only after every rank has drained its device AND said so on the
+        host: synchronize, barrier, then free."""
+
         if self._closed:
             return
         self._closed = True
@@ -294,6 +332,11 @@ class PeerGroup:
             torch.cuda.synchronize(self.device)
         except Exception:  # noqa: BLE001
             pass
+        if self.process_group is not None and self.world_size > 1:
+            try:
+                (self._barrier or self._store_barrier)()
+            except Exception:  # noqa: BLE001
+                pass
         for ptr in self._opened:
             try:
                 self._ext.ipc_close_handle(ptr)
@@ -302,9 +345,7 @@ class PeerGroup:
         self._ext.status_free(self.status_host)
         if self._owner and free_arena and self.process_group is not None:
             self._ext.arena_free(self.local_ptr)
-        # Every collective ends with a wait for all ranks' last stores, so once this rank's stream has
-        # drained nobody is still writing into its arena; dropping the symmetric tensor unmaps it.
-        self._keepalive = None
+        self._keepalive = None                    # dropping the symmetric-memory tensor unmaps it
 
     @staticmethod
     def close_loopback(groups: list["PeerGroup"], *, check: bool = True) -> None:

@@ -38,25 +38,34 @@ def collectives_case(rank: int, world: int) -> None:
         for strategy, want in (("all_gather", y), ("reduce_scatter", two)):
             mine = xs[rank].cuda()
             ws = comm.workspace(mine, cfg, name)
-            if n > 50_000:  # small chunks: the pipelined multi-stream launcher runs with up to 8 chunks
-                ws.set_chunking(1 << 17, 8)
+            assert ws.engine == "pipe"      # the default: one persistent kernel per all-reduce
+            if n > 50_000:
+                ws._pipe.set_chunk_rows(16)     # many chunks: the phases of neighbouring chunks overlap across GPUs
             got = compressed_all_reduce(mine, config=cfg, op="mean", strategy=strategy)
             torch.cuda.synchronize()
             assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), (strategy, n, rank)
-            # with error feedback (residual starts at zero, so prepared == input); the gather stage both as
-            # peer loads by the decode kernel and as peer stores by the reduce kernel
+            # with error feedback (residual starts at zero, so prepared == input), through both engines; the
+            # kernel sequence of the legacy engine runs its gather stage both as peer loads by the decode
+            # kernel and as peer stores by the reduce kernel
             reduced32 = (oracle.reduce_mean(payloads, n, cfg, name)[1] if strategy == "all_gather"
                          else oracle.decode_fp32(oracle.encode(y, cfg), n, cfg, name))
             want_res = oracle.residual_update(xs[rank], reduced32)
-            for gather in ("push", "pull"):
+            for engine, gather, gate in (("pipe", "pull", False), ("pipe", "pull", True), ("legacy", "push", False),
+                                         ("legacy", "pull", False)):
+                ws.set_engine(engine)
                 ws.set_gather_mode(gather)
+                ws.gate = gate
+                if engine == "legacy" and n > 50_000:   # the multi-stream launcher with up to 8 chunks
+                    ws.set_chunking(1 << 17, 8)
                 residual = torch.zeros_like(mine)
                 got = ws.all_reduce(xs[rank].cuda(), residual=residual, op="mean",
                                     stages=1 if strategy == "all_gather" else 2)
                 torch.cuda.synchronize()
-                assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), (strategy, n, gather, "ef")
+                assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), (strategy, n, engine, gather)
                 assert torch.equal(residual.cpu().view(torch.uint8), want_res.view(torch.uint8)), \
-                    (strategy, n, gather, "residual")
+                    (strategy, n, engine, gather, "residual")
+            ws.set_engine("pipe")
+            ws.gate = False
         work = compressed_all_reduce(xs[rank].cuda(), config=cfg, strategy="reduce_scatter", async_op=True)
         got = work.wait()
         torch.cuda.current_stream().synchronize()

@@ -52,13 +52,14 @@ def _make(world, dtype, cfg, max_numel, **kw):
                     for g in groups]
 
 
+@pytest.mark.parametrize("engine", ("pipe", "legacy"))
 @pytest.mark.parametrize("world", (1, 2, 4, 8))
 @pytest.mark.parametrize("dtype,bit,group", [("bf16", 8, 64), ("fp16", 8, 32), ("fp32", 8, 64), ("bf16", 4, 16)])
 @pytest.mark.parametrize("stages", (1, 2))
-def test_all_reduce_matches_oracle(ext, world, dtype, bit, group, stages):
+def test_all_reduce_matches_oracle(ext, engine, world, dtype, bit, group, stages):
     cfg = CompressionConfig(bit=bit, group_size=group, allow_experimental=True)
     max_numel = 40_000
-    groups, wss = _make(world, dtype, cfg, max_numel)
+    groups, wss = _make(world, dtype, cfg, max_numel, engine=engine)
     try:
         for step, n in enumerate((world * group * 8, 3001, 1, max_numel, 64 * 511 + 7)):
             xs = _inputs(world, n, dtype, seed=step)
@@ -95,7 +96,7 @@ def test_every_push_variant_writes_the_same_bytes(ext, push_variant, reduce_bulk
 
     cfg = CompressionConfig(bit=bit, group_size=group, allow_experimental=True)
     world, max_numel = 4, 300_000
-    groups, wss = _make(world, dtype, cfg, max_numel)
+    groups, wss = _make(world, dtype, cfg, max_numel, engine="legacy")
     ext.set_push_variant(push_variant, reduce_bulk, push_blocks)
     try:
         for step, n in enumerate((world * group * 8, 70_001, max_numel)):
@@ -129,7 +130,7 @@ def test_gather_sweep_orders(ext, order, world, dtype, bit, group):
 
     cfg = CompressionConfig(bit=bit, group_size=group, allow_experimental=True)
     max_numel = 200_000
-    groups, wss = _make(world, dtype, cfg, max_numel)
+    groups, wss = _make(world, dtype, cfg, max_numel, engine="legacy")
     ext.set_gather_order(order)
     try:
         for step, n in enumerate((world * group * 8, 12_345, 1, max_numel, group * 8 * world * 31 + 5)):
@@ -148,8 +149,6 @@ def test_gather_sweep_orders(ext, order, world, dtype, bit, group):
         PeerGroup.close_loopback(groups)
 
 
-@pytest.mark.skipif(os.environ.get("LBC_TEST_NEW_KERNELS") != "1",
-                    reason="gather_decode_kernel has not run on a GPU yet; set LBC_TEST_NEW_KERNELS=1 to run it")
 @pytest.mark.parametrize("depth", (2, 4))
 @pytest.mark.parametrize("world", (3, 8))
 @pytest.mark.parametrize("dtype,group", [("bf16", 64), ("fp16", 16), ("fp32", 32)])
@@ -158,7 +157,7 @@ def test_gather_decode_with_tiles_in_flight(ext, depth, world, dtype, group):
 
     cfg = CompressionConfig(bit=8, group_size=group)
     max_numel = 200_000
-    groups, wss = _make(world, dtype, cfg, max_numel)
+    groups, wss = _make(world, dtype, cfg, max_numel, engine="legacy")
     ext.set_gather_prefetch(depth)
     try:
         assert ext.get_gather_prefetch() == depth
@@ -181,14 +180,15 @@ def test_gather_decode_with_tiles_in_flight(ext, depth, world, dtype, group):
         PeerGroup.close_loopback(groups)
 
 
+@pytest.mark.parametrize("engine", ("pipe", "legacy"))
 @pytest.mark.parametrize("world,stages", [(2, 1), (4, 2), (8, 2)])
 @pytest.mark.parametrize("dtype", ("bf16", "fp32"))
-def test_local_error_feedback_mode(ext, world, stages, dtype):
+def test_local_error_feedback_mode(ext, engine, world, stages, dtype):
     """ef_mode="local": the residual becomes this rank's own quantization error, over several steps."""
 
     cfg = CompressionConfig()
     n = 64 * 777 + 5
-    groups, wss = _make(world, dtype, cfg, n)
+    groups, wss = _make(world, dtype, cfg, n, engine=engine)
     try:
         residual_ref = [torch.zeros(n, dtype=DT[dtype]) for _ in range(world)]
         dev_r = [r.cuda() for r in residual_ref]
@@ -236,6 +236,101 @@ def test_reduce_scatter_and_all_gather(ext, world):
         torch.cuda.synchronize()
         for g in groups:
             g.check_status()
+    finally:
+        PeerGroup.close_loopback(groups)
+
+
+@pytest.mark.parametrize("world,stages", [(2, 1), (3, 2), (8, 2)])
+@pytest.mark.parametrize("dtype,group", [("bf16", 64), ("fp32", 16)])
+@pytest.mark.parametrize("chunk_rows,ring", [(1, 2), (8, 3), (64, 4)])
+def test_pipelined_engine_many_chunks_and_ring_depths(ext, world, stages, dtype, group, chunk_rows, ring):
+    """Tensors of many rows, cut into many chunks, through shared-memory rings of every depth: the
+    ticket schedule, the chunk flags and the stage re-use must not change a bit of the result.  Unaligned
+    views exercise the rows that bypass the copy engine."""
+
+    cfg = CompressionConfig(bit=8, group_size=group)
+    max_numel = 700_000
+    groups, wss = _make(world, dtype, cfg, max_numel, engine="pipe")
+    for ws in wss:
+        ws._pipe.set_chunk_rows(chunk_rows)
+        ws._pipe.set_ring_depth(ring)
+    expected = _expected_one_stage if stages == 1 else _expected_two_stage
+    try:
+        for step, (n, skew) in enumerate(((max_numel, 0), (4096 * world * 5, 0), (333_333, 0), (250_001, 3))):
+            xs = _inputs(world, n, dtype, seed=800 + step)
+            rs = _inputs(world, n, dtype, seed=900 + step)
+            # `skew` elements of offset make x, the output and the residual 16-byte unaligned
+            dev_x = [torch.cat([torch.zeros(skew, dtype=x.dtype), x]).cuda()[skew:] for x in xs]
+            dev_r = [torch.cat([torch.zeros(skew, dtype=r.dtype), r]).cuda()[skew:] for r in rs]
+            run_loopback(wss, "all_reduce", [(dev_x[r],) for r in range(world)],
+                         [{"residual": dev_r[r]} for r in range(world)], stages=stages)
+            want = expected(xs, rs, cfg, dtype)
+            for r in range(world):
+                assert torch.equal(dev_x[r].cpu().view(torch.uint8), want[0].view(torch.uint8)), (n, r)
+                assert torch.equal(dev_r[r].cpu().view(torch.uint8), want[1][r].view(torch.uint8)), (n, r)
+        torch.cuda.synchronize()
+        for g in groups:
+            g.check_status()
+    finally:
+        PeerGroup.close_loopback(groups)
+
+
+def test_pipelined_engine_single_rank_runs_all_phases_in_one_launch(ext):
+    """World size 1 (a one-GPU DDP job): the three phases run inside one launch and meet through the flags."""
+
+    cfg = CompressionConfig()
+    n = 3_000_000
+    groups, wss = _make(1, "bf16", cfg, n, engine="pipe")
+    wss[0]._pipe.set_chunk_rows(16)
+    try:
+        for stages in (1, 2):
+            xs, rs = _inputs(1, n, "bf16", seed=11), _inputs(1, n, "bf16", seed=12)
+            dev_x, dev_r = xs[0].cuda(), rs[0].cuda()
+            before = wss[0].launches
+            wss[0].all_reduce(dev_x, residual=dev_r, stages=stages)
+            assert wss[0].launches == before + 1
+            want = (_expected_one_stage if stages == 1 else _expected_two_stage)(xs, rs, cfg, "bf16")
+            assert torch.equal(dev_x.cpu().view(torch.uint8), want[0].view(torch.uint8)), stages
+            assert torch.equal(dev_r.cpu().view(torch.uint8), want[1][0].view(torch.uint8)), stages
+        groups[0].check_status()
+    finally:
+        PeerGroup.close_loopback(groups)
+
+
+def test_pipelined_engine_wait_runs_out_on_a_flag_nobody_sets(ext):
+    """REDUCE rows of a rank whose peer never quantized: the bounded wait gives up, the status word says
+    which peer was missing, and after a reset the workspace serves the next collective."""
+
+    cfg = CompressionConfig()
+    n = 100_000
+    need = FusedWorkspace.required_bytes(2, "bf16", cfg, n, True) + (1 << 20)
+    groups = PeerGroup.loopback(2, need, timeout_ns=50_000_000)   # 50 ms
+    try:
+        wss = [FusedWorkspace(g, dtype="bf16", config=cfg, max_numel=n, engine="pipe") for g in groups]
+        x = torch.randn(n).to(torch.bfloat16).cuda()
+        ws, g = wss[0], groups[0]
+        epoch = g.next_epoch(ws.channel)
+        stream = torch.cuda.current_stream().cuda_stream
+        # rank 0 quantizes and then wants to reduce; rank 1 never runs, so its flag never comes
+        ext.pipe_all_reduce(ws._pipe, x.data_ptr(), x.data_ptr(), 0, n, 1, 0.5, False, False, epoch, stream,
+                            int(ext.PIPE_QUANT), False)
+        ext.pipe_all_reduce(ws._pipe, x.data_ptr(), x.data_ptr(), 0, n, 1, 0.5, False, False, epoch, stream,
+                            int(ext.PIPE_REDUCE), False)
+        torch.cuda.synchronize()      # returns: the wait is bounded
+        with pytest.raises(AsyncCommunicationError) as info:
+            g.check_status()
+        assert info.value.status["expected"] == epoch and info.value.status["peer"] == 1
+        g.reset_after_error()
+        ws.reset_pipe_control()
+        groups[1].next_epoch(wss[1].channel)
+        g.check_status()
+        xs = _inputs(2, n, "bf16", seed=3)
+        dev = [t.cuda() for t in xs]
+        run_loopback(wss, "all_reduce", [(dev[r],) for r in range(2)], stages=1)
+        want = _expected_one_stage(xs, [None, None], cfg, "bf16")
+        for r in range(2):
+            assert torch.equal(dev[r].cpu().view(torch.uint8), want[0].view(torch.uint8)), r
+        g.check_status()
     finally:
         PeerGroup.close_loopback(groups)
 

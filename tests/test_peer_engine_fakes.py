@@ -1,0 +1,245 @@
+"""Host-side logic of the peer-memory engine, exercised with fakes (no GPU, no process group):
+arena sizing and growth in the DDP hook, the order of teardown, epoch arithmetic across the 32-bit wrap,
+and the status check in front of every bucket."""
+
+import pytest
+import torch
+
+from lowbit_comm_b200.config import CompressionConfig
+from lowbit_comm_b200.exceptions import AsyncCommunicationError, CCDLUnavailableError
+from lowbit_comm_b200.parallel import ddp_hook, peer_memory
+from lowbit_comm_b200.parallel.fused import FusedWorkspace
+from lowbit_comm_b200.parallel.peer_memory import PeerGroup
+
+
+class FakeExt:
+    """Records the calls `PeerGroup` makes into the native extension."""
+
+    def __init__(self, log):
+        self.log = log
+        self.status = (0, 0, 0, 0, 0)
+
+    def status_alloc(self):
+        return 1, 2
+
+    def status_read(self, host):
+        return self.status
+
+    def status_clear(self, host):
+        self.status = (0, 0, 0, 0, 0)
+
+    def status_free(self, host):
+        self.log.append("status_free")
+
+    def ipc_close_handle(self, ptr):
+        self.log.append(f"ipc_close {ptr}")
+
+    def arena_free(self, ptr):
+        self.log.append(f"arena_free {ptr}")
+
+    def memset_async(self, ptr, value, nbytes):
+        pass
+
+
+def _group(log, world=2, nbytes=1 << 30, **kw):
+    return PeerGroup(rank=0, world_size=world, device=torch.device("cpu"), nbytes=nbytes,
+                     peer_ptrs=[1000 * (r + 1) for r in range(world)], ext=FakeExt(log), owner=True,
+                     process_group=object(), opened=[2000], **kw)
+
+
+def test_close_synchronises_then_meets_the_peers_then_frees(monkeypatch):
+    log = []
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda device=None: log.append("synchronize"))
+    monkeypatch.setattr(torch.cuda, "device", lambda device: __import__("contextlib").nullcontext())
+    group = _group(log, barrier=lambda: log.append("barrier"))
+    group.close()
+    assert log == ["synchronize", "barrier", "ipc_close 2000", "status_free", "arena_free 1000"]
+    group.close()                                   # idempotent
+    assert len(log) == 5
+
+
+def test_close_of_a_single_rank_group_needs_no_barrier(monkeypatch):
+    log = []
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda device=None: log.append("synchronize"))
+    group = PeerGroup(rank=0, world_size=1, device=torch.device("cpu"), nbytes=1 << 20, peer_ptrs=[1000],
+                      ext=FakeExt(log), owner=True, process_group=object(),
+                      barrier=lambda: log.append("barrier"))
+    group.close()
+    assert "barrier" not in log and log[0] == "synchronize" and log[-1] == "arena_free 1000"
+
+
+def test_store_barrier_counts_every_rank_and_is_bounded(monkeypatch):
+    import torch.distributed as dist
+
+    class Store:
+        def __init__(self):
+            self.values = {}
+
+        def add(self, key, amount):
+            self.values[key] = self.values.get(key, 0) + amount
+            return self.values[key]
+
+    store = Store()
+    monkeypatch.setattr(dist.distributed_c10d, "_get_default_store", lambda: store)
+    monkeypatch.setenv("LBC_CLOSE_TIMEOUT_S", "0.2")
+    group = _group([], uid="abc")
+    store.add("lbc_close_abc", 1)                   # the other rank already arrived
+    group._store_barrier()
+    assert store.values["lbc_close_abc"] == 2
+    lonely = _group([], uid="xyz")                  # nobody else arrives: returns after the limit
+    lonely._store_barrier()
+    assert store.values["lbc_close_xyz"] == 1
+
+
+def _reached(seen: int, epoch: int) -> bool:
+    """The kernels' test `int(seen - epoch) >= 0` on 32-bit words."""
+
+    return ((seen - epoch) & 0xFFFFFFFF) < 0x80000000
+
+
+def test_epochs_wrap_through_the_whole_32_bit_range():
+    group = _group([])
+    ch = group.new_channel()
+    group._epochs[ch] = 0xFFFFFFF0
+    flag = 0xFFFFFFF0                               # the value the last collective left in the flag
+    for _ in range(40):
+        epoch = group.next_epoch(ch)
+        assert 0 <= epoch <= 0xFFFFFFFF
+        assert not _reached(flag, epoch), (flag, epoch)     # the stale flag never passes for the new epoch
+        flag = epoch                                        # ... and the new signal does
+        assert _reached(flag, epoch)
+    assert group._epochs[ch] == 0x18                # walked across zero
+
+
+def test_mailbox_epochs_wrap_and_every_peer_has_its_own_counter(monkeypatch):
+    import contextlib
+
+    from lowbit_comm_b200.parallel.p2p import PeerMailbox
+
+    monkeypatch.setattr(torch.cuda, "device", lambda device: contextlib.nullcontext())
+
+    calls = []
+
+    class Ext(FakeExt):
+        PUSH_BROADCAST = 0
+
+        def wait_signal(self, wait, signal):
+            calls.append(("wait", wait[2]))
+
+        def quant_push(self, *args):
+            calls.append(("push", args[11]))
+
+    group = _group([], world=4)
+    group._ext = Ext([])
+    box = PeerMailbox(group, capacity_bytes=4096)
+    box._sent[1], box._any_sent[1] = 0xFFFFFFFF, True
+    x = torch.zeros(64, dtype=torch.bfloat16)
+    box.send(x, 1, CompressionConfig(), "bf16")
+    box.send(x, 2, CompressionConfig(), "bf16")
+    assert calls[0] == ("wait", 0xFFFFFFFF) and calls[1][1][2] == 0      # waits for the old ack, sends epoch 0
+    assert calls[2][0] == "push" and calls[2][1][2] == 1                  # first message to rank 2: no wait
+    counters = {calls[1][1][3], calls[2][1][3]}
+    assert len(counters) == 2                                            # two destinations, two block counters
+
+
+# ---------------------------------------------------------------------------------------------------
+# arena sizing of the hook's engine
+# ---------------------------------------------------------------------------------------------------
+class FakeGroup:
+    def __init__(self, total, world):
+        self.nbytes, self.world_size, self.used, self.closed = total, world, 0, False
+
+    @property
+    def bytes_free(self):
+        return self.nbytes - self.used
+
+    def check_status(self):
+        pass
+
+    def close(self):
+        self.closed = True
+
+
+class FakeWorkspace:
+    launches = 0
+
+    def __init__(self, group, need, cap):
+        if group.bytes_free < need:
+            raise CCDLUnavailableError("peer arena exhausted")
+        group.used += need
+        self.group, self.max_numel = group, cap
+
+
+def _engine(world, **kw):
+    eng = ddp_hook._PeerEngine(config=CompressionConfig(), process_group=None, peer_group=kw.pop("peer_group", None),
+                               arena_bytes=kw.pop("arena_bytes", None), max_bucket_numel=kw.pop("max_bucket_numel", None),
+                               max_blocks=0, ef_mode="reference")
+    made = []
+    eng._world = lambda: world
+    eng._make_group = lambda total, device: made.append(FakeGroup(total, world)) or made[-1]
+    eng._make_workspace = lambda dtype, cap: FakeWorkspace(eng.group, eng._need(world, dtype, cap) - (1 << 20), cap)
+    eng.stream = object()
+    return eng, made
+
+
+class Bucket:
+    def __init__(self, numel):
+        self._numel = numel
+        self.device = torch.device("cpu")
+
+    def numel(self):
+        return self._numel
+
+
+@pytest.mark.parametrize("world", (2, 4, 8))
+def test_growing_bucket_sizes_never_exhaust_the_arena(world):
+    """The first-iteration bucket sizes DDP produces for GPT-2 small with `find_unused_parameters=True`
+    (tiny first, then growing), followed by the rebuilt 25 MB buckets."""
+
+    eng, made = _engine(world)
+    for numel in (2304, 14_200_000, 15_000_000, 38_600_000, 13_000_000, 2304, 38_600_000):
+        ws = eng.ensure(Bucket(numel), "bf16")
+        assert ws.max_numel >= numel
+    assert eng.rebuilds >= 1 and all(g.closed for g in made[:-1]) and not made[-1].closed
+    # no arena is a multiple of what the largest bucket needs
+    need = FusedWorkspace.required_bytes(world, "bf16", CompressionConfig(), 1 << 26, False, engine="pipe")
+    assert made[-1].nbytes <= 2 * need + (8 << 20)
+
+
+def test_a_stated_maximum_sizes_the_arena_once():
+    eng, made = _engine(4, max_bucket_numel=40_000_000)
+    for numel in (2304, 14_200_000, 38_600_000):
+        eng.ensure(Bucket(numel), "bf16")
+    assert len(made) == 1 and eng.rebuilds == 0
+
+
+def test_a_callers_arena_is_never_rebuilt():
+    group = FakeGroup(64 << 20, 2)
+    eng, made = _engine(2, peer_group=group)
+    eng.ensure(Bucket(1 << 20), "bf16")
+    with pytest.raises(CCDLUnavailableError):
+        eng.ensure(Bucket(1 << 27), "bf16")
+    assert not made and not group.closed
+
+
+def test_the_hook_checks_the_status_word_before_every_bucket():
+    """A wait that ran out in an earlier bucket must surface in the next hook call, and `reset_after_error`
+    must restore service."""
+
+    log = []
+    group = _group(log)
+    group._ext.status = (1, 9, 1, 0, 7)
+    eng, _ = _engine(2, peer_group=group)
+    with pytest.raises(AsyncCommunicationError) as info:
+        eng.check_status()
+    assert info.value.status["peer"] == 1 and "quantized rows" in str(info.value)
+    holder = ddp_hook.DDPCommHook(lambda bucket: None, lambda: None)
+    holder.peer_engine = eng
+    with pytest.raises(AsyncCommunicationError):
+        holder.check_status()
+    group._ext.status_clear(0)
+    holder.check_status()
+
+
+def test_default_wait_limit_is_on_the_scale_of_a_watchdog():
+    assert peer_memory.DEFAULT_TIMEOUT_NS >= 300 * 10**9

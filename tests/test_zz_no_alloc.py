@@ -76,6 +76,36 @@ def test_two_calls_in_a_row_match_the_allocating_path(ext, dtype, group, bit):
         assert torch.equal(res.view(torch.uint8), want_res.view(torch.uint8)), n
 
 
+@pytest.mark.parametrize("dtype,group,bit", [(torch.float32, 16, 8), (torch.bfloat16, 64, 8)])
+def test_the_largest_accepted_size_fits_the_fixed_array(ext, dtype, group, bit):
+    """`numel == lbc_no_alloc_max_numel()`: for fp32 / groups of 16 / 8 bit the payload fills the array to its last
+    byte.  Bit-for-bit agreement with the allocating path shows that neither region is cut short."""
+
+    lib = _library()
+    cfg = CompressionConfig(bit=bit, group_size=group, allow_experimental=True)
+    n = lib.lbc_no_alloc_max_numel()
+    gen = torch.Generator().manual_seed(9)
+    x = (torch.randn(n, generator=gen) * 1e-2).to(dtype).cuda()
+    residual = (torch.randn(n, generator=gen) * 1e-4).to(dtype).cuda()
+    want_out, want_res = _existing_path(x, residual, cfg)
+    out, res = torch.empty_like(x), residual.clone()
+    for _ in range(2):                      # two calls in a row, the second on the first one's leftovers
+        res.copy_(residual)
+        code = _call(lib, x, res, out, res, cfg)
+        assert code == 0, lib.lbc_no_alloc_error_string(code)
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.uint8), want_out.view(torch.uint8))
+        assert torch.equal(res.view(torch.uint8), want_res.view(torch.uint8))
+    # one element more, with valid pointers: refused before anything is launched
+    big = torch.zeros(n + 1, dtype=dtype, device="cuda")
+    sentinel = torch.full((n + 1,), 3.0, dtype=dtype, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    code = lib.lbc_no_alloc_roundtrip(_DTYPE_CODE[dtype], group, bit, big.data_ptr(), None, sentinel.data_ptr(), None,
+                                      n + 1, stream)
+    torch.cuda.synchronize()
+    assert code == -2 and bool((sentinel == 3.0).all())
+
+
 def test_without_error_feedback_and_limits(ext):
     lib = _library()
     cfg = CompressionConfig()
