@@ -37,8 +37,9 @@ def main() -> None:
     ap.add_argument("--ref-arms", default="all_gather,topology,shard",
                     help="reference paths to time: all_gather, topology (compiled ring), shard (reduce-scatter shard)")
     ap.add_argument("--ref-max-mib", type=float, default=1024)
-    ap.add_argument("--engine", choices=("pipe", "legacy"), default="pipe",
-                    help="pipe: one persistent kernel per all-reduce; legacy: the K1/K2/K3 kernel sequence")
+    ap.add_argument("--engine", choices=("auto", "pipe", "legacy"), default="auto",
+                    help="pipe: one persistent kernel per all-reduce; legacy: the K1/K2/K3 kernel sequence; "
+                         "auto: the library's choice by size")
     ap.add_argument("--arms", default="auto,1,2", help="paths of this library to time: auto, 1 (one stage), 2 (two stages)")
     ap.add_argument("--chunk-rows", type=int, default=None, help="pipelined engine: rows of one chunk over all shards")
     ap.add_argument("--ring", type=int, default=None, help="pipelined engine: rows in flight per block (2..4)")
@@ -98,9 +99,9 @@ def main() -> None:
         _req().set_gather_prefetch(args.gather_prefetch)
     if args.gather is not None:
         big.set_gather_mode(args.gather)
-    if args.engine == "pipe" and args.chunk_rows is not None:
+    if args.engine != "legacy" and args.chunk_rows is not None:
         big._pipe.set_chunk_rows(args.chunk_rows)
-    if args.engine == "pipe" and args.ring is not None:
+    if args.engine != "legacy" and args.ring is not None:
         big._pipe.set_ring_depth(args.ring)
     if args.chunk_mib is not None:
         big.set_chunking(int(max(args.chunk_mib, 1e-3) * (1 << 20)), 1 if args.chunk_mib == 0 else 8)

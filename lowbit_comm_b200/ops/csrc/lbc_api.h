@@ -142,7 +142,7 @@ typedef struct {
     unsigned long long timeout_ns;
     void* status;               // LbcStatus*, device visible
     int max_blocks;             // 0 = two blocks per SM
-    int ring_depth;             // rows in flight per block, 0 = default (3)
+    int ring_depth;             // rows in flight per block, 0 = as many as two blocks per SM leave room for (2..8)
     int stage_bytes;            // filled in by the launcher
     unsigned long long* profile;  // optional [gridDim.x][8] cycle counters (see pipe_kernels.cu), NULL = off
 } LbcPipe;

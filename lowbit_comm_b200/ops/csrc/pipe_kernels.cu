@@ -1,25 +1,31 @@
-// Pipelined compressed all-reduce for sm_100a: ONE persistent kernel per collective.
+// Fused compressed all-reduce for sm_100a: ONE persistent kernel per collective.
 //
-// Work unit: a row of 4096 elements (256 threads x 16).  Three kinds of rows:
+// Work unit: a row of 4096 elements (256 threads x 16).  Three phases, each a sweep over rows:
 //   QUANT   x (+ residual) -> int8/int4 groups + scales, written into this rank's own arena
 //   REDUCE  the owner of a shard pulls the row from all W ranks (bulk asynchronous loads over NVLink,
 //           `cp.async.bulk` global -> shared, no multicast, no tensor map), sums it in fp32 and
-//           requantizes it into its own arena (stages == 1: writes the result instead)
+//           requantizes it into its own arena (stages == 1: every rank reduces every row and writes
+//           the result instead)
 //   DECODE  every rank pulls the reduced row from its owner and decodes it into the output, updating
 //           the error-feedback residual
 // All cross-GPU traffic is loads issued by the copy engine of the SM into a ring of shared-memory
-// stages (3 rows in flight per block by default), so neither the load/store pipeline nor the register
-// file limits the bytes in flight over NVLink; flags are the only remote stores.
+// stages (as many rows in flight per block as two blocks per SM leave room for), so neither the
+// load/store pipeline nor the register file limits the bytes in flight over NVLink; flags are the
+// only remote stores.
 //
-// Scheduling: rows are handed out by a ticket counter in an order in which every row depends only on
-// rows with smaller tickets (QUANT of chunk s, REDUCE of chunk s-1 and DECODE of chunk s-2 are
-// interleaved row by row).  A block claims tickets in order and never blocks on a dependency while it
-// still holds claimed, unprocessed rows, therefore the schedule cannot deadlock whatever the grid size
-// or the number of resident blocks; HBM-bound QUANT rows, NVLink-bound REDUCE rows and DECODE rows of
-// neighbouring chunks are in flight at the same time.
+// Scheduling is static: block b takes rows b, b + grid, ... of every phase, so a row costs no atomics and
+// no bookkeeping beyond a few integer operations, and one lane issues the loads of the row that is
+// ring-depth rows ahead before the block computes the current one.  (Two dynamic schedules were built
+// and measured first -- a ticket counter with a helper warp, and one with the duties shared among the
+// computing warps; on a B200 both spent more time handing out rows than computing them: 2700-3300 cycles
+// per row against 1000-1300 of arithmetic.)  Between phases the ranks meet through one epoch flag per
+// (rank, phase): a block counts itself done on a local counter, the last block of the grid raises this
+// rank's flag on every rank, and every block's first warp waits (bounded) for the flags of the ranks it
+// is going to read from.  The grid must therefore be co-resident; the launcher sizes it from the
+// occupancy of the kernel, and one GPU must not run two of these kernels at once.
 //
-// Every wait (dependency flags, load completion barriers) is bounded: when it runs out the kernel
-// records where in the status word, waits (bounded again) for its own loads in flight and returns.
+// Every wait (phase flags, load completion barriers) is bounded: when it runs out the kernel records
+// where in the status word, waits (bounded again) for its own loads in flight and returns.
 //
 // Math is identical, bit for bit, to quant_push_kernel / reduce_kernel (fast_kernels.cu).
 // The reference runs the same algorithm as quantize -> NCCL all_to_all -> dequantize-reduce ->
@@ -32,27 +38,23 @@
 namespace lbc {
 
 constexpr int kRow = kThreads * kElemsPerThread;   // 4096 elements
-constexpr int kMaxRing = 4;
+constexpr int kMaxRing = 8;
 constexpr unsigned int kPhasePipeFlag = 8u;        // status.phase values 8..10: flag wait of QUANT/REDUCE/DECODE rows
 constexpr unsigned int kPhasePipeLoad = 12u;       // status.phase: a bulk load that never completed
 
 enum PipeKind : int { kQuant = 0, kReduce = 1, kDecode = 2 };
 
-struct __align__(16) PipeItem {
+struct PipeItem {
     int kind;
-    int chunk;
     int shard;        // QUANT: destination shard; REDUCE: this rank's shard; DECODE: owner of the row
-    int live;         // groups of the row that hold data
+    int live;         // groups of the row that hold data (0: a padding row, nothing to do)
     int copy;         // live rounded up to 8 groups: what the bulk loads move
     int dense_tma;    // the dense row (x / residual / prepared) comes through the copy engine
     int gl0;          // first group of the row inside its shard
-    int pad;
     long long first;      // first element of the row inside the tensor
     long long code_off;   // REDUCE / DECODE: arena offset of the row's codes ...
     long long scale_off;  // ... and of its scales
-    long long pad2;
 };
-static_assert(sizeof(PipeItem) == 64, "PipeItem is copied as four 16-byte vectors");
 
 // ---------------------------------------------------------------------------
 // mbarrier + bulk load helpers (shared::cta barriers, transaction counts in bytes)
@@ -63,11 +65,24 @@ __device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned int 
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned int bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned int parity) {
     unsigned int ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0u;
+}
+// Non-blocking look at a phase (`try_wait` may suspend the thread for a while before it answers "not yet").
+__device__ __forceinline__ bool mbar_test_wait(unsigned long long* bar, unsigned int parity) {
+    unsigned int ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
     return ok != 0u;
@@ -152,7 +167,7 @@ __device__ __forceinline__ void store_row_scales(ScaleStage& stage, uint8_t* sca
 // the kernel
 // ---------------------------------------------------------------------------
 template <typename T, int G, int BIT>
-__global__ void __launch_bounds__(kThreads + 32, 2) pipe_allreduce_kernel(const __grid_constant__ LbcPipe p) {
+__global__ void __launch_bounds__(kThreads, 2) pipe_allreduce_kernel(const __grid_constant__ LbcPipe p) {
     constexpr int lanes = G / kElemsPerThread;
     constexpr int VB = G * BIT / 8;
     constexpr int MB = sizeof(T);
@@ -165,18 +180,10 @@ __global__ void __launch_bounds__(kThreads + 32, 2) pipe_allreduce_kernel(const 
     constexpr int lim = BIT == 8 ? 127 : 7;
 
     extern __shared__ __align__(128) unsigned char ring[];
-    __shared__ __align__(8) unsigned long long full_bar[kMaxRing];
-    __shared__ PipeItem meta[kMaxRing];
-    __shared__ int s_tail, s_tail_refill, s_stop;       // s_stop: 1 = all rows done, 2 = a wait ran out
-    __shared__ unsigned short s_ready_reduce[LBC_MAX_RANKS];   // per owner: chunks whose REDUCE flag was seen
+    __shared__ __align__(8) unsigned long long full_bar[kMaxRing];    // a row's bytes have landed
+    __shared__ __align__(8) unsigned long long empty_bar[kMaxRing];   // all eight warps have left a row
+    __shared__ int s_fail;                              // a wait ran out
     __shared__ __align__(16) ScaleStage scale_stage;
-    // the schedule: segment s holds the QUANT rows of chunk s, the REDUCE rows of chunk s - 1 and the DECODE
-    // rows of chunk s - 2 (those that exist and that this launch runs), interleaved row by row
-    __shared__ long long seg_start[LBC_PIPE_MAX_CHUNKS + 3];
-    // A segment opens with `seg_lead` QUANT-only super-rows: the rows behind them wait for flags that the
-    // last rows of the previous segment raise, and the lead gives those stragglers time to finish while
-    // every block still has work that depends on nothing.
-    __shared__ int seg_lead[LBC_PIPE_MAX_CHUNKS + 3];
 
     const int W = p.world, me = p.rank;
     const bool two = p.stages == 2;
@@ -184,16 +191,11 @@ __global__ void __launch_bounds__(kThreads + 32, 2) pipe_allreduce_kernel(const 
     const int64_t SG = p.shard_groups;
     const int64_t n = p.numel;
     const int64_t num_groups = (n + G - 1) / G;
-    const int64_t shard_rows = (SG + RG - 1) / RG;
-    const int64_t rpc = p.rows_per_chunk;
-    const int C = p.num_chunks;
-    const int segs = C + (two ? 2 : 1);
-    const bool run_quant = (p.phase_mask & LBC_PIPE_QUANT) != 0, run_reduce = (p.phase_mask & LBC_PIPE_REDUCE) != 0;
-    const bool run_decode = two && (p.phase_mask & LBC_PIPE_DECODE) != 0;
+    const int shard_rows = int((SG + RG - 1) / RG);
     const int S = p.ring_depth;
     const int stage_bytes = p.stage_bytes;
     const int wlane = threadIdx.x & 31;
-    const bool producer = threadIdx.x >= kThreads;      // the ninth warp
+    const bool first_warp = threadIdx.x < 32;
 
     const T* x = static_cast<const T*>(p.x);
     const T* res = static_cast<const T*>(p.residual);
@@ -217,379 +219,235 @@ __global__ void __launch_bounds__(kThreads + 32, 2) pipe_allreduce_kernel(const 
     unsigned char* ctl = my_arena + p.ctl_off;
     const unsigned int* flags_quant = reinterpret_cast<const unsigned int*>(ctl + LBC_PIPE_CTL_FLAGS_QUANT);
     const unsigned int* flags_reduce = reinterpret_cast<const unsigned int*>(ctl + LBC_PIPE_CTL_FLAGS_REDUCE);
-    unsigned int* ticket = reinterpret_cast<unsigned int*>(ctl + LBC_PIPE_CTL_LOCAL);
-    unsigned int* exit_count = ticket + 1;
-    unsigned int* done_count = ticket + 2;              // [2][LBC_PIPE_MAX_CHUNKS]: QUANT rows, REDUCE rows
+    unsigned int* done_count = reinterpret_cast<unsigned int*>(ctl + LBC_PIPE_CTL_LOCAL) + 2;   // [kind]: blocks done
     volatile DeviceStatus* status = static_cast<volatile DeviceStatus*>(p.status);
 
-    auto rows_in_chunk = [&](int c) -> int64_t {
-        if (c < 0 || c >= C) return 0;
-        const int64_t left = shard_rows - int64_t(c) * rpc;
-        return left < 0 ? 0 : (left < rpc ? left : rpc);
-    };
-    // kinds a segment holds and the tickets of one of its super-rows
-    auto seg_kinds = [&](int sg, bool& q, bool& r, bool& d) -> int {
-        q = run_quant && sg < C;
-        r = run_reduce && sg >= 1 && sg - 1 < C;
-        d = run_decode && sg >= 2 && sg - 2 < C;
-        return (q ? shards : 0) + (r ? 1 : 0) + (d ? W : 0);
-    };
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kMaxRing; ++s) mbar_init(&full_bar[s], 1u);
-        s_tail = 0;
-        s_tail_refill = 0;
-        s_stop = 0;
+        for (int s = 0; s < kMaxRing; ++s) {
+            mbar_init(&full_bar[s], 1u);
+            mbar_init(&empty_bar[s], (unsigned int)(kThreads / 32));
+        }
+        s_fail = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        long long at = 0;
-        for (int sg = 0; sg < segs; ++sg) {
-            bool q, r, d;
-            const int per = seg_kinds(sg, q, r, d);
-            int64_t rows = 0;
-            if (q) rows = rows_in_chunk(sg);
-            if (r && rows_in_chunk(sg - 1) > rows) rows = rows_in_chunk(sg - 1);
-            if (d && rows_in_chunk(sg - 2) > rows) rows = rows_in_chunk(sg - 2);
-            int lead = 0;
-            if (q && (r || d)) lead = int(rows_in_chunk(sg) / 2);   // half a segment of slack
-            seg_lead[sg] = lead;
-            seg_start[sg] = at;
-            at += rows * per + int64_t(lead) * shards;
-        }
-        seg_start[segs] = at;
     }
-    if (threadIdx.x < LBC_MAX_RANKS) s_ready_reduce[threadIdx.x] = 0;
     __syncthreads();
-    const int64_t total_tickets = seg_start[segs];
-    // tickets are claimed a few at a time: one atomic per ticket on one address was most of the run time
-    int batch = int(total_tickets / (int64_t(gridDim.x) * 4));
-    batch = batch < 1 ? 1 : (batch > 8 ? 8 : batch);
 
-    // ---- state of the producer warp (uniform across its lanes) ----
-    int head = 0, tail = 0;                // rows consumed / rows issued (head is tracked by every thread)
-    bool has_pending = false, exhausted = false, failed = false;
-    PipeItem pend{};
-    unsigned int ready_quant = 0;          // chunks whose QUANT flags of all ranks were seen
-    int pub_chunk[2] = {-1, -1}, pub_rows[2] = {0, 0};   // finished rows not yet published: QUANT, REDUCE
-    PipeItem mine{};                                      // lane i decodes ticket i of the claimed batch ...
-    bool mine_valid = false;
-    int batch_at = 0, batch_count = 0, pend_from = 0;     // ... and the rows are issued one after the other
-    int cur_seg = 0;                                      // tickets only grow: the scan for a segment resumes here
+    auto vload = [](const int* w) -> int { return *reinterpret_cast<const volatile int*>(w); };
+    auto vstore = [](int* w, int v) { *reinterpret_cast<volatile int*>(w) = v; };
 
-    // Publishes finished rows of (kind, chunk): the last row of a chunk raises the chunk's flag on every rank.
-    // Called by all lanes of warp 0 after a block barrier behind the rows' stores.
-    auto publish = [&](int kind) {
-        if (pub_rows[kind] == 0) return;
-        const int c = pub_chunk[kind];
-        unsigned int prev = 0;
-        if (wlane == 0) {
-            // device scope is enough here (and far cheaper than system scope, which cost tens of microseconds
-            // per chunk when every block paid it): the one block that raises the flags fences at system scope
-            // after it has seen everybody's count, which orders all the rows before the flags
-            __threadfence();
-            prev = atomicAdd(done_count + kind * LBC_PIPE_MAX_CHUNKS + c, (unsigned int)pub_rows[kind]);
-        }
-        prev = __shfl_sync(0xffffffffu, prev, 0);
-        const int64_t expected = rows_in_chunk(c) * (kind == kQuant ? shards : 1);
-        if (int64_t(prev) + pub_rows[kind] == expected) {
-            if (wlane == 0) {
-                done_count[kind * LBC_PIPE_MAX_CHUNKS + c] = 0u;   // ready for the next collective
-                __threadfence_system();
-            }
-            __syncwarp();
-            if (wlane < W) {
-                const int64_t off = p.ctl_off + (kind == kQuant ? LBC_PIPE_CTL_FLAGS_QUANT : LBC_PIPE_CTL_FLAGS_REDUCE) +
-                                    (int64_t(me) * LBC_PIPE_MAX_CHUNKS + c) * 4;
-                st_release_sys(reinterpret_cast<unsigned int*>(p.arena[wlane] + off), p.epoch);
-            }
-        }
-        pub_rows[kind] = 0;
-        pub_chunk[kind] = -1;
+    // Position inside a phase's sweep.  A block's rows are `gridDim.x` apart, so the position is stepped with
+    // a few 32-bit additions per row; nothing is divided in the row loop.
+    //   QUANT : row r = shard * shard_rows + row     (a shard's rows are neighbours in memory)
+    //   REDUCE: row r = row of this rank's shard
+    //   DECODE: row r = row * W + k, owner (k + me) % W   (neighbouring rows come from different owners, and
+    //           every rank starts its sweep at itself)
+    struct Cursor {
+        int shard, row, k;
     };
-    auto note_done = [&](int kind, int chunk) {
-        if (kind == kDecode) return;
-        if (kind == kReduce && !two) return;               // one stage: nobody waits for reduced rows
-        // Only a chunk's last row matters to the waiting ranks, so a block publishes its rows of a chunk once:
-        // when it meets a later chunk (tickets are handed out in order: no more rows of the old one will come),
-        // before it sleeps on a flag, and when it leaves.
-        if (pub_chunk[kind] != chunk) publish(kind);
-        pub_chunk[kind] = chunk;
-        ++pub_rows[kind];
+    const int num_groups_i = int(num_groups), SG_i = int(SG);       // group counts fit 32 bits
+    auto cursor_at = [&](int kind, int r) -> Cursor {
+        Cursor c;
+        if (kind == kQuant) { c.shard = r / shard_rows; c.row = r - c.shard * shard_rows; c.k = 0; }
+        else if (kind == kReduce) { c.shard = two ? me : 0; c.row = r; c.k = 0; }
+        else { c.row = r / W; c.k = r - c.row * W; c.shard = (c.k + me) % W; }
+        return c;
     };
-
-    // ticket -> row; false for the empty slots of the schedule
-    auto decode_ticket = [&](int64_t t, PipeItem& it) -> bool {
-        while (cur_seg + 1 < segs && t >= seg_start[cur_seg + 1]) ++cur_seg;
-        const int seg = cur_seg;
-        bool q, r, d;
-        const unsigned int per = (unsigned int)seg_kinds(seg, q, r, d);
-        unsigned int rem = (unsigned int)(t - seg_start[seg]);       // a segment's tickets fit 32 bits
-        const unsigned int lead = (unsigned int)seg_lead[seg], lead_tickets = lead * (unsigned int)shards;
-        unsigned int j;
-        int k;
-        it.kind = -1;
-        if (rem < lead_tickets) {                       // the QUANT-only opening of the segment
-            j = rem / (unsigned int)shards;
-            it.kind = kQuant; it.chunk = seg; it.shard = int(rem - j * (unsigned int)shards);
-            k = 0;
+    const int step = int(gridDim.x);
+    const int step_shards = step / shard_rows, step_rows = step - step_shards * shard_rows;   // QUANT
+    const int step_w_rows = step / W, step_w_k = step - step_w_rows * W;                      // DECODE
+    auto advance = [&](int kind, Cursor& c) {
+        if (kind == kQuant) {
+            c.shard += step_shards;
+            c.row += step_rows;
+            if (c.row >= shard_rows) { c.row -= shard_rows; ++c.shard; }
+        } else if (kind == kReduce) {
+            c.row += step;
         } else {
-            rem -= lead_tickets;
-            j = rem / per;
-            k = int(rem - j * per);
+            c.row += step_w_rows;
+            c.k += step_w_k;
+            if (c.k >= W) { c.k -= W; ++c.row; }
+            c.shard = c.k + me;
+            if (c.shard >= W) c.shard -= W;
         }
-        if (it.kind < 0 && q) {
-            if (k < shards) { it.kind = kQuant; it.chunk = seg; it.shard = k; j += lead; }
-            k -= shards;
-        }
-        if (it.kind < 0 && r) {
-            if (k == 0) { it.kind = kReduce; it.chunk = seg - 1; it.shard = two ? me : 0; }
-            k -= 1;
-        }
-        if (it.kind < 0) { it.kind = kDecode; it.chunk = seg - 2; it.shard = (k + me) % W; }
-        if (int64_t(j) >= rows_in_chunk(it.chunk)) return false;   // an empty slot of the schedule
-        const int64_t row = int64_t(it.chunk) * rpc + j;
-        const int64_t gl0 = row * RG;
-        it.gl0 = int(gl0);
-        int64_t valid = num_groups - int64_t(it.shard) * SG;
-        valid = valid < 0 ? 0 : (valid > SG ? SG : valid);
-        int64_t live = valid - gl0;
+    };
+    // what the computing threads need to know about a row
+    auto item_at = [&](int kind, const Cursor& c) -> PipeItem {
+        PipeItem it;
+        it.kind = kind;
+        it.shard = c.shard;
+        it.gl0 = c.row * RG;
+        int valid = num_groups_i - c.shard * SG_i;
+        valid = valid < 0 ? 0 : (valid > SG_i ? SG_i : valid);
+        int live = valid - it.gl0;
         live = live < 0 ? 0 : (live > RG ? RG : live);
-        it.live = int(live);
-        it.copy = (it.live + 7) / 8 * 8;
-        it.first = (int64_t(it.shard) * SG + gl0) * G;
+        it.live = live;
+        it.copy = (live + 7) / 8 * 8;
+        it.first = int64_t(c.shard * SG_i + it.gl0) * G;
         // a dense row goes through the copy engine when its source is 16-byte aligned and no group of it is cut
         // by the end of the tensor; the other rows are read with plain guarded loads
-        const bool whole = it.first + live * G <= n;
-        if (it.kind == kQuant) {
-            it.dense_tma = (quant_tma_ok && whole) ? 1 : 0;
-            it.code_off = it.scale_off = 0;
-        } else {
-            const bool want_prep = prep != nullptr && (it.kind == kDecode || !two);
-            it.dense_tma = (want_prep && prep_tma_ok && whole) ? 1 : 0;
+        const bool whole = it.first + int64_t(live) * G <= n;
+        if (kind == kQuant) it.dense_tma = (quant_tma_ok && whole) ? 1 : 0;
+        else it.dense_tma = (prep != nullptr && (kind == kDecode || !two) && prep_tma_ok && whole) ? 1 : 0;
+        it.code_off = it.scale_off = 0;
+        return it;
+    };
+    // ... and what the issuing lanes need on top of that
+    auto with_sources = [&](PipeItem it) -> PipeItem {
+        if (it.kind != kQuant) {
             const int64_t region = it.kind == kReduce ? p.q_off + int64_t(it.shard) * p.shard_stride : p.ag_off;
-            it.code_off = region + gl0 * VB;
-            it.scale_off = region + SG * VB + gl0 * MB;
+            it.code_off = region + int64_t(it.gl0) * VB;
+            it.scale_off = region + SG * VB + int64_t(it.gl0) * MB;
         }
-        return true;
+        return it;
     };
 
-    // Non-blocking look at the flags a row depends on (all lanes of warp 0).
-    auto dep_ready = [&](const PipeItem& it, unsigned int& seen_out, int& peer_out) -> bool {
-        if (it.kind == kQuant) return true;
+    // Hands a row's loads to the copy engine (first warp; lane 0 arms the barrier, a REDUCE row spreads its
+    // sources over the lanes).
+    auto issue_row = [&](const PipeItem& it, int slot) {
+        unsigned long long* bar = &full_bar[slot];
+        unsigned char* base = ring + size_t(slot) * stage_bytes;
+        if (it.live == 0) {                             // padding row: nothing to move, the barrier still turns
+            if (wlane == 0) mbar_expect_tx(bar, 0u);
+            return;
+        }
+        const unsigned int dense_bytes = it.dense_tma ? (unsigned int)(it.live) * G * sizeof(T) : 0u;
+        const unsigned int code_bytes = (unsigned int)(it.copy) * VB, scale_bytes = (unsigned int)(it.copy) * MB;
         if (it.kind == kReduce) {
-            if ((ready_quant >> it.chunk) & 1u) return true;
-            unsigned int seen = p.epoch;
-            if (wlane < W) seen = ld_relaxed_sys(flags_quant + wlane * LBC_PIPE_MAX_CHUNKS + it.chunk);
-            const bool ok = int(seen - p.epoch) >= 0;
-            const unsigned int late = __ballot_sync(0xffffffffu, !ok);
-            if (late == 0u) {
-                fence_acq_rel_sys();                   // the rows behind the flags are visible from here on ...
-                fence_async_global();                  // ... also to the bulk loads (another memory proxy)
-                __syncwarp();
-                ready_quant |= 1u << it.chunk;
-                return true;
-            }
-            peer_out = __ffs(late) - 1;
-            seen_out = __shfl_sync(0xffffffffu, seen, peer_out);
-            return false;
-        }
-        if ((s_ready_reduce[it.shard] >> it.chunk) & 1u) return true;
-        unsigned int seen = 0;
-        if (wlane == 0) seen = ld_relaxed_sys(flags_reduce + it.shard * LBC_PIPE_MAX_CHUNKS + it.chunk);
-        seen = __shfl_sync(0xffffffffu, seen, 0);
-        if (int(seen - p.epoch) >= 0) {
-            fence_acq_rel_sys();
-            fence_async_global();
-            if (wlane == 0) s_ready_reduce[it.shard] |= (unsigned short)(1u << it.chunk);
-            __syncwarp();
-            return true;
-        }
-        peer_out = it.shard;
-        seen_out = seen;
-        return false;
-    };
-
-    // Hands the pending row's loads to the copy engine.  The row was decoded by lane `pend_from`, which also
-    // issues it; only a REDUCE row, with one source per rank, spreads its loads over the lanes.
-    auto issue = [&](int stage) {
-        unsigned long long* bar = &full_bar[stage];
-        unsigned char* base = ring + size_t(stage) * stage_bytes;
-        const bool mine_turn = wlane == pend_from;
-        if (pend.kind == kReduce) {
-            const long long code_off = __shfl_sync(0xffffffffu, mine.code_off, pend_from);
-            const long long scale_off = __shfl_sync(0xffffffffu, mine.scale_off, pend_from);
-            const unsigned int code_bytes = (unsigned int)(pend.copy) * VB, scale_bytes = (unsigned int)(pend.copy) * MB;
-            if (mine_turn) {
-                const unsigned int prep_bytes = mine.dense_tma ? (unsigned int)(mine.live) * G * sizeof(T) : 0u;
-                mbar_expect_tx(bar, (unsigned int)(W) * (code_bytes + scale_bytes) + prep_bytes);
-            }
+            if (wlane == 0) mbar_expect_tx(bar, (unsigned int)(W) * (code_bytes + scale_bytes) + dense_bytes);
             __syncwarp();
             if (wlane < W) {
                 unsigned char* dst = base + wlane * SUB;
-                bulk_load(dst, p.arena[wlane] + code_off, code_bytes, bar);
-                bulk_load(dst + RC, p.arena[wlane] + scale_off, scale_bytes, bar);
+                bulk_load(dst, p.arena[wlane] + it.code_off, code_bytes, bar);
+                bulk_load(dst + RC, p.arena[wlane] + it.scale_off, scale_bytes, bar);
             }
-            if (mine_turn && mine.dense_tma)
-                bulk_load(base + W * SUB, prep + mine.first, (unsigned int)(mine.live) * G * sizeof(T), bar);
-        } else if (mine_turn) {
-            const unsigned int dense_bytes = mine.dense_tma ? (unsigned int)(mine.live) * G * sizeof(T) : 0u;
-            if (mine.kind == kQuant) {
+            if (wlane == 0 && it.dense_tma) bulk_load(base + W * SUB, prep + it.first, dense_bytes, bar);
+        } else if (wlane == 0) {
+            if (it.kind == kQuant) {
                 mbar_expect_tx(bar, dense_bytes * (res != nullptr ? 2u : 1u));
-                if (mine.dense_tma) {
-                    bulk_load(base, x + mine.first, dense_bytes, bar);
-                    if (res != nullptr) bulk_load(base + RX, res + mine.first, dense_bytes, bar);
+                if (it.dense_tma) {
+                    bulk_load(base, x + it.first, dense_bytes, bar);
+                    if (res != nullptr) bulk_load(base + RX, res + it.first, dense_bytes, bar);
                 }
             } else {
-                const unsigned int code_bytes = (unsigned int)(mine.copy) * VB, scale_bytes = (unsigned int)(mine.copy) * MB;
-                const uint8_t* owner = p.arena[mine.shard];
+                const uint8_t* owner = p.arena[it.shard];
                 mbar_expect_tx(bar, code_bytes + scale_bytes + dense_bytes);
-                bulk_load(base, owner + mine.code_off, code_bytes, bar);
-                bulk_load(base + RC, owner + mine.scale_off, scale_bytes, bar);
-                if (mine.dense_tma) bulk_load(base + SUB, prep + mine.first, dense_bytes, bar);
+                bulk_load(base, owner + it.code_off, code_bytes, bar);
+                bulk_load(base + RC, owner + it.scale_off, scale_bytes, bar);
+                if (it.dense_tma) bulk_load(base + SUB, prep + it.first, dense_bytes, bar);
             }
-        }
-        if (mine_turn) {
-            const uint4* from = reinterpret_cast<const uint4*>(&mine);
-            uint4* to = reinterpret_cast<uint4*>(&meta[stage]);
-            to[0] = from[0]; to[1] = from[1]; to[2] = from[2]; to[3] = from[3];
         }
         __syncwarp();
     };
 
-    // Claims tickets and hands their loads to the copy engine until the ring is full, the schedule is used up
-    // or a row's flags are not there yet.  Only with an empty ring (`may_block`) does it sleep on a flag.
-    auto fill = [&](bool may_block) {
-        while (!failed && tail - head < S) {
-            if (!has_pending) {
-                if (batch_at >= batch_count) {
-                    if (exhausted) break;
-                    unsigned int t = 0;
-                    if (wlane == 0) t = atomicAdd(ticket, (unsigned int)batch);
-                    t = __shfl_sync(0xffffffffu, t, 0);
-                    if (int64_t(t) >= total_tickets) {
-                        exhausted = true;
-                        break;
-                    }
-                    const int64_t left = total_tickets - int64_t(t);
-                    batch_count = left < batch ? int(left) : batch;
-                    batch_at = 0;
-                    // the arithmetic of a ticket is a long dependent chain: the lanes do it side by side
-                    mine_valid = wlane < batch_count && decode_ticket(int64_t(t) + wlane, mine);
-                }
-                pend_from = batch_at++;
-                const bool valid = __shfl_sync(0xffffffffu, mine_valid ? 1 : 0, pend_from) != 0;
-                if (!valid) continue;
-                // what every lane has to know about the row; the rest stays with the lane that decoded it
-                pend.kind = __shfl_sync(0xffffffffu, mine.kind, pend_from);
-                pend.chunk = __shfl_sync(0xffffffffu, mine.chunk, pend_from);
-                pend.shard = __shfl_sync(0xffffffffu, mine.shard, pend_from);
-                pend.live = __shfl_sync(0xffffffffu, mine.live, pend_from);
-                pend.copy = __shfl_sync(0xffffffffu, mine.copy, pend_from);
-                if (pend.live == 0) {              // padding row: nothing to move, but its chunk still counts it
-                    note_done(pend.kind, pend.chunk);
-                    continue;
-                }
-                has_pending = true;
-            }
-            unsigned int seen = 0;
-            int peer = 0;
-            bool ready = dep_ready(pend, seen, peer);
-            if (!ready) {
-                if (!may_block || tail != head) break;   // first process what this block already holds
-                publish(kQuant);                   // nothing may stay unpublished while this block sleeps
-                publish(kReduce);
+    // optional cycle accounting (thread 0), per block: [0] rows  [1] waiting for a row's bytes  [2] computing
+    // [3] at the barrier that ends a phase  [4] waiting for the other ranks' phase flags  [5] publishing phases
+    // [6] total  [7] leaving rows and (every eighth row) handing a row to the copy engine
+    const bool prof = p.profile != nullptr && threadIdx.x == 0;
+    long long pc_wait = 0, pc_work = 0, pc_bar = 0, pc_flags = 0, pc_pub = 0, pc_rows = 0, pc_issue = 0;
+    const long long pc_start = clock64();
+
+    int consumed = 0;                                   // rows this block has been through: slot and parity of the ring
+    bool failed = false;
+    for (int kind = kQuant; kind <= kDecode && !failed; ++kind) {
+        if (((p.phase_mask >> kind) & 1) == 0 || (kind == kDecode && !two)) continue;
+        const int total = kind == kQuant ? shard_rows * shards : (kind == kReduce ? shard_rows : shard_rows * W);
+        const int first_row = blockIdx.x;
+        const int count = total > first_row ? (total - first_row + int(gridDim.x) - 1) / int(gridDim.x) : 0;
+        const int consumed_at_phase_start = consumed;
+
+        // ---- the other ranks' flags: QUANT of all ranks before REDUCE, REDUCE of all owners before DECODE ----
+        if (kind != kQuant) {
+            const long long pc_t0 = prof ? clock64() : 0;
+            if (first_warp) {
+                const unsigned int* flags = kind == kReduce ? flags_quant : flags_reduce;
                 const unsigned long long t0 = global_ns();
-                unsigned int spins = 0;
+                unsigned int spins = 0, seen = p.epoch;
                 for (;;) {
-                    ready = dep_ready(pend, seen, peer);
-                    if (ready) break;
-                    if ((++spins & 1023u) == 0) {      // the status word lives in host memory: look rarely
+                    seen = p.epoch;
+                    if (wlane < W) seen = ld_relaxed_sys(flags + wlane * LBC_PIPE_MAX_CHUNKS);
+                    const unsigned int late = __ballot_sync(0xffffffffu, int(seen - p.epoch) < 0);
+                    if (late == 0u) break;
+                    if ((++spins & 1023u) == 0) {       // the status word lives in host memory: look rarely
                         const bool failed_before = status != nullptr && status->code != 0u;
-                        const bool late = global_ns() - t0 > p.timeout_ns;
-                        if (failed_before || late) {
-                            if (late && !failed_before && wlane == 0 && status != nullptr) {
-                                status->phase = kPhasePipeFlag + (unsigned int)pend.kind;
+                        const bool too_long = global_ns() - t0 > p.timeout_ns;
+                        if (failed_before || too_long) {
+                            const int peer = __ffs(late) - 1;
+                            const unsigned int peer_seen = __shfl_sync(0xffffffffu, seen, peer);
+                            if (too_long && !failed_before && wlane == 0 && status != nullptr) {
+                                status->phase = kPhasePipeFlag + (unsigned int)kind;
                                 status->peer = (unsigned int)peer;
-                                status->seen = seen;
+                                status->seen = peer_seen;
                                 status->expected = p.epoch;
                                 __threadfence_system();
                                 status->code = 1u;
                                 __threadfence_system();
                             }
-                            failed = true;
+                            if (wlane == 0) s_fail = 1;
                             break;
                         }
                     }
                     __nanosleep(spins < 64u ? 100 : 500);
                 }
-                if (!ready) break;
+                fence_acq_rel_sys();                    // the rows behind the flags are visible from here on ...
+                fence_async_global();                   // ... also to the bulk loads (another memory proxy)
             }
-            issue(tail % S);
-            ++tail;
-            has_pending = false;
+            __syncthreads();
+            if (prof) pc_flags += clock64() - pc_t0;
+            if (s_fail != 0) {
+                failed = true;
+                break;
+            }
         }
-    };
-    // Ring state for the other warps.  Two words, so that nobody ever reads a word in the phase in which it
-    // is written with a different meaning: `s_tail` is written while the others compute (before the row's
-    // barrier) and read right after that barrier; `s_tail_refill` is written while the others wait for a
-    // refill of the empty ring (between the row's barrier and the refill barrier) and read after the latter.
-    auto publish_refill = [&]() {
-        if (wlane == 0) {
-            s_tail_refill = tail;
-            if (failed) s_stop = 2;
-            else if (tail == head && exhausted && !has_pending) s_stop = 1;
-        }
-    };
 
-    // Warps 0..7 compute, warp 8 produces: it claims rows and issues their loads while the others work on
-    // the row at the head of the ring.  One block barrier per row; a second one only when the ring ran empty.
-    if (producer) {
-        fill(true);
-        publish_refill();
-    }
-    __syncthreads();
-    int tail_seen = s_tail_refill, stop_seen = s_stop;
-    // optional cycle accounting (one consumer thread and the producer's first lane per block):
-    // [0] rows  [1] consumer: waiting for loads  [2] consumer: computing  [3] consumer: at barriers
-    // [4] producer: claiming and issuing  [5] producer: asleep on flags + refills  [6] total  [7] rows issued
-    const bool prof = p.profile != nullptr && (threadIdx.x == 0 || threadIdx.x == kThreads);
-    long long pc_wait = 0, pc_work = 0, pc_bar = 0, pc_fill = 0, pc_refill = 0, pc_rows = 0;
-    const long long pc_start = clock64();
-    // leaves when a wait ran out, or when nothing is left: the producer only leaves the ring empty once the
-    // schedule is used up
-    while (stop_seen != 2 && head < tail_seen) {
-        const int stage = head % S;
-        const PipeItem it = meta[stage];
-        const unsigned char* base = ring + size_t(stage) * stage_bytes;
-        long long pc_t0 = prof ? clock64() : 0, pc_t1 = 0;
-        if (producer) {
-            fill(false);
-            if (wlane == 0) s_tail = tail;
-            if (prof) pc_fill += clock64() - pc_t0;
+        // ---- the sweep ----
+        // S rows are in flight.  The eight warps walk the rows at their own pace: a warp waits for a row's bytes,
+        // computes its 512 elements and arrives on the slot's "empty" barrier; there is no block barrier per
+        // row.  Handing a row to the copy engine costs one warp several hundred cycles, so that duty rotates:
+        // warp i % 8 waits until all eight have left row i and issues row i + S into the freed slot, while the
+        // other seven are already at work on the rows behind it.
+        Cursor here = cursor_at(kind, first_row), ahead = here;   // the row being computed, the next row to issue
+        if (first_warp) {
+            for (int k = 0; k < S && k < count; ++k) {
+                issue_row(with_sources(item_at(kind, ahead)), (consumed + k) % S);
+                advance(kind, ahead);
+            }
         } else {
-            // ---- wait for the row's loads ----
-            const unsigned int parity = (unsigned int)(head / S) & 1u;
-            bool arrived = mbar_try_wait(&full_bar[stage], parity);
+            for (int k = 0; k < S && k < count; ++k) advance(kind, ahead);
+        }
+        const int warp = threadIdx.x >> 5;
+        for (int i = 0; i < count; ++i) {
+            const long long pc_t0 = prof ? clock64() : 0;
+            const int slot = consumed % S;
+            const PipeItem it = item_at(kind, here);
+            advance(kind, here);
+            const unsigned char* base = ring + size_t(slot) * stage_bytes;
+            const unsigned int parity = (unsigned int)(consumed / S) & 1u;
+            bool arrived = mbar_try_wait(&full_bar[slot], parity);
             if (!arrived) {
                 const unsigned long long t0 = global_ns();
                 unsigned int spins = 0;
-                while (!(arrived = mbar_try_wait(&full_bar[stage], parity))) {
-                    if ((++spins & 63u) == 0 && global_ns() - t0 > p.timeout_ns) break;
+                while (!(arrived = mbar_try_wait(&full_bar[slot], parity))) {
+                    if ((++spins & 63u) == 0 && (global_ns() - t0 > p.timeout_ns || vload(&s_fail) != 0)) break;
                 }
             }
             arrived = __all_sync(0xffffffffu, arrived) != 0;   // the row's math shuffles across the whole warp
             if (!arrived) {
-                if (status != nullptr && status->code == 0u) {
-                    status->phase = kPhasePipeLoad;
-                    status->peer = (unsigned int)it.shard;
-                    status->seen = (unsigned int)it.kind;
-                    status->expected = p.epoch;
-                    __threadfence_system();
-                    status->code = 1u;
-                    __threadfence_system();
+                if (wlane == 0 && vload(&s_fail) == 0) {
+                    if (status != nullptr && status->code == 0u) {
+                        status->phase = kPhasePipeLoad;
+                        status->peer = (unsigned int)it.shard;
+                        status->seen = (unsigned int)it.kind;
+                        status->expected = p.epoch;
+                        __threadfence_system();
+                        status->code = 1u;
+                        __threadfence_system();
+                    }
+                    vstore(&s_fail, 1);
                 }
-                s_stop = 2;
+                break;
             }
-            if (prof) { pc_t1 = clock64(); pc_wait += pc_t1 - pc_t0; }
-            if (arrived) {
+            const long long pc_t1 = prof ? clock64() : 0;
+            if (it.live != 0) {
                 const int gl = int(threadIdx.x) / lanes;           // my group inside the row
                 const int lane = int(threadIdx.x) - gl * lanes;
                 const bool live = gl < it.live;
@@ -690,66 +548,86 @@ __global__ void __launch_bounds__(kThreads + 32, 2) pipe_allreduce_kernel(const 
                     }
                 }
             }
+            const long long pc_t2 = prof ? clock64() : 0;
+            __syncwarp();                               // this warp's stores of the row are issued
+            if (wlane == 0) mbar_arrive(&empty_bar[slot]);
+            if (i + S < count && warp == (i & 7)) {     // my turn: refill the slot with row i + S once all have left it
+                bool freed = mbar_try_wait(&empty_bar[slot], parity);
+                if (!freed) {
+                    const unsigned long long t0 = global_ns();
+                    unsigned int spins = 0;
+                    while (!(freed = mbar_try_wait(&empty_bar[slot], parity))) {
+                        if ((++spins & 63u) == 0 && (global_ns() - t0 > p.timeout_ns || vload(&s_fail) != 0)) break;
+                    }
+                }
+                if (__all_sync(0xffffffffu, freed) == 0) {
+                    if (wlane == 0) vstore(&s_fail, 1);   // a warp never left the row: its own wait says why
+                    break;
+                }
+                issue_row(with_sources(item_at(kind, ahead)), slot);
+            }
+            advance(kind, ahead);
+            ++consumed;
+            if (prof) {
+                const long long pc_t3 = clock64();
+                pc_wait += pc_t1 - pc_t0; pc_work += pc_t2 - pc_t1; pc_issue += pc_t3 - pc_t2; ++pc_rows;
+            }
         }
-        long long pc_t2 = 0;
-        if (prof) { pc_t2 = clock64(); if (!producer) pc_work += pc_t2 - pc_t1; ++pc_rows; }
-        __syncthreads();                 // the stage is free again and the row's stores are issued
-        if (prof) pc_bar += clock64() - pc_t2;
-        stop_seen = s_stop;              // 2 if a load wait ran out in this row
-        if (stop_seen == 2) break;
-        ++head;
-        // The producer may already be writing the next row's value into `s_tail`; whichever value a thread
-        // reads, it is the count of rows issued so far or more, and "ring empty" (equal to head) can only be
-        // read while the producer sits in the refill branch below, where it does not write this word.
-        tail_seen = s_tail;
-        if (head == tail_seen) {         // the ring ran empty: the producer claims, and may have to sleep on a flag
-            const long long pc_t3 = prof ? clock64() : 0;
-            if (producer) {
-                note_done(it.kind, it.chunk);
-                fill(true);
-                publish_refill();
+        // every warp is through with the phase's rows (or a wait ran out)
+        {
+            const long long pc_t0 = prof ? clock64() : 0;
+            __syncthreads();
+            if (prof) pc_bar += clock64() - pc_t0;
+        }
+        if (s_fail != 0) {
+            failed = true;
+            // loads may still be in flight: give them a bounded time to land before this block's shared memory is
+            // handed to another block (a load from a rank that is gone never lands; nothing more can be done)
+            if (threadIdx.x == 0) {
+                const unsigned long long t0 = global_ns();
+                while (global_ns() - t0 < 100000ull) __nanosleep(1000);
             }
             __syncthreads();
-            if (prof) pc_refill += clock64() - pc_t3;
-            tail_seen = s_tail_refill;
-            stop_seen = s_stop;
-        } else if (producer) {
-            note_done(it.kind, it.chunk);
+            break;
         }
-    }
+        // `consumed` is the same in every warp again: count rows of the phase
+        consumed = consumed_at_phase_start + count;
+        if (failed) break;
 
-    if (stop_seen == 2) {
-        // a wait ran out: give this block's loads that are still in flight a bounded chance to land,
-        // then leave; the host resets the control block before the workspace is used again
-        const int issued = s_tail > s_tail_refill ? s_tail : s_tail_refill;
-        for (int h = head; h < issued; ++h) {
-            const unsigned int parity = (unsigned int)(h / S) & 1u;
-            const unsigned long long t0 = global_ns();
-            while (!mbar_try_wait(&full_bar[h % S], parity)) {
-                if (global_ns() - t0 > 2000000ull) break;
+        // ---- this block is through with the phase; the last block of the grid tells every rank ----
+        if (kind == kQuant || (kind == kReduce && two)) {
+            const long long pc_t0 = prof ? clock64() : 0;
+            if (first_warp) {
+                unsigned int prev = 0;
+                if (wlane == 0) {
+                    // device scope is enough here (and far cheaper than system scope): the one block that raises
+                    // the flags fences at system scope after it has seen everybody's count, which orders all the
+                    // rows of all blocks before the flags
+                    __threadfence();
+                    prev = atomicAdd(done_count + kind, 1u);
+                }
+                prev = __shfl_sync(0xffffffffu, prev, 0);
+                if (prev == gridDim.x - 1) {
+                    if (wlane == 0) {
+                        done_count[kind] = 0u;          // ready for the next collective
+                        __threadfence_system();
+                    }
+                    __syncwarp();
+                    if (wlane < W) {
+                        const int64_t off = p.ctl_off + (kind == kQuant ? LBC_PIPE_CTL_FLAGS_QUANT : LBC_PIPE_CTL_FLAGS_REDUCE) +
+                                            int64_t(me) * LBC_PIPE_MAX_CHUNKS * 4;
+                        st_release_sys(reinterpret_cast<unsigned int*>(p.arena[wlane] + off), p.epoch);
+                    }
+                }
             }
+            if (prof) pc_pub += clock64() - pc_t0;
         }
-        return;
     }
     if (prof) {
         unsigned long long* row = p.profile + size_t(blockIdx.x) * 8;
-        if (!producer) {
-            row[0] = pc_rows; row[1] = pc_wait; row[2] = pc_work; row[3] = pc_bar; row[6] = clock64() - pc_start;
-        } else {
-            row[4] = pc_fill; row[5] = pc_refill; row[7] = (unsigned long long)tail;
-        }
-    }
-    if (producer) {
-        publish(kQuant);
-        publish(kReduce);
-        if (wlane == 0) {
-            const unsigned int gone = atomicAdd(exit_count, 1u);
-            if (gone == gridDim.x - 1) {               // every block has claimed its last ticket
-                *ticket = 0u;
-                *exit_count = 0u;
-                __threadfence();
-            }
-        }
+        row[0] = pc_rows; row[1] = pc_wait; row[2] = pc_work; row[3] = pc_bar; row[4] = pc_flags; row[5] = pc_pub;
+        row[6] = clock64() - pc_start;
+        row[7] = pc_issue;
     }
 }
 
@@ -799,9 +677,10 @@ struct PipeLauncher {
         LbcPipe launch = *p;
         launch.stage_bytes = stage_bytes_for(p->dtype, G, BIT, p->world, p->stages, p->residual != nullptr,
                                              p->prepared != nullptr);
-        int depth = p->ring_depth > 0 ? p->ring_depth : 3;
+        // as many rows in flight as two blocks per SM leave room for (the default), at least two
+        int depth = p->ring_depth > 0 ? p->ring_depth : kMaxRing;
         if (depth > kMaxRing) depth = kMaxRing;
-        while (depth > 2 && depth * launch.stage_bytes > 110 * 1024) --depth;
+        while (depth > 2 && depth * launch.stage_bytes > 108 * 1024) --depth;
         if (depth < 2) depth = 2;
         const int smem = depth * launch.stage_bytes;
         if (smem > 220 * 1024) return cudaErrorInvalidValue;
@@ -818,15 +697,21 @@ struct PipeLauncher {
             err = cudaFuncSetAttribute(pipe_allreduce_kernel<T, G, BIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
             if (err != cudaSuccess) return err;
         }
-        const int per_sm = smem <= 110 * 1024 ? 2 : 1;
+        // The phases meet through grid-wide counters, so every block must be resident: the grid is what the
+        // occupancy of this kernel allows (two blocks per SM by design), never more.
+        int per_sm = 0;
+        err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, pipe_allreduce_kernel<T, G, BIT>, kThreads, smem);
+        if (err != cudaSuccess) return err;
+        if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+        if (per_sm > 2) per_sm = 2;
         const int64_t shard_rows = (p->shard_groups + (kRow / G) - 1) / (kRow / G);
-        const int shards = p->stages == 2 ? p->world : 1;
-        int64_t rows = shard_rows * shards * (p->stages == 2 ? 2 : 1) + shard_rows;   // upper bound of the work
+        int64_t rows = shard_rows * p->world;          // the longest sweep (QUANT or DECODE of a two-stage call)
+        if (p->stages == 1) rows = shard_rows;
         int grid = sms * per_sm;
         if (p->max_blocks > 0 && grid > p->max_blocks) grid = p->max_blocks;
         if (rows < 1) rows = 1;
         if (int64_t(grid) > rows) grid = int(rows);
-        pipe_allreduce_kernel<T, G, BIT><<<grid, kThreads + 32, smem, stream>>>(launch);
+        pipe_allreduce_kernel<T, G, BIT><<<grid, kThreads, smem, stream>>>(launch);
         return cudaGetLastError();
     }
 };
@@ -856,9 +741,7 @@ cudaError_t lbc_pipe_allreduce(const LbcPipe* p, cudaStream_t stream) {
     const int64_t row_groups = LBC_PIPE_ROW_ELEMS / p->group_size;
     const int64_t shard_rows = (p->shard_groups + row_groups - 1) / row_groups;
     if (int64_t(p->num_chunks) * p->rows_per_chunk < shard_rows) return cudaErrorInvalidValue;
-    // tickets are 32-bit
-    const int64_t per = p->stages == 2 ? 2 * p->world + 1 : 2;
-    if ((p->num_chunks + 2) * p->rows_per_chunk * per >= (int64_t(1) << 31)) return cudaErrorInvalidValue;
+    if (shard_rows * p->world >= (int64_t(1) << 31)) return cudaErrorInvalidValue;   // row indices are 32-bit
     for (int r = 0; r < p->world; ++r)
         if (p->arena[r] == nullptr || (reinterpret_cast<uintptr_t>(p->arena[r]) & 15) != 0) return cudaErrorInvalidValue;
     if (p->numel == 0) return cudaSuccess;

@@ -112,6 +112,36 @@ class Communicator:
             return False
         return True
 
+    def general_peer_usable(self, tensor: Any, config: CompressionConfig) -> bool:
+        """CUDA tensor with a profile the production kernels do not serve (top-k, code-books, stochastic
+        rounding): the general kernels plus this library's own peer-memory transport can take it."""
+
+        if self.transport == "torch" or not bool(getattr(tensor, "is_cuda", False)) or codec.is_fast_profile(config):
+            return False
+        status = self._ext()
+        return bool(status.available) and self._peer_failed is None and hasattr(status.module, "quant_general")
+
+    def general_workspace(self, tensor: Any, config: CompressionConfig, dtype: str):
+        """Workspace of the general-profile all-reduce able to hold `tensor` (capacity grows in powers of two)."""
+
+        from .fused_general import GeneralPeerWorkspace
+
+        if self.peer_group is not None:
+            self.peer_group.check_status()
+        key = ("general", dtype, config)
+        ws = self._workspaces.get(key)
+        if ws is not None and ws.max_numel >= tensor.numel():
+            return ws
+        cap = 1 << max(16, (max(1, tensor.numel()) - 1).bit_length())
+        need = GeneralPeerWorkspace.required_bytes(self.world_size, dtype, config, cap)
+        group = self._ensure_peer_group(tensor.device, need)
+        if group.bytes_free < need:
+            raise CCDLUnavailableError(
+                f"peer arena too small for a {cap}-element general-profile workspace ({group.bytes_free} < {need} bytes)")
+        ws = GeneralPeerWorkspace(group, dtype=dtype, config=config, max_numel=cap, max_blocks=self.max_blocks)
+        self._workspaces[key] = ws
+        return ws
+
     def _ensure_peer_group(self, device, need_bytes: int):
         from .peer_memory import PeerGroup
 
@@ -220,6 +250,19 @@ class Communicator:
                 with scope:
                     result = ws.all_reduce(tensor, out, residual=residual, update_residual=update_residual, op=op,
                                            stages=stages, ef_mode=ef_mode)
+                self.stats["peer_ops"] += 1
+                return self._finish(result, side, resources=(tensor, out, residual))
+        if self.general_peer_usable(tensor, config) and tensor.is_contiguous() and (out is None or out.is_contiguous()):
+            try:
+                gws = self.general_workspace(tensor, config, name)
+            except CCDLUnavailableError:
+                if self.transport == "peer":
+                    raise
+                gws = None
+            if gws is not None:
+                scope, side = self._stream_scope(tensor, async_op)
+                with scope:
+                    result = gws.all_reduce(tensor, out, residual=residual, update_residual=update_residual, op=op)
                 self.stats["peer_ops"] += 1
                 return self._finish(result, side, resources=(tensor, out, residual))
         result = self._torch_all_reduce(tensor, config, op, stages, name, out, residual, update_residual)
@@ -404,20 +447,45 @@ class Communicator:
                                 async_op: bool = False, dtype: str = "auto", out: Any = None,
                                 local_group_size: int | None = None) -> Any:
         """Three stages: intra-group compressed reduce-scatter (full -> shard), inter-group
-        compressed all-reduce of the shard, intra-group compressed all-gather (shard -> full)."""
+        compressed all-reduce of the shard, intra-group compressed all-gather (shard -> full).
+
+        On CUDA tensors the three stages are chained on one stream over the sub-groups' fused workspaces:
+        scatter + reduce kernels leave this rank's shard in a cached dense buffer, the pipelined kernel
+        all-reduces it in place across the groups, and one quantize launch plus one decode launch gather the
+        group's shards straight into the output (reference: the compiled three-stage chain with one stream
+        per stage, ccdl_comm/cuda/transports/hierarchical.py:184-265).
+        """
 
         torch = import_module("torch")
         L = local_group_size or self._default_local_group()
         local, inter = self.sub_communicators(L)
         name = codec.resolve_dtype(dtype, tensor)
         n = tensor.numel()
+        target = tensor if out is None else out
+        if self.peer_usable(tensor, config) and tensor.is_contiguous() and target.is_contiguous():
+            from .fused import geometry
+
+            geo = geometry(n, local.world_size, name, config)
+            ws_local = local.workspace(tensor, config, name)
+            key = ("hier_shard", name, geo.shard_numel, str(tensor.device))
+            shard = self._subcomms.get(key)
+            if shard is None:
+                shard = self._subcomms[key] = torch.empty(geo.shard_numel, dtype=tensor.dtype, device=tensor.device)
+            ws_inter = inter.workspace(shard, config, name) if inter.world_size > 1 else None
+            scope, side = self._stream_scope(tensor, async_op)
+            with scope:
+                ws_local.reduce_scatter(tensor.reshape(-1), shard, op=op)
+                if ws_inter is not None:
+                    ws_inter.all_reduce(shard, op=op, stages=1)
+                ws_local.gather_shards(shard, target.reshape(-1))
+            self.stats["peer_ops"] += 1
+            return self._finish(target, side, resources=(tensor, target, shard))
         shard = local.reduce_scatter_shard(tensor, config=config, op=op, dtype=name)
         piece = shard.shard
         if inter.world_size > 1:
             piece = inter.all_reduce(piece, config=config, op=op, strategy="all_gather", dtype=name)
         parts = local.all_gather(piece, config=config, dtype=name)
         full = torch.cat([p.reshape(-1) for p in parts])[:n].reshape(tensor.shape)
-        target = tensor if out is None else out
         target.copy_(full)
         return ImmediateWork(target) if async_op else target
 
@@ -441,9 +509,10 @@ class Communicator:
         if self.closed:
             return
         self.closed = True
-        for local, inter in self._subcomms.values():
-            local.close()
-            inter.close()
+        for entry in self._subcomms.values():
+            if isinstance(entry, tuple):             # (local communicator, inter communicator); other entries are buffers
+                for sub in entry:
+                    sub.close()
         if self.peer_group is not None:
             self.peer_group.close()
             self.peer_group = None

@@ -324,14 +324,17 @@ class _PeerEngine:
     def _make_workspace(self, dtype: str, cap: int):
         from .fused import FusedWorkspace
 
-        ws = FusedWorkspace(self.group, dtype=dtype, config=self.config, max_numel=cap, max_blocks=self.max_blocks)
+        # buckets always go through the single persistent kernel: the arena is sized for its regions only
+        ws = FusedWorkspace(self.group, dtype=dtype, config=self.config, max_numel=cap, max_blocks=self.max_blocks,
+                            engine=os.environ.get("LBC_ENGINE") or "pipe")
         ws.gate = ws.group.world_size > 1     # line the ranks up before the persistent kernel takes the SMs
         return ws
 
     def _need(self, world: int, dtype: str, cap: int) -> int:
         from .fused import FusedWorkspace
 
-        return FusedWorkspace.required_bytes(world, dtype, self.config, cap, False, engine="pipe") + (1 << 20)
+        engine = "pipe" if (os.environ.get("LBC_ENGINE") or "pipe") == "pipe" else "both"
+        return FusedWorkspace.required_bytes(world, dtype, self.config, cap, world <= 2, engine=engine) + (1 << 20)
 
     def _world(self) -> int:
         if self.group is not None:
@@ -672,7 +675,7 @@ def create_ddp_comm_hook(
         ws = peer.ensure(tensor, name)
         decision = policy.decide(key, numel=tensor.numel())
         residual = feedback.residual_for(key, tensor) if (decision.apply or decision.update) else None
-        stages = {"all_gather": 1, "reduce_scatter": 2, "topology": 2, "hierarchical": 2}.get(effective)
+        stages = {"all_gather": 1, "reduce_scatter": 2, "topology": 2}.get(effective)
         producer = torch.cuda.current_stream(tensor.device)
         peer.stream.wait_stream(producer)
         with torch.cuda.stream(peer.stream):
@@ -682,6 +685,74 @@ def create_ddp_comm_hook(
             future.set_result(tensor)
         policy.advance(key)
         hook_ref[0].stats["peer"] += 1
+        return future
+
+    def peer_hierarchical_bucket(bucket: Any) -> Any:
+        """strategy="hierarchical" on CUDA: the communicator's three-stage chain (reduce-scatter inside the local
+        group, all-reduce of the shard across groups, gather inside the group) on the side stream, with the
+        reference's error-feedback rule around it: prepared = T(gradient + residual) goes in, and the residual
+        becomes T(prepared - result)."""
+
+        torch = import_module("torch")
+        from .communicator import get_communicator
+        from .completion import comm_stream
+
+        tensor = bucket.buffer()
+        key = _bucket_key(bucket)
+        comm = get_communicator(process_group)
+        comm.check_status()
+        decision = policy.decide(key, numel=tensor.numel())
+        residual = feedback.residual_for(key, tensor) if (decision.apply or decision.update) else None
+        if peer.stream is None:
+            peer.stream = comm_stream(tensor.device)
+        peer.stream.wait_stream(torch.cuda.current_stream(tensor.device))
+        with torch.cuda.stream(peer.stream):
+            if residual is not None and decision.apply:
+                tensor.add_(residual)
+            if residual is not None and decision.update:
+                residual.copy_(tensor)                              # `prepared`, parked in the residual buffer
+            comm.hierarchical_all_reduce(tensor, config=config, op=reduce, local_group_size=local_group_size)
+            if residual is not None and decision.update:
+                codec.update_error_feedback_residual(residual, tensor, residual, extension_status=extension_status)
+            future = torch.futures.Future(devices=[tensor.device])
+            future.set_result(tensor)
+        policy.advance(key)
+        hook_ref[0].stats["peer"] += 1
+        hook_ref[0].stats["hierarchical"] = hook_ref[0].stats.get("hierarchical", 0) + 1
+        return future
+
+    def use_general_peer(tensor: Any) -> bool:
+        """CUDA bucket with a top-k / code-book / stochastic profile: general kernels + peer-memory transport."""
+
+        if transport == "torch" or injected or not bool(getattr(tensor, "is_cuda", False)):
+            return False
+        if codec.is_fast_profile(config) or effective == "native_nccl":
+            return False
+        status = extension_status if extension_status is not None else load_cuda_extension()
+        return bool(status.available)
+
+    def peer_general_bucket(bucket: Any) -> Any:
+        torch = import_module("torch")
+        from .communicator import get_communicator
+        from .completion import comm_stream
+
+        tensor = bucket.buffer()
+        key = _bucket_key(bucket)
+        comm = get_communicator(process_group)
+        comm.check_status()
+        decision = policy.decide(key, numel=tensor.numel())
+        residual = feedback.residual_for(key, tensor) if (decision.apply or decision.update) else None
+        if peer.stream is None:
+            peer.stream = comm_stream(tensor.device)
+        peer.stream.wait_stream(torch.cuda.current_stream(tensor.device))
+        with torch.cuda.stream(peer.stream):
+            comm.all_reduce(tensor, config=config, op=reduce, strategy="all_gather",
+                            residual=residual if decision.apply else None, update_residual=decision.update)
+            future = torch.futures.Future(devices=[tensor.device])
+            future.set_result(tensor)
+        policy.advance(key)
+        hook_ref[0].stats["peer"] += 1
+        hook_ref[0].stats["general"] = hook_ref[0].stats.get("general", 0) + 1
         return future
 
     # --------------------------------------------------------------- torch engine
@@ -870,7 +941,9 @@ def create_ddp_comm_hook(
             hook_ref[0].stats["bypassed"] += 1
             return plain_all_reduce(_clone(tensor), reduce)
         if use_peer(tensor):
-            return peer_bucket(bucket)
+            return peer_hierarchical_bucket(bucket) if effective == "hierarchical" else peer_bucket(bucket)
+        if use_general_peer(tensor) and bool(getattr(tensor, "is_contiguous", lambda: False)()):
+            return peer_general_bucket(bucket)
         return torch_bucket(bucket)
 
     holder = DDPCommHook(process_bucket, future_factory)

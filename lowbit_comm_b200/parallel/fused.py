@@ -160,14 +160,17 @@ class FusedWorkspace:
         self.gather_off: list[int] | None = None
         self._want_gather = bool(with_gather_region or (with_gather_region is None and W <= 2))
         # pipelined engine: own quantized payload, own reduced shard, control block
-        self.engine = (engine or os.environ.get("LBC_ENGINE", "pipe")).lower()
-        if self.engine not in ("pipe", "legacy"):
-            raise ValueError("engine must be 'pipe' or 'legacy'")
+        self.engine = (engine or os.environ.get("LBC_ENGINE", "auto")).lower()
+        if self.engine not in ("auto", "pipe", "legacy"):
+            raise ValueError("engine must be 'auto', 'pipe' or 'legacy'")
         if not hasattr(self.ext, "PipeAllReducePlan"):
             self.engine = "legacy"
-        self.gate = False                           # rendezvous kernel in front of the pipelined kernel
+        # "auto": the single persistent kernel up to this many bytes, the kernel sequence above (measured on
+        # 4 x B200: the single kernel is ahead up to 128 MiB, by a fifth around 32 MiB, and 4-9 % behind from 256 MiB)
+        self.pipe_max_bytes = int(float(os.environ.get("LBC_PIPE_MAX_MIB", "192")) * (1 << 20))
+        self.gate = False                           # rendezvous kernel in front of the single persistent kernel
         self._pipe = None
-        if self.engine == "pipe":
+        if self.engine in ("auto", "pipe"):
             self._build_pipe()
         else:
             self._ensure_legacy()
@@ -210,16 +213,24 @@ class FusedWorkspace:
         two = world_size * _round_up(shard_groups * group_bytes, 256)
         return max(one, two), _round_up(shard_groups * group_bytes, 256)
 
+    def _pipe_numel(self) -> int:
+        """Elements the single-kernel engine has to hold: everything, or in "auto" what fits its size limit."""
+
+        if self.engine != "auto":
+            return self.max_numel
+        return min(self.max_numel, self.pipe_max_bytes // dtype_bytes(self.dtype))
+
     def _build_pipe(self) -> None:
         group = self.group
-        q_bytes, ag_bytes = self.pipe_region_bytes(group.world_size, self.dtype, self.config, self.max_numel)
+        self.pipe_numel = self._pipe_numel()
+        q_bytes, ag_bytes = self.pipe_region_bytes(group.world_size, self.dtype, self.config, self.pipe_numel)
         self.pipe_q_off, self.pipe_q_bytes = group.alloc(q_bytes), q_bytes
         self.pipe_ag_off, self.pipe_ag_bytes = group.alloc(ag_bytes), ag_bytes
         self.pipe_ctl_off = group.alloc(int(self.ext.PIPE_CTL_BYTES))
         self._pipe = self.ext.PipeAllReducePlan(
             _DTYPE_CODE[self.dtype], self.config.group_size, self.config.bit, group.rank, list(group.peer_ptrs),
             self.pipe_q_off, q_bytes, self.pipe_ag_off, ag_bytes, self.pipe_ctl_off, group.timeout_ns,
-            group.status_device, self.max_blocks, self.max_numel)
+            group.status_device, self.max_blocks, self.pipe_numel)
         rows = os.environ.get("LBC_PIPE_CHUNK_ROWS")
         if rows:
             self._pipe.set_chunk_rows(int(rows))
@@ -228,17 +239,19 @@ class FusedWorkspace:
             self._pipe.set_ring_depth(int(depth))
 
     def set_engine(self, engine: str) -> None:
-        """"pipe": one persistent kernel per all-reduce; "legacy": the K1/K2/K3 kernel sequence."""
+        """"pipe": one persistent kernel per all-reduce; "legacy": the K1/K2/K3 kernel sequence; "auto": the
+        single kernel up to `pipe_max_bytes`, the sequence above."""
 
-        if engine not in ("pipe", "legacy"):
-            raise ValueError("engine must be 'pipe' or 'legacy'")
-        if engine == "pipe" and self._pipe is None:
-            if not hasattr(self.ext, "PipeAllReducePlan"):
-                raise ValueError("this build has no pipelined engine")
-            self._build_pipe()
+        if engine not in ("auto", "pipe", "legacy"):
+            raise ValueError("engine must be 'auto', 'pipe' or 'legacy'")
+        if engine != "legacy" and not hasattr(self.ext, "PipeAllReducePlan"):
+            raise ValueError("this build has no single-kernel engine")
+        previous, self.engine = self.engine, engine
+        if engine != "legacy" and (self._pipe is None or self.pipe_numel < self._pipe_numel()):
+            self._build_pipe()                      # first use, or "pipe" after "auto": regions for every size
         if engine == "legacy":
             self._ensure_legacy()
-        self.engine = engine
+        del previous
 
     def reset_pipe_control(self) -> None:
         """After a failed collective: zero this rank's local counters of the pipelined engine."""
@@ -433,7 +446,8 @@ class FusedWorkspace:
         scale = self._scale(op)
         if ef_mode not in ("reference", "local"):
             raise ValueError("ef_mode must be 'reference' or 'local'")
-        if self.engine == "pipe" and self.phase_timer is None:
+        through_pipe = self.engine == "pipe" or (self.engine == "auto" and x.numel() <= self.pipe_numel)
+        if through_pipe and self.phase_timer is None:
             return self._pipe_all_reduce(x, out, residual, update_residual, scale, stages, ef_mode)
         self._ensure_legacy()
         if self._native is not None and self.phase_timer is None:
@@ -546,6 +560,46 @@ class FusedWorkspace:
         return outs
 
 
+    def gather_shards(self, shard: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """Compressed all-gather of reduced shards, straight into one tensor (the closing stage of the
+        hierarchical all-reduce): rank r contributes `shard`, the `shard_numel` elements it owns of a tensor of
+        `out.numel()` elements (the geometry of `reduce_scatter`); every rank ends up with
+        out = concat(decode(encode(shard_0)), decode(encode(shard_1)), ...)[:numel].
+
+        Two launches and a one-warp gate: the shard is quantized into this rank's own region, and one decode
+        kernel loads every owner's payload from that owner's memory and writes the output in place -- no list
+        of W tensors, no concatenation, no copy.
+        """
+
+        self._ensure_legacy()
+        g = self.group
+        geo = self._geom(out)
+        flat_out = out.reshape(-1)
+        if shard.numel() != geo.shard_numel or shard.dtype != out.dtype or not shard.is_contiguous():
+            raise ValueError(f"shard must be a contiguous tensor of {geo.shard_numel} elements of the output's dtype")
+        if geo.numel == 0:
+            return out
+        epoch = g.next_epoch(self.channel)
+        # Own payload of shard_groups groups in this rank's all-gather region; the W flags of the all-gather
+        # phase tell every rank that every payload is complete.  Two halves of the region alternate by epoch
+        # parity: a peer may still be decoding the previous payload when this rank writes the next one, and
+        # by the time the half is reused that peer has signalled once more, i.e. finished that decode.
+        half = _round_up(geo.shard_groups * geo.group_bytes, 256) if g.world_size > 1 else 0
+        if 2 * half > self.ag_bytes:
+            raise ValueError("workspace too small to gather shards of this tensor")
+        region = self.ag_off + (epoch & 1) * half
+        self.ext.quant_push(shard.reshape(-1), None, None, None, [g.local_ptr + region], self.ext.PUSH_BROADCAST,
+                            0, geo.shard_groups, 0, geo.group_size, self.config.bit,
+                            g.signal_all(self.channel, PHASE_ALL_GATHER, epoch), self.max_blocks, 0)
+        self.ext.wait_signal(g.wait_all(self.channel, PHASE_ALL_GATHER, epoch), None)
+        src = [g.addr(r, region) for r in range(g.world_size)]
+        self.ext.reduce(src, geo.shard_groups, 0, False, geo.numel, self._code, geo.group_size, self.config.bit, 1.0,
+                        flat_out, False, None, None, [], 0, 0, None, g.wait_all(self.channel, PHASE_ALL_GATHER, epoch),
+                        self.max_blocks, 0, geo.shard_groups, g.rank)
+        self.launches += 3
+        return out
+
+
 def run_loopback(workspaces: list[FusedWorkspace], method: str, per_rank_args: list[tuple],
                  per_rank_kwargs: list[dict] | None = None, **kwargs) -> list:
     """Single-GPU emulation: run one collective for all emulated ranks, phase by phase.
@@ -586,7 +640,8 @@ class _Recorder:
 
     def __getattr__(self, name):
         attr = getattr(self._ext, name)
-        if name in ("quant_push", "reduce", "push_bytes", "wait_signal", "pipe_all_reduce"):
+        if name in ("quant_push", "reduce", "push_bytes", "wait_signal", "pipe_all_reduce", "quant_general",
+                    "dequant_general", "scale_inplace", "error_feedback_update"):
             def defer(*a, **k):
                 self._steps.append(lambda: attr(*a, **k))
             return defer

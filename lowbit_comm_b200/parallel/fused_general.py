@@ -1,0 +1,105 @@
+"""Compressed all-reduce over peer memory for the profiles the production kernels do not serve:
+top-k outliers (1 or 2 values per group kept verbatim), the 4-bit code-books, stochastic rounding.
+
+The reference sends any `CompressionConfig` through every collective because its transports call the one
+codec and move the payload with NCCL (ccdl_comm/quantization/codec.py:104-158, top-k selection
+csrc/quantization/quant_kernel.cuh:38-97, records :249-257, write-back dequant_kernel.cuh:130-148).  Here
+such a profile takes the general kernels of this library for the math and this library's own kernels for
+the movement; no NCCL call is involved:
+
+  quant_general        x (+ residual) -> payload (values, scale, top-k index word and values) in this
+                       rank's own arena; `prepared` parked in the residual buffer
+  push_bytes           the payload to slot [me] of every rank's receive region (peer stores over NVLink),
+                       then a release signal on every rank
+  wait (one warp)      for the W signals
+  dequant_general x W  decode every slot, accumulate in the source dtype in rank order (the reference's
+                       unfused SUM rule), scale by 1/W for a mean
+  error_feedback_update residual = T(prepared - result)
+
+Every rank reduces all W payloads (the one-stage exchange).  The result is, bit for bit, what
+`codec.dequantize_reduce_tensors` gives for the same payloads, so the torch.distributed path and this one
+are interchangeable.  Receive regions alternate by epoch parity; the argument for reuse without extra
+barriers is the one in `parallel/fused.py`.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..config import CompressionConfig
+from ..ops import oracle
+from ..ops.codec import _DTYPE_CODE, _QUANT_CODE, _seed, is_fast_profile
+from ..ops.sizing import estimate_quantized_size
+from .peer_memory import PHASE_REDUCE_SCATTER, PeerGroup
+
+
+def _round_up(value: int, align: int) -> int:
+    return -(-value // align) * align
+
+
+class GeneralPeerWorkspace:
+    """Symmetric regions + one signal channel for general-profile tensors of up to `max_numel` elements."""
+
+    def __init__(self, group: PeerGroup, *, dtype: str, config: CompressionConfig, max_numel: int,
+                 max_blocks: int = 0) -> None:
+        if is_fast_profile(config):
+            raise ValueError("linear / top-k 0 / deterministic profiles are served by FusedWorkspace")
+        self.group, self.dtype, self.config = group, dtype, config
+        self.max_numel, self.max_blocks = int(max_numel), int(max_blocks)
+        self.ext = group._ext
+        self._torch_dtype = oracle.TORCH_DTYPES[dtype]
+        self.slot_bytes = self.payload_bytes(dtype, config, self.max_numel)
+        self.stage_off = group.alloc(self.slot_bytes)
+        self.recv_off = [group.alloc(self.slot_bytes * group.world_size) for _ in range(2)]
+        self.channel = group.new_channel()
+        self.launches = 0
+
+    @staticmethod
+    def payload_bytes(dtype: str, config: CompressionConfig, numel: int) -> int:
+        return _round_up(estimate_quantized_size(max(1, numel), dtype=dtype, config=config).quantized_bytes, 256)
+
+    @staticmethod
+    def required_bytes(world_size: int, dtype: str, config: CompressionConfig, max_numel: int) -> int:
+        return GeneralPeerWorkspace.payload_bytes(dtype, config, max_numel) * (1 + 2 * world_size) + 8 * 512
+
+    def all_reduce(self, x: torch.Tensor, out: torch.Tensor | None = None, *, residual: torch.Tensor | None = None,
+                   update_residual: bool = True, op: str = "mean") -> torch.Tensor:
+        """Compressed all-reduce of `x` into `out` (default: in place); `residual` as in `FusedWorkspace`
+        with the reference's rule (residual = T(prepared - result))."""
+
+        if op not in ("mean", "sum"):
+            raise ValueError(f"unsupported reduce op {op!r}")
+        n = x.numel()
+        if n > self.max_numel:
+            raise ValueError(f"tensor has {n} elements, workspace holds {self.max_numel}")
+        if x.dtype != self._torch_dtype or not x.is_contiguous():
+            raise TypeError(f"workspace was built for contiguous {self.dtype} tensors")
+        target = x if out is None else out
+        if n == 0:
+            return target
+        g, cfg, ext = self.group, self.config, self.ext
+        W, me = g.world_size, g.rank
+        nbytes = estimate_quantized_size(n, dtype=self.dtype, config=cfg).quantized_bytes
+        epoch = g.next_epoch(self.channel)
+        region = self.recv_off[epoch & 1]
+        flat = x.reshape(-1)
+        res = None if residual is None else residual.reshape(-1)
+        keep = res if (res is not None and update_residual) else None      # `prepared` is parked here
+        payload = g.local_view(self.stage_off, nbytes)
+        ext.quant_general(flat, res, keep, payload, cfg.group_size, cfg.bit, cfg.topk, _QUANT_CODE[cfg.quant_type],
+                          cfg.stochastic, cfg.compact, _seed() if cfg.stochastic else 0)
+        dst = [g.addr(d, region + me * self.slot_bytes) for d in range(W)]
+        ext.push_bytes(g.local_ptr + self.stage_off, _round_up(nbytes, 16), dst, None,
+                       g.signal_all(self.channel, PHASE_REDUCE_SCATTER, epoch), self.max_blocks)
+        ext.wait_signal(g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch), None)
+        out_flat = target.reshape(-1)
+        for r in range(W):
+            slot = g.local_view(region + r * self.slot_bytes, nbytes)
+            ext.dequant_general(slot, out_flat, cfg.group_size, cfg.bit, cfg.topk, _QUANT_CODE[cfg.quant_type],
+                                cfg.compact, r > 0)
+        if op == "mean" and W > 1:
+            ext.scale_inplace(out_flat, 1.0 / W)
+        if keep is not None:
+            ext.error_feedback_update(keep, out_flat, keep)
+        self.launches += 3 + W + (1 if op == "mean" and W > 1 else 0) + (1 if keep is not None else 0)
+        return target

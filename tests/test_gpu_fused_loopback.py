@@ -335,6 +335,78 @@ def test_pipelined_engine_wait_runs_out_on_a_flag_nobody_sets(ext):
         PeerGroup.close_loopback(groups)
 
 
+@pytest.mark.parametrize("world", (2, 4))
+@pytest.mark.parametrize("dtype,group", [("bf16", 64), ("fp32", 32)])
+def test_gather_shards_writes_the_whole_tensor_in_one_decode(ext, world, dtype, group):
+    """The closing stage of the hierarchical all-reduce: every rank's dense shard, quantized once, decoded by
+    every rank straight into the full tensor; twice in a row (the two halves of the region alternate)."""
+
+    cfg = CompressionConfig(bit=8, group_size=group)
+    n = group * 8 * world * 13 + 37
+    groups, wss = _make(world, dtype, cfg, n)
+    try:
+        geo = geometry(n, world, dtype, cfg)
+        for step in range(3):
+            full = _inputs(1, geo.shard_numel * world, dtype, seed=40 + step)[0]
+            shards = [full[r * geo.shard_numel:(r + 1) * geo.shard_numel].clone() for r in range(world)]
+            outs = [torch.full((n,), 5.0, dtype=DT[dtype], device="cuda") for _ in range(world)]
+            run_loopback(wss, "gather_shards", [(shards[r].cuda(), outs[r]) for r in range(world)])
+            want = torch.cat([oracle.decode(oracle.encode(sh, cfg), geo.shard_numel, cfg, dtype) for sh in shards])[:n]
+            for r in range(world):
+                assert torch.equal(outs[r].cpu().view(torch.uint8), want.view(torch.uint8)), (step, r)
+        torch.cuda.synchronize()
+        for g in groups:
+            g.check_status()
+    finally:
+        PeerGroup.close_loopback(groups)
+
+
+@pytest.mark.parametrize("world", (2, 4, 8))
+@pytest.mark.parametrize("dtype", ("bf16", "fp32"))
+@pytest.mark.parametrize("kw", [dict(bit=8, group_size=64, topk=1), dict(bit=8, group_size=64, topk=2),
+                                dict(bit=4, group_size=32, topk=1, quant_type="e2m1"),
+                                dict(bit=4, group_size=16, quant_type="normal")])
+def test_topk_and_codebook_profiles_through_peer_memory(ext, world, dtype, kw):
+    """Profiles outside the production kernels (top-k outliers, 4-bit code-books) all-reduced with the general
+    kernels and this library's own transport: bit for bit what the codec gives for the gathered payloads, and
+    the reference's error-feedback rule."""
+
+    from lowbit_comm_b200.ops import codec
+    from lowbit_comm_b200.parallel.fused_general import GeneralPeerWorkspace
+
+    cfg = CompressionConfig(allow_experimental=True, **kw)
+    max_numel = 70_000
+    need = GeneralPeerWorkspace.required_bytes(world, dtype, cfg, max_numel) + (1 << 20)
+    groups = PeerGroup.loopback(world, need, timeout_ns=2_000_000_000)
+    try:
+        wss = [GeneralPeerWorkspace(g, dtype=dtype, config=cfg, max_numel=max_numel) for g in groups]
+        for step, n in enumerate((cfg.group_size * 8 * world, 12_347, 1, max_numel)):
+            xs = _inputs(world, n, dtype, seed=30 + step)
+            rs = _inputs(world, n, dtype, seed=60 + step)
+            dev_x = [x.cuda() for x in xs]
+            dev_r = [r.cuda() for r in rs]
+            payloads, prepared = [], []
+            for x, r in zip(xs, rs):
+                keep = r.cuda()
+                payloads.append(codec.quantize_tensor(x.cuda(), cfg, residual=keep, prepared_out=keep))
+                prepared.append(keep)
+            want = codec.dequantize_reduce_tensors(payloads, (n,), cfg, dtype=dtype, reduce="mean")
+            want_res = [codec.update_error_feedback_residual(p, want, p.clone()) for p in prepared]
+            run_loopback(wss, "all_reduce", [(dev_x[r],) for r in range(world)],
+                         [{"residual": dev_r[r]} for r in range(world)])
+            torch.cuda.synchronize()
+            for r in range(world):
+                assert torch.equal(dev_x[r].view(torch.uint8), want.view(torch.uint8)), (n, r)
+                assert torch.equal(dev_r[r].view(torch.uint8), want_res[r].view(torch.uint8)), (n, r, "residual")
+            exact = torch.stack([(x.float() + r.float()) for x, r in zip(xs, rs)]).mean(0)
+            rel = ((want.float().cpu() - exact).norm() / exact.norm()).item()
+            assert rel < (0.05 if cfg.bit == 8 else 0.25), rel
+        for g in groups:
+            g.check_status()
+    finally:
+        PeerGroup.close_loopback(groups)
+
+
 def test_bounded_wait_reports_status_instead_of_hanging(ext):
     """A flag that nothing sets: the kernel gives up after its time limit and says why."""
 

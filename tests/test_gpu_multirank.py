@@ -22,7 +22,8 @@ def _gpu_count() -> int:
 
 
 def _launch(case: str, world: int, multicast: bool = False) -> str:
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    # Short device waits: should one rank fail, the kernels of the others give up in seconds, not minutes.
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT, LBC_WAIT_TIMEOUT_MS="20000")
     if multicast:
         # short device waits: if one rank fails, the others drain in seconds and nobody unmaps early
         env.update(LBC_MULTICAST="1", LBC_WAIT_TIMEOUT_MS="3000")

@@ -46,10 +46,13 @@ def test_grouping_follows_the_order_of_the_given_ranks_and_rejects_ragged_splits
 
 
 def test_sweep_roofline_formula():
-    sweep = _load("benchmarks/allreduce_sweep.py", "allreduce_sweep_script")
+    # one roofline function for the library and its benchmarks: the sweep script states none of its own
+    from lowbit_comm_b200.utils.roofline import fused_all_reduce_roofline
+
+    assert "def roofline_us" not in open(os.path.join(ROOT, "benchmarks", "allreduce_sweep.py")).read()
     nbytes = 256 << 20
-    two = sweep.roofline_us(nbytes, 8, 2, True, 6552.3)
-    one = sweep.roofline_us(nbytes, 8, 1, True, 6552.3)
+    two = fused_all_reduce_roofline(nbytes, 8, stages=2, error_feedback=True, hbm_gbs=6552.3)
+    one = fused_all_reduce_roofline(nbytes, 8, stages=1, error_feedback=True, hbm_gbs=6552.3)
     payload = nbytes * 66 / 128
     assert two["t_link_us"] == pytest.approx(2 * payload * 7 / 8 / 770e9 * 1e6)
     assert one["t_link_us"] == pytest.approx(payload * 7 / 770e9 * 1e6)
