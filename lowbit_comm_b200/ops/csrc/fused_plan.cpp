@@ -344,8 +344,8 @@ class FusedAllReducePlan {
 };
 
 // ---------------------------------------------------------------------------------------------
-// Pipelined all-reduce: one persistent kernel per collective (pipe_kernels.cu).  The plan resolves
-// the geometry (shards, rows, chunks) from the element count; regions are fixed at construction.
+// Single-launch all-reduce: one persistent kernel per collective (pipe_kernels.cu).  The plan resolves
+// the geometry (shards, rows) from the element count; regions are fixed at construction.
 // ---------------------------------------------------------------------------------------------
 class PipeAllReducePlan {
   public:
@@ -362,7 +362,9 @@ class PipeAllReducePlan {
         group_bytes_ = group_ * bit_ / 8 + (dtype_ == LBC_FP32 ? 4 : 2);
     }
 
-    // Rows of one chunk over all shards: below this a chunk is too small to keep the grid busy.
+    // Reserved.  The kernel runs every phase as one sweep over its rows (a schedule that cut the tensor into
+    // chunks whose phases overlapped was measured slower: it paid a grid-wide meeting per chunk); the chunk
+    // geometry is still computed and validated so that callers written against it keep working.
     void set_chunk_rows(int64_t min_rows, int max_chunks) {
         min_chunk_rows_ = std::max<int64_t>(min_rows, 1);
         max_chunks_ = std::max(1, std::min(max_chunks, LBC_PIPE_MAX_CHUNKS));

@@ -96,14 +96,13 @@ typedef struct {
 cudaError_t lbc_quant_push(const LbcQuantPush* p, cudaStream_t stream);
 cudaError_t lbc_reduce(const LbcReduce* p, cudaStream_t stream);
 
-// ---- pipelined all-reduce: one persistent kernel, every NVLink byte moved by bulk loads ----------
+// ---- single-launch all-reduce: one persistent kernel, every NVLink byte moved by bulk loads ----------
 // Every rank quantizes its tensor into its OWN arena (phase QUANT), the owner of a shard pulls that
 // shard's rows from all ranks with bulk asynchronous loads, reduces and requantizes them into its own
 // arena (phase REDUCE), and every rank pulls the reduced shards and decodes them (phase DECODE).  Rows of
-// 4096 elements are the unit of work; a tensor is cut into up to LBC_PIPE_MAX_CHUNKS chunks and a
-// chunk's rows become visible to the other ranks through one epoch flag per (rank, chunk), so the three
-// phases of different chunks overlap inside one launch.  With stages == 1 there is one "shard" (the
-// whole tensor), every rank reduces all W payloads and writes the result directly (no DECODE phase).
+// 4096 elements are the unit of work, dealt to the blocks statically; the ranks meet between the phases
+// through one epoch flag per (rank, phase).  With stages == 1 there is one "shard" (the whole tensor),
+// every rank reduces all W payloads and writes the result directly (no DECODE phase).
 // The reference moves the same bytes with NCCL calls between kernels (ccdl_comm/cuda/transports/
 // pipelined_ring.py:236-316); it has no counterpart of this kernel.
 #define LBC_PIPE_MAX_CHUNKS 16
@@ -113,7 +112,7 @@ enum LbcPipePhase { LBC_PIPE_QUANT = 1, LBC_PIPE_REDUCE = 2, LBC_PIPE_DECODE = 4
 #define LBC_PIPE_CTL_FLAGS_QUANT 0      // u32 [LBC_MAX_RANKS][LBC_PIPE_MAX_CHUNKS], written by the peers
 #define LBC_PIPE_CTL_FLAGS_REDUCE 1024  // u32 [LBC_MAX_RANKS][LBC_PIPE_MAX_CHUNKS], written by the peers
 #define LBC_PIPE_CTL_FLAGS_GATE 2048    // u32 [LBC_MAX_RANKS], written by the peers (rendezvous)
-#define LBC_PIPE_CTL_LOCAL 2304         // u32 ticket, exit count, done[2][LBC_PIPE_MAX_CHUNKS]: local scratch
+#define LBC_PIPE_CTL_LOCAL 2304         // u32 [2] reserved, then blocks done per phase: local scratch
 #define LBC_PIPE_CTL_BYTES 2560
 
 typedef struct {
@@ -136,8 +135,8 @@ typedef struct {
     int64_t ag_off;             // own reduced shard, one planar payload (stages == 2)
     int64_t ctl_off;            // control block
     int64_t shard_groups;       // groups per shard, a multiple of 8
-    int num_chunks;             // <= LBC_PIPE_MAX_CHUNKS
-    int64_t rows_per_chunk;     // rows of one shard per chunk
+    int num_chunks;             // reserved (<= LBC_PIPE_MAX_CHUNKS): every phase is one sweep
+    int64_t rows_per_chunk;     // reserved: num_chunks * rows_per_chunk covers a shard's rows
     unsigned int epoch;
     unsigned long long timeout_ns;
     void* status;               // LbcStatus*, device visible

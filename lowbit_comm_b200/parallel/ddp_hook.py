@@ -324,17 +324,24 @@ class _PeerEngine:
     def _make_workspace(self, dtype: str, cap: int):
         from .fused import FusedWorkspace
 
-        # buckets always go through the single persistent kernel: the arena is sized for its regions only
         ws = FusedWorkspace(self.group, dtype=dtype, config=self.config, max_numel=cap, max_blocks=self.max_blocks,
-                            engine=os.environ.get("LBC_ENGINE") or "pipe")
+                            engine=self._engine(self.group.world_size))
         ws.gate = ws.group.world_size > 1     # line the ranks up before the persistent kernel takes the SMs
         return ws
+
+    @staticmethod
+    def _engine(world: int) -> str:
+        """Buckets go through the single persistent kernel whatever their size and world size: the arena then holds
+        that kernel's regions only (about 1.1 x the bucket's payload; the kernel sequence needs 3-7 x)."""
+
+        return os.environ.get("LBC_ENGINE") or "pipe"
 
     def _need(self, world: int, dtype: str, cap: int) -> int:
         from .fused import FusedWorkspace
 
-        engine = "pipe" if (os.environ.get("LBC_ENGINE") or "pipe") == "pipe" else "both"
-        return FusedWorkspace.required_bytes(world, dtype, self.config, cap, world <= 2, engine=engine) + (1 << 20)
+        engine = self._engine(world)
+        return FusedWorkspace.required_bytes(world, dtype, self.config, cap, world <= 2,
+                                             engine=engine if engine in ("pipe", "legacy") else "both") + (1 << 20)
 
     def _world(self) -> int:
         if self.group is not None:
