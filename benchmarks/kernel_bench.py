@@ -43,6 +43,9 @@ def main() -> None:
     ap.add_argument("--profile", action="store_true", help="one warm-up + one timed launch per kernel (for ncu)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--with-reference", action="store_true")
+    ap.add_argument("--engine", choices=("auto", "pipe", "legacy"), default="auto",
+                    help="all-reduce engine of the emulated-rank part: single persistent kernel or kernel sequence")
+    ap.add_argument("--skip-codec", action="store_true", help="only the all-reduce on emulated ranks (for captures)")
     ap.add_argument("--out", default="bench_out/kernel_bench.json")
     args = ap.parse_args()
     ref = None
@@ -79,63 +82,64 @@ def main() -> None:
         res = torch.zeros_like(x)
         out = codec.allocate_quantized_buffer(x, cfg)
         pb = out.numel()
-        t = time_cuda(lambda: codec.quantize_tensor(x, cfg, output=out), iters=args.iters, flush=flush, warmup=warm)
-        record("quant_push(local)", mib, 2 * n + pb, t)
-        t = time_cuda(lambda: codec.quantize_tensor(x, cfg, output=out, residual=res, prepared_out=res),
-                      iters=args.iters, flush=flush, warmup=warm)
-        record("quant_push(local,+EF in place)", mib, 6 * n + pb, t)
-        y = torch.empty_like(x)
-        t = time_cuda(lambda: codec.dequantize_tensor(out, x.shape, cfg, dtype="bf16", output=y),
-                      iters=args.iters, flush=flush, warmup=warm)
-        record("reduce(1 payload)", mib, 2 * n + pb, t)
-        t = time_cuda(lambda: codec.inplace_dequantize_reduce_mean_update_error_feedback(
-            [out], res, y, res, cfg, reduce="mean"), iters=args.iters, flush=flush, warmup=warm)
-        record("reduce(1 payload,+EF in place)", mib, 6 * n + pb, t)
-        bufs = [out] + [out.clone() for _ in range(7)]
-        t = time_cuda(lambda: codec.inplace_dequantize_reduce_mean(bufs, y, cfg, reduce="mean"),
-                      iters=args.iters, flush=flush, warmup=warm)
-        record("reduce(8 payloads)", mib, 2 * n + 8 * pb, t)
-        z = torch.empty_like(x)
-        t = time_cuda(lambda: z.copy_(x), iters=args.iters, flush=flush, warmup=warm)
-        record("torch copy_ (reference point)", mib, 4 * n, t)
-        if ref is not None:
-            rc, rcfg, rstatus = ref
-            rout = rc.allocate_quantized_buffer(x, rcfg) if hasattr(rc, "allocate_quantized_buffer") else out.clone()
-            rout = rout.reshape(-1) if rout.numel() == pb else torch.empty(pb, dtype=torch.uint8, device="cuda")
-            try:
-                ok = rc.inplace_quantize_pack(x, rout, None, rcfg, extension_status=rstatus)
-                t = time_cuda(lambda: rc.inplace_quantize_pack(x, rout, None, rcfg, extension_status=rstatus),
-                              iters=args.iters, flush=flush, warmup=warm)
-                record("reference inplace_quantize_pack", mib, 2 * n + pb, t, fused=bool(ok))
-                t = time_cuda(lambda: rc.inplace_quantize_pack(x, rout, res, rcfg, extension_status=rstatus),
-                              iters=args.iters, flush=flush, warmup=warm)
-                record("reference inplace_quantize_pack(+residual)", mib, 4 * n + pb, t)
-                rbufs = [rout] + [rout.clone() for _ in range(7)]
-                t = time_cuda(lambda: rc.inplace_dequantize_reduce_mean(rbufs[:1], y, rcfg, extension_status=rstatus,
-                                                                        reduce="mean"),
-                              iters=args.iters, flush=flush, warmup=warm)
-                record("reference inplace_dequantize_reduce_mean(1 payload)", mib, 2 * n + pb, t)
-                t = time_cuda(lambda: rc.inplace_dequantize_reduce_mean(rbufs, y, rcfg, extension_status=rstatus,
-                                                                        reduce="mean"),
-                              iters=args.iters, flush=flush, warmup=warm)
-                record("reference inplace_dequantize_reduce_mean(8 payloads)", mib, 2 * n + 8 * pb, t)
-                prep, restored = x.clone(), torch.empty_like(x)
-                t = time_cuda(lambda: rc.inplace_dequantize_reduce_mean_update_error_feedback(
-                    rbufs[:1], prep, restored, res, rcfg, extension_status=rstatus, reduce="mean"),
-                    iters=args.iters, flush=flush, warmup=warm)
-                record("reference inplace_dequantize_reduce_mean_update_error_feedback(1 payload)", mib,
-                       6 * n + pb, t)
-                del rbufs, prep, restored
-            except Exception as exc:  # noqa: BLE001
-                print(json.dumps({"impl": "reference", "mib": mib, "error": f"{type(exc).__name__}: {exc}"[:300]}),
-                      flush=True)
-        del bufs
+        if not args.skip_codec:
+            t = time_cuda(lambda: codec.quantize_tensor(x, cfg, output=out), iters=args.iters, flush=flush, warmup=warm)
+            record("quant_push(local)", mib, 2 * n + pb, t)
+            t = time_cuda(lambda: codec.quantize_tensor(x, cfg, output=out, residual=res, prepared_out=res),
+                          iters=args.iters, flush=flush, warmup=warm)
+            record("quant_push(local,+EF in place)", mib, 6 * n + pb, t)
+            y = torch.empty_like(x)
+            t = time_cuda(lambda: codec.dequantize_tensor(out, x.shape, cfg, dtype="bf16", output=y),
+                          iters=args.iters, flush=flush, warmup=warm)
+            record("reduce(1 payload)", mib, 2 * n + pb, t)
+            t = time_cuda(lambda: codec.inplace_dequantize_reduce_mean_update_error_feedback(
+                [out], res, y, res, cfg, reduce="mean"), iters=args.iters, flush=flush, warmup=warm)
+            record("reduce(1 payload,+EF in place)", mib, 6 * n + pb, t)
+            bufs = [out] + [out.clone() for _ in range(7)]
+            t = time_cuda(lambda: codec.inplace_dequantize_reduce_mean(bufs, y, cfg, reduce="mean"),
+                          iters=args.iters, flush=flush, warmup=warm)
+            record("reduce(8 payloads)", mib, 2 * n + 8 * pb, t)
+            z = torch.empty_like(x)
+            t = time_cuda(lambda: z.copy_(x), iters=args.iters, flush=flush, warmup=warm)
+            record("torch copy_ (reference point)", mib, 4 * n, t)
+            if ref is not None:
+                rc, rcfg, rstatus = ref
+                rout = rc.allocate_quantized_buffer(x, rcfg) if hasattr(rc, "allocate_quantized_buffer") else out.clone()
+                rout = rout.reshape(-1) if rout.numel() == pb else torch.empty(pb, dtype=torch.uint8, device="cuda")
+                try:
+                    ok = rc.inplace_quantize_pack(x, rout, None, rcfg, extension_status=rstatus)
+                    t = time_cuda(lambda: rc.inplace_quantize_pack(x, rout, None, rcfg, extension_status=rstatus),
+                                  iters=args.iters, flush=flush, warmup=warm)
+                    record("reference inplace_quantize_pack", mib, 2 * n + pb, t, fused=bool(ok))
+                    t = time_cuda(lambda: rc.inplace_quantize_pack(x, rout, res, rcfg, extension_status=rstatus),
+                                  iters=args.iters, flush=flush, warmup=warm)
+                    record("reference inplace_quantize_pack(+residual)", mib, 4 * n + pb, t)
+                    rbufs = [rout] + [rout.clone() for _ in range(7)]
+                    t = time_cuda(lambda: rc.inplace_dequantize_reduce_mean(rbufs[:1], y, rcfg, extension_status=rstatus,
+                                                                            reduce="mean"),
+                                  iters=args.iters, flush=flush, warmup=warm)
+                    record("reference inplace_dequantize_reduce_mean(1 payload)", mib, 2 * n + pb, t)
+                    t = time_cuda(lambda: rc.inplace_dequantize_reduce_mean(rbufs, y, rcfg, extension_status=rstatus,
+                                                                            reduce="mean"),
+                                  iters=args.iters, flush=flush, warmup=warm)
+                    record("reference inplace_dequantize_reduce_mean(8 payloads)", mib, 2 * n + 8 * pb, t)
+                    prep, restored = x.clone(), torch.empty_like(x)
+                    t = time_cuda(lambda: rc.inplace_dequantize_reduce_mean_update_error_feedback(
+                        rbufs[:1], prep, restored, res, rcfg, extension_status=rstatus, reduce="mean"),
+                        iters=args.iters, flush=flush, warmup=warm)
+                    record("reference inplace_dequantize_reduce_mean_update_error_feedback(1 payload)", mib,
+                           6 * n + pb, t)
+                    del rbufs, prep, restored
+                except Exception as exc:  # noqa: BLE001
+                    print(json.dumps({"impl": "reference", "mib": mib, "error": f"{type(exc).__name__}: {exc}"[:300]}),
+                          flush=True)
+            del bufs, y, z
         for world in args.worlds:
             need = FusedWorkspace.required_bytes(world, "bf16", cfg, n, world <= 2) + (1 << 20)
             if need * world > 60 * (1 << 30):
                 continue
             groups = PeerGroup.loopback(world, need)
-            wss = [FusedWorkspace(g, dtype="bf16", config=cfg, max_numel=n) for g in groups]
+            wss = [FusedWorkspace(g, dtype="bf16", config=cfg, max_numel=n, engine=args.engine) for g in groups]
             xs = [x] + [x.clone() for _ in range(world - 1)]
             rs = [torch.zeros_like(x) for _ in range(world)]
 
@@ -149,7 +153,7 @@ def main() -> None:
             stages = 1 if world <= 2 else 2
             c = pb / n
             hbm = (6 * n + c * n) + (stages == 2) * (2 * c * n) + (c * n * (world if stages == 1 else 1) + 6 * n)
-            rows.append({"kernel": f"all_reduce loopback W={world} ({stages}-stage, EF)", "mib": mib,
+            rows.append({"kernel": f"all_reduce loopback W={world} ({stages}-stage, EF, engine {wss[0].engine})", "mib": mib,
                          "per_rank_ms": per_rank_ms, "hbm_bytes_model": hbm,
                          "gbs": hbm / (per_rank_ms * 1e-3) / 1e9, "frac_of_peak": hbm / (per_rank_ms * 1e-3) / 1e9 / peak,
                          "launches_per_rank": wss[0].launches // max(1, (3 + max(3, args.iters // 2)))})
@@ -158,7 +162,7 @@ def main() -> None:
             groups[0].check_status()
             PeerGroup.close_loopback(groups)
             del wss, xs, rs
-        del x, res, out, y, z
+        del x, res, out
         torch.cuda.empty_cache()
     os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
     json.dump(rows, open(args.out, "w"), indent=1)

@@ -8,6 +8,10 @@ Values N(0, 1e-3), int8 group 64 with error feedback (this rank's own quantizati
 error on the scatter stage).  One timed iteration = all buckets through
 reduce-scatter then all-gather; timed on the device with CUDA events, max over
 ranks.  The working set (64 x 32 MiB = 2 GiB per rank) is far larger than L2.
+Arms: this library flat (reduce-scatter shard + all-gather of the shards) and hierarchical
+(2 x 4: the three-stage chain), NCCL bf16 reduce-scatter + all-gather, and with
+`--with-reference` the unmodified reference: its `compressed_reduce_scatter_shard` followed by
+its `compressed_all_gather` of the shard, and its `compressed_hierarchical_all_reduce`.
 """
 
 from __future__ import annotations
@@ -29,6 +33,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--local-group", type=int, default=4)
+    ap.add_argument("--with-reference", action="store_true")
+    ap.add_argument("--ref-iters", type=int, default=10)
     ap.add_argument("--out", default="bench_out/sharded_rs_ag.json")
     args = ap.parse_args()
 
@@ -89,14 +95,48 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return {"median_ms": float(t[0]), "mean_ms": float(t[1]), "iters": iters}
 
+    ref_arms = []
+    if args.with_reference:
+        try:
+            sys.path.insert(0, os.path.join(ROOT, "baseline"))
+            import reference_env
+
+            reference_env.activate(need_cuda_extension=True)
+            from ccdl_comm.collectives import compressed_all_gather as ref_gather
+            from ccdl_comm.collectives import compressed_hierarchical_all_reduce as ref_hier
+            from ccdl_comm.collectives import compressed_reduce_scatter_shard as ref_shard
+            from ccdl_comm.config import CompressionConfig as RefConfig
+
+            rcfg = RefConfig(bit=8, group_size=64, topk=0)
+
+            def ref_flat_step() -> None:
+                for b in buckets:
+                    shard = ref_shard(b, config=rcfg, op="mean")
+                    ref_gather(shard.shard, config=rcfg)
+
+            def ref_hier_step() -> None:
+                os.environ.setdefault("CCDL_LOCAL_GROUP_SIZE", str(args.local_group))
+                for b in buckets:
+                    ref_hier(b, config=rcfg, op="mean")
+
+            ref_arms = [("reference_rs_shard_ag", ref_flat_step), ("reference_hierarchical", ref_hier_step)]
+        except Exception as exc:  # noqa: BLE001
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}), flush=True)
+
     total_bytes = args.buckets * n * 2
     rows = []
     arms = [("ours_flat_rs_ag", flat_step), ("nccl_bf16_rs_ag", nccl_step)]
     if world % args.local_group == 0 and world > args.local_group:
         arms.insert(1, (f"ours_hierarchical_{world // args.local_group}x{args.local_group}", hierarchical_step))
-    for name, fn in arms:
-        iters = args.iters if name != arms[1][0] or len(arms) == 2 else max(5, args.iters // 5)
-        t = measure(fn, iters)
+    for name, fn in arms + ref_arms:
+        iters = args.ref_iters if name.startswith("reference") else args.iters
+        try:
+            t = measure(fn, iters)
+        except Exception as exc:  # noqa: BLE001
+            if rank == 0:
+                print(json.dumps({"impl": name, "error": f"{type(exc).__name__}: {exc}"[:300]}), flush=True)
+            continue
         comm.check_status()
         rows.append({"impl": name, "world": world, "buckets": args.buckets, "bucket_mib": args.mib, **t,
                      "algbw_gbs": total_bytes / (t["median_ms"] * 1e-3) / 1e9,
