@@ -9,6 +9,10 @@ Cases (each row names the call that is timed):
   async_vs_sync      compressed_all_reduce(async_op=True) + wait() vs the synchronous call
   dynamic_gather     compressed_all_gather_dynamic with metadata_protocol tensor_v1 vs object_v1 (ragged sizes)
   p2p                qsend / qrecv of one tensor between ranks 0 and 1: time and relative L2 error
+  dispatch_overhead  host time per call (no synchronisation inside the loop) of a compiled plan's `run()`, of the
+                     public `compressed_all_reduce` and of the workspace's own `all_reduce`, against the device time
+                     of the collective: what planning and dispatch add (the reference requires < 1 % for its
+                     compiled dispatch, tests/distributed/executor_overhead_perf.py)
 
 Timing: CUDA events on the launching stream, 3 warm-up calls, median of `--iters`, a 256 MiB write between calls
 to flush the 126 MB L2, a barrier before every call, maximum over ranks.  fp16 sources, int8 codes, 64-element
@@ -32,7 +36,8 @@ def main() -> None:
     ap.add_argument("--sizes-mib", type=float, nargs="+", default=[1, 16, 64])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--cases", nargs="+", default=["reduced_shard", "async_vs_sync", "dynamic_gather", "p2p"])
+    ap.add_argument("--cases", nargs="+",
+                    default=["reduced_shard", "async_vs_sync", "dynamic_gather", "p2p", "dispatch_overhead"])
     ap.add_argument("--out", default="bench_out/micro_suite.json")
     ap.add_argument("--cpu", action="store_true",
                     help="dry run on CPU ranks (gloo, host timer, no L2 flush): checks the script, measures nothing useful")
@@ -123,6 +128,38 @@ def main() -> None:
             record(case="reduced_shard", mib=mib, ours_ms=t_ours, nccl_reduce_scatter_ms=t_rs, nccl_all_reduce_ms=t_full,
                    speedup_vs_nccl_full=t_full / t_ours, speedup_vs_nccl_reduce_scatter=t_rs / t_ours, rel_l2=err,
                    transport=probe.transport)
+
+        if "dispatch_overhead" in args.cases and not args.cpu:
+            import time
+
+            from lowbit_comm_b200.parallel.backend_cuda import compile_cuda_shortcut
+            from lowbit_comm_b200.parallel.communicator import get_communicator
+
+            comm = get_communicator(None)
+            ws = comm.workspace(x, cfg, "fp16")
+            work = x.clone()
+            compiled = compile_cuda_shortcut(x, collective="all_reduce", strategy="auto", output_layout="full",
+                                             config=cfg, reduce_op="mean")
+
+            def host_us(fn, calls=200) -> float:
+                fn()
+                torch.cuda.synchronize()
+                dist.barrier()
+                t0 = time.perf_counter()
+                for _ in range(calls):
+                    fn()
+                dt = time.perf_counter() - t0
+                torch.cuda.synchronize()
+                return dt / calls * 1e6
+
+            direct = host_us(lambda: ws.all_reduce(x, work))
+            public = host_us(lambda: lbc.compressed_all_reduce(x, config=cfg, op="mean", strategy="auto", out=work))
+            planned = host_us(lambda: compiled.run(x))
+            device = measure(lambda: ws.all_reduce(x, work)) * 1e3
+            record(case="dispatch_overhead", mib=mib, direct_host_us=direct, public_api_host_us=public,
+                   compiled_run_host_us=planned, device_us=device,
+                   compiled_over_direct_pct_of_device=100.0 * (planned - direct) / device,
+                   public_over_direct_pct_of_device=100.0 * (public - direct) / device)
 
         if "async_vs_sync" in args.cases:
             work = x.clone()

@@ -63,6 +63,15 @@ def _check_tensor(tensor: Any, context: CompileContext) -> None:
         raise TypeError(f"tensor dtype {tensor.dtype} does not match the compiled dtype {context.dtype}")
 
 
+def _reason_iff_negative(flag: bool, reason: str | None, *, what: str, positive: str) -> None:
+    """A record that says "yes" carries no explanation, one that says "no" must say why."""
+
+    if flag and reason is not None:
+        raise ValueError(f"{what}: {positive}, so there is nothing to explain (got reason {reason!r})")
+    if not flag and not (isinstance(reason, str) and reason.strip()):
+        raise ValueError(f"{what}: not {positive}, so the reason has to be stated")
+
+
 @dataclass(frozen=True)
 class PrecollectedPayloadExecution:
     """What reducing already-gathered payloads did: where the result is, and whether the fused
@@ -73,10 +82,8 @@ class PrecollectedPayloadExecution:
     fallback_reason: str | None = None
 
     def __post_init__(self) -> None:
-        if self.fused and self.fallback_reason is not None:
-            raise ValueError("fused execution must not provide a fallback reason")
-        if not self.fused and not self.fallback_reason:
-            raise ValueError("fallback execution requires a fallback reason")
+        _reason_iff_negative(self.fused, self.fallback_reason, what="precollected-payload execution",
+                             positive="served by the fused kernel")
 
 
 @dataclass(frozen=True)
@@ -88,10 +95,8 @@ class FusedReducedShardCapability:
     reason: str | None = None
 
     def __post_init__(self) -> None:
-        if self.available and self.reason is not None:
-            raise ValueError("available fused ReducedShard capability must not have a fallback reason")
-        if not self.available and not self.reason:
-            raise ValueError("unavailable fused ReducedShard capability requires a fallback reason")
+        _reason_iff_negative(self.available, self.reason, what="fused reduced-shard capability",
+                             positive="available")
 
 
 def fused_reduced_shard_capability(plan: CommunicationPlan, context: CompileContext,

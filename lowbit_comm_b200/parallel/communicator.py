@@ -396,7 +396,8 @@ class Communicator:
         shape = tuple(tensor.shape)
         if self.peer_usable(tensor, config):
             ws = self.workspace(tensor, config, name)
-            outs = [torch.empty(shape, dtype=tensor.dtype, device=tensor.device) for _ in range(self.world_size)]
+            # rows of one buffer: the decode of all W payloads is then a single launch
+            outs = list(torch.empty((self.world_size,) + shape, dtype=tensor.dtype, device=tensor.device).unbind(0))
             scope, side = self._stream_scope(tensor, async_op)
             with scope:
                 ws.all_gather(tensor.contiguous(), outs)

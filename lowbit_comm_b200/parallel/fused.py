@@ -558,11 +558,25 @@ class FusedWorkspace:
         region = self.gather_off[parity]
         self.ext.wait_signal(g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch), None)
         self.launches += 1
+        wait = g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch)
+        step = geo.numel * x.element_size()
+        one_buffer = all(o.is_contiguous() and o.dtype == x.dtype and o.numel() == geo.numel and
+                         o.data_ptr() == outs[0].data_ptr() + r * step for r, o in enumerate(outs))
+        if one_buffer and geo.num_groups == geo.full_groups and geo.numel % geo.group_size == 0:
+            # the outputs are rows of one buffer and every payload is a whole number of 8-group units: ONE decode
+            # launch reads payload r for the groups of row r (the gather mode of the reduce kernel)
+            whole = self.ext.tensor_from_address(outs[0].data_ptr(), step * g.world_size, x.device.index) \
+                .view(self._torch_dtype)
+            src = [g.local_ptr + region + r * self.gather_stride for r in range(g.world_size)]
+            self.ext.reduce(src, geo.full_groups, 0, False, geo.numel * g.world_size, self._code, geo.group_size,
+                            self.config.bit, 1.0, whole, False, None, None, [], 0, 0, None, wait, self.max_blocks, 0,
+                            geo.full_groups, 0)
+            self.launches += 1
+            return outs
         for r, out in enumerate(outs):
-            wait = g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch) if r == 0 else None
             self.ext.reduce([g.local_ptr + region + r * self.gather_stride], geo.full_groups, 0, False, geo.numel,
                             self._code, geo.group_size, self.config.bit, 1.0, out.reshape(-1), False, None, None,
-                            [], 0, 0, None, wait, self.max_blocks)
+                            [], 0, 0, None, wait if r == 0 else None, self.max_blocks)
             self.launches += 1
         return outs
 

@@ -94,12 +94,22 @@ def make_native_topology_all_reduce(*, method: str | None = None, group: Any | N
         hops = {None: "ring", "overlap-p2p": "p2p", "overlap-tree": "tree"}.get(method, method)
         return make_schedule_all_reduce(method=hops, group=group)
 
+    # The reference's overlap-* methods start the exchange and leave its last step to `wait()`
+    # (ccdl_comm/communication/topology_transport.py:53-107, 524-748).  Here an overlap-* call is always issued
+    # on the communicator's side stream, whatever `async_op` says, and joined when the work is waited for: a
+    # synchronous caller gets the result after that join, an asynchronous one gets the work object.
+    overlapped = bool(method) and str(method).startswith("overlap-")
+
     def transport(tensor: Any, *, config: CompressionConfig, op: str, async_op: bool, dtype: str,
                   extension_status: Any | None = None) -> Any:
         _check_op(op, "topology_all_reduce")
-        return _communicator(group).all_reduce(tensor.clone(), config=config, op=op, strategy=strategy,
-                                               async_op=async_op, dtype=dtype)
+        work = _communicator(group).all_reduce(tensor.clone(), config=config, op=op, strategy=strategy,
+                                               async_op=async_op or overlapped, dtype=dtype)
+        if overlapped and not async_op and hasattr(work, "wait"):
+            return work.wait()
+        return work
 
+    transport.overlapped = overlapped
     return transport
 
 

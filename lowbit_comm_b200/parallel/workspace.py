@@ -126,11 +126,11 @@ class CudaWorkspacePool:
     def __init__(self, *, allocator: Callable[[WorkspaceKey, Any], Any], max_cached_bytes: int | None = None,
                  max_entries: int | None = None) -> None:
         if not callable(allocator):
-            raise TypeError("allocator must be callable")
+            raise TypeError(f"the pool needs a function that allocates a workspace, got {type(allocator).__name__}")
         if max_cached_bytes is not None and max_cached_bytes < 0:
-            raise ValueError("max_cached_bytes must be >= 0 or None")
+            raise ValueError(f"a byte budget cannot be negative (max_cached_bytes={max_cached_bytes}); None means unlimited")
         if max_entries is not None and max_entries < 1:
-            raise ValueError("max_entries must be >= 1 or None")
+            raise ValueError(f"an entry budget below one caches nothing (max_entries={max_entries}); None means unlimited")
         self._alloc = allocator
         self._byte_budget, self._entry_budget = max_cached_bytes, max_entries
         self._idle: "OrderedDict[int, _Entry]" = OrderedDict()      # ready for anyone, LRU order

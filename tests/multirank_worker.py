@@ -103,6 +103,19 @@ def collectives_case(rank: int, world: int) -> None:
             shards.append(oracle.reduce_mean([oracle.encode(p, cfg) for p in pieces], geo.shard_numel, cfg, name)[0])
         want = torch.cat([oracle.decode(oracle.encode(sh, cfg), geo.shard_numel, cfg, name) for sh in shards])[:n]
         assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), ("hierarchical", rank)
+    # the hop-by-hop ring and tree executors over NCCL send / receive (the path for groups without peer access):
+    # bit for bit what a single-process replay of the same schedule through the same codec gives
+    import test_cpu_gloo_schedule_executors as replay
+    from lowbit_comm_b200.parallel.transports import make_native_topology_all_reduce
+
+    n = 64 * world * 37 + 11
+    xs = _inputs(world, n, dt, seed=300)
+    for method, expected in (("ring", replay._replay_ring), ("tree", replay._replay_tree)):
+        transport = make_native_topology_all_reduce(method=method, hop_by_hop=True)
+        got = transport(xs[rank].cuda(), config=cfg, op="mean", async_op=False, dtype=name)
+        torch.cuda.synchronize()
+        want = expected(xs, cfg, name, "mean")
+        assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), ("hop by hop", method, rank)
     # quantized point-to-point through the peer mailboxes: a ring, three rounds (the second and third
     # sends first wait for the receiver's acknowledgement of the previous message)
     import lowbit_comm_b200 as lbc

@@ -407,6 +407,28 @@ def test_topk_and_codebook_profiles_through_peer_memory(ext, world, dtype, kw):
         PeerGroup.close_loopback(groups)
 
 
+@pytest.mark.parametrize("world", (2, 8))
+def test_all_gather_into_one_buffer_is_a_single_decode_launch(ext, world):
+    """Outputs that are the rows of one buffer, payloads of whole 8-group units: one decode launch for all W."""
+
+    cfg = CompressionConfig()
+    dtype, n = "bf16", 64 * 8 * 25
+    groups, wss = _make(world, dtype, cfg, n)
+    try:
+        xs = _inputs(world, n, dtype, seed=9)
+        dev = [x.cuda() for x in xs]
+        bufs = [torch.empty(world, n, dtype=DT[dtype], device="cuda") for _ in range(world)]
+        before = wss[0].launches
+        run_loopback(wss, "all_gather", [(dev[r], list(bufs[r].unbind(0))) for r in range(world)])
+        assert wss[0].launches - before == 3          # quantize + broadcast, gate, one decode
+        for r in range(world):
+            for src in range(world):
+                want = oracle.decode(oracle.encode(xs[src], cfg), n, cfg, dtype)
+                assert torch.equal(bufs[r][src].cpu().view(torch.uint8), want.view(torch.uint8)), (r, src)
+    finally:
+        PeerGroup.close_loopback(groups)
+
+
 def test_bounded_wait_reports_status_instead_of_hanging(ext):
     """A flag that nothing sets: the kernel gives up after its time limit and says why."""
 
