@@ -79,6 +79,23 @@ class DynamicGatherCacheKey(NamedTuple):
     dequantize: ObjectIdentity
 
 
+class _GatherSlots:
+    """What an executor keeps on one device between runs: the send buffer, one receive buffer cut into a slot per
+    rank, and the metadata words on both sides of the bus (pinned on the host for a CUDA device).  The capacity of
+    the shape class is fixed, so nothing here is allocated again after the first run."""
+
+    def __init__(self, torch, device, capacity_bytes: int, world: int) -> None:
+        cuda = device.type == "cuda"
+        self.send = torch.zeros(capacity_bytes, dtype=torch.uint8, device=device)
+        self.recv = torch.empty(world * capacity_bytes, dtype=torch.uint8, device=device)
+        self.slots = list(self.recv.view(world, capacity_bytes).unbind(0))
+        self.words = torch.zeros(PACKET_WORDS, dtype=torch.int64, device=device)
+        self.gathered = torch.empty(world * PACKET_WORDS, dtype=torch.int64, device=device)
+        self.words_host = torch.zeros(PACKET_WORDS, dtype=torch.int64, pin_memory=cuda) if cuda else self.words
+        self.gathered_host = (torch.empty(world * PACKET_WORDS, dtype=torch.int64, pin_memory=True) if cuda
+                              else self.gathered)
+
+
 class CudaDynamicGatherExecutor:
     def __init__(self, *, shape_class: tuple[int, ...], config: CompressionConfig, dtype: str, group: Any | None = None,
                  extension_status: Any | None = None, metadata_protocol: str = "object_v1",
@@ -107,6 +124,8 @@ class CudaDynamicGatherExecutor:
             details={"shape_class": self.shape_class, "metadata_protocol": self.protocol})
         self.execution_counters = ExecutionCounters()
         self.host_sync_count = 0
+        self.slot_allocations = 0                       # times a `_GatherSlots` was built (once per device and world)
+        self._slots: dict[tuple, _GatherSlots] = {}
 
     @property
     def metadata_protocol(self) -> str:
@@ -119,7 +138,15 @@ class CudaDynamicGatherExecutor:
     def _kw(self) -> dict:
         return {} if self.group is None else {"group": self.group}
 
-    def _gather_metadata(self, dist, torch, local: MetadataPacket, device) -> list[MetadataPacket]:
+    def _slots_for(self, torch, device, world: int) -> _GatherSlots:
+        key = (device.type, device.index, world)
+        held = self._slots.get(key)
+        if held is None:
+            held = self._slots[key] = _GatherSlots(torch, device, max(self.capacity_bytes, 1), world)
+            self.slot_allocations += 1
+        return held
+
+    def _gather_metadata(self, dist, torch, local: MetadataPacket, device, held: _GatherSlots) -> list[MetadataPacket]:
         world = dist.get_world_size(**self._kw())
         if self.protocol == "object_v1":
             objs: list[Any] = [None] * world
@@ -127,13 +154,17 @@ class CudaDynamicGatherExecutor:
                                          local.payload_numel, local.flags)
             dist.all_gather_object(objs, mine.to_wire(), **self._kw())
             return [DynamicGatherMetadata.from_wire(o).packet() for o in objs]
-        words = torch.tensor(local.encode(), dtype=torch.int64)
-        if device.type == "cuda":
-            words = words.pin_memory().to(device, non_blocking=True)
-        gathered = torch.empty(world * PACKET_WORDS, dtype=torch.int64, device=device)
-        dist.all_gather_into_tensor(gathered, words, **self._kw())
+        # the packet goes host (pinned) -> device -> all ranks -> host (pinned); the one wait below is the only
+        # host synchronisation of a run (the shapes have to be known here to allocate the outputs)
+        held.words_host.copy_(torch.tensor(local.encode(), dtype=torch.int64))
+        if held.words_host is not held.words:
+            held.words.copy_(held.words_host, non_blocking=True)
+        dist.all_gather_into_tensor(held.gathered, held.words, **self._kw())
+        if held.gathered_host is not held.gathered:
+            held.gathered_host.copy_(held.gathered, non_blocking=True)
+            torch.cuda.current_stream(device).synchronize()
         self.host_sync_count += 1
-        return decode_all(gathered.tolist(), world)
+        return decode_all(held.gathered_host.tolist(), world)
 
     def run(self, tensor: Any) -> list[Any]:
         torch = self._importer("torch")
@@ -148,12 +179,12 @@ class CudaDynamicGatherExecutor:
             device = tensor.device
             payload_bytes = estimate_quantized_size(n, dtype=self.dtype, config=self.config).quantized_bytes
             local = MetadataPacket(tuple(tensor.shape), self.dtype, payload_bytes, FLAG_EMPTY if n == 0 else 0)
-            send = torch.zeros(self.capacity_bytes, dtype=torch.uint8, device=device)
+            held = self._slots_for(torch, device, dist.get_world_size(**self._kw()))
+            send, slots = held.send, held.slots          # bytes past a payload are never read: no clearing
             if n:  # zero-element tensors never reach a kernel
                 self._quantize(tensor.contiguous(), self.config, extension_status=self._status,
                                output=send[:payload_bytes])
-            metas = self._gather_metadata(dist, torch, local, device)
-            slots = [torch.empty_like(send) for _ in metas]
+            metas = self._gather_metadata(dist, torch, local, device, held)
             dist.all_gather(slots, send, **self._kw())
             outs = []
             for meta, slot in zip(metas, slots):

@@ -104,3 +104,25 @@ def test_compiled_executor_rejects_what_does_not_fit():
     assert snap.run_calls == 2 and snap.failed_runs == 2 and fake.calls == []
     outs = ex.run(torch.ones(64, dtype=torch.bfloat16))
     assert len(outs) == 2 and ex.execution_counters.snapshot().completed_runs == 1
+
+
+def test_executor_keeps_its_send_and_receive_slots_between_runs():
+    cfg = CompressionConfig()
+    fake = FakeDist(cfg, [torch.full((40,), 0.25, dtype=torch.bfloat16)])
+    seen = []
+    plain = fake.all_gather
+
+    def watching(slots, send, **kw):
+        seen.append((send.data_ptr(), tuple(s.data_ptr() for s in slots)))
+        plain(slots, send, **kw)
+
+    fake.all_gather = watching
+    ex = CudaDynamicGatherExecutor(shape_class=(128,), config=cfg, dtype="bf16", metadata_protocol="tensor_v1",
+                                   import_module_fn=_importer(fake))
+    first = ex.run(torch.full((128,), 0.5, dtype=torch.bfloat16))
+    second = ex.run(torch.full((3, 5), -0.5, dtype=torch.bfloat16))     # a smaller tensor of the same shape class
+    assert ex.slot_allocations == 1 and seen[0] == seen[1] and ex.host_sync_count == 2
+    assert seen[0][1][1] - seen[0][1][0] == ex.capacity_bytes           # slots are rows of one receive buffer
+    assert tuple(first[0].shape) == (128,) and tuple(second[0].shape) == (3, 5)
+    assert torch.equal(second[0], torch.full((3, 5), -0.5, dtype=torch.bfloat16))
+    assert torch.equal(first[1], second[1]) and first[1].data_ptr() != second[1].data_ptr()   # results own their memory
