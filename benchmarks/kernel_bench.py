@@ -104,9 +104,8 @@ def main() -> None:
             record("torch copy_ (reference point)", mib, 4 * n, t)
             if ref is not None:
                 rc, rcfg, rstatus = ref
-                rout = rc.allocate_quantized_buffer(x, rcfg) if hasattr(rc, "allocate_quantized_buffer") else out.clone()
-                rout = rout.reshape(-1) if rout.numel() == pb else torch.empty(pb, dtype=torch.uint8, device="cuda")
                 try:
+                    rout = rc.allocate_quantized_buffer(x, rcfg, dtype="bf16").reshape(-1)
                     ok = rc.inplace_quantize_pack(x, rout, None, rcfg, extension_status=rstatus)
                     t = time_cuda(lambda: rc.inplace_quantize_pack(x, rout, None, rcfg, extension_status=rstatus),
                                   iters=args.iters, flush=flush, warmup=warm)
