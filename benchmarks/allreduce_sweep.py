@@ -41,7 +41,6 @@ def main() -> None:
                     help="pipe: one persistent kernel per all-reduce; legacy: the K1/K2/K3 kernel sequence; "
                          "auto: the library's choice by size")
     ap.add_argument("--arms", default="auto,1,2", help="paths of this library to time: auto, 1 (one stage), 2 (two stages)")
-    ap.add_argument("--chunk-rows", type=int, default=None, help="pipelined engine: rows of one chunk over all shards")
     ap.add_argument("--ring", type=int, default=None, help="pipelined engine: rows in flight per block (2..4)")
     ap.add_argument("--no-ef", action="store_true", help="time the collectives without error feedback")
     ap.add_argument("--chunk-mib", type=float, default=None, help="pipeline chunk size (0 = no pipelining)")
@@ -99,8 +98,6 @@ def main() -> None:
         _req().set_gather_prefetch(args.gather_prefetch)
     if args.gather is not None:
         big.set_gather_mode(args.gather)
-    if args.engine != "legacy" and args.chunk_rows is not None:
-        big._pipe.set_chunk_rows(args.chunk_rows)
     if args.engine != "legacy" and args.ring is not None:
         big._pipe.set_ring_depth(args.ring)
     if args.chunk_mib is not None:

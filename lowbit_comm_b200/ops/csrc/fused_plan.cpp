@@ -362,13 +362,6 @@ class PipeAllReducePlan {
         group_bytes_ = group_ * bit_ / 8 + (dtype_ == LBC_FP32 ? 4 : 2);
     }
 
-    // Reserved.  The kernel runs every phase as one sweep over its rows (a schedule that cut the tensor into
-    // chunks whose phases overlapped was measured slower: it paid a grid-wide meeting per chunk); the chunk
-    // geometry is still computed and validated so that callers written against it keep working.
-    void set_chunk_rows(int64_t min_rows, int max_chunks) {
-        min_chunk_rows_ = std::max<int64_t>(min_rows, 1);
-        max_chunks_ = std::max(1, std::min(max_chunks, LBC_PIPE_MAX_CHUNKS));
-    }
     void set_ring_depth(int depth) { ring_depth_ = depth; }
     void set_max_blocks(int blocks) { max_blocks_ = blocks; }
     // Device buffer of [grid][8] 64-bit cycle counters filled by every launch (0 = off): where the blocks'
@@ -414,12 +407,6 @@ class PipeAllReducePlan {
         p.q_off = q_off_;
         p.ag_off = ag_off_;
         p.ctl_off = ctl_off_;
-        const int64_t row_groups = LBC_PIPE_ROW_ELEMS / group_;
-        const int64_t shard_rows = ceil_div(p.shard_groups, row_groups);
-        int64_t chunks = std::min<int64_t>(max_chunks_, (shard_rows * shards) / min_chunk_rows_);
-        chunks = std::max<int64_t>(1, chunks);
-        p.rows_per_chunk = ceil_div(shard_rows, chunks);
-        p.num_chunks = static_cast<int>(ceil_div(shard_rows, p.rows_per_chunk));
         p.epoch = epoch;
         p.timeout_ns = timeout_ns_;
         p.status = reinterpret_cast<void*>(status_);
@@ -444,8 +431,6 @@ class PipeAllReducePlan {
     int max_blocks_;
     int64_t max_numel_;
     int64_t group_bytes_ = 66;
-    int64_t min_chunk_rows_ = 4096;
-    int max_chunks_ = LBC_PIPE_MAX_CHUNKS;
     int ring_depth_ = 0;
     uintptr_t profile_ = 0;
 };
@@ -473,8 +458,6 @@ void bind_fused_plan(py::module_& m) {
              py::arg("dtype"), py::arg("group_size"), py::arg("bit"), py::arg("rank"), py::arg("peer_ptrs"),
              py::arg("q_off"), py::arg("q_bytes"), py::arg("ag_off"), py::arg("ag_bytes"), py::arg("ctl_off"),
              py::arg("timeout_ns"), py::arg("status_device"), py::arg("max_blocks"), py::arg("max_numel"))
-        .def("set_chunk_rows", &PipeAllReducePlan::set_chunk_rows, py::arg("min_rows"),
-             py::arg("max_chunks") = LBC_PIPE_MAX_CHUNKS)
         .def("set_ring_depth", &PipeAllReducePlan::set_ring_depth, py::arg("depth"))
         .def("set_max_blocks", &PipeAllReducePlan::set_max_blocks, py::arg("blocks"))
         .def("set_profile_buffer", &PipeAllReducePlan::set_profile_buffer, py::arg("ptr"))

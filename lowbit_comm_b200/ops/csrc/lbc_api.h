@@ -105,12 +105,12 @@ cudaError_t lbc_reduce(const LbcReduce* p, cudaStream_t stream);
 // every rank reduces all W payloads and writes the result directly (no DECODE phase).
 // The reference moves the same bytes with NCCL calls between kernels (ccdl_comm/cuda/transports/
 // pipelined_ring.py:236-316); it has no counterpart of this kernel.
-#define LBC_PIPE_MAX_CHUNKS 16
+#define LBC_PIPE_FLAG_STRIDE 16   // u32 words between two ranks' flags (one 64-byte line per rank)
 #define LBC_PIPE_ROW_ELEMS 4096
 enum LbcPipePhase { LBC_PIPE_QUANT = 1, LBC_PIPE_REDUCE = 2, LBC_PIPE_DECODE = 4, LBC_PIPE_ALL = 7 };
 // Control block of one workspace (same offset in every arena; zero when the arena is created):
-#define LBC_PIPE_CTL_FLAGS_QUANT 0      // u32 [LBC_MAX_RANKS][LBC_PIPE_MAX_CHUNKS], written by the peers
-#define LBC_PIPE_CTL_FLAGS_REDUCE 1024  // u32 [LBC_MAX_RANKS][LBC_PIPE_MAX_CHUNKS], written by the peers
+#define LBC_PIPE_CTL_FLAGS_QUANT 0      // u32 [LBC_MAX_RANKS][LBC_PIPE_FLAG_STRIDE], word 0 of each line written by that peer
+#define LBC_PIPE_CTL_FLAGS_REDUCE 1024  // u32 [LBC_MAX_RANKS][LBC_PIPE_FLAG_STRIDE], word 0 of each line written by that peer
 #define LBC_PIPE_CTL_FLAGS_GATE 2048    // u32 [LBC_MAX_RANKS], written by the peers (rendezvous)
 #define LBC_PIPE_CTL_LOCAL 2304         // u32 [2] reserved, then blocks done per phase: local scratch
 #define LBC_PIPE_CTL_BYTES 2560
@@ -135,8 +135,6 @@ typedef struct {
     int64_t ag_off;             // own reduced shard, one planar payload (stages == 2)
     int64_t ctl_off;            // control block
     int64_t shard_groups;       // groups per shard, a multiple of 8
-    int num_chunks;             // reserved (<= LBC_PIPE_MAX_CHUNKS): every phase is one sweep
-    int64_t rows_per_chunk;     // reserved: num_chunks * rows_per_chunk covers a shard's rows
     unsigned int epoch;
     unsigned long long timeout_ns;
     void* status;               // LbcStatus*, device visible

@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(kThreads, 2) pipe_allreduce_kernel(const __gri
                 unsigned int spins = 0, seen = p.epoch;
                 for (;;) {
                     seen = p.epoch;
-                    if (wlane < W) seen = ld_relaxed_sys(flags + wlane * LBC_PIPE_MAX_CHUNKS);
+                    if (wlane < W) seen = ld_relaxed_sys(flags + wlane * LBC_PIPE_FLAG_STRIDE);
                     const unsigned int late = __ballot_sync(0xffffffffu, int(seen - p.epoch) < 0);
                     if (late == 0u) break;
                     if ((++spins & 1023u) == 0) {       // the status word lives in host memory: look rarely
@@ -615,7 +615,7 @@ __global__ void __launch_bounds__(kThreads, 2) pipe_allreduce_kernel(const __gri
                     __syncwarp();
                     if (wlane < W) {
                         const int64_t off = p.ctl_off + (kind == kQuant ? LBC_PIPE_CTL_FLAGS_QUANT : LBC_PIPE_CTL_FLAGS_REDUCE) +
-                                            int64_t(me) * LBC_PIPE_MAX_CHUNKS * 4;
+                                            int64_t(me) * LBC_PIPE_FLAG_STRIDE * 4;
                         st_release_sys(reinterpret_cast<unsigned int*>(p.arena[wlane] + off), p.epoch);
                     }
                 }
@@ -731,7 +731,6 @@ cudaError_t lbc_pipe_allreduce(const LbcPipe* p, cudaStream_t stream) {
     if (p->stages != 1 && p->stages != 2) return cudaErrorInvalidValue;
     if ((p->phase_mask & ~LBC_PIPE_ALL) != 0 || p->phase_mask == 0) return cudaErrorInvalidValue;
     if (p->shard_groups <= 0 || (p->shard_groups & 7) != 0) return cudaErrorInvalidValue;
-    if (p->num_chunks < 1 || p->num_chunks > LBC_PIPE_MAX_CHUNKS || p->rows_per_chunk < 1) return cudaErrorInvalidValue;
     if (p->x == nullptr || p->out == nullptr) return cudaErrorInvalidValue;
     if ((p->prepared == nullptr) != (p->residual_out == nullptr)) return cudaErrorInvalidValue;
     if (((p->q_off | p->ag_off | p->shard_stride) & 15) != 0 || (p->ctl_off & 255) != 0) return cudaErrorInvalidValue;
@@ -740,7 +739,6 @@ cudaError_t lbc_pipe_allreduce(const LbcPipe* p, cudaStream_t stream) {
     if (groups > p->shard_groups * shards) return cudaErrorInvalidValue;
     const int64_t row_groups = LBC_PIPE_ROW_ELEMS / p->group_size;
     const int64_t shard_rows = (p->shard_groups + row_groups - 1) / row_groups;
-    if (int64_t(p->num_chunks) * p->rows_per_chunk < shard_rows) return cudaErrorInvalidValue;
     if (shard_rows * p->world >= (int64_t(1) << 31)) return cudaErrorInvalidValue;   // row indices are 32-bit
     for (int r = 0; r < p->world; ++r)
         if (p->arena[r] == nullptr || (reinterpret_cast<uintptr_t>(p->arena[r]) & 15) != 0) return cudaErrorInvalidValue;

@@ -231,9 +231,6 @@ class FusedWorkspace:
             _DTYPE_CODE[self.dtype], self.config.group_size, self.config.bit, group.rank, list(group.peer_ptrs),
             self.pipe_q_off, q_bytes, self.pipe_ag_off, ag_bytes, self.pipe_ctl_off, group.timeout_ns,
             group.status_device, self.max_blocks, self.pipe_numel)
-        rows = os.environ.get("LBC_PIPE_CHUNK_ROWS")
-        if rows:
-            self._pipe.set_chunk_rows(int(rows))
         depth = os.environ.get("LBC_PIPE_RING")
         if depth:
             self._pipe.set_ring_depth(int(depth))

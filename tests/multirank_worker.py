@@ -39,8 +39,6 @@ def collectives_case(rank: int, world: int) -> None:
             mine = xs[rank].cuda()
             ws = comm.workspace(mine, cfg, name)
             assert ws.engine == "auto"      # the default: one persistent kernel per all-reduce up to a size limit
-            if n > 50_000:
-                ws._pipe.set_chunk_rows(16)     # many chunks: the phases of neighbouring chunks overlap across GPUs
             got = compressed_all_reduce(mine, config=cfg, op="mean", strategy=strategy)
             torch.cuda.synchronize()
             assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), (strategy, n, rank)
