@@ -243,6 +243,60 @@ void dequant_general(const at::Tensor& src, at::Tensor& out, int group_size, int
     cuda_check(lbc_dequant_general(&p, at::cuda::getCurrentCUDAStream()), "lbc_dequant_general");
 }
 
+// quant_general with the stores going straight into every destination slot, and a signal at the end.
+void quant_general_push(const at::Tensor& x, const std::optional<at::Tensor>& residual,
+                        const std::optional<at::Tensor>& prepared_out, const Ptrs& dst, int group_size, int bit, int topk,
+                        int quant_type, bool stochastic, bool compact, uint64_t seed, const SignalArg& signal,
+                        int max_blocks) {
+    check_dense(x, "input");
+    TORCH_CHECK(!dst.empty(), "dst: at least one destination");
+    c10::cuda::CUDAGuard guard(x.device());
+    LbcQuantGeneral p{};
+    p.dtype = dtype_code(x);
+    p.group_size = group_size;
+    p.bit = bit;
+    p.topk = topk;
+    p.quant_type = quant_type;
+    p.stochastic = stochastic ? 1 : 0;
+    p.compact = compact ? 1 : 0;
+    p.x = x.data_ptr();
+    p.residual = opt_ptr(residual, x, "residual");
+    p.prepared_out = const_cast<void*>(opt_ptr(prepared_out, x, "prepared_out"));
+    p.numel = x.numel();
+    p.seed = seed;
+    fill_ptrs(p.dst, &p.num_dst, dst, "dst");
+    p.signal = make_signal(signal);
+    p.max_blocks = max_blocks;
+    cuda_check(lbc_quant_general(&p, at::cuda::getCurrentCUDAStream()), "lbc_quant_general(push)");
+}
+
+// Bounded wait, then one pass that decodes and sums every source payload, scales, and updates the residual.
+void reduce_general(const Ptrs& src, at::Tensor& out, int group_size, int bit, int topk, int quant_type, bool compact,
+                    double scale, const std::optional<at::Tensor>& prepared, const std::optional<at::Tensor>& residual_out,
+                    const WaitArg& wait, int max_blocks) {
+    check_dense(out, "output");
+    TORCH_CHECK(prepared.has_value() == residual_out.has_value(), "prepared and residual_out come together");
+    c10::cuda::CUDAGuard guard(out.device());
+    LbcReduceGeneral p{};
+    p.dtype = dtype_code(out);
+    p.group_size = group_size;
+    p.bit = bit;
+    p.topk = topk;
+    p.quant_type = quant_type;
+    p.compact = compact ? 1 : 0;
+    uint8_t* ptrs[LBC_MAX_RANKS];
+    fill_ptrs(ptrs, &p.num_src, src, "src");
+    for (int r = 0; r < p.num_src; ++r) p.src[r] = ptrs[r];
+    p.numel = out.numel();
+    p.out = out.data_ptr();
+    p.scale = static_cast<float>(scale);
+    p.prepared = opt_ptr(prepared, out, "prepared");
+    p.residual_out = const_cast<void*>(opt_ptr(residual_out, out, "residual_out"));
+    p.wait = make_wait(wait);
+    p.max_blocks = max_blocks;
+    cuda_check(lbc_reduce_general(&p, at::cuda::getCurrentCUDAStream()), "lbc_reduce_general");
+}
+
 void error_feedback_update(const at::Tensor& prepared, const at::Tensor& restored, at::Tensor& residual) {
     check_dense(prepared, "prepared");
     check_dense(restored, "restored");
@@ -316,6 +370,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("src_shard_groups") = 0, py::arg("first_src") = 0);
     m.def("quant_general", &quant_general);
     m.def("dequant_general", &dequant_general);
+    m.def("quant_general_push", &quant_general_push, py::arg("x"), py::arg("residual"), py::arg("prepared_out"),
+          py::arg("dst"), py::arg("group_size"), py::arg("bit"), py::arg("topk"), py::arg("quant_type"),
+          py::arg("stochastic"), py::arg("compact"), py::arg("seed"), py::arg("signal") = py::none(),
+          py::arg("max_blocks") = 0);
+    m.def("reduce_general", &reduce_general, py::arg("src"), py::arg("out"), py::arg("group_size"), py::arg("bit"),
+          py::arg("topk"), py::arg("quant_type"), py::arg("compact"), py::arg("scale"), py::arg("prepared") = py::none(),
+          py::arg("residual_out") = py::none(), py::arg("wait") = py::none(), py::arg("max_blocks") = 0);
     m.def("error_feedback_update", &error_feedback_update);
     m.def("scale_inplace", &scale_inplace);
     m.def("push_bytes", &push_bytes, py::arg("src"), py::arg("nbytes"), py::arg("dst"), py::arg("wait") = py::none(),

@@ -219,24 +219,84 @@ __global__ void __launch_bounds__(kThreads) quant_general_kernel(const LbcQuantG
             const uint2 c = pack16_i4<sizeof(T)>(q);
             w[0] = c.x; w[1] = c.y;
         }
-        uint8_t* vptr;
-        uint8_t* mptr;
-        if (p.compact) {
-            vptr = p.out + g * (VB + MB);
-            mptr = vptr + VB;
-        } else {
-            vptr = p.out + g * VB;
-            mptr = p.out + num_groups * VB + g * MB;
+        uint32_t index_word = 0;
+        if (p.topk >= 1) {
+            index_word = uint32_t(top[0].idx);
+            if (p.topk == 2) index_word |= uint32_t(top[1].idx) << 8;
         }
-        store_bytes(vptr + lane * CB, w, CB);
-        if (lane == 0) {
-            store_word<T>(mptr, bits_of<T>(stored));
-            if (p.topk >= 1) {
-                uint32_t index_word = uint32_t(top[0].idx);
-                if (p.topk == 2) index_word |= uint32_t(top[1].idx) << 8;
-                store_word<T>(mptr + sizeof(T), index_word);
-                store_word<T>(mptr + 2 * sizeof(T), bits_of<T>(kept[0]));
-                if (p.topk == 2) store_word<T>(mptr + 3 * sizeof(T), bits_of<T>(kept[1]));
+        const int copies = p.num_dst > 0 ? p.num_dst : 1;
+        for (int d = 0; d < copies; ++d) {      // one payload, or the same payload in every rank's slot
+            uint8_t* base = p.num_dst > 0 ? p.dst[d] : p.out;
+            uint8_t* vptr;
+            uint8_t* mptr;
+            if (p.compact) {
+                vptr = base + g * (VB + MB);
+                mptr = vptr + VB;
+            } else {
+                vptr = base + g * VB;
+                mptr = base + num_groups * VB + g * MB;
+            }
+            store_bytes(vptr + lane * CB, w, CB);
+            if (lane == 0) {
+                store_word<T>(mptr, bits_of<T>(stored));
+                if (p.topk >= 1) {
+                    store_word<T>(mptr + sizeof(T), index_word);
+                    store_word<T>(mptr + 2 * sizeof(T), bits_of<T>(kept[0]));
+                    if (p.topk == 2) store_word<T>(mptr + 3 * sizeof(T), bits_of<T>(kept[1]));
+                }
+            }
+        }
+    }
+    grid_signal(p.signal);      // no-op without destinations to notify
+}
+
+// Decodes the 16 elements of (group g, lane) of one payload into d, rounded to T, top-k values written back.
+template <typename T>
+__device__ __forceinline__ void decode_general_chunk(const uint8_t* src, int compact, int bit, int topk, int quant_type,
+                                                     int VB, int MB, int CB, int64_t num_groups, int64_t g, int lane,
+                                                     float (&d)[16]) {
+    const uint8_t* vptr;
+    const uint8_t* mptr;
+    if (compact) {
+        vptr = src + g * (VB + MB);
+        mptr = vptr + VB;
+    } else {
+        vptr = src + g * VB;
+        mptr = src + num_groups * VB + g * MB;
+    }
+    uint32_t w[4];
+    load_bytes(vptr + lane * CB, w, CB);
+    const float stored = value_of<T>(load_word<T>(mptr));
+    if (quant_type == LBC_LINEAR) {
+        if (bit == 8) {
+            unpack16_i8<sizeof(T)>(make_uint4(w[0], w[1], w[2], w[3]), d);
+            const float step = stored / 127.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) d[i] *= step;
+        } else {
+            int c[16];
+            unpack16_i4<sizeof(T)>(make_uint2(w[0], w[1]), c);
+            const float step = stored / 7.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) d[i] = int4_value(c[i]) * step;
+        }
+    } else {
+        int c[16];
+        unpack16_i4<sizeof(T)>(make_uint2(w[0], w[1]), c);
+        const float* table = kCodebooks[quant_type - 1];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) d[i] = table[c[i]] * stored;
+    }
+    round16<T>(d);
+    if (topk >= 1) {
+        const uint32_t index_word = load_word<T>(mptr + sizeof(T));
+        for (int j = 0; j < topk; ++j) {
+            const int at = int((index_word >> (8 * j)) & 0xffu) - lane * 16;
+            if (at >= 0 && at < 16) {
+                const float kept = value_of<T>(load_word<T>(mptr + (2 + j) * sizeof(T)));
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    if (i == at) d[i] = kept;
             }
         }
     }
@@ -259,52 +319,8 @@ __global__ void __launch_bounds__(kThreads) dequant_general_kernel(const LbcDequ
         const int64_t first = chunk * kElemsPerThread;
         const int64_t g = chunk / lanes;
         const int lane = int(chunk - g * lanes);
-        const uint8_t* vptr;
-        const uint8_t* mptr;
-        if (p.compact) {
-            vptr = p.src + g * (VB + MB);
-            mptr = vptr + VB;
-        } else {
-            vptr = p.src + g * VB;
-            mptr = p.src + num_groups * VB + g * MB;
-        }
-        uint32_t w[4];
-        load_bytes(vptr + lane * CB, w, CB);
-        const float stored = value_of<T>(load_word<T>(mptr));
         float d[16];
-        if (p.quant_type == LBC_LINEAR) {
-            if (p.bit == 8) {
-                unpack16_i8<sizeof(T)>(make_uint4(w[0], w[1], w[2], w[3]), d);
-                const float step = stored / 127.0f;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) d[i] *= step;
-            } else {
-                int c[16];
-                unpack16_i4<sizeof(T)>(make_uint2(w[0], w[1]), c);
-                const float step = stored / 7.0f;
-#pragma unroll
-                for (int i = 0; i < 16; ++i) d[i] = int4_value(c[i]) * step;
-            }
-        } else {
-            int c[16];
-            unpack16_i4<sizeof(T)>(make_uint2(w[0], w[1]), c);
-            const float* table = kCodebooks[p.quant_type - 1];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) d[i] = table[c[i]] * stored;
-        }
-        round16<T>(d);
-        if (p.topk >= 1) {
-            const uint32_t index_word = load_word<T>(mptr + sizeof(T));
-            for (int j = 0; j < p.topk; ++j) {
-                const int at = int((index_word >> (8 * j)) & 0xffu) - lane * 16;
-                if (at >= 0 && at < 16) {
-                    const float kept = value_of<T>(load_word<T>(mptr + (2 + j) * sizeof(T)));
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (i == at) d[i] = kept;
-                }
-            }
-        }
+        decode_general_chunk<T>(p.src, p.compact, p.bit, p.topk, p.quant_type, VB, MB, CB, num_groups, g, lane, d);
         if (p.accumulate) {
             float prev[16];
             load16<T>(out, first, n, o_vec, prev, false);
@@ -315,9 +331,56 @@ __global__ void __launch_bounds__(kThreads) dequant_general_kernel(const LbcDequ
     }
 }
 
-static int general_grid(int64_t chunks) {
+template <typename T, int G>
+__global__ void __launch_bounds__(kThreads) reduce_general_kernel(const LbcReduceGeneral p) {
+    constexpr int lanes = G / kElemsPerThread;
+    if (!block_wait(p.wait)) return;      // bounded; the status word says which flag never came
+    const int VB = G * p.bit / 8;
+    const int meta_words = p.topk == 0 ? 1 : (p.topk == 1 ? 3 : 4);
+    const int MB = meta_words * int(sizeof(T));
+    const int CB = kElemsPerThread * p.bit / 8;
+    T* out = static_cast<T*>(p.out);
+    const T* prep = static_cast<const T*>(p.prepared);
+    T* res = static_cast<T*>(p.residual_out);
+    const int64_t n = p.numel;
+    const int64_t num_groups = (n + G - 1) / G;
+    const int64_t num_chunks = num_groups * lanes;
+    const bool o_vec = (reinterpret_cast<uintptr_t>(out) & 31) == 0;
+    const bool p_vec = prep == nullptr || (reinterpret_cast<uintptr_t>(prep) & 31) == 0;
+    const bool r_vec = res == nullptr || (reinterpret_cast<uintptr_t>(res) & 31) == 0;
+    for (int64_t chunk = int64_t(blockIdx.x) * kThreads + threadIdx.x; chunk < num_chunks;
+         chunk += int64_t(gridDim.x) * kThreads) {
+        const int64_t first = chunk * kElemsPerThread;
+        const int64_t g = chunk / lanes;
+        const int lane = int(chunk - g * lanes);
+        float acc[16];
+        decode_general_chunk<T>(p.src[0], p.compact, p.bit, p.topk, p.quant_type, VB, MB, CB, num_groups, g, lane, acc);
+        for (int r = 1; r < p.num_src; ++r) {
+            float d[16];
+            decode_general_chunk<T>(p.src[r], p.compact, p.bit, p.topk, p.quant_type, VB, MB, CB, num_groups, g, lane, d);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] += d[i];
+            round16<T>(acc);                // the sum lives in the source dtype between payloads
+        }
+        if (p.scale != 1.0f) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] *= p.scale;
+            round16<T>(acc);
+        }
+        if (prep != nullptr) {
+            float e[16];
+            load16<T>(prep, first, n, p_vec, e, prep != res);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) e[i] -= acc[i];
+            store16<T>(res, first, n, r_vec, e);
+        }
+        store16<T>(out, first, n, o_vec, acc);
+    }
+}
+
+static int general_grid(int64_t chunks, int max_blocks = 0) {
     int64_t want = (chunks + kThreads - 1) / kThreads;
-    const int cap = lbc_default_max_blocks();
+    const int cap = max_blocks > 0 ? max_blocks : lbc_default_max_blocks();
     if (want < 1) want = 1;
     return int(want < cap ? want : cap);
 }
@@ -326,7 +389,7 @@ template <typename T>
 static cudaError_t launch_quant(const LbcQuantGeneral* p, cudaStream_t s) {
     const int64_t groups = (p->numel + p->group_size - 1) / p->group_size;
     if (groups == 0) return cudaSuccess;
-    const int grid = general_grid(groups * (p->group_size / kElemsPerThread));
+    const int grid = general_grid(groups * (p->group_size / kElemsPerThread), p->max_blocks);
     switch (p->group_size) {
         case 64: quant_general_kernel<T, 64><<<grid, kThreads, 0, s>>>(*p); break;
         case 32: quant_general_kernel<T, 32><<<grid, kThreads, 0, s>>>(*p); break;
@@ -350,6 +413,20 @@ static cudaError_t launch_dequant(const LbcDequantGeneral* p, cudaStream_t s) {
     return cudaGetLastError();
 }
 
+template <typename T>
+static cudaError_t launch_reduce_general(const LbcReduceGeneral* p, cudaStream_t s) {
+    const int64_t groups = (p->numel + p->group_size - 1) / p->group_size;
+    if (groups == 0) return cudaSuccess;
+    const int grid = general_grid(groups * (p->group_size / kElemsPerThread), p->max_blocks);
+    switch (p->group_size) {
+        case 64: reduce_general_kernel<T, 64><<<grid, kThreads, 0, s>>>(*p); break;
+        case 32: reduce_general_kernel<T, 32><<<grid, kThreads, 0, s>>>(*p); break;
+        case 16: reduce_general_kernel<T, 16><<<grid, kThreads, 0, s>>>(*p); break;
+        default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
 static bool general_args_ok(int bit, int topk, int quant_type) {
     if (bit != 4 && bit != 8) return false;
     if (topk < 0 || topk > 2) return false;
@@ -364,6 +441,9 @@ extern "C" {
 
 cudaError_t lbc_quant_general(const LbcQuantGeneral* p, cudaStream_t stream) {
     if (p == nullptr || p->numel < 0 || !lbc::general_args_ok(p->bit, p->topk, p->quant_type)) return cudaErrorInvalidValue;
+    if (p->num_dst < 0 || p->num_dst > LBC_MAX_RANKS || (p->num_dst == 0 && p->out == nullptr)) return cudaErrorInvalidValue;
+    for (int d = 0; d < p->num_dst; ++d)
+        if (p->dst[d] == nullptr) return cudaErrorInvalidValue;
     switch (p->dtype) {
         case LBC_BF16: return lbc::launch_quant<__nv_bfloat16>(p, stream);
         case LBC_FP16: return lbc::launch_quant<__half>(p, stream);
@@ -378,6 +458,20 @@ cudaError_t lbc_dequant_general(const LbcDequantGeneral* p, cudaStream_t stream)
         case LBC_BF16: return lbc::launch_dequant<__nv_bfloat16>(p, stream);
         case LBC_FP16: return lbc::launch_dequant<__half>(p, stream);
         case LBC_FP32: return lbc::launch_dequant<float>(p, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t lbc_reduce_general(const LbcReduceGeneral* p, cudaStream_t stream) {
+    if (p == nullptr || p->numel < 0 || !lbc::general_args_ok(p->bit, p->topk, p->quant_type)) return cudaErrorInvalidValue;
+    if (p->num_src < 1 || p->num_src > LBC_MAX_RANKS || p->out == nullptr) return cudaErrorInvalidValue;
+    if ((p->prepared == nullptr) != (p->residual_out == nullptr)) return cudaErrorInvalidValue;
+    for (int r = 0; r < p->num_src; ++r)
+        if (p->src[r] == nullptr) return cudaErrorInvalidValue;
+    switch (p->dtype) {
+        case LBC_BF16: return lbc::launch_reduce_general<__nv_bfloat16>(p, stream);
+        case LBC_FP16: return lbc::launch_reduce_general<__half>(p, stream);
+        case LBC_FP32: return lbc::launch_reduce_general<float>(p, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -163,6 +163,12 @@ typedef struct {
     int64_t numel;
     uint8_t* out;
     unsigned long long seed;
+    // Fused push (num_dst > 0): every piece of the payload is stored to dst[0..num_dst) instead of `out`
+    // (own arena or a peer's over NVLink), and the grid raises `signal` after its last store.
+    uint8_t* dst[LBC_MAX_RANKS];
+    int num_dst;
+    LbcSignal signal;
+    int max_blocks;            // 0 = library default
 } LbcQuantGeneral;
 
 typedef struct {
@@ -173,8 +179,26 @@ typedef struct {
     int accumulate;
 } LbcDequantGeneral;
 
+// Waits (bounded) for `wait`, then decodes src[0..num_src) group by group, sums them in the source dtype in
+// source order (acc = T(acc + T(decode))), the rule of decoding one payload after the other with `accumulate`),
+// applies out = T(float(acc) * scale) when scale != 1, and with `prepared` also writes
+// residual_out = T(float(prepared) - float(out)).  One pass over the output for W payloads.
+typedef struct {
+    int dtype, group_size, bit, topk, quant_type, compact;
+    const uint8_t* src[LBC_MAX_RANKS];
+    int num_src;
+    int64_t numel;
+    void* out;
+    float scale;
+    const void* prepared;      // optional T[numel] (may alias residual_out)
+    void* residual_out;        // optional T[numel]
+    LbcWait wait;
+    int max_blocks;            // 0 = library default
+} LbcReduceGeneral;
+
 cudaError_t lbc_quant_general(const LbcQuantGeneral* p, cudaStream_t stream);
 cudaError_t lbc_dequant_general(const LbcDequantGeneral* p, cudaStream_t stream);
+cudaError_t lbc_reduce_general(const LbcReduceGeneral* p, cudaStream_t stream);
 
 // ---- elementwise helpers ----------------------------------------------------
 // residual = T(float(prepared) - float(restored))

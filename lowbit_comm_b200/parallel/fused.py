@@ -659,7 +659,8 @@ class _Recorder:
     def __getattr__(self, name):
         attr = getattr(self._ext, name)
         if name in ("quant_push", "reduce", "push_bytes", "wait_signal", "pipe_all_reduce", "quant_general",
-                    "dequant_general", "scale_inplace", "error_feedback_update"):
+                    "dequant_general", "scale_inplace", "error_feedback_update", "quant_general_push",
+                    "reduce_general"):
             def defer(*a, **k):
                 self._steps.append(lambda: attr(*a, **k))
             return defer

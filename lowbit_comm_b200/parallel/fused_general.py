@@ -4,22 +4,21 @@ top-k outliers (1 or 2 values per group kept verbatim), the 4-bit code-books, st
 The reference sends any `CompressionConfig` through every collective because its transports call the one
 codec and move the payload with NCCL (ccdl_comm/quantization/codec.py:104-158, top-k selection
 csrc/quantization/quant_kernel.cuh:38-97, records :249-257, write-back dequant_kernel.cuh:130-148).  Here
-such a profile takes the general kernels of this library for the math and this library's own kernels for
-the movement; no NCCL call is involved:
+such a profile takes two kernels that fuse the codec with the movement; no NCCL call is involved:
 
-  quant_general        x (+ residual) -> payload (values, scale, top-k index word and values) in this
-                       rank's own arena; `prepared` parked in the residual buffer
-  push_bytes           the payload to slot [me] of every rank's receive region (peer stores over NVLink),
-                       then a release signal on every rank
-  wait (one warp)      for the W signals
-  dequant_general x W  decode every slot, accumulate in the source dtype in rank order (the reference's
-                       unfused SUM rule), scale by 1/W for a mean
-  error_feedback_update residual = T(prepared - result)
+  quant_general (push)  x (+ residual) -> payload (values, scale, top-k index word and values), every
+                        piece stored straight into slot [me] of every rank's receive region (own memory and
+                        peer stores over NVLink); `prepared` parked in the residual buffer; the last block
+                        of the grid raises a release signal on every rank
+  reduce_general        bounded wait for the W signals, then ONE pass: decode every slot, accumulate in the
+                        source dtype in rank order (the reference's unfused SUM rule), scale by 1/W for a
+                        mean, write the result and residual = T(prepared - result)
 
 Every rank reduces all W payloads (the one-stage exchange).  The result is, bit for bit, what
 `codec.dequantize_reduce_tensors` gives for the same payloads, so the torch.distributed path and this one
 are interchangeable.  Receive regions alternate by epoch parity; the argument for reuse without extra
-barriers is the one in `parallel/fused.py`.
+barriers is the one in `parallel/fused.py`.  `fused=False` keeps the earlier composition of separate
+launches (quantize, copy-and-signal, wait, W decodes, scale, residual update) for comparison.
 """
 
 from __future__ import annotations
@@ -41,11 +40,11 @@ class GeneralPeerWorkspace:
     """Symmetric regions + one signal channel for general-profile tensors of up to `max_numel` elements."""
 
     def __init__(self, group: PeerGroup, *, dtype: str, config: CompressionConfig, max_numel: int,
-                 max_blocks: int = 0) -> None:
+                 max_blocks: int = 0, fused: bool = True) -> None:
         if is_fast_profile(config):
             raise ValueError("linear / top-k 0 / deterministic profiles are served by FusedWorkspace")
         self.group, self.dtype, self.config = group, dtype, config
-        self.max_numel, self.max_blocks = int(max_numel), int(max_blocks)
+        self.max_numel, self.max_blocks, self.fused = int(max_numel), int(max_blocks), bool(fused)
         self.ext = group._ext
         self._torch_dtype = oracle.TORCH_DTYPES[dtype]
         self.slot_bytes = self.payload_bytes(dtype, config, self.max_numel)
@@ -85,14 +84,24 @@ class GeneralPeerWorkspace:
         flat = x.reshape(-1)
         res = None if residual is None else residual.reshape(-1)
         keep = res if (res is not None and update_residual) else None      # `prepared` is parked here
+        out_flat = target.reshape(-1)
+        dst = [g.addr(d, region + me * self.slot_bytes) for d in range(W)]
+        if self.fused:
+            ext.quant_general_push(flat, res, keep, dst, cfg.group_size, cfg.bit, cfg.topk, _QUANT_CODE[cfg.quant_type],
+                                   cfg.stochastic, cfg.compact, _seed() if cfg.stochastic else 0,
+                                   g.signal_all(self.channel, PHASE_REDUCE_SCATTER, epoch), self.max_blocks)
+            ext.reduce_general([g.local_ptr + region + r * self.slot_bytes for r in range(W)], out_flat, cfg.group_size,
+                               cfg.bit, cfg.topk, _QUANT_CODE[cfg.quant_type], cfg.compact,
+                               1.0 / W if (op == "mean" and W > 1) else 1.0, keep, keep,
+                               g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch), self.max_blocks)
+            self.launches += 2
+            return target
         payload = g.local_view(self.stage_off, nbytes)
         ext.quant_general(flat, res, keep, payload, cfg.group_size, cfg.bit, cfg.topk, _QUANT_CODE[cfg.quant_type],
                           cfg.stochastic, cfg.compact, _seed() if cfg.stochastic else 0)
-        dst = [g.addr(d, region + me * self.slot_bytes) for d in range(W)]
         ext.push_bytes(g.local_ptr + self.stage_off, _round_up(nbytes, 16), dst, None,
                        g.signal_all(self.channel, PHASE_REDUCE_SCATTER, epoch), self.max_blocks)
         ext.wait_signal(g.wait_all(self.channel, PHASE_REDUCE_SCATTER, epoch), None)
-        out_flat = target.reshape(-1)
         for r in range(W):
             slot = g.local_view(region + r * self.slot_bytes, nbytes)
             ext.dequant_general(slot, out_flat, cfg.group_size, cfg.bit, cfg.topk, _QUANT_CODE[cfg.quant_type],

@@ -364,10 +364,12 @@ def test_gather_shards_writes_the_whole_tensor_in_one_decode(ext, world, dtype, 
 @pytest.mark.parametrize("kw", [dict(bit=8, group_size=64, topk=1), dict(bit=8, group_size=64, topk=2),
                                 dict(bit=4, group_size=32, topk=1, quant_type="e2m1"),
                                 dict(bit=4, group_size=16, quant_type="normal")])
-def test_topk_and_codebook_profiles_through_peer_memory(ext, world, dtype, kw):
-    """Profiles outside the production kernels (top-k outliers, 4-bit code-books) all-reduced with the general
-    kernels and this library's own transport: bit for bit what the codec gives for the gathered payloads, and
-    the reference's error-feedback rule."""
+@pytest.mark.parametrize("fused", (True, False))
+def test_topk_and_codebook_profiles_through_peer_memory(ext, world, dtype, kw, fused):
+    """Profiles outside the production kernels (top-k outliers, 4-bit code-books) all-reduced over peer memory,
+    by the two fused kernels (quantize-and-push, wait-decode-sum-scale-residual) and by the composition of
+    separate launches: bit for bit what the codec gives for the gathered payloads, and the reference's
+    error-feedback rule."""
 
     from lowbit_comm_b200.ops import codec
     from lowbit_comm_b200.parallel.fused_general import GeneralPeerWorkspace
@@ -377,7 +379,7 @@ def test_topk_and_codebook_profiles_through_peer_memory(ext, world, dtype, kw):
     need = GeneralPeerWorkspace.required_bytes(world, dtype, cfg, max_numel) + (1 << 20)
     groups = PeerGroup.loopback(world, need, timeout_ns=2_000_000_000)
     try:
-        wss = [GeneralPeerWorkspace(g, dtype=dtype, config=cfg, max_numel=max_numel) for g in groups]
+        wss = [GeneralPeerWorkspace(g, dtype=dtype, config=cfg, max_numel=max_numel, fused=fused) for g in groups]
         for step, n in enumerate((cfg.group_size * 8 * world, 12_347, 1, max_numel)):
             xs = _inputs(world, n, dtype, seed=30 + step)
             rs = _inputs(world, n, dtype, seed=60 + step)
@@ -399,8 +401,45 @@ def test_topk_and_codebook_profiles_through_peer_memory(ext, world, dtype, kw):
             exact = torch.stack([(x.float() + r.float()) for x, r in zip(xs, rs)]).mean(0)
             rel = ((want.float().cpu() - exact).norm() / exact.norm()).item()
             assert rel < (0.05 if cfg.bit == 8 else 0.25), rel
+        if fused:
+            assert wss[0].launches == 2 * 4          # two kernels per collective
+            # no residual, a separate output, a sum: the other branches of the fused reduce
+            xs = _inputs(world, 4_001, dtype, seed=99)
+            outs = [torch.empty(4_001, dtype=xs[0].dtype, device="cuda") for _ in range(world)]
+            payloads = [codec.quantize_tensor(x.cuda(), cfg) for x in xs]
+            want = codec.dequantize_reduce_tensors(payloads, (4_001,), cfg, dtype=dtype, reduce="sum")
+            run_loopback(wss, "all_reduce", [(xs[r].cuda(), outs[r]) for r in range(world)], op="sum")
+            torch.cuda.synchronize()
+            for r in range(world):
+                assert torch.equal(outs[r].view(torch.uint8), want.view(torch.uint8)), r
         for g in groups:
             g.check_status()
+    finally:
+        PeerGroup.close_loopback(groups)
+
+
+def test_fused_general_reduce_wait_runs_out_on_a_signal_nobody_sends(ext):
+    """One emulated rank of two never pushes: the reduce kernel of the other gives up after its bound, reports
+    the missing peer in the status word and leaves the output untouched; the context stays usable."""
+
+    from lowbit_comm_b200.exceptions import AsyncCommunicationError
+    from lowbit_comm_b200.parallel.fused_general import GeneralPeerWorkspace
+
+    cfg = CompressionConfig(allow_experimental=True, bit=8, group_size=64, topk=1)
+    n = 5_000
+    need = GeneralPeerWorkspace.required_bytes(2, "bf16", cfg, n) + (1 << 20)
+    groups = PeerGroup.loopback(2, need, timeout_ns=50_000_000)
+    try:
+        ws = GeneralPeerWorkspace(groups[0], dtype="bf16", config=cfg, max_numel=n)
+        x = _inputs(1, n, "bf16", seed=5)[0].cuda()
+        before = x.clone()
+        ws.all_reduce(x)                       # rank 1 stays silent
+        torch.cuda.synchronize()
+        with pytest.raises(AsyncCommunicationError):
+            groups[0].check_status()
+        assert torch.equal(x, before)
+        groups[0].reset_after_error()
+        groups[0].check_status()
     finally:
         PeerGroup.close_loopback(groups)
 
