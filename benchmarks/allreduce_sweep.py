@@ -41,6 +41,8 @@ def main() -> None:
                     help="pipe: one persistent kernel per all-reduce; legacy: the K1/K2/K3 kernel sequence; "
                          "auto: the library's choice by size")
     ap.add_argument("--arms", default="auto,1,2", help="paths of this library to time: auto, 1 (one stage), 2 (two stages)")
+    ap.add_argument("--topk", default="", help="also time top-k profiles (e.g. 1,2) through the fused general kernels")
+    ap.add_argument("--topk-max-mib", type=float, default=64, help="largest tensor of the top-k arms")
     ap.add_argument("--ring", type=int, default=None, help="pipelined engine: rows in flight per block (2..4)")
     ap.add_argument("--no-ef", action="store_true", help="time the collectives without error feedback")
     ap.add_argument("--chunk-mib", type=float, default=None, help="pipeline chunk size (0 = no pipelining)")
@@ -84,6 +86,13 @@ def main() -> None:
     from lowbit_comm_b200.parallel.fused import FusedWorkspace
 
     arena = FusedWorkspace.required_bytes(world, "bf16", cfg, 1 << (max_numel - 1).bit_length(), True) + (256 << 20)
+    topks = [int(k) for k in args.topk.split(",") if k]
+    topk_cfgs = {k: CompressionConfig(topk=k, allow_experimental=True) for k in topks}
+    topk_numel = int(min(args.topk_max_mib, args.max_mib) * 1024 * 1024 // 2)
+    if topks:
+        from lowbit_comm_b200.parallel.fused_general import GeneralPeerWorkspace
+
+        arena += sum(GeneralPeerWorkspace.required_bytes(world, "bf16", c, topk_numel) for c in topk_cfgs.values())
     if args.multicast:
         os.environ["LBC_MULTICAST"] = "1"
     comm = Communicator(None, arena_bytes=arena)
@@ -216,6 +225,26 @@ def main() -> None:
                          "gather": "pull" if big.pull_gather else "push",
                          "gather_prefetch": ext.get_gather_prefetch(), "kernels": launched})
         ext.set_push_variant(1, True, 0)
+        for k, kcfg in topk_cfgs.items():
+            if n > topk_numel:
+                continue
+            if mib == args.min_mib:                      # the largest size first, so that the workspace fits them all
+                comm.general_workspace(torch.empty(topk_numel, dtype=torch.bfloat16, device=dev), kcfg, "bf16")
+
+            def general():
+                comm.all_reduce(x, out=work, config=kcfg, op="mean", residual=residual)
+
+            if residual is not None:
+                residual.zero_()
+            t = measure(general)
+            comm.check_status()
+            if residual is not None:
+                residual.zero_()
+            general()
+            torch.cuda.synchronize()
+            rows.append({"impl": f"ours_topk{k}", "mib": mib, "world": world, "ms": t, "error_feedback": residual is not None,
+                         "algbw_gbs": nbytes / (t * 1e-3) / 1e9,
+                         "rel_l2": ((work.float() - exact).norm() / exact.norm()).item()})
         nccl_buf = x.clone()
 
         def nccl():

@@ -114,6 +114,28 @@ def collectives_case(rank: int, world: int) -> None:
         torch.cuda.synchronize()
         want = expected(xs, cfg, name, "mean")
         assert torch.equal(got.cpu().view(torch.uint8), want.view(torch.uint8)), ("hop by hop", method, rank)
+    # top-k profiles through the two fused general kernels (quantize-and-push over NVLink, then wait + decode +
+    # sum + scale + residual in one pass): bit for bit the codec's result for the same payloads, twice in a row
+    # (both receive regions), with the reference's error-feedback rule
+    from lowbit_comm_b200.ops import codec
+
+    for k in (1, 2):
+        kcfg = CompressionConfig(topk=k, allow_experimental=True)
+        n = 77_777
+        residual = torch.zeros(n, dtype=dt, device="cuda")
+        expect_res = [torch.zeros(n, dtype=dt, device="cuda") for _ in range(world)]
+        for it in range(2):
+            xs = _inputs(world, n, dt, seed=400 + 10 * k + it)
+            payloads = [codec.quantize_tensor(xs[r].cuda(), kcfg, residual=expect_res[r], prepared_out=expect_res[r])
+                        for r in range(world)]
+            want = codec.dequantize_reduce_tensors(payloads, (n,), kcfg, dtype=name, reduce="mean")
+            for r in range(world):      # every rank's residual moves on: prepared -> T(prepared - result)
+                codec.update_error_feedback_residual(expect_res[r], want, expect_res[r])
+            got = comm.all_reduce(xs[rank].cuda(), config=kcfg, op="mean", residual=residual)
+            torch.cuda.synchronize()
+            assert torch.equal(got.view(torch.uint8), want.view(torch.uint8)), ("top-k", k, it, rank)
+            assert torch.equal(residual.view(torch.uint8), expect_res[rank].view(torch.uint8)), ("top-k residual", k, it)
+        assert comm.general_workspace(residual, kcfg, name).fused
     # quantized point-to-point through the peer mailboxes: a ring, three rounds (the second and third
     # sends first wait for the receiver's acknowledgement of the previous message)
     import lowbit_comm_b200 as lbc

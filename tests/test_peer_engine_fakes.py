@@ -243,3 +243,81 @@ def test_the_hook_checks_the_status_word_before_every_bucket():
 
 def test_default_wait_limit_is_on_the_scale_of_a_watchdog():
     assert peer_memory.DEFAULT_TIMEOUT_NS >= 300 * 10**9
+
+
+class _FakeGeneralExt:
+    def __init__(self):
+        self.calls = []
+
+    def __getattr__(self, name):
+        def record(*a, **k):
+            self.calls.append((name, a))
+
+        return record
+
+
+class _FakeGeneralGroup:
+    """Symmetric bump allocation and address arithmetic of a peer group, nothing else."""
+
+    world_size, rank, local_ptr = 4, 2, 0x20000
+
+    def __init__(self):
+        self._ext, self._top, self._epoch = _FakeGeneralExt(), 0, 0
+
+    def alloc(self, nbytes):
+        off, self._top = self._top, self._top + nbytes
+        return off
+
+    def new_channel(self):
+        return 0
+
+    def next_epoch(self, channel):
+        self._epoch += 1
+        return self._epoch
+
+    def addr(self, rank, off):
+        return 0x10000 * (rank + 1) + off       # rank 2's own arena is local_ptr
+
+    def signal_all(self, channel, phase, epoch):
+        return ("signal", epoch)
+
+    def wait_all(self, channel, phase, epoch):
+        return ("wait", epoch)
+
+    def local_view(self, off, nbytes):
+        return ("view", off, nbytes)
+
+
+@pytest.mark.parametrize("fused", (True, False))
+def test_general_profile_all_reduce_launch_plan(fused):
+    """Top-k all-reduce over peer memory: the fused form is two launches whose destinations are slot [me] of every
+    rank's receive region and whose sources are this rank's W slots; regions alternate with the epoch."""
+
+    import torch
+
+    from lowbit_comm_b200 import CompressionConfig
+    from lowbit_comm_b200.parallel.fused_general import GeneralPeerWorkspace
+
+    cfg = CompressionConfig(topk=2, allow_experimental=True)
+    group = _FakeGeneralGroup()
+    ws = GeneralPeerWorkspace(group, dtype="bf16", config=cfg, max_numel=4096, fused=fused)
+    x, res = torch.zeros(1000, dtype=torch.bfloat16), torch.zeros(1000, dtype=torch.bfloat16)
+    ws.all_reduce(x, residual=res)
+    names = [c[0] for c in group._ext.calls]
+    if not fused:
+        assert names == (["quant_general", "push_bytes", "wait_signal"] + ["dequant_general"] * 4
+                         + ["scale_inplace", "error_feedback_update"]) and ws.launches == 9
+        return
+    assert names == ["quant_general_push", "reduce_general"] and ws.launches == 2
+    push, reduce = group._ext.calls[0][1], group._ext.calls[1][1]
+    region = ws.recv_off[1]                                     # first epoch is 1: the odd region
+    assert push[3] == [0x10000 * (r + 1) + region + 2 * ws.slot_bytes for r in range(4)]
+    assert reduce[0] == [group.local_ptr + region + r * ws.slot_bytes for r in range(4)]
+    same = lambda t: t is not None and t.data_ptr() == res.data_ptr()      # noqa: E731
+    assert reduce[7] == 0.25 and same(reduce[8]) and same(reduce[9]) and same(push[2]) and same(push[1])
+    assert push[-2] == ("signal", 1) and reduce[-2] == ("wait", 1)
+    group._ext.calls.clear()
+    ws.all_reduce(x, op="sum", update_residual=False, residual=res)
+    push, reduce = group._ext.calls[0][1], group._ext.calls[1][1]
+    assert push[3][0] == 0x10000 + ws.recv_off[0] + 2 * ws.slot_bytes and push[2] is None and same(push[1])
+    assert reduce[7] == 1.0 and reduce[8] is None and reduce[9] is None
