@@ -32,6 +32,7 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--dtype", choices=("fp16", "bf16", "fp32"), default="fp16")
     ap.add_argument("--strategy", default="auto")
+    ap.add_argument("--max-blocks", type=int, default=0, help="grid cap of the hook's kernels (0 = library default)")
     ap.add_argument("--out", default="bench_out/mlp_ddp.json")
     ap.add_argument("--cpu", action="store_true",
                     help="dry run on CPU ranks (gloo, host timer, narrow model): checks the script, measures nothing useful")
@@ -68,9 +69,11 @@ def main() -> None:
         from lowbit_comm_b200 import CompressionConfig, create_ddp_comm_hook
 
         cfg = CompressionConfig(bit=8, group_size=64, error_feedback=True, target="ddp_gradient_bucket")
-        hook = create_ddp_comm_hook(cfg, strategy=args.strategy, reduce="mean", module=ddp.module)
+        hook = create_ddp_comm_hook(cfg, strategy=args.strategy, reduce="mean", module=ddp.module,
+                                    max_blocks=args.max_blocks)
         ddp.register_comm_hook(state=None, hook=hook)
-        note = f"lowbit_comm_b200 int8 g64 EF strategy={args.strategy}"
+        note = f"lowbit_comm_b200 int8 g64 EF strategy={args.strategy}" + (
+            f" max_blocks={args.max_blocks}" if args.max_blocks else "")
     elif args.impl == "reference":
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
         import reference_env

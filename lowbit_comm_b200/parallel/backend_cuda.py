@@ -63,6 +63,21 @@ def _check_tensor(tensor: Any, context: CompileContext) -> None:
         raise TypeError(f"tensor dtype {tensor.dtype} does not match the compiled dtype {context.dtype}")
 
 
+def _tensor_checker(context: CompileContext) -> Callable[[Any], None]:
+    """`_check_tensor` for a hot path: the shape is compared as a tuple prepared once, and a dtype object that
+    passed before is recognised by identity instead of being turned into a name again."""
+
+    want_shape = tuple(context.shape)
+    passed: list[Any] = [None]
+
+    def check(tensor: Any) -> None:
+        if tensor.shape != want_shape or tensor.dtype is not passed[0]:
+            _check_tensor(tensor, context)
+            passed[0] = tensor.dtype
+
+    return check
+
+
 def _reason_iff_negative(flag: bool, reason: str | None, *, what: str, positive: str) -> None:
     """A record that says "yes" carries no explanation, one that says "no" must say why."""
 
@@ -265,10 +280,18 @@ class CudaCommunicationBackend:
             return CudaAllReduceExecutor(self._staged_hierarchy(plan, context, dtype), info)
         if plan.collective == "all_reduce":
             strategy = plan.strategy
+            check = _tensor_checker(context)
+            if plan.async_op:
+                def operation(tensor):
+                    check(tensor)
+                    return comm.all_reduce(tensor, config=cfg, op=op, strategy=strategy, async_op=True, dtype=dtype)
+            else:
+                # compile once: the workspace and the stage count are bound here, not looked up per call
+                bound = comm.bind_all_reduce(config=cfg, op=op, strategy=strategy, dtype=dtype)
 
-            def operation(tensor):
-                _check_tensor(tensor, context)
-                return comm.all_reduce(tensor, config=cfg, op=op, strategy=strategy, async_op=plan.async_op, dtype=dtype)
+                def operation(tensor):
+                    check(tensor)
+                    return bound(tensor)
 
             def precollected(payloads, prepared, output, residual):
                 from ..ops import codec

@@ -21,6 +21,8 @@ same algorithms run over torch.distributed with the codec facade (CPU/gloo too).
 
 from __future__ import annotations
 
+import os
+
 import threading
 from importlib import import_module
 from typing import Any
@@ -148,7 +150,11 @@ class Communicator:
         if self.peer_group is None:
             dist = _dist()
             pg = self.process_group if self.process_group is not None else dist.group.WORLD
-            total = int(self.arena_bytes) if self.arena_bytes else max(2 * need_bytes + (64 << 20), 256 << 20)
+            # The arena is fixed once the ranks have exchanged its handles: take what the first request needs
+            # twice over, and never less than the default (LBC_ARENA_MIB, 1 GiB: small beside 180 GB of HBM,
+            # and enough for workspaces of 64 MiB tensors in three dtypes).
+            floor = int(float(os.environ.get("LBC_ARENA_MIB", "1024")) * (1 << 20))
+            total = int(self.arena_bytes) if self.arena_bytes else max(2 * need_bytes + (64 << 20), floor)
             try:
                 self.peer_group = PeerGroup.create(pg, total, device)
             except CCDLUnavailableError as exc:
@@ -268,6 +274,39 @@ class Communicator:
         result = self._torch_all_reduce(tensor, config, op, stages, name, out, residual, update_residual)
         self.stats["torch_ops"] += 1
         return ImmediateWork(result) if async_op else result
+
+    def bind_all_reduce(self, *, config: CompressionConfig, op: str = "mean", strategy: str = "auto",
+                        dtype: str = "auto"):
+        """`f(tensor)` for repeated blocking, in-place all-reduces of tensors of one kind (a compiled plan's hot
+        path).  What `all_reduce` settles on every call (profile, extension, stage count, dtype name, workspace
+        lookup) is settled on the first call here and again only when a tensor outgrows the workspace; the status
+        word is still read before every launch.  Everything the fused kernels do not serve goes to `all_reduce`."""
+
+        if op not in ("sum", "mean"):
+            raise UnsupportedCollective(f"all_reduce:{op}", reason="only op='sum' and op='mean' are implemented")
+        general = strategy in ("native_nccl", "hierarchical")
+        stages = None if general else self._stages(strategy)
+        held: list[Any] = [None]
+
+        def call(tensor: Any) -> Any:
+            ws = held[0]
+            if ws is None or tensor.numel() > ws.max_numel or not tensor.is_cuda:
+                ws = None
+                if not general and self.peer_usable(tensor, config):
+                    try:
+                        ws = held[0] = self.workspace(tensor, config, codec.resolve_dtype(dtype, tensor))
+                    except CCDLUnavailableError:
+                        if self.transport == "peer":
+                            raise
+                if ws is None:
+                    return self.all_reduce(tensor, config=config, op=op, strategy=strategy, dtype=dtype)
+            else:
+                self.peer_group.check_status()
+            result = ws.all_reduce(tensor, None, op=op, stages=stages)
+            self.stats["peer_ops"] += 1
+            return result
+
+        return call
 
     def _stages(self, strategy: str) -> int | None:
         if strategy in ("auto", "all_reduce"):

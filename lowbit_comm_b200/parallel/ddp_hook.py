@@ -324,10 +324,24 @@ class _PeerEngine:
     def _make_workspace(self, dtype: str, cap: int):
         from .fused import FusedWorkspace
 
-        ws = FusedWorkspace(self.group, dtype=dtype, config=self.config, max_numel=cap, max_blocks=self.max_blocks,
+        ws = FusedWorkspace(self.group, dtype=dtype, config=self.config, max_numel=cap,
+                            max_blocks=self.max_blocks or self._blocks_beside_backward(),
                             engine=self._engine(self.group.world_size))
         ws.gate = ws.group.world_size > 1     # line the ranks up before the persistent kernel takes the SMs
         return ws
+
+    def _blocks_beside_backward(self) -> int:
+        """Default grid cap of the hook's kernels: one block per SM.  The hook's kernels run while the backward
+        pass still has GEMMs to issue; two blocks per SM (the library's default for a collective on its own) take
+        all of an SM's shared memory, one leaves room for a GEMM block beside it (GPT-2 small, 2 GPUs: 28.86 ms
+        per step against 29.06 with two blocks per SM and 29.13 with a block on every other SM)."""
+
+        torch = import_module("torch")
+        device = getattr(self.group, "device", None)
+        try:
+            return int(torch.cuda.get_device_properties(device).multi_processor_count)
+        except Exception:  # noqa: BLE001 - no CUDA device behind this group (tests with stand-ins)
+            return 0
 
     @staticmethod
     def _engine(world: int) -> str:
