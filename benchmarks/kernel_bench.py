@@ -106,13 +106,24 @@ def main() -> None:
                 rc, rcfg, rstatus = ref
                 try:
                     rout = rc.allocate_quantized_buffer(x, rcfg, dtype="bf16").reshape(-1)
-                    ok = rc.inplace_quantize_pack(x, rout, None, rcfg, extension_status=rstatus)
-                    t = time_cuda(lambda: rc.inplace_quantize_pack(x, rout, None, rcfg, extension_status=rstatus),
+                    # the default (planar) profile: what the reference's hook and transports run per bucket
+                    t = time_cuda(lambda: rc.quantize_tensor(x, rcfg, extension_status=rstatus, output=rout),
                                   iters=args.iters, flush=flush, warmup=warm)
-                    record("reference inplace_quantize_pack", mib, 2 * n + pb, t, fused=bool(ok))
-                    t = time_cuda(lambda: rc.inplace_quantize_pack(x, rout, res, rcfg, extension_status=rstatus),
+                    record("reference quantize_tensor(output=)", mib, 2 * n + pb, t)
+                    t = time_cuda(lambda: rc.quantize_tensor(x, rcfg, extension_status=rstatus, output=rout, residual=res),
                                   iters=args.iters, flush=flush, warmup=warm)
-                    record("reference inplace_quantize_pack(+residual)", mib, 4 * n + pb, t)
+                    record("reference quantize_tensor(output=, residual=)", mib, 4 * n + pb, t)
+                    # its fused quantize-and-pack kernel serves compact payloads only (it answers False otherwise)
+                    from dataclasses import replace as _replace
+
+                    rcompact, ccompact = _replace(rcfg, compact=True), CompressionConfig(compact=True)
+                    ok = rc.inplace_quantize_pack(x, rout, res, rcompact, extension_status=rstatus)
+                    t = time_cuda(lambda: rc.inplace_quantize_pack(x, rout, res, rcompact, extension_status=rstatus),
+                                  iters=args.iters, flush=flush, warmup=warm)
+                    record("reference inplace_quantize_pack(compact,+residual)", mib, 4 * n + pb, t, fused=bool(ok))
+                    t = time_cuda(lambda: codec.quantize_tensor(x, ccompact, output=out, residual=res),
+                                  iters=args.iters, flush=flush, warmup=warm)
+                    record("quant_push(local,compact,+residual)", mib, 4 * n + pb, t)
                     rbufs = [rout] + [rout.clone() for _ in range(7)]
                     t = time_cuda(lambda: rc.inplace_dequantize_reduce_mean(rbufs[:1], y, rcfg, extension_status=rstatus,
                                                                             reduce="mean"),
