@@ -290,8 +290,9 @@ class Communicator:
 
         def call(tensor: Any) -> Any:
             ws = held[0]
-            if ws is None or tensor.numel() > ws.max_numel or not tensor.is_cuda:
-                ws = None
+            # a held workspace is only good while its arena is this communicator's live one (close() frees it)
+            if ws is None or ws.group is not self.peer_group or tensor.numel() > ws.max_numel or not tensor.is_cuda:
+                ws = held[0] = None
                 if not general and self.peer_usable(tensor, config):
                     try:
                         ws = held[0] = self.workspace(tensor, config, codec.resolve_dtype(dtype, tensor))

@@ -284,3 +284,67 @@ def test_plan_context_info_and_choice_helpers():
             StrategyChoice("a", "b", "c", matched, **kwargs)
     with pytest.raises(ValueError, match="positive integers"):
         BackendCapabilities(backend="x", available=True, bits=frozenset({0}))
+
+
+def test_bound_all_reduce_settles_once_and_lets_go_of_a_closed_arena():
+    """`Communicator.bind_all_reduce` (the compiled plan's hot path) resolves the workspace on the first call, reuses
+    it while the arena it lives in is the communicator's live one, and resolves again after a close or when a
+    tensor outgrows it; everything the fused kernels do not serve goes through `all_reduce`."""
+
+    from lowbit_comm_b200.parallel.communicator import Communicator
+
+    class Group:
+        def __init__(self):
+            self.checks = 0
+
+        def check_status(self):
+            self.checks += 1
+
+    class Workspace:
+        def __init__(self, group, max_numel):
+            self.group, self.max_numel, self.calls = group, max_numel, []
+
+        def all_reduce(self, tensor, out, *, op, stages):
+            self.calls.append((tensor.numel(), op, stages))
+            return tensor
+
+    class Tensor:
+        is_cuda = True
+
+        def __init__(self, n):
+            self._n = n
+
+        def numel(self):
+            return self._n
+
+    comm = Communicator.__new__(Communicator)
+    comm.transport, comm.peer_group, comm.stats, comm.closed = "auto", Group(), {"peer_ops": 0, "torch_ops": 0}, False
+    made, slow = [], []
+    comm.peer_usable = lambda tensor, config: True
+
+    def workspace(tensor, config, dtype):
+        made.append(Workspace(comm.peer_group, 1 << (tensor.numel() - 1).bit_length()))
+        return made[-1]
+
+    comm.workspace = workspace
+    comm.all_reduce = lambda tensor, **kw: slow.append(kw["strategy"]) or tensor
+    call = comm.bind_all_reduce(config=CompressionConfig(), op="mean", strategy="reduce_scatter", dtype="bf16")
+    for n in (1000, 900, 1024):
+        call(Tensor(n))
+    assert len(made) == 1 and made[0].calls == [(1000, "mean", 2), (900, "mean", 2), (1024, "mean", 2)]
+    assert comm.peer_group.checks == 2 and comm.stats["peer_ops"] == 3       # the first call checked inside workspace()
+    call(Tensor(5000))                                                        # outgrown: resolved again
+    assert len(made) == 2 and made[1].calls == [(5000, "mean", 2)]
+    comm.peer_group = Group()                                                 # the arena was closed and made anew
+    call(Tensor(10))
+    assert len(made) == 3 and made[2].group is comm.peer_group and made[1].calls == [(5000, "mean", 2)]
+    cpu = Tensor(10)
+    cpu.is_cuda = False
+    comm.peer_usable = lambda tensor, config: False
+    call(cpu)
+    assert slow == ["reduce_scatter"]
+    with pytest.raises(UnsupportedCollective):
+        comm.bind_all_reduce(config=CompressionConfig(), op="max")
+    routed = comm.bind_all_reduce(config=CompressionConfig(), strategy="hierarchical")
+    routed(Tensor(10))
+    assert slow == ["reduce_scatter", "hierarchical"]
