@@ -205,7 +205,7 @@ def _worker(rank: int, world: int, port: int) -> None:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", (2, 3, 4))
+@pytest.mark.parametrize("world", (2, 3, 4, 8))
 def test_ring_and_tree_executors_match_their_replay(world):
     spawn_ranks(_worker, lambda port: (world, port), world)
 
