@@ -151,7 +151,9 @@ struct PushTile {
 };
 
 template <typename T, int G, int BIT, bool kBulk>
-__global__ void __launch_bounds__(kThreads, kBulk ? 3 : 4) quant_push_tiled_kernel(const LbcQuantPush p) {
+// (16-bit sources hold the next tile's raw words in registers: three blocks per SM, two tiles in flight each)
+__global__ void __launch_bounds__(kThreads, (kBulk || sizeof(T) == 2) ? 3 : 4)
+quant_push_tiled_kernel(const LbcQuantPush p) {
     constexpr int lanes = G / kElemsPerThread;
     constexpr int VB = G * BIT / 8;
     constexpr int MB = sizeof(T);
@@ -180,19 +182,63 @@ __global__ void __launch_bounds__(kThreads, kBulk ? 3 : 4) quant_push_tiled_kern
     PushTile& tile = *reinterpret_cast<PushTile*>(tile_raw);
     __shared__ __align__(16) unsigned char scale_buf[kBulk ? 1 : 2][kBulk ? 16 : kThreads * 4];
     int buf = 0;
+    const int gl = int(threadIdx.x) / lanes;                        // my group inside a tile
+    const int lane = int(threadIdx.x) - gl * lanes;
+    // Where tile `vt` sits: its shard, its first group inside the shard, how many of its groups hold data,
+    // and this thread's first element.
+    struct Spot {
+        int shard;
+        int64_t gl0, live_groups, first;
+    };
+    auto spot_of = [&](int64_t vt) {
+        Spot s;
+        s.shard = int((vt + rot) % shards);
+        s.gl0 = (vt / shards) * tile_groups;
+        const int64_t shard_first = int64_t(s.shard) * span_groups;   // first group of the shard in the tensor
+        s.live_groups = max(int64_t(0), min(int64_t(tile_groups), min(span_groups, num_groups - shard_first) - s.gl0));
+        s.first = ((shard_first + s.gl0) * lanes + threadIdx.x) * kElemsPerThread;
+        return s;
+    };
+    // 16-bit sources on 32-byte aligned tensors: the loads of tile i + 1 are issued before tile i is encoded,
+    // so that every warp keeps 32 (with a residual 64) bytes per thread in flight while it computes; one
+    // load per thread and tile left the memory system idle for about half of the time.  The raw words wait
+    // in registers.  Everything else (fp32 sources, unaligned views, the ragged last tile) loads in place.
+    constexpr bool kAhead = sizeof(T) == 2;
+    const bool ahead_ok = kAhead && x_vec && r_vec;
+    U8x32 raw_x, raw_r;
+    bool raw_held = false;
+    auto fetch = [&](const Spot& s) {
+        raw_held = ahead_ok && gl < s.live_groups && s.first + 16 <= n;
+        if (raw_held) {
+            raw_x = ld32_stream(x + s.first);
+            if (res != nullptr) raw_r = (prep != res) ? ld32_stream(res + s.first) : ld32(res + s.first);
+        }
+    };
+    Spot here = spot_of(blockIdx.x);
+    if (int64_t(blockIdx.x) < num_tiles) fetch(here);
     for (int64_t vt = blockIdx.x; vt < num_tiles; vt += gridDim.x, buf ^= 1) {
-        const int shard = int((vt + rot) % shards);
-        const int64_t k = vt / shards;
-        const int64_t gl0 = k * tile_groups;                       // first group of the tile inside its shard
-        const int64_t shard_first = int64_t(shard) * span_groups;   // first group of the shard in the tensor
-        int64_t live_groups = min(span_groups, num_groups - shard_first) - gl0;
-        live_groups = max(int64_t(0), min(int64_t(tile_groups), live_groups));
-        const int gl = int(threadIdx.x) / lanes;                    // my group inside the tile
-        const int lane = int(threadIdx.x) - gl * lanes;
+        const int shard = here.shard;
+        const int64_t gl0 = here.gl0;
+        const int64_t live_groups = here.live_groups;
         const bool live = gl < live_groups;
-        const int64_t first = ((shard_first + gl0) * lanes + threadIdx.x) * kElemsPerThread;
+        const int64_t first = here.first;
         float v[16];
-        if (live) {
+        if (live && raw_held) {
+            if constexpr (kAhead) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) Src<T>::up2(raw_x.w[i], v[2 * i], v[2 * i + 1]);
+                if (res != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float a, b;
+                        Src<T>::up2(raw_r.w[i], a, b);
+                        v[2 * i] += a;
+                        v[2 * i + 1] += b;
+                    }
+                    round16<T>(v);
+                }
+            }
+        } else if (live) {
             load16<T>(x, first, n, x_vec, v, true);
             if (res != nullptr) {
                 float r[16];
@@ -204,6 +250,10 @@ __global__ void __launch_bounds__(kThreads, kBulk ? 3 : 4) quant_push_tiled_kern
         } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[i] = 0.0f;
+        }
+        if (vt + gridDim.x < num_tiles) {       // the next tile's loads go out before this one is encoded
+            here = spot_of(vt + gridDim.x);
+            fetch(here);
         }
         float amax = 0.0f;
 #pragma unroll
