@@ -1,7 +1,7 @@
 """Synthetic-MLP DDP throughput (samples/s): the shape of the reference's own end-to-end benchmark.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-        benchmarks/mlp_ddp.py --impl ours|nccl|reference [--steps 20 --warmup 5]
+        benchmarks/mlp_ddp.py --impl ours|nccl|reference|fsdp [--steps 20 --warmup 5]
 
 Model and schedule follow the reference's published run (fp16 MLP 2048 -> 4096 x 4 -> 1024, 62.9 M parameters,
 batch 16 per rank, SGD, 20 timed steps after 5 warm-up steps; its numbers are for 2 x RTX A6000:
@@ -9,6 +9,8 @@ tests/benchmarks/reports/a6000_scale_20260804).  Timing: CUDA events around the 
 barrier and a device synchronise, maximum over ranks.  Every step copies its batch from pinned host memory and
 reads the loss back, so the figure is end to end.  A step touches the 126 MB of parameters and as much again
 of gradients, more than the L2, so nothing is flushed between steps.  One JSON line on rank 0.
+`--impl fsdp` wraps the same model in torch's FullyShardedDataParallel instead of DDP: the baseline mode of the
+reference's comparison script (tests/distributed/synthetic_ddp_compare.py:100-105), uncompressed, GPU only.
 """
 
 from __future__ import annotations
@@ -26,7 +28,7 @@ WIDTHS = (2048, 4096, 4096, 4096, 4096, 1024)
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--impl", choices=("ours", "nccl", "reference"), default="ours")
+    ap.add_argument("--impl", choices=("ours", "nccl", "reference", "fsdp"), default="ours")
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=16)
@@ -62,8 +64,19 @@ def main() -> None:
 
     torch.manual_seed(1234)
     model = SyntheticMLP(widths, dtype=dtype, bias=False).to(device)      # 62 914 560 weights, as published
-    ddp = DDP(model, device_ids=None if args.cpu else [local_rank], bucket_cap_mb=25, gradient_as_bucket_view=True)
-    note = "none (NCCL all-reduce)"
+    if args.impl == "fsdp":
+        if args.cpu:
+            if rank == 0:
+                print(json.dumps({"impl": "fsdp", "unavailable": "the FSDP baseline arm runs on CUDA ranks only"}), flush=True)
+            dist.destroy_process_group()
+            return
+        from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+
+        ddp = FSDP(model, device_id=local_rank, use_orig_params=True)
+        note = "none (torch FullyShardedDataParallel, full shard, uncompressed)"
+    else:
+        ddp = DDP(model, device_ids=None if args.cpu else [local_rank], bucket_cap_mb=25, gradient_as_bucket_view=True)
+        note = "none (NCCL all-reduce)"
     hook = None
     if args.impl == "ours":
         from lowbit_comm_b200 import CompressionConfig, create_ddp_comm_hook
