@@ -12,6 +12,8 @@
 // Tie-breaking between equal magnitudes: lowest index first for 16-bit
 // sources, highest index first for fp32 sources.
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "lbc_api.h"
 
@@ -151,18 +153,55 @@ __global__ void __launch_bounds__(kThreads) quant_general_kernel(const LbcQuantG
         }
         // three best (magnitude, index) candidates of the group
         Cand top[3] = {{-1.0f, -1}, {-1.0f, -1}, {-1.0f, -1}};
+        if constexpr (sizeof(T) == 2) {
+            // 16-bit sources: the values are exact in T, so (|v| as T bits) << 8 | (255 - index) is a 24-bit key
+            // whose integer order is the order above (larger magnitude first, lower index on ties); the three
+            // largest keys come out of a branch-free chain of five integer min/max per candidate.
+            uint32_t k0 = 0, k1 = 0, k2 = 0;          // below every real key (an index is at most 63)
+            auto put = [&](uint32_t c) {
+                uint32_t t = max(k0, c);
+                c = min(k0, c);
+                k0 = t;
+                t = max(k1, c);
+                c = min(k1, c);
+                k1 = t;
+                k2 = max(k2, c);
+            };
 #pragma unroll
-        for (int i = 0; i < 16; ++i) insert3<kHighWins>(top, Cand{fabsf(v[i]), lane * 16 + i});
-#pragma unroll
-        for (int off = lanes / 2; off > 0; off >>= 1) {
-            Cand other[3];
-#pragma unroll
-            for (int j = 0; j < 3; ++j) {
-                other[j].mag = __shfl_xor_sync(0xffffffffu, top[j].mag, off, lanes);
-                other[j].idx = __shfl_xor_sync(0xffffffffu, top[j].idx, off, lanes);
+            for (int i = 0; i < 16; ++i) {
+                uint32_t mag_bits;      // |v| as T bits, shifted up by 8
+                if constexpr (std::is_same<T, __nv_bfloat16>::value)
+                    mag_bits = (__float_as_uint(v[i]) & 0x7fffffffu) >> 8;      // bf16: the high half of the fp32 pattern
+                else
+                    mag_bits = uint32_t(Src<T>::down(fabsf(v[i]))) << 8;
+                put(mag_bits | uint32_t(255 - (lane * 16 + i)));
             }
 #pragma unroll
-            for (int j = 0; j < 3; ++j) insert3<kHighWins>(top, other[j]);
+            for (int off = lanes / 2; off > 0; off >>= 1) {
+                const uint32_t o0 = __shfl_xor_sync(0xffffffffu, k0, off, lanes);
+                const uint32_t o1 = __shfl_xor_sync(0xffffffffu, k1, off, lanes);
+                const uint32_t o2 = __shfl_xor_sync(0xffffffffu, k2, off, lanes);
+                put(o0);
+                put(o1);
+                put(o2);
+            }
+            const uint32_t keys[3] = {k0, k1, k2};
+#pragma unroll
+            for (int j = 0; j < 3; ++j) top[j] = Cand{Src<T>::up(uint16_t(keys[j] >> 8)), 255 - int(keys[j] & 0xffu)};
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) insert3<kHighWins>(top, Cand{fabsf(v[i]), lane * 16 + i});
+#pragma unroll
+            for (int off = lanes / 2; off > 0; off >>= 1) {
+                Cand other[3];
+#pragma unroll
+                for (int j = 0; j < 3; ++j) {
+                    other[j].mag = __shfl_xor_sync(0xffffffffu, top[j].mag, off, lanes);
+                    other[j].idx = __shfl_xor_sync(0xffffffffu, top[j].idx, off, lanes);
+                }
+#pragma unroll
+                for (int j = 0; j < 3; ++j) insert3<kHighWins>(top, other[j]);
+            }
         }
         if (!live) continue;
         const float amax = top[p.topk].mag;  // (k+1)-th largest magnitude

@@ -327,7 +327,8 @@ class _PeerEngine:
         ws = FusedWorkspace(self.group, dtype=dtype, config=self.config, max_numel=cap,
                             max_blocks=self.max_blocks or self._blocks_beside_backward(),
                             engine=self._engine(self.group.world_size))
-        ws.gate = ws.group.world_size > 1     # line the ranks up before the persistent kernel takes the SMs
+        # line the ranks up before the persistent kernel takes the SMs (LBC_HOOK_GATE=0 launches it at once)
+        ws.gate = ws.group.world_size > 1 and os.environ.get("LBC_HOOK_GATE", "1") != "0"
         return ws
 
     def _blocks_beside_backward(self) -> int:
