@@ -31,6 +31,8 @@ def main() -> None:
     ap.add_argument("--impl", choices=("ours", "nccl", "reference", "fsdp"), default="ours")
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=3,
+                    help="timed regions of --steps steps each; the median is reported, every sample is kept")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--dtype", choices=("fp16", "bf16", "fp32"), default="fp16")
     ap.add_argument("--strategy", default="auto")
@@ -124,28 +126,40 @@ def main() -> None:
 
     for i in range(args.warmup):
         step(i)
-    dist.barrier()
     last, peak_mib = 0.0, 0.0
-    if args.cpu:
-        import time
+    samples: list[float] = []
+    launches_before = hook.gpu_launches() if hook is not None else 0
+    # A region of 20 steps lasts some tens of milliseconds, so one stall doubles it: several regions, the median
+    # reported, every sample kept (the reference's script reports the median of three runs as well,
+    # tests/distributed/synthetic_ddp_compare.py:157-249).
+    for _ in range(max(1, args.repeats)):
+        dist.barrier()
+        if args.cpu:
+            import time
 
-        began = time.perf_counter()
-        for i in range(args.warmup, total):
-            last = step(i)
-        elapsed_ms = (time.perf_counter() - began) * 1e3
-    else:
-        torch.cuda.synchronize()
-        torch.cuda.reset_peak_memory_stats()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for i in range(args.warmup, total):
-            last = step(i)
-        stop.record()
-        torch.cuda.synchronize()
-        elapsed_ms, peak_mib = start.elapsed_time(stop), torch.cuda.max_memory_allocated() / 2**20
+            began = time.perf_counter()
+            for i in range(args.warmup, total):
+                last = step(i)
+            elapsed_ms = (time.perf_counter() - began) * 1e3
+        else:
+            torch.cuda.synchronize()
+            torch.cuda.reset_peak_memory_stats()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for i in range(args.warmup, total):
+                last = step(i)
+            stop.record()
+            torch.cuda.synchronize()
+            elapsed_ms = start.elapsed_time(stop)
+            peak_mib = max(peak_mib, torch.cuda.max_memory_allocated() / 2**20)
+        region = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(region, op=dist.ReduceOp.MAX)
+        samples.append(float(region.item()))
     dist.barrier()
-    ms = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    import statistics
+
+    ms = torch.tensor([statistics.median(samples)], dtype=torch.float64, device=device)
+    launches = ((hook.gpu_launches() - launches_before) // max(1, args.repeats)) if hook is not None else 0
     if rank == 0:
         line = {"metric": "synthetic MLP DDP training throughput", "value": args.batch * world * args.steps / (ms.item() * 1e-3),
                 "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -155,8 +169,8 @@ def main() -> None:
                            "micro_batch_per_gpu": args.batch, "optimizer": "SGD lr 0.01", "bucket_cap_mb": 25, "hook": note,
                            "l2": "a step touches more than 126 MB; no explicit flush"},
                 "e2e": {"h2d_bytes_per_step": int(xs[0].numel() + ys[0].numel()) * xs.element_size(), "d2h_bytes_per_step": 4},
-                "peak_memory_mib": peak_mib,
-                "gpu_launches": hook.gpu_launches() if hook is not None else 0, "final_loss": last}
+                "peak_memory_mib": peak_mib, "ms_per_step_samples": [round(m / args.steps, 4) for m in samples],
+                "gpu_launches": launches, "final_loss": last}
         print(json.dumps(line), flush=True)
         os.makedirs(os.path.dirname(os.path.join(ROOT, args.out)), exist_ok=True)
         with open(os.path.join(ROOT, args.out), "w") as fh:
