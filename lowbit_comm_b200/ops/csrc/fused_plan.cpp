@@ -167,6 +167,60 @@ class FusedAllReducePlan {
         return launches;
     }
 
+    // Reduce-scatter to a dense shard: rank r receives the reduced elements [r * shard_numel, (r + 1) * shard_numel)
+    // in `out_shard` (shard_numel = shard_groups * group size; the caller has zeroed what lies past the tensor's
+    // end).  With a residual, error feedback uses this rank's own quantization error, written back in place.
+    // Three launches (quantize-and-scatter, gate, reduce), one binding crossing.
+    int reduce_scatter(uintptr_t x, uintptr_t out_shard, uintptr_t residual, int64_t numel, double scale,
+                       bool update_residual, unsigned int epoch, uintptr_t stream_ptr) {
+        if (numel < 0 || numel > max_numel_) throw std::invalid_argument("numel exceeds the workspace capacity");
+        if (numel == 0) return 0;
+        cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+        const int parity = static_cast<int>(epoch & 1u);
+        const int64_t groups = ceil_div(numel, group_);
+        const int64_t shard_groups = round_up(ceil_div(groups, world_), kAlignGroups);
+        Regions r;
+        r.channel = channels_[0];
+        r.shard_stride = round_up(shard_groups * group_bytes_, 256);
+        r.gather_stride = 0;
+        r.rs = rs_off_[parity];
+        r.ag = ag_off_;
+        r.gather = 0;
+        if (r.shard_stride * world_ > rs_bytes_) throw std::runtime_error("shards exceed the workspace");
+        grid_cap_ = max_blocks_;
+        LbcQuantPush q{};
+        q.dtype = dtype_;
+        q.group_size = group_;
+        q.bit = bit_;
+        q.x = reinterpret_cast<const void*>(x);
+        q.residual = reinterpret_cast<const void*>(residual);
+        q.local_ef_out = (residual != 0 && update_residual) ? reinterpret_cast<void*>(residual) : nullptr;
+        q.numel = numel;
+        q.num_dst = world_;
+        q.max_blocks = grid_cap_;
+        q.mode = LBC_PUSH_SCATTER;
+        q.shard_groups = shard_groups;
+        q.layout_groups = shard_groups;
+        for (int d = 0; d < world_; ++d)
+            q.dst[d] = reinterpret_cast<uint8_t*>(peers_[d] + r.rs + rank_ * r.shard_stride);
+        fill_signal(q.signal, r.channel, kPhaseRS, epoch);
+        check(lbc_quant_push(&q, stream), "quant_push(scatter)");
+
+        const int64_t shard_numel = shard_groups * group_;
+        const int64_t lo = rank_ * shard_numel;
+        const int64_t valid = std::max<int64_t>(0, std::min(numel, lo + shard_numel) - lo);
+        LbcReduce k = base_reduce(valid, scale);
+        k.num_src = world_;
+        for (int s = 0; s < world_; ++s)
+            k.src[s] = reinterpret_cast<const uint8_t*>(peers_[rank_] + r.rs + s * r.shard_stride);
+        k.layout_groups = shard_groups;
+        k.out = valid > 0 ? reinterpret_cast<void*>(out_shard) : nullptr;
+        fill_wait(k.wait, r.channel, kPhaseRS, epoch);
+        gate(k.wait, stream);
+        check(lbc_reduce(&k, stream), "reduce(shard, dense)");
+        return 3;
+    }
+
   private:
     struct Side {
         cudaStream_t stream = nullptr;
@@ -451,7 +505,10 @@ void bind_fused_plan(py::module_& m) {
         .def("set_pull_gather", &FusedAllReducePlan::set_pull_gather, py::arg("on"))
         .def("all_reduce", &FusedAllReducePlan::all_reduce, py::arg("x"), py::arg("out"), py::arg("residual"),
              py::arg("numel"), py::arg("stages"), py::arg("scale"), py::arg("update_residual"), py::arg("ef_local"),
-             py::arg("epoch"), py::arg("stream"));
+             py::arg("epoch"), py::arg("stream"))
+        .def("reduce_scatter", &FusedAllReducePlan::reduce_scatter, py::arg("x"), py::arg("out_shard"),
+             py::arg("residual"), py::arg("numel"), py::arg("scale"), py::arg("update_residual"), py::arg("epoch"),
+             py::arg("stream"));
     py::class_<PipeAllReducePlan>(m, "PipeAllReducePlan")
         .def(py::init<int, int, int, int, std::vector<uintptr_t>, int64_t, int64_t, int64_t, int64_t, int64_t,
                       unsigned long long, uintptr_t, int, int64_t>(),

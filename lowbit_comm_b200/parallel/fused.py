@@ -534,6 +534,13 @@ class FusedWorkspace:
         flat_out = out_shard.reshape(-1)
         if valid < geo.shard_numel:
             flat_out[valid:].zero_()
+        if self._native is not None and self.phase_timer is None and hasattr(self._native, "reduce_scatter"):
+            # hot path: one binding crossing for the three launches
+            if geo.numel:
+                self.launches += self._native.reduce_scatter(
+                    x.data_ptr(), flat_out.data_ptr(), 0 if res is None else res.data_ptr(), geo.numel, self._scale(op),
+                    bool(update_residual), epoch, _current_stream_ptr(x.device))
+            return geo
         self._k1_scatter(x.reshape(-1), res, None, res if (res is not None and update_residual) else None, geo,
                          epoch, parity)
         self._k2_reduce(geo, epoch, parity, self._scale(op), flat_out[:valid] if valid else None, False)
