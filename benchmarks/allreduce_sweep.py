@@ -179,8 +179,6 @@ def main() -> None:
         if args.variants:
             combos = [(0, True, 0), (1, True, 0), (2, True, 0), (1, False, 0), (1, False, -1), (1, True, -1),
                       (1, True, 592)]
-        from lowbit_comm_b200.parallel.fused import default_stages
-
         arms = [{"auto": 0, "1": 1, "2": 2}[a] for a in args.arms.split(",") if a]
         for stages, (push_variant, reduce_bulk, k2_blocks) in [(s, c) for s in arms for c in combos]:
             if stages == 1 and (not reduce_bulk or k2_blocks):
@@ -195,7 +193,7 @@ def main() -> None:
             ours(stages)()
             torch.cuda.synchronize()
             rel = ((work.float() - exact).norm() / exact.norm()).item()
-            ran = stages or default_stages(world, nbytes)
+            ran = stages or comm.workspace(x, cfg, "bf16").route(n, 2)[1]
             roof = fused_all_reduce_roofline(nbytes, world, stages=ran, error_feedback=residual is not None,
                                              hbm_gbs=hbm_gbs)
             phases = None

@@ -437,20 +437,10 @@ class FusedWorkspace:
         rank's own quantization error.
         """
 
-        requested_stages = stages
-        if stages is None:
-            stages = default_stages(self.group.world_size, x.numel() * x.element_size(),
-                                    bool(self.group.multicast_ptr))
+        through_pipe, stages = self.route(x.numel(), x.element_size(), stages)
         scale = self._scale(op)
         if ef_mode not in ("reference", "local"):
             raise ValueError("ef_mode must be 'reference' or 'local'")
-        # "auto": the single persistent kernel, except where the kernel sequence measured faster: on two ranks
-        # (46 vs 50 us at 1 MiB, 155 vs 185 us at 64 MiB) and above the size limit
-        through_pipe = self.engine == "pipe" or (self.engine == "auto" and self.group.world_size != 2 and
-                                                 x.numel() <= self.pipe_numel)
-        if requested_stages is None and through_pipe and self.group.world_size > 2:
-            # the single kernel pays less per stage, which moves the crossover down: one stage up to 32 MiB / W
-            stages = 1 if x.numel() * x.element_size() * self.group.world_size <= (32 << 20) else 2
         if through_pipe and self.phase_timer is None:
             return self._pipe_all_reduce(x, out, residual, update_residual, scale, stages, ef_mode)
         self._ensure_legacy()
@@ -513,6 +503,24 @@ class FusedWorkspace:
         if timer is not None:
             timer.flush()
         return x if out is None else out
+
+    def route(self, numel: int, element_size: int, stages: int | None = None) -> tuple[bool, int]:
+        """(through the single kernel?, stage count) an all-reduce of `numel` elements takes on this workspace.
+
+        "auto" takes the single persistent kernel, except where the kernel sequence measured faster: on two ranks
+        (46 vs 50 us at 1 MiB, 155 vs 185 us at 64 MiB) and above the size limit.  Without a requested stage
+        count the kernel sequence uses `default_stages`; the single kernel pays less per stage, which moves the
+        crossover down: one stage up to 16 MiB / W (4 GPUs: 4 MiB 63 vs 74 us, 8 MiB 103 vs 82 us; 8 GPUs: 2 MiB
+        71 vs 79 us, 4 MiB 84 vs 79 us, one stage against two)."""
+
+        world, nbytes = self.group.world_size, numel * element_size
+        through_pipe = self.engine == "pipe" or (self.engine == "auto" and world != 2 and numel <= self.pipe_numel)
+        if stages is None:
+            if through_pipe and world > 2:
+                stages = 1 if nbytes * world <= (16 << 20) else 2
+            else:
+                stages = default_stages(world, nbytes, bool(self.group.multicast_ptr))
+        return through_pipe, stages
 
     def reduce_scatter(self, x: torch.Tensor, out_shard: torch.Tensor, *, residual: torch.Tensor | None = None,
                        update_residual: bool = True, op: str = "mean") -> FusedGeometry:
