@@ -119,6 +119,10 @@ def parse_args() -> argparse.Namespace:
     ap.add_argument("--repeats", type=int, default=3, help="timed samples of each region (the median is reported)")
     ap.add_argument("--settle-s", type=float, default=3.0,
                     help="minimum length of the untimed settle phase after the warm-up (0 = none)")
+    ap.add_argument("--gc-mode", choices=("default", "between"), default="default",
+                    help="default: Python's cyclic collector runs when it wants; between: it is switched off inside "
+                         "the timed regions and a full collection runs, untimed, between them (diagnostic: tells a "
+                         "collector pause from a stall of the library)")
     ap.add_argument("--hook-max-blocks", type=int, default=0,
                     help="grid cap of the hook's kernels (0 = library default: the full persistent grid)")
     return ap.parse_args()
@@ -238,7 +242,12 @@ def main() -> None:
                 break
         settle_s = time.perf_counter() - t_start
 
+    import gc
+
     def timed(fn) -> float:
+        if args.gc_mode == "between":
+            gc.collect()
+            gc.disable()
         dist.barrier()
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -247,6 +256,8 @@ def main() -> None:
         stop.record()
         torch.cuda.synchronize()
         dist.barrier()
+        if args.gc_mode == "between":
+            gc.enable()
         ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
@@ -263,10 +274,15 @@ def main() -> None:
         for tok in staged:
             train_step(tok)
 
+    step_marks: list[list[float]] = []      # host clock after every read-back of an end-to-end region (diagnostic)
+
     def e2e_region():        # through the public API: H2D of the inputs and D2H of the loss, every step
+        marks = [time.perf_counter()]
         for i in range(args.steps):
             tok = host_tokens[args.warmup + args.steps + i].to(device, non_blocking=True)
             losses.append(train_step(tok).item())
+            marks.append(time.perf_counter())
+        step_marks.append([round((b - a) * 1e3, 3) for a, b in zip(marks, marks[1:])])
 
     device_samples, e2e_samples, launches = [], [], 0
     for _ in range(repeats):
@@ -303,6 +319,7 @@ def main() -> None:
             "timing": {"settle_steps": settle_steps, "settle_s": round(settle_s, 2), "repeats": repeats,
                        "value_ms_per_step_samples": [round(m / args.steps, 4) for m in device_samples],
                        "e2e_ms_per_step_samples": [round(m / args.steps, 4) for m in e2e_samples],
+                       "e2e_host_ms_of_every_step": step_marks, "gc_mode": args.gc_mode,
                        "reported": "median of the samples; regions alternate value, e2e"},
             "clocks": clocks,
             "final_loss": losses[-1] if losses else last,
