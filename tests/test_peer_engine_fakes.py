@@ -321,3 +321,28 @@ def test_general_profile_all_reduce_launch_plan(fused):
     push, reduce = group._ext.calls[0][1], group._ext.calls[1][1]
     assert push[3][0] == 0x10000 + ws.recv_off[0] + 2 * ws.slot_bytes and push[2] is None and same(push[1])
     assert reduce[7] == 1.0 and reduce[8] is None and reduce[9] is None
+
+
+def test_route_picks_engine_and_stage_count_from_size_and_world():
+    """`FusedWorkspace.route`: "auto" is the single kernel except on two ranks and above its size limit; without a
+    requested stage count the single kernel reduces in one stage up to 16 MiB / W, the kernel sequence up to its own
+    crossover; a requested count is kept."""
+
+    from types import SimpleNamespace
+
+    from lowbit_comm_b200.parallel.fused import FusedWorkspace, default_stages
+
+    def ws(world, engine="auto", pipe_mib=192):
+        return SimpleNamespace(engine=engine, pipe_numel=pipe_mib << 19,
+                               group=SimpleNamespace(world_size=world, multicast_ptr=0))
+
+    route = FusedWorkspace.route
+    mib = 1 << 19                                            # bf16 elements per MiB
+    assert route(ws(8), 2 * mib, 2) == (True, 1) and route(ws(8), 4 * mib, 2) == (True, 2)
+    assert route(ws(4), 4 * mib, 2) == (True, 1) and route(ws(4), 8 * mib, 2) == (True, 2)
+    assert route(ws(8), 256 * mib, 2) == (False, default_stages(8, 256 << 20))       # above the single kernel's limit
+    assert route(ws(2), 8 * mib, 2) == (False, default_stages(2, 8 << 20))            # two ranks: the kernel sequence
+    assert route(ws(2, "pipe"), 8 * mib, 2) == (True, default_stages(2, 8 << 20))     # forced engine, its stage rule at W <= 2
+    assert route(ws(8, "legacy"), 2 * mib, 2) == (False, default_stages(8, 2 << 20))
+    assert route(ws(8), 2 * mib, 2, stages=2) == (True, 2) and route(ws(8, "legacy"), 64 * mib, 2, stages=1) == (False, 1)
+    assert route(ws(1), 64 * mib, 2)[0] is True                                       # a one-GPU job takes the single kernel
