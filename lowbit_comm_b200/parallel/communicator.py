@@ -21,8 +21,8 @@ same algorithms run over torch.distributed with the codec facade (CPU/gloo too).
 
 from __future__ import annotations
 
+import contextlib
 import os
-
 import threading
 from importlib import import_module
 from typing import Any
@@ -36,6 +36,7 @@ from ..exceptions import CCDLUnavailableError, UnsupportedCollective
 from ..ops import codec
 from ..ops.loader import load_cuda_extension
 from ..ops.sizing import estimate_quantized_size
+from ..utils import tracing
 from .payload import payload_buffer
 from .torch_transport import make_torch_all_gather, make_torch_all_to_all, make_torch_tensor_all_reduce
 
@@ -45,6 +46,7 @@ ONE_STAGE = frozenset({"all_gather"})
 
 _REGISTRY: dict[int, "Communicator"] = {}
 _REGISTRY_LOCK = threading.Lock()
+_NO_RANGE = contextlib.nullcontext()      # stands in for an NVTX range when LBC_TRACE is off
 
 
 def _dist():
@@ -253,7 +255,7 @@ class Communicator:
                 ws = None
             if ws is not None:
                 scope, side = self._stream_scope(tensor, async_op)
-                with scope:
+                with scope, tracing.nvtx_range("lbc.all_reduce") if tracing.ENABLED else _NO_RANGE:
                     result = ws.all_reduce(tensor, out, residual=residual, update_residual=update_residual, op=op,
                                            stages=stages, ef_mode=ef_mode)
                 self.stats["peer_ops"] += 1

@@ -34,6 +34,7 @@ from ..exceptions import CCDLUnavailableError
 from ..ops import codec
 from ..ops.error_feedback import ErrorFeedbackPolicy, ErrorFeedbackState
 from ..ops.loader import CudaExtensionStatus, load_cuda_extension
+from ..utils import tracing
 from .completion import CudaCompletionManager
 from .payload import (CompressedAllGatherReduce, CompressedAllReduce, CompressedPayload, GatheredPayloads,
                       coerce_payload, payload_buffer)
@@ -441,7 +442,11 @@ class DDPCommHook:
     def __call__(self, state, bucket):  # no annotations: DDP validates them when present
         self.stats["buckets"] += 1
         self._follow_layout(bucket)
-        result = self._process_bucket(bucket)
+        if tracing.ENABLED:      # LBC_TRACE=1: one NVTX range per bucket on the host timeline
+            with tracing.nvtx_range(f"lbc.ddp_bucket[{_bucket_key(bucket)}]"):
+                result = self._process_bucket(bucket)
+        else:
+            result = self._process_bucket(bucket)
         if hasattr(result, "set_result") or hasattr(result, "then"):
             return result
         future = self._future_factory()

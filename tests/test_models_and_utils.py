@@ -99,3 +99,32 @@ def test_kernel_names_is_empty_without_a_gpu_and_counts_device_events_with_a_fak
         cuda=types.SimpleNamespace(is_available=lambda: True, synchronize=lambda: ran.append("sync")))
     counts = kernel_names(lambda: ran.append("fn"), torch_module=fake)
     assert counts == {"quant_push_tiled_kernel": 2, "reduce_kernel": 1} and ran == ["fn", "sync"]
+
+
+def test_trace_switch_puts_one_nvtx_range_around_every_bucket(monkeypatch):
+    """LBC_TRACE=1: the hook wraps each bucket in a named NVTX range on the host timeline; off, it calls nothing."""
+
+    import torch
+
+    from lowbit_comm_b200.parallel.ddp_hook import DDPCommHook
+    from lowbit_comm_b200.utils import tracing
+
+    calls = []
+    monkeypatch.setattr(torch.cuda.nvtx, "range_push", lambda name: calls.append(("push", name)))
+    monkeypatch.setattr(torch.cuda.nvtx, "range_pop", lambda: calls.append(("pop",)))
+
+    class Bucket:
+        def index(self):
+            return 3
+
+        def buffer(self):
+            return torch.zeros(4)
+
+    hook = DDPCommHook(lambda bucket: calls.append(("bucket",)) or bucket.buffer(), torch.futures.Future)
+    monkeypatch.setattr(tracing, "ENABLED", False)
+    hook(None, Bucket())
+    assert calls == [("bucket",)]
+    calls.clear()
+    monkeypatch.setattr(tracing, "ENABLED", True)
+    assert hook(None, Bucket()).wait().numel() == 4
+    assert calls == [("push", "lbc.ddp_bucket[3]"), ("bucket",), ("pop",)]
