@@ -140,8 +140,7 @@ class Communicator:
         need = GeneralPeerWorkspace.required_bytes(self.world_size, dtype, config, cap)
         group = self._ensure_peer_group(tensor.device, need)
         if group.bytes_free < need:
-            raise CCDLUnavailableError(
-                f"peer arena too small for a {cap}-element general-profile workspace ({group.bytes_free} < {need} bytes)")
+            group = self._grow_peer_group(tensor.device, need, f"a {cap}-element general-profile workspace")
         ws = GeneralPeerWorkspace(group, dtype=dtype, config=config, max_numel=cap, max_blocks=self.max_blocks)
         self._workspaces[key] = ws
         return ws
@@ -162,6 +161,37 @@ class Communicator:
             except CCDLUnavailableError as exc:
                 self._peer_failed = str(exc)
                 raise
+        return self.peer_group
+
+    def _grow_peer_group(self, device, need_bytes: int, what: str):
+        """The arena has no room for `what`: close it and create a larger one.  Collective over the group, like the
+        creation itself; every rank gets here in the same call because tensors of one collective have the same size
+        on every rank and the arenas are allocated symmetrically.  The old arena is closed the safe way
+        (`PeerGroup.close`: device synchronise, host barrier, then unmap and free); the workspaces that lived in
+        it are dropped and come back on their next use, for which the new size leaves room.  A caller-fixed
+        `arena_bytes` and an enabled peer mailbox (whose slots and counters live in the arena) rule growth out."""
+
+        old = self.peer_group
+        if self.arena_bytes or self.mailbox is not None:
+            why = "its size was fixed by arena_bytes" if self.arena_bytes else "a peer mailbox lives in it"
+            raise CCDLUnavailableError(
+                f"peer arena too small for {what} ({old.bytes_free} < {need_bytes} bytes) and it cannot grow: {why}; "
+                "create the communicator with a larger arena_bytes")
+        used = old.nbytes - old.bytes_free
+        total = max(2 * old.nbytes, used + 2 * need_bytes + (64 << 20))
+        old.close()
+        self.peer_group = None
+        self._workspaces.clear()
+        self.stats["arena_rebuilds"] = self.stats.get("arena_rebuilds", 0) + 1
+        dist = _dist()
+        pg = self.process_group if self.process_group is not None else dist.group.WORLD
+        from .peer_memory import PeerGroup
+
+        try:
+            self.peer_group = PeerGroup.create(pg, total, device)
+        except CCDLUnavailableError as exc:
+            self._peer_failed = str(exc)
+            raise
         return self.peer_group
 
     def enable_peer_mailbox(self, capacity_bytes: int, device: Any = None):
@@ -197,9 +227,7 @@ class Communicator:
         need = FusedWorkspace.required_bytes(self.world_size, dtype, config, cap, True)
         group = self._ensure_peer_group(tensor.device, need)
         if group.bytes_free < need:
-            raise CCDLUnavailableError(
-                f"peer arena too small for a {cap}-element workspace ({group.bytes_free} < {need} bytes); "
-                "create the communicator with a larger arena_bytes")
+            group = self._grow_peer_group(tensor.device, need, f"a {cap}-element workspace")
         ws = FusedWorkspace(group, dtype=dtype, config=config, max_numel=cap, max_blocks=self.max_blocks,
                             with_gather_region=True)
         self._workspaces[key] = ws

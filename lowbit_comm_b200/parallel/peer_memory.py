@@ -258,6 +258,10 @@ class PeerGroup:
         """Epochs count modulo 2^32, 0 included: the kernels compare `int(seen - epoch) >= 0`, which stays
         right across the wrap as long as a flag is never more than 2^31 collectives behind."""
 
+        if self._closed:
+            # every collective of every workspace starts here: one that outlived its arena (a communicator closed
+            # or grew it) must not launch kernels on freed memory
+            raise CCDLUnavailableError("this workspace's peer arena was closed; ask the communicator for a workspace again")
         self._epochs[channel] = (self._epochs[channel] + 1) & 0xFFFFFFFF
         return self._epochs[channel]
 
@@ -283,6 +287,8 @@ class PeerGroup:
         """Raises when a kernel of this group gave up waiting.  Reads pinned host memory: no device
         synchronisation, cheap enough to call before every collective."""
 
+        if self._closed:
+            return                                   # the status word went with the arena
         status = DeviceWaitStatus(*self._ext.status_read(self.status_host))
         if status.timed_out:
             raise AsyncCommunicationError.from_wait(self.rank, status)

@@ -346,3 +346,79 @@ def test_route_picks_engine_and_stage_count_from_size_and_world():
     assert route(ws(8, "legacy"), 2 * mib, 2) == (False, default_stages(8, 2 << 20))
     assert route(ws(8), 2 * mib, 2, stages=2) == (True, 2) and route(ws(8, "legacy"), 64 * mib, 2, stages=1) == (False, 1)
     assert route(ws(1), 64 * mib, 2)[0] is True                                       # a one-GPU job takes the single kernel
+
+
+def test_communicator_arena_grows_collectively_and_refuses_when_it_cannot(monkeypatch):
+    """A workspace that does not fit: the communicator closes its arena (the safe close) and creates a larger one,
+    drops the workspaces that lived in the old one, and counts the rebuild; a caller-fixed size or an enabled
+    mailbox make it say why it cannot."""
+
+    import torch
+
+    from lowbit_comm_b200 import CompressionConfig
+    from lowbit_comm_b200.exceptions import CCDLUnavailableError
+    from lowbit_comm_b200.parallel import communicator as mod
+    from lowbit_comm_b200.parallel import fused, peer_memory
+
+    made = []
+
+    class Group:
+        def __init__(self, nbytes):
+            self.nbytes, self.bytes_free, self.closed, self.world_size, self.rank = nbytes, nbytes, False, 2, 0
+
+        def check_status(self):
+            assert not self.closed
+
+        def close(self):
+            self.closed = True
+
+    class Workspace:
+        @staticmethod
+        def required_bytes(world_size, dtype, config, max_numel, with_gather_region, engine="both"):
+            return 8 * max_numel                      # any fixed rule will do: the test is about growing, not sizing
+
+        def __init__(self, group, *, dtype, config, max_numel, **kw):
+            need = self.required_bytes(group.world_size, dtype, config, max_numel, True)
+            assert group.bytes_free >= need
+            group.bytes_free -= need
+            self.group, self.max_numel = group, max_numel
+
+    def create(pg, total, device):
+        made.append(Group(total))
+        return made[-1]
+
+    fake_dist = type("D", (), {"group": type("G", (), {"WORLD": object()})(), "is_available": staticmethod(lambda: True),
+                               "is_initialized": staticmethod(lambda: True), "get_rank": staticmethod(lambda *a: 0),
+                               "get_world_size": staticmethod(lambda *a: 2)})
+    monkeypatch.setattr(mod, "_dist", lambda: fake_dist)
+    monkeypatch.setattr(peer_memory.PeerGroup, "create", staticmethod(create))
+    monkeypatch.setattr(fused, "FusedWorkspace", Workspace)
+    monkeypatch.setenv("LBC_ARENA_MIB", "8")
+    cfg = CompressionConfig()
+
+    class T:
+        device = torch.device("cpu")
+
+        def __init__(self, n):
+            self._n = n
+
+        def numel(self):
+            return self._n
+
+    comm = mod.Communicator(None)
+    small = comm.workspace(T(100_000), cfg, "bf16")
+    assert len(made) == 1 and small.group is made[0]
+    big = comm.workspace(T(16_000_000), cfg, "bf16")          # does not fit beside the first one
+    assert len(made) == 2 and made[0].closed and not made[1].closed and big.group is made[1]
+    assert made[1].nbytes >= 2 * made[0].nbytes and comm.stats["arena_rebuilds"] == 1
+    again = comm.workspace(T(100_000), cfg, "bf16")          # same key, now served by the larger workspace
+    assert again is big and len(made) == 2
+    fixed = mod.Communicator(None, arena_bytes=8 << 20)
+    fixed.workspace(T(100_000), cfg, "bf16")
+    with pytest.raises(CCDLUnavailableError, match="fixed by arena_bytes"):
+        fixed.workspace(T(16_000_000), cfg, "bf16")
+    boxed = mod.Communicator(None)
+    boxed.workspace(T(100_000), cfg, "bf16")
+    boxed.mailbox = object()
+    with pytest.raises(CCDLUnavailableError, match="mailbox"):
+        boxed.workspace(T(16_000_000), cfg, "bf16")
