@@ -258,7 +258,7 @@ class PeerGroup:
         """Epochs count modulo 2^32, 0 included: the kernels compare `int(seen - epoch) >= 0`, which stays
         right across the wrap as long as a flag is never more than 2^31 collectives behind."""
 
-        if self._closed:
+        if getattr(self, "_closed", False):
             # every collective of every workspace starts here: one that outlived its arena (a communicator closed
             # or grew it) must not launch kernels on freed memory
             raise CCDLUnavailableError("this workspace's peer arena was closed; ask the communicator for a workspace again")
@@ -287,7 +287,7 @@ class PeerGroup:
         """Raises when a kernel of this group gave up waiting.  Reads pinned host memory: no device
         synchronisation, cheap enough to call before every collective."""
 
-        if self._closed:
+        if getattr(self, "_closed", False):
             return                                   # the status word went with the arena
         status = DeviceWaitStatus(*self._ext.status_read(self.status_host))
         if status.timed_out:
