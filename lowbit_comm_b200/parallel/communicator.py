@@ -151,9 +151,9 @@ class Communicator:
         if self.peer_group is None:
             dist = _dist()
             pg = self.process_group if self.process_group is not None else dist.group.WORLD
-            # The arena is fixed once the ranks have exchanged its handles: take what the first request needs
-            # twice over, and never less than the default (LBC_ARENA_MIB, 1 GiB: small beside 180 GB of HBM,
-            # and enough for workspaces of 64 MiB tensors in three dtypes).
+            # Growing an arena is a collective rebuild (`_grow_peer_group`), so start with room: what the first
+            # request needs twice over, and never less than the default (LBC_ARENA_MIB, 1 GiB: small beside
+            # 180 GB of HBM, and enough for workspaces of 64 MiB tensors in three dtypes).
             floor = int(float(os.environ.get("LBC_ARENA_MIB", "1024")) * (1 << 20))
             total = int(self.arena_bytes) if self.arena_bytes else max(2 * need_bytes + (64 << 20), floor)
             try:
