@@ -247,7 +247,7 @@ void dequant_general(const at::Tensor& src, at::Tensor& out, int group_size, int
 void quant_general_push(const at::Tensor& x, const std::optional<at::Tensor>& residual,
                         const std::optional<at::Tensor>& prepared_out, const Ptrs& dst, int group_size, int bit, int topk,
                         int quant_type, bool stochastic, bool compact, uint64_t seed, const SignalArg& signal,
-                        int max_blocks) {
+                        int max_blocks, int64_t shard_groups) {
     check_dense(x, "input");
     TORCH_CHECK(!dst.empty(), "dst: at least one destination");
     c10::cuda::CUDAGuard guard(x.device());
@@ -267,13 +267,14 @@ void quant_general_push(const at::Tensor& x, const std::optional<at::Tensor>& re
     fill_ptrs(p.dst, &p.num_dst, dst, "dst");
     p.signal = make_signal(signal);
     p.max_blocks = max_blocks;
+    p.shard_groups = shard_groups;
     cuda_check(lbc_quant_general(&p, at::cuda::getCurrentCUDAStream()), "lbc_quant_general(push)");
 }
 
 // Bounded wait, then one pass that decodes and sums every source payload, scales, and updates the residual.
 void reduce_general(const Ptrs& src, at::Tensor& out, int group_size, int bit, int topk, int quant_type, bool compact,
                     double scale, const std::optional<at::Tensor>& prepared, const std::optional<at::Tensor>& residual_out,
-                    const WaitArg& wait, int max_blocks) {
+                    const WaitArg& wait, int max_blocks, int64_t layout_groups, int64_t src_shard_groups) {
     check_dense(out, "output");
     TORCH_CHECK(prepared.has_value() == residual_out.has_value(), "prepared and residual_out come together");
     c10::cuda::CUDAGuard guard(out.device());
@@ -294,6 +295,8 @@ void reduce_general(const Ptrs& src, at::Tensor& out, int group_size, int bit, i
     p.residual_out = const_cast<void*>(opt_ptr(residual_out, out, "residual_out"));
     p.wait = make_wait(wait);
     p.max_blocks = max_blocks;
+    p.layout_groups = layout_groups;
+    p.src_shard_groups = src_shard_groups;
     cuda_check(lbc_reduce_general(&p, at::cuda::getCurrentCUDAStream()), "lbc_reduce_general");
 }
 
@@ -373,10 +376,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("quant_general_push", &quant_general_push, py::arg("x"), py::arg("residual"), py::arg("prepared_out"),
           py::arg("dst"), py::arg("group_size"), py::arg("bit"), py::arg("topk"), py::arg("quant_type"),
           py::arg("stochastic"), py::arg("compact"), py::arg("seed"), py::arg("signal") = py::none(),
-          py::arg("max_blocks") = 0);
+          py::arg("max_blocks") = 0, py::arg("shard_groups") = 0);
     m.def("reduce_general", &reduce_general, py::arg("src"), py::arg("out"), py::arg("group_size"), py::arg("bit"),
           py::arg("topk"), py::arg("quant_type"), py::arg("compact"), py::arg("scale"), py::arg("prepared") = py::none(),
-          py::arg("residual_out") = py::none(), py::arg("wait") = py::none(), py::arg("max_blocks") = 0);
+          py::arg("residual_out") = py::none(), py::arg("wait") = py::none(), py::arg("max_blocks") = 0,
+          py::arg("layout_groups") = 0, py::arg("src_shard_groups") = 0);
     m.def("error_feedback_update", &error_feedback_update);
     m.def("scale_inplace", &scale_inplace);
     m.def("push_bytes", &push_bytes, py::arg("src"), py::arg("nbytes"), py::arg("dst"), py::arg("wait") = py::none(),

@@ -263,17 +263,25 @@ __global__ void __launch_bounds__(kThreads) quant_general_kernel(const LbcQuantG
             index_word = uint32_t(top[0].idx);
             if (p.topk == 2) index_word |= uint32_t(top[1].idx) << 8;
         }
-        const int copies = p.num_dst > 0 ? p.num_dst : 1;
-        for (int d = 0; d < copies; ++d) {      // one payload, or the same payload in every rank's slot
+        const bool scatter = p.num_dst > 0 && p.shard_groups > 0;
+        const int copies = (p.num_dst > 0 && !scatter) ? p.num_dst : 1;
+        for (int d = 0; d < copies; ++d) {      // one payload, the same payload in every rank's slot, or one shard
             uint8_t* base = p.num_dst > 0 ? p.dst[d] : p.out;
+            int64_t gl = g, layout = num_groups;
+            if (scatter) {
+                const int64_t owner = g / p.shard_groups;
+                base = p.dst[owner];
+                gl = g - owner * p.shard_groups;
+                layout = p.shard_groups;
+            }
             uint8_t* vptr;
             uint8_t* mptr;
             if (p.compact) {
-                vptr = base + g * (VB + MB);
+                vptr = base + gl * (VB + MB);
                 mptr = vptr + VB;
             } else {
-                vptr = base + g * VB;
-                mptr = base + num_groups * VB + g * MB;
+                vptr = base + gl * VB;
+                mptr = base + layout * VB + gl * MB;
             }
             store_bytes(vptr + lane * CB, w, CB);
             if (lane == 0) {
@@ -393,13 +401,21 @@ __global__ void __launch_bounds__(kThreads) reduce_general_kernel(const LbcReduc
         const int64_t g = chunk / lanes;
         const int lane = int(chunk - g * lanes);
         float acc[16];
-        decode_general_chunk<T>(p.src[0], p.compact, p.bit, p.topk, p.quant_type, VB, MB, CB, num_groups, g, lane, acc);
-        for (int r = 1; r < p.num_src; ++r) {
-            float d[16];
-            decode_general_chunk<T>(p.src[r], p.compact, p.bit, p.topk, p.quant_type, VB, MB, CB, num_groups, g, lane, d);
+        if (p.src_shard_groups > 0) {
+            // gather: the group lives in exactly one source, its owner's reduced shard
+            const int64_t owner = g / p.src_shard_groups;
+            decode_general_chunk<T>(p.src[owner], p.compact, p.bit, p.topk, p.quant_type, VB, MB, CB, p.src_shard_groups,
+                                    g - owner * p.src_shard_groups, lane, acc);
+        } else {
+            const int64_t layout = p.layout_groups > 0 ? p.layout_groups : num_groups;
+            decode_general_chunk<T>(p.src[0], p.compact, p.bit, p.topk, p.quant_type, VB, MB, CB, layout, g, lane, acc);
+            for (int r = 1; r < p.num_src; ++r) {
+                float d[16];
+                decode_general_chunk<T>(p.src[r], p.compact, p.bit, p.topk, p.quant_type, VB, MB, CB, layout, g, lane, d);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] += d[i];
-            round16<T>(acc);                // the sum lives in the source dtype between payloads
+                for (int i = 0; i < 16; ++i) acc[i] += d[i];
+                round16<T>(acc);                // the sum lives in the source dtype between payloads
+            }
         }
         if (p.scale != 1.0f) {
 #pragma unroll
@@ -481,6 +497,11 @@ extern "C" {
 cudaError_t lbc_quant_general(const LbcQuantGeneral* p, cudaStream_t stream) {
     if (p == nullptr || p->numel < 0 || !lbc::general_args_ok(p->bit, p->topk, p->quant_type)) return cudaErrorInvalidValue;
     if (p->num_dst < 0 || p->num_dst > LBC_MAX_RANKS || (p->num_dst == 0 && p->out == nullptr)) return cudaErrorInvalidValue;
+    if (p->shard_groups < 0) return cudaErrorInvalidValue;
+    if (p->shard_groups > 0 && p->num_dst > 0) {      // every group must have an owner among the destinations
+        const int64_t groups = (p->numel + p->group_size - 1) / p->group_size;
+        if (groups > p->shard_groups * p->num_dst) return cudaErrorInvalidValue;
+    }
     for (int d = 0; d < p->num_dst; ++d)
         if (p->dst[d] == nullptr) return cudaErrorInvalidValue;
     switch (p->dtype) {
@@ -505,6 +526,12 @@ cudaError_t lbc_reduce_general(const LbcReduceGeneral* p, cudaStream_t stream) {
     if (p == nullptr || p->numel < 0 || !lbc::general_args_ok(p->bit, p->topk, p->quant_type)) return cudaErrorInvalidValue;
     if (p->num_src < 1 || p->num_src > LBC_MAX_RANKS || p->out == nullptr) return cudaErrorInvalidValue;
     if ((p->prepared == nullptr) != (p->residual_out == nullptr)) return cudaErrorInvalidValue;
+    if (p->layout_groups < 0 || p->src_shard_groups < 0) return cudaErrorInvalidValue;
+    {
+        const int64_t groups = (p->numel + p->group_size - 1) / p->group_size;
+        if (p->src_shard_groups > 0 && groups > p->src_shard_groups * p->num_src) return cudaErrorInvalidValue;
+        if (p->src_shard_groups == 0 && p->layout_groups > 0 && groups > p->layout_groups) return cudaErrorInvalidValue;
+    }
     for (int r = 0; r < p->num_src; ++r)
         if (p->src[r] == nullptr) return cudaErrorInvalidValue;
     switch (p->dtype) {

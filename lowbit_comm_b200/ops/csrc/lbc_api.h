@@ -169,6 +169,9 @@ typedef struct {
     int num_dst;
     LbcSignal signal;
     int max_blocks;            // 0 = library default
+    // Scatter (shard_groups > 0, with destinations): group g goes to dst[g / shard_groups] only, as group
+    // g % shard_groups of a self-contained payload of shard_groups groups (a reduce-scatter's first half).
+    int64_t shard_groups;
 } LbcQuantGeneral;
 
 typedef struct {
@@ -194,6 +197,10 @@ typedef struct {
     void* residual_out;        // optional T[numel]
     LbcWait wait;
     int max_blocks;            // 0 = library default
+    int64_t layout_groups;     // groups in every source layout (planar payloads keep their scales behind that many
+                               // groups of codes); 0 = the groups of `numel`
+    int64_t src_shard_groups;  // > 0: gather mode, group g is read from src[g / src_shard_groups] only, as group
+                               // g % src_shard_groups of a payload of src_shard_groups groups (layout_groups unused)
 } LbcReduceGeneral;
 
 cudaError_t lbc_quant_general(const LbcQuantGeneral* p, cudaStream_t stream);

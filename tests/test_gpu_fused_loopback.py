@@ -418,6 +418,62 @@ def test_topk_and_codebook_profiles_through_peer_memory(ext, world, dtype, kw, f
         PeerGroup.close_loopback(groups)
 
 
+@pytest.mark.parametrize("world", (2, 4, 8))
+@pytest.mark.parametrize("dtype", ("bf16", "fp32"))
+@pytest.mark.parametrize("kw", [dict(bit=8, group_size=64, topk=1), dict(bit=8, group_size=64, topk=2, compact=True),
+                                dict(bit=4, group_size=16, quant_type="normal")])
+def test_topk_two_stage_all_reduce_matches_the_two_quantizations(ext, world, dtype, kw):
+    """stages=2 of the general-profile all-reduce (scatter, reduce, quantize again, gather): the result is
+    decode(quant(y)) for y = the one-stage mean of the ranks' payloads, and the residual T(prepared - result), bit
+    for bit, on sizes that leave shards partly or wholly empty."""
+
+    from lowbit_comm_b200.ops import codec
+    from lowbit_comm_b200.parallel.fused_general import GeneralPeerWorkspace
+
+    cfg = CompressionConfig(allow_experimental=True, **kw)
+    max_numel = 70_000
+    need = GeneralPeerWorkspace.required_bytes(world, dtype, cfg, max_numel) + (1 << 20)
+    groups = PeerGroup.loopback(world, need, timeout_ns=2_000_000_000)
+    try:
+        wss = [GeneralPeerWorkspace(g, dtype=dtype, config=cfg, max_numel=max_numel) for g in groups]
+        for step, n in enumerate((cfg.group_size * 8 * world, 12_347, 1, cfg.group_size * 8 + 3, max_numel)):
+            xs = _inputs(world, n, dtype, seed=130 + step)
+            rs = _inputs(world, n, dtype, seed=160 + step)
+            dev_x = [x.cuda() for x in xs]
+            dev_r = [r.cuda() for r in rs]
+            payloads, prepared = [], []
+            for x, r in zip(xs, rs):
+                keep = r.cuda()
+                payloads.append(codec.quantize_tensor(x.cuda(), cfg, residual=keep, prepared_out=keep))
+                prepared.append(keep)
+            y = codec.dequantize_reduce_tensors(payloads, (n,), cfg, dtype=dtype, reduce="mean")
+            want = codec.dequantize_tensor(codec.quantize_tensor(y, cfg), (n,), cfg, dtype=dtype)
+            want_res = [codec.update_error_feedback_residual(p, want, p.clone()) for p in prepared]
+            run_loopback(wss, "all_reduce", [(dev_x[r],) for r in range(world)],
+                         [{"residual": dev_r[r]} for r in range(world)], stages=2)
+            torch.cuda.synchronize()
+            for r in range(world):
+                assert torch.equal(dev_x[r].view(torch.uint8), want.view(torch.uint8)), (n, r)
+                assert torch.equal(dev_r[r].view(torch.uint8), want_res[r].view(torch.uint8)), (n, r, "residual")
+        assert wss[0].launches == 4 * 5
+        # one- and two-stage calls share the receive regions: alternate them, no residual, a sum
+        xs = _inputs(world, 9_999, dtype, seed=199)
+        payloads = [codec.quantize_tensor(x.cuda(), cfg) for x in xs]
+        y = codec.dequantize_reduce_tensors(payloads, (9_999,), cfg, dtype=dtype, reduce="sum")
+        two = codec.dequantize_tensor(codec.quantize_tensor(y, cfg), (9_999,), cfg, dtype=dtype)
+        for stages, want in ((1, y), (2, two), (2, two), (1, y)):
+            outs = [torch.empty(9_999, dtype=xs[0].dtype, device="cuda") for _ in range(world)]
+            run_loopback(wss, "all_reduce", [(xs[r].cuda(), outs[r]) for r in range(world)], op="sum", stages=stages)
+            torch.cuda.synchronize()
+            for r in range(world):
+                assert torch.equal(outs[r].view(torch.uint8), want.view(torch.uint8)), (stages, r)
+        for g in groups:
+            g.check_status()
+            g.check_canaries()
+    finally:
+        PeerGroup.close_loopback(groups)
+
+
 def test_fused_general_reduce_wait_runs_out_on_a_signal_nobody_sends(ext):
     """One emulated rank of two never pushes: the reduce kernel of the other gives up after its bound, reports
     the missing peer in the status word and leaves the output untouched; the context stays usable."""

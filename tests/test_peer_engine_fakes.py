@@ -321,6 +321,27 @@ def test_general_profile_all_reduce_launch_plan(fused):
     push, reduce = group._ext.calls[0][1], group._ext.calls[1][1]
     assert push[3][0] == 0x10000 + ws.recv_off[0] + 2 * ws.slot_bytes and push[2] is None and same(push[1])
     assert reduce[7] == 1.0 and reduce[8] is None and reduce[9] is None
+    # two stages: scatter to the owners, reduce my shard, push it to everybody, gather-decode: four launches
+    group._ext.calls.clear()
+    before = ws.launches
+    big = torch.zeros(4096, dtype=torch.bfloat16)
+    ws.all_reduce(big, residual=torch.zeros(4096, dtype=torch.bfloat16), stages=2)
+    names = [c[0] for c in group._ext.calls]
+    assert names == ["quant_general_push", "reduce_general", "quant_general_push", "reduce_general"]
+    assert ws.launches == before + 4
+    scatter, shard_reduce, push, gather = (c[1] for c in group._ext.calls)
+    shard_groups = GeneralPeerWorkspace.shard_numel(4, cfg, 4096) // 64
+    assert shard_groups == 16 and scatter[-1] == shard_groups and push[-1] == 0
+    assert shard_reduce[-2:] == (shard_groups, 0) and gather[-2:] == (0, shard_groups)
+    assert shard_reduce[1].numel() == 16 * 64 and push[0].numel() == 16 * 64          # rank 2's shard is full
+    assert push[3] == [0x10000 * (r + 1) + ws.gather_off[1] + 2 * (ws.gather_off[1] - ws.gather_off[0]) // 4
+                       for r in range(4)]
+    tiny = torch.zeros(100, dtype=torch.bfloat16)              # two groups: ranks 1..3 own nothing
+    group._ext.calls.clear()
+    ws.all_reduce(tiny, stages=2)
+    assert [c[0] for c in group._ext.calls] == ["quant_general_push", "wait_signal", "quant_general_push", "reduce_general"]
+    with pytest.raises(ValueError):
+        GeneralPeerWorkspace(_FakeGeneralGroup(), dtype="bf16", config=cfg, max_numel=64, fused=False).all_reduce(tiny, stages=2)
 
 
 def test_route_picks_engine_and_stage_count_from_size_and_world():
