@@ -297,8 +297,12 @@ class Communicator:
                 gws = None
             if gws is not None:
                 scope, side = self._stream_scope(tensor, async_op)
+                # a strategy that names the two-stage algorithm gets it (reduce-scatter, requantize, gather); "auto"
+                # and "all_gather" keep the one-stage exchange, and so does stochastic rounding
+                two = stages == 2 and not config.stochastic
                 with scope:
-                    result = gws.all_reduce(tensor, out, residual=residual, update_residual=update_residual, op=op)
+                    result = gws.all_reduce(tensor, out, residual=residual, update_residual=update_residual, op=op,
+                                            stages=2 if two else 1)
                 self.stats["peer_ops"] += 1
                 return self._finish(result, side, resources=(tensor, out, residual))
         result = self._torch_all_reduce(tensor, config, op, stages, name, out, residual, update_residual)
