@@ -1,6 +1,6 @@
 """Single-GPU microbenchmark of the codec and fused kernels (HBM roofline check).
 
-Usage: python benchmarks/kernel_bench.py [--mib 64 256] [--worlds 1 2 8] [--with-reference] [--profile] [--out FILE]
+Usage: python benchmarks/kernel_bench.py [--mib 64 256] [--worlds 1 2 8] [--with-reference] [--topk K] [--profile] [--out FILE]
 Every kernel is timed with CUDA events after warm-up with an L2 flush between
 iterations; bandwidth = algorithmic bytes / median time, reported as a fraction
 of the measured copy bandwidth in MEASURED_PEAKS.json (fallback 6650 GB/s).
@@ -9,6 +9,8 @@ built for sm_100 under baseline/_ref, loaded into the same process) on the same
 tensors: `inplace_quantize_pack`, `inplace_dequantize_reduce_mean` and
 `inplace_dequantize_reduce_mean_update_error_feedback`
 (ccdl_comm/quantization/codec.py:161-217, 355-466).
+`--topk K` also times the general-profile all-reduce (K outliers per group kept verbatim) on the emulated ranks,
+in its one-stage and its two-stage form.
 """
 
 from __future__ import annotations
@@ -46,6 +48,8 @@ def main() -> None:
     ap.add_argument("--engine", choices=("auto", "pipe", "legacy"), default="auto",
                     help="all-reduce engine of the emulated-rank part: single persistent kernel or kernel sequence")
     ap.add_argument("--skip-codec", action="store_true", help="only the all-reduce on emulated ranks (for captures)")
+    ap.add_argument("--topk", type=int, default=0, choices=(0, 1, 2),
+                    help="also time the general-profile (top-k) all-reduce on the emulated ranks, one and two stages")
     ap.add_argument("--out", default="bench_out/kernel_bench.json")
     args = ap.parse_args()
     ref = None
@@ -172,6 +176,29 @@ def main() -> None:
             groups[0].check_status()
             PeerGroup.close_loopback(groups)
             del wss, xs, rs
+            if args.topk and world > 1:
+                from lowbit_comm_b200.parallel.fused_general import GeneralPeerWorkspace
+
+                kcfg = CompressionConfig(topk=args.topk, allow_experimental=True)
+                need = GeneralPeerWorkspace.required_bytes(world, "bf16", kcfg, n) + (1 << 20)
+                if need * world <= 60 * (1 << 30):
+                    groups = PeerGroup.loopback(world, need)
+                    gws = [GeneralPeerWorkspace(g, dtype="bf16", config=kcfg, max_numel=n) for g in groups]
+                    xs = [x] + [x.clone() for _ in range(world - 1)]
+                    rs = [torch.zeros_like(x) for _ in range(world)]
+                    for stages in (1, 2):
+                        def general_step(stages=stages):
+                            run_loopback(gws, "all_reduce", [(xs[r],) for r in range(world)],
+                                         [{"residual": rs[r]} for r in range(world)], stages=stages)
+
+                        t = time_cuda(general_step, iters=max(3, args.iters // 2), flush=flush)
+                        rows.append({"kernel": f"top-k {args.topk} all_reduce loopback W={world} ({stages}-stage, EF)",
+                                     "mib": mib, "per_rank_ms": t["median_ms"] / world})
+                        print(json.dumps(rows[-1]), flush=True)
+                    torch.cuda.synchronize()
+                    groups[0].check_status()
+                    PeerGroup.close_loopback(groups)
+                    del gws, xs, rs
         del x, res, out
         torch.cuda.empty_cache()
     os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
