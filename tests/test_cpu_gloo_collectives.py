@@ -38,6 +38,19 @@ def _worker(rank: int, world: int, port: int) -> None:
                 continue
             got = lbc.compressed_all_reduce(xs[rank].clone(), config=cfg, strategy=strategy)
             assert ((got.float() - exact).norm() / exact.norm()).item() < 0.03, strategy
+        # general profiles: one stage = the codec's in-dtype sum of the payloads, two stages = that result quantized
+        # once more; the peer-memory kernels are held to the same two values on GPUs
+        from lowbit_comm_b200.ops import codec
+
+        for k in (1, 2):
+            kcfg = lbc.CompressionConfig(topk=k, allow_experimental=True)
+            packed = [codec.quantize_tensor(x, kcfg) for x in xs]
+            y = codec.dequantize_reduce_tensors(packed, (n,), kcfg, dtype="bf16", reduce="mean")
+            twice = codec.dequantize_tensor(codec.quantize_tensor(y, kcfg), (n,), kcfg, dtype="bf16")
+            got = lbc.compressed_all_reduce(xs[rank].clone(), config=kcfg, strategy="all_gather")
+            assert torch.equal(got.view(torch.uint8), y.view(torch.uint8)), k
+            got = lbc.compressed_all_reduce(xs[rank].clone(), config=kcfg, strategy="reduce_scatter")
+            assert torch.equal(got.view(torch.uint8), twice.view(torch.uint8)), k
         work = lbc.compressed_all_reduce(xs[rank].clone(), config=cfg, strategy="all_gather", async_op=True)
         assert torch.equal(work.wait().view(torch.uint8), one.view(torch.uint8)) and work.query()
         summed = lbc.compressed_all_reduce(xs[rank].clone(), config=cfg, op="sum")
