@@ -120,5 +120,9 @@ def test_benchmark_scripts_dry_run_on_two_cpu_ranks(tmp_path):
     assert all(r["rel_l2"] < 0.01 for r in rows if "rel_l2" in r)
     assert [r["case"] for r in json.loads(out.read_text())] == [r["case"] for r in rows]
     out = tmp_path / "mlp.json"
-    (line,) = torchrun("benchmarks/mlp_ddp.py", "--steps", "2", "--warmup", "1", "--out", str(out))
+    (line,) = torchrun("benchmarks/mlp_ddp.py", "--steps", "2", "--warmup", "1", "--repeats", "2", "--out", str(out))
     assert line["unit"] == "samples/s" and line["n_gpus"] == 2 and line["value"] > 0 and line["impl"] == "ours"
+    assert len(line["ms_per_step_samples"]) == 2 and line["ms_per_step"] == pytest.approx(
+        sum(line["ms_per_step_samples"]) / 2, rel=1e-3)                      # the median of two is their mean
+    (line,) = torchrun("benchmarks/mlp_ddp.py", "--impl", "fsdp", "--steps", "1", "--warmup", "1")
+    assert line == {"impl": "fsdp", "unavailable": "the FSDP baseline arm runs on CUDA ranks only"}
